@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the Stella-1.5B-architecture ragged-batch embedding forward on B200.
+
+Workload (the configuration the headline metric "Stella-1.5B embeddings/s" is quoted on): a
+Qwen2-style encoder with 28 layers, hidden 1536, 12 query / 2 KV heads of 128, SwiGLU 8960, vocab
+151646, mean pooling -> 1536->1024 dense -> L2; seeded random weights N(0, 0.02); a batch of 8
+sequences with lengths uniform in [32, 512] and uniform token ids. One step = one forward of the
+batch. Weak scaling over GPUs: every rank holds a full replica and its own batch (request
+sharding, no collective on the data path).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+`value`  embeddings/s with ids already resident on the device (CUDA events on the launch stream)
+`e2e`    the same through lg_stella_encode_ids_batch with host buffers (H2D + D2H inside)
+`roofline`      the dominant kernel (gate/up tcgen05 GEMM) against the measured bf16 peak
+`extra_rooflines` the two HBM-bound decode kernels (int4 GEMV, paged attention) against HBM peak
+`cpu_baseline`  the CPU oracle (a port of the reference's fp32 path) on the host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from stella_weights import STELLA_1_5B, make_batch, make_weights  # noqa: E402
+
+SEED_W, SEED_B = 2024, 7
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf_sust=d.get("bf16_tflops_sustained", d["bf16_tflops"]), src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sust=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def flops_per_forward(cfg, lens, n_layers):
+    h, i, kv = cfg["hidden"], cfg["intermediate"], cfg["n_kv_heads"] * (cfg["hidden"] // cfg["n_heads"])
+    per_tok = 2 * (h * h + 2 * kv * h + h * h + 3 * h * i) * n_layers
+    attn = sum(4 * cfg["n_heads"] * (cfg["hidden"] // cfg["n_heads"]) * L * L for L in lens) * n_layers
+    return per_tok * int(sum(lens)) + attn
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+
+def cpu_baseline(cfg, w, ids, cu, budget_s=20.0):
+    """The oracle's encode_batch (one worker per sequence on the physical cores, single-threaded
+    GEMM inside each, as crates/embed/src/stella.rs:264-294) on a bounded sample: all sequences
+    of the batch through the first L' layers, the time scaled by n_layers / L'."""
+    import oracle_lib as O
+    cores = O.physical_cores()
+    n_seq = len(cu) - 1
+    threads = min(cores, n_seq)
+    probe = dict(cfg, n_layers=1)
+    m1 = O.OracleStella(probe, dict(w, layers=w["layers"][:1]))
+    t0 = time.perf_counter(); m1.encode_batch(ids, cu, threads); t1 = time.perf_counter() - t0
+    layers = int(max(1, min(cfg["n_layers"], budget_s / max(t1, 1e-3))))
+    if layers > 1:
+        mL = O.OracleStella(dict(cfg, n_layers=layers), dict(w, layers=w["layers"][:layers]))
+        t0 = time.perf_counter(); mL.encode_batch(ids, cu, threads); tL = time.perf_counter() - t0
+    else:
+        tL = t1
+    full = tL * cfg["n_layers"] / layers
+    return {"value": n_seq / full, "unit": "embeddings/s", "cores": threads, "kind": "port",
+            "sample": f"{n_seq} sequences x {layers} of {cfg['n_layers']} layers, {tL:.1f} s measured, scaled by {cfg['n_layers']}/{layers}; "
+                      f"oracle C++ port of the reference fp32 path (blocked SGEMM standing in for matrixmultiply), "
+                      f"{cores} physical cores detected"}, full
+
+
+def run_reference(args, cfg, rank, world):
+    if rank != 0:
+        return
+    w = make_weights(cfg, SEED_W)
+    ids, cu = make_batch(cfg, SEED_B, n_seq=8, lo=32, hi=512)
+    vals = []
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_baseline(cfg, w, ids, cu, budget_s=3.0)
+    t_all = 0.0
+    for _ in range(args.steps):
+        cb, full = cpu_baseline(cfg, w, ids, cu, budget_s=max(3.0, 60.0 / max(args.steps, 1)))
+        vals.append(cb["value"]); t_all += full
+    v = float(np.mean(vals))
+    cb["value"] = v
+    print(json.dumps({"impl": "reference", "metric": "stella_1.5b_embeddings_per_s", "value": v, "unit": "embeddings/s",
+                      "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": workload_config(cfg, cu), "cpu_baseline": cb,
+                      "e2e": {"value": v, "unit": "embeddings/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def workload_config(cfg, cu):
+    return {"workload": "stella-1.5b-arch embedding forward, 8 sequences x U[32,512] tokens, 28 layers, seeded random weights",
+            "tokens_per_step": int(cu[-1]), "n_layers": cfg["n_layers"], "l2": "weights (2.6 GB bf16) exceed L2 (126 MB); no explicit flush",
+            "parallelism": "request sharding, one replica per GPU"}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+
+def time_kernel(fn, iters, stream):
+    import torch
+    for _ in range(3):
+        fn(0)
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        fn(i)
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def micro_rooflines(peaks, T, cfg):
+    """Per-launch rooflines of the dominant GEMM and the two HBM-bound decode kernels, timed with
+    CUDA events on the launch stream, operands rotated so that each launch reads from HBM."""
+    import torch
+    from logismos_b200 import ops
+    dev = "cuda"
+    st = torch.cuda.current_stream()
+    out = {}
+    # gate/up GEMM with fused SwiGLU at the benchmark's token count
+    h, i2 = cfg["hidden"], 2 * cfg["intermediate"]
+    a = torch.randn((T, h), device=dev).to(torch.bfloat16)
+    ws = [(torch.randn((i2, h), device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]
+    t = time_kernel(lambda i: ops.linear_t(a, ws[i % 4], swiglu=True, sync=False), 20, st)
+    fl = 2.0 * T * i2 * h
+    out["gemm"] = {"kernel": "linear_t_tcgen05 (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": fl / t / 1e12,
+                   "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": fl / t / 1e12 / peaks["tf_burst"], "traffic": None,
+                   "flops_per_launch": fl, "us_per_launch": t * 1e6, "peak_source": peaks["src"] + " burst"}
+    del ws
+    # int4 GEMV, lm_head shape, batch 1
+    n, k = 151936, 1536
+    codes = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev) for _ in range(3)]
+    scales = [(torch.rand((n, k // 32), device=dev) * 0.02).to(torch.float16) for _ in range(3)]
+    x = torch.randn((1, k), device=dev).to(torch.bfloat16)
+    y = torch.empty((1, n), dtype=torch.bfloat16, device=dev)
+    t = time_kernel(lambda i: ops.gemv_int4(codes[i % 3], scales[i % 3], x, out=y, sync=False), 30, st)
+    by = n * k / 2 + n * (k // 32) * 2 + k * 2 + n * 2
+    out["gemv"] = {"kernel": "gemv_int4_g32 (151936 x 1536, batch 1)", "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"],
+                   "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"], "traffic": None, "bytes_per_launch": by, "us_per_launch": t * 1e6,
+                   "peak_source": peaks["src"]}
+    del codes, scales
+    # paged-attention decode: 256 sequences, contexts log-uniform in [128, 32768], block 16, fused append
+    rng = np.random.default_rng(3)
+    ctx = np.exp(rng.uniform(np.log(128), np.log(32768), 256)).round().astype(np.int64)
+    nb = (ctx + 15) // 16
+    n_pool = int(nb.sum())
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.zeros((256, int(nb.max())), np.int32); o = 0
+    for s_ in range(256):
+        tables[s_, :nb[s_]] = perm[o:o + nb[s_]]; o += nb[s_]
+    kp = torch.randn((n_pool, 16, 256), device=dev).to(torch.bfloat16); vp = torch.randn((n_pool, 16, 256), device=dev).to(torch.bfloat16)
+    q = torch.randn((256, 2048), device=dev).to(torch.bfloat16)
+    nk = torch.randn((256, 256), device=dev).to(torch.bfloat16); nv = torch.randn((256, 256), device=dev).to(torch.bfloat16)
+    off, total = ops.build_decode_chunks(ctx.astype(np.int32), 512)
+    d_tab, d_ctx, d_off = torch.from_numpy(tables).to(dev), torch.from_numpy(ctx.astype(np.int32)).to(dev), off.to(dev)
+    scratch = torch.empty(int(ops.lib.logismos_paged_decode_scratch_bytes(total, 16, 128)), dtype=torch.uint8, device=dev)
+    t = time_kernel(lambda i: ops.paged_attention_decode(q, kp, vp, nk, nv, d_tab, d_ctx, d_off, total, 512, 16, 2, 128, scratch=scratch,
+                                                         sync=False), 10, st)
+    by = float(ctx.sum()) * 1024 + 256 * (2048 * 2 * 2 + 512 * 2) + tables.size * 4
+    out["paged"] = {"kernel": "paged_attention_decode (256 seqs, ctx log-U[128,32768], GQA 16/2, fused append) incl. merge kernel",
+                    "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"],
+                    "traffic": None, "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()),
+                    "peak_source": peaks["src"]}
+    return out
+
+
+def run_ours(args, cfg, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from logismos_b200.embed import StellaModel
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = measured_peaks()
+    w = make_weights(cfg, SEED_W)
+    ids, cu = make_batch(cfg, SEED_B + rank, n_seq=8, lo=32, hi=512)
+    lens = (cu[1:] - cu[:-1]).tolist()
+    T, n_seq = int(cu[-1]), len(lens)
+    model = StellaModel(cfg, w, device=local_rank, max_batch_tokens=4608, max_batch_seqs=16)
+    pos = np.concatenate([np.arange(L) for L in lens]).astype(np.int32)
+    d_ids = torch.from_numpy(ids.view(np.int32)).cuda(); d_cu = torch.from_numpy(cu).cuda(); d_pos = torch.from_numpy(pos).cuda()
+    d_out = torch.empty((n_seq, cfg["head_out_dim"]), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step():
+        model.forward_device(d_ids.data_ptr(), d_cu.data_ptr(), d_pos.data_ptr(), T, n_seq, max(lens), d_out.data_ptr(), stream.cuda_stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    dt = e0.elapsed_time(e1) * 1e-3
+    # end to end through the public entry point, host buffers in, host embeddings out
+    for _ in range(2):
+        emb = model.encode_ids_batch(ids, cu)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        emb = model.encode_ids_batch(ids, cu)
+    dt_e2e = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        tt = torch.tensor([dt, dt_e2e], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt, dt_e2e = float(tt[0]), float(tt[1])
+    status = model.device_status()
+    if rank == 0:
+        total_emb = world * n_seq * args.steps
+        fl = flops_per_forward(cfg, lens, cfg["n_layers"])
+        line = {"metric": "stella_1.5b_embeddings_per_s", "value": total_emb / dt, "unit": "embeddings/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(cfg, cu),
+                "e2e": {"value": total_emb / dt_e2e, "unit": "embeddings/s", "h2d_bytes_per_step": int(T * 8 + (n_seq + 1) * 4),
+                        "d2h_bytes_per_step": int(n_seq * cfg["head_out_dim"] * 4)},
+                "gpu_launches": model.launches_per_forward() * args.steps, "clocks": clocks, "device_status": status,
+                "model_tflops": fl * args.steps / dt / 1e12, "model_frac_of_sustained_peak": fl * args.steps / dt / 1e12 / peaks["tf_sust"],
+                "embedding_norm_check": float(np.abs(np.linalg.norm(emb, axis=1) - 1).max())}
+        if world == 1 and not args.no_micro:
+            mr = micro_rooflines(peaks, T, cfg)
+            line["roofline"] = mr["gemm"]
+            line["extra_rooflines"] = [mr["gemv"], mr["paged"]]
+        else:
+            line["roofline"] = {"bound": "tensor", "achieved": fl * args.steps / dt / 1e12 / 1.0, "peak": peaks["tf_sust"], "unit": "TFLOP/s",
+                                "frac": fl * args.steps / dt / 1e12 / peaks["tf_sust"], "traffic": None,
+                                "note": "whole-forward FLOPs over whole-forward time (per-kernel rooflines are reported at N=1)"}
+        if world == 1 and not args.no_cpu:
+            del model
+            line["cpu_baseline"], _ = cpu_baseline(cfg, w, ids, cu, budget_s=args.cpu_budget)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override depth (development only; the reported config is 28)")
+    ap.add_argument("--no-micro", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=20.0)
+    args = ap.parse_args()
+    cfg = dict(STELLA_1_5B)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, cfg, rank, world)
+    else:
+        run_ours(args, cfg, rank, world, local)
+
+
+if __name__ == "__main__":
+    main()

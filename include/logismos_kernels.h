@@ -1,0 +1,211 @@
+/*
+ * logismos_kernels.h - C ABI of the sm_100a kernel launchers.
+ *
+ * Convention of the reference's launchers (crates/kernels/src/<op>/mod.rs `unsafe extern "C"`
+ * blocks; e.g. matmul/mod.rs:36-56 and matmul/hip/matmul_launchers.cpp:14-52), kept for every
+ * entry point here:
+ *   - the caller owns every buffer; all pointers are DEVICE pointers unless a parameter is
+ *     named host_*; a launcher never allocates and never synchronises;
+ *   - dims are int32; `stream` is a cudaStream_t passed as void* (NULL = the null stream);
+ *   - the return value is the raw runtime status read right after the launch (0 = success); a
+ *     shape the kernel cannot address is rejected before launching with cudaErrorInvalidValue
+ *     (1), the counterpart of the Rust-side guards check_matmul_shape / check_rope_shape
+ *     (matmul/mod.rs:89-117, rope/mod.rs:79-132).
+ * The library is built as liblogismos_kernels.so (and .a, the archive name the reference's
+ * build script links, crates/kernels/build.rs:117-122).
+ */
+#ifndef LOGISMOS_KERNELS_H
+#define LOGISMOS_KERNELS_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ====================================================================================
+ * The reference's four fp16 launchers, same symbols and argument lists.
+ * ==================================================================================== */
+
+/* crates/kernels/src/matmul/mod.rs:37-45 -> matmul_naive.hip. D[M,N] = A[M,K] B[K,N], row-major
+ * fp16, fp32 accumulate. */
+uint32_t logismos_launch_matmul_naive_fp16(const void* a_fp16, const void* b_fp16, void* d_fp16,
+                                           int32_t m, int32_t n, int32_t k, void* stream);
+/* crates/kernels/src/matmul/mod.rs:47-55 -> matmul_wmma.hip. Same contract on tensor cores; M, N,
+ * K must be multiples of 16 (the only case crates/praxis/src/matmul.rs:113-117 selects it). */
+uint32_t logismos_launch_matmul_wmma_fp16(const void* a_fp16, const void* b_fp16, void* d_fp16,
+                                          int32_t m, int32_t n, int32_t k, void* stream);
+/* crates/kernels/src/rms_norm/mod.rs:33-43 -> rms_norm.hip */
+uint32_t logismos_launch_rms_norm_fp16(const void* x_fp16, const void* w_fp16, void* y_fp16,
+                                       int32_t m, int32_t n, float eps, void* stream);
+/* crates/kernels/src/softmax/mod.rs:28-36 -> softmax.hip. An all -inf row yields 1/n. */
+uint32_t logismos_launch_softmax_fp16(const void* x_fp16, void* y_fp16, int32_t m, int32_t n,
+                                      void* stream);
+/* crates/kernels/src/rope/mod.rs:44-54 -> rope.hip. In-place interleaved-pair rotation of
+ * (batch, seq, heads, head_dim) fp16 with an fp32 (seq, head_dim) table of (cos, sin) pairs. */
+uint32_t logismos_launch_rope_fp16(void* qk_fp16, const void* cos_sin_f32, int32_t batch,
+                                   int32_t seq, int32_t heads, int32_t head_dim, void* stream);
+
+/* ====================================================================================
+ * Encoder / prefill path (bf16 storage, fp32 accumulation). Each entry replaces the CPU
+ * function of crates/kernels/src/cpu_f32/mod.rs named beside it.
+ * ==================================================================================== */
+
+/* cpu_f32::embed_lookup (mod.rs:106-127): out[i,:] = table[ids[i],:]; an id >= vocab yields a
+ * zero row. table bf16 [vocab, hidden]; out f32 [n_ids, hidden] (the fp32 residual stream). */
+uint32_t logismos_launch_embed_lookup_bf16(const void* table_bf16, const void* ids_u32,
+                                           void* out_f32, int32_t n_ids, int32_t hidden,
+                                           int32_t vocab, void* stream);
+
+/* cpu_f32::rms_norm (mod.rs:137-159) over the fp32 residual stream: y = x * rsqrt(mean(x^2)+eps)
+ * * w. x f32 [rows, n], w f32 [n]; y bf16 [rows, n] (out_f32 == 0) or f32 (out_f32 != 0). */
+uint32_t logismos_launch_rms_norm_f32(const void* x_f32, const void* w_f32, void* y, int32_t rows,
+                                      int32_t n, float eps, int32_t out_f32, void* stream);
+
+/* cpu_f32::linear_t (mod.rs:271-345) on the tcgen05 tensor cores:  C = A W^T (+ bias).
+ * A bf16 [m, k] row-major (row stride lda elements), W bf16 [n, k] row-major (the HF [out, in]
+ * layout, untransposed). k % 64 == 0, n % 16 == 0, lda % 8 == 0, pointers 16-byte aligned.
+ * epilogue selects what is stored:
+ *   LG_EPI_BF16      out bf16 [m, n]      = acc + bias
+ *   LG_EPI_RESID_F32 out f32  [m, n]     += acc + bias       (residual add, in place)
+ *   LG_EPI_SWIGLU    out bf16 [m, n / 2]  = silu(gate) * up, W holding gate and up rows
+ *                    interleaved in blocks of 32 rows (32 gate rows, then the 32 matching up
+ *                    rows); n % 64 == 0; fuses cpu_f32::silu + hadamard (mod.rs:349-374)
+ * bias_f32 may be NULL. ldc is the row stride of out in elements. status_i32 (may be NULL)
+ * receives 2 if a bounded wait inside the kernel expired (the output is then invalid). */
+enum { LG_EPI_BF16 = 0, LG_EPI_RESID_F32 = 1, LG_EPI_SWIGLU = 2 };
+uint32_t logismos_launch_linear_t_bf16(const void* a_bf16, const void* w_bf16,
+                                       const void* bias_f32, void* out, int32_t m, int32_t n,
+                                       int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
+                                       void* status_i32, void* stream);
+/* The same contract one thread per output, as the on-device correctness anchor (the role
+ * matmul_naive.hip plays in the reference). LG_EPI_SWIGLU is not supported here. */
+uint32_t logismos_launch_linear_t_naive_bf16(const void* a_bf16, const void* w_bf16,
+                                             const void* bias_f32, void* out, int32_t m, int32_t n,
+                                             int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
+                                             void* stream);
+
+/* cpu_f32::rope_halves_in_place (mod.rs:502-547) with RopeTable::gather (crates/transformers/
+ * src/rope.rs:50-92) folded in: rotates, in place, the first n_rot_heads heads of every token row
+ * of a packed bf16 [n_tokens, row_stride] buffer (q heads followed by k heads), head h at
+ * column h * head_dim, using cos/sin f32 [max_pos, head_dim/2] rows selected by positions[token].
+ * A position >= max_pos leaves the row untouched and sets *status (may be NULL) to 1. */
+uint32_t logismos_launch_rope_halves_bf16(void* qk_bf16, const void* cos_f32, const void* sin_f32,
+                                          const void* positions_i32, int32_t n_tokens,
+                                          int32_t n_rot_heads, int32_t head_dim,
+                                          int32_t row_stride, int32_t max_pos, void* status_i32,
+                                          void* stream);
+
+/* cpu_f32::silu + hadamard (mod.rs:349-374): out[t, j] = silu(gu[t, j]) * gu[t, inter + j].
+ * gu bf16 [rows, 2*inter] (gate columns then up columns), out bf16 [rows, inter]. */
+uint32_t logismos_launch_swiglu_bf16(const void* gu_bf16, void* out_bf16, int32_t rows,
+                                     int32_t inter, void* stream);
+
+/* QwenAttention::forward's score/softmax/PV stage (crates/transformers/src/attention.rs
+ * :226-296) for a ragged batch, without materialising scores. qkv bf16 [n_tokens, row_stride]
+ * with q heads at column 0, k heads at k_off, v heads at v_off (RoPE already applied); sequence
+ * i owns token rows cu_seqlens[i] .. cu_seqlens[i+1]; q head j reads kv head j / (n_heads /
+ * n_kv_heads) (attention.rs:366-382). causal = 0 is the reference's bidirectional encoder
+ * attention, causal = 1 masks keys after the query. head_dim must be 128. out bf16
+ * [n_tokens, n_heads * head_dim]. max_seqlen bounds the grid. */
+uint32_t logismos_launch_varlen_attention_bf16(const void* qkv_bf16, const void* cu_seqlens_i32,
+                                               void* out_bf16, int32_t n_seqs, int32_t max_seqlen,
+                                               int32_t n_heads, int32_t n_kv_heads,
+                                               int32_t head_dim, int32_t row_stride, int32_t k_off,
+                                               int32_t v_off, int32_t causal, void* stream);
+
+/* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
+ * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), one CTA per
+ * sequence, mask all ones. hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden];
+ * head_b f32 [dim]; out f32 [n_seqs, dim]. A sequence of length 0 pools to zeros. */
+uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu_seqlens_i32,
+                                       const void* head_w_bf16, const void* head_b_f32,
+                                       void* out_f32, int32_t n_seqs, int32_t hidden, int32_t dim,
+                                       void* stream);
+
+/* ====================================================================================
+ * Decode path. No reference GPU or CPU implementation exists for these; the anchors are the
+ * contracts named beside each.
+ * ==================================================================================== */
+
+/* int4 group-32 dequant GEMV / skinny GEMM: y[b,n] = sum_g s[n,g] sum_{k in g} q[n,k] x[b,k].
+ * codes u8 [n, k/2]: value k of a row in byte k/2, even k in the low nibble (the nibble order of
+ * Turbo4Block, crates/quant/src/lib.rs:272-301), two's-complement 4-bit; scales fp16 [n, k/32];
+ * x bf16 [batch, k]; y bf16 [batch, n]. 1 <= batch <= 64, k % 128 == 0. */
+uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
+                                            const void* x_bf16, void* y_bf16, int32_t batch,
+                                            int32_t n, int32_t k, void* stream);
+
+/* Paged-attention decode with fused KV append. The paged cache keeps the row layout of
+ * FlatKvCache (crates/cache/src/flat.rs:36-69: one row = all kv heads of one token, contiguous):
+ * k_pool / v_pool bf16 [n_pool_blocks, block_size = 16, n_kv_heads * head_dim]; logical token t
+ * of sequence s lives in block block_tables[s * max_blocks + t / 16], slot t % 16.
+ * For each sequence: the new token's k/v row (new_k / new_v bf16 [n_seqs, n_kv_heads*head_dim])
+ * is written at position context_lens[s] - 1 (context_lens counts the new token), then
+ * q bf16 [n_seqs, n_heads * head_dim] attends causally to positions 0 .. context_lens[s] - 1.
+ * new_k == NULL skips the append. head_dim == 128, n_heads / n_kv_heads <= 16.
+ * Work is split along the context in chunks of `chunk_tokens` (a multiple of 64):
+ * chunk_offsets i32 [n_seqs + 1] is the exclusive prefix sum of ceil(context_lens / chunk_tokens)
+ * and total_chunks its last entry (host copy). scratch must hold
+ * logismos_paged_decode_scratch_bytes(total_chunks, n_heads, head_dim) bytes. status_i32 (may be
+ * NULL) receives 1 if a block id fell outside the pool (that block is then skipped). */
+size_t logismos_paged_decode_scratch_bytes(int32_t total_chunks, int32_t n_heads, int32_t head_dim);
+uint32_t logismos_launch_paged_attention_decode_bf16(
+    const void* q_bf16, void* k_pool_bf16, void* v_pool_bf16, const void* new_k_bf16,
+    const void* new_v_bf16, const void* block_tables_i32, const void* context_lens_i32,
+    const void* chunk_offsets_i32, void* out_bf16, void* scratch, void* status_i32, int32_t n_seqs,
+    int32_t total_chunks, int32_t chunk_tokens, int32_t max_blocks, int32_t n_pool_blocks,
+    int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, void* stream);
+
+/* KvCache::put for a ragged batch (crates/cache/src/lib.rs:57-82): row i of k/v bf16
+ * [n_tokens, row_elems] is stored at physical slot slot_mapping[i] (i64: block * 16 + offset).
+ * A slot outside the pool is skipped and sets *status to 1. */
+uint32_t logismos_launch_paged_kv_store_bf16(const void* k_bf16, const void* v_bf16,
+                                             int32_t src_row_stride, void* k_pool_bf16,
+                                             void* v_pool_bf16, const void* slot_mapping_i64,
+                                             int32_t n_tokens, int32_t row_elems,
+                                             int64_t n_pool_slots, void* status_i32, void* stream);
+/* KvCache::get: the first len rows of one sequence gathered through its block table into
+ * contiguous bf16 [len, row_elems] buffers (bit-exact copy). */
+uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool_bf16, const void* v_pool_bf16,
+                                              const void* block_table_i32, int32_t table_len,
+                                              int32_t len, int32_t row_elems,
+                                              int32_t n_pool_blocks, void* k_out_bf16,
+                                              void* v_out_bf16, void* status_i32, void* stream);
+
+/* gated_delta_rule_recurrent_fwd (crates/kernels/src/gated_delta_rule/cpu.rs:92-182), one decode
+ * step for a batch of sequences and heads: state f32 [n_seqs, heads, K=128, V=128] updated in
+ * place; q,k f32/bf16 ... see gdn.cu. q, k bf16 [n_seqs, heads, 128]; v bf16 [n_seqs, heads, 128];
+ * g, beta f32 [n_seqs, heads]; o bf16 [n_seqs, heads, 128]. */
+uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, const void* k_bf16,
+                                         const void* v_bf16, const void* g_f32,
+                                         const void* beta_f32, void* o_bf16, int32_t n_seqs,
+                                         int32_t heads, float scale, void* stream);
+
+/* decode::greedy (crates/decode/src/lib.rs:73-83): argmax per row, first maximum wins, NaN
+ * never selected. logits bf16 or f32 [rows, n]; out u32 [rows]. */
+uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, void* out_u32,
+                                       int32_t rows, int32_t n, void* stream);
+
+/* ====================================================================================
+ * Host-side index builders (no device work). crates/sched is an empty scaffold in the reference
+ * (src/lib.rs:1-30); these define the packing of a mixed prefill/decode step.
+ * ==================================================================================== */
+
+/* For sequence i with cached_lens[i] tokens already in the cache and new_lens[i] new tokens:
+ * cu_seqlens [n+1], positions [total] (continuing from the cached length), slot_mapping [total]
+ * (block * block_size + offset through block_tables [n, max_blocks]), seq_ids [total].
+ * Returns the total token count, or -1 if a needed table entry is negative or >= n_pool_blocks. */
+int64_t logismos_build_packing(const int32_t* host_cached_lens, const int32_t* host_new_lens,
+                               int32_t n_seqs, const int32_t* host_block_tables,
+                               int32_t max_blocks, int32_t block_size, int32_t n_pool_blocks,
+                               int32_t* host_cu_seqlens, int32_t* host_positions,
+                               int64_t* host_slot_mapping, int32_t* host_seq_ids);
+/* chunk_offsets [n+1] for the paged decode kernel; returns total_chunks. */
+int32_t logismos_build_decode_chunks(const int32_t* host_context_lens, int32_t n_seqs,
+                                     int32_t chunk_tokens, int32_t* host_chunk_offsets);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,104 @@
+/*
+ * logismos_model.h - C ABI of the host-side executors above the kernel launchers.
+ *
+ * lg_stella_* is the GPU form of the reference's Stella embedding model:
+ *   StellaEncoder::forward        crates/encoders/src/stella.rs:278-313 (layer body :190-206)
+ *   StellaModel::encode_raw       crates/embed/src/stella.rs:221-248
+ *   StellaModel::encode_batch     crates/embed/src/stella.rs:264-294
+ * behind the consumer contract core::EmbeddingModel (crates/core/src/lib.rs:139-163). Text
+ * handling (prompt, tokenizer) stays on the caller's side of this boundary: the entry points
+ * take token ids, which is what `encode_raw(ids, mask, dim)` takes in the reference. There is no
+ * padding in this path (the reference builds an all-ones mask, crates/embed/src/stella.rs:318),
+ * so a batch is a ragged concatenation of id runs delimited by cu_seqlens.
+ *
+ * Results are EmbeddingError-shaped status codes; 0 is success.
+ */
+#ifndef LOGISMOS_MODEL_H
+#define LOGISMOS_MODEL_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* EmbeddingError (crates/core/src/lib.rs:75-133) as status codes */
+enum lg_embedding_status {
+  LG_EMB_OK = 0,
+  LG_EMB_INPUT_TOO_LONG = 1,   /* InputTooLong { got, limit }: never truncates (:63-66) */
+  LG_EMB_UNSUPPORTED_DIM = 2,  /* UnsupportedDim { dim } */
+  LG_EMB_TOKENIZE = 3,         /* unused at id level */
+  LG_EMB_COMPUTE = 4,          /* Compute { message }: shape errors, CUDA failures */
+  LG_EMB_IO = 5,
+  LG_EMB_UNSUPPORTED_PROMPT = 6
+};
+
+/* StellaConfig (crates/encoders/src/stella.rs:45-80). head_dim = hidden / n_heads must be 128. */
+typedef struct lg_stella_config {
+  int32_t vocab, hidden, n_layers, n_heads, n_kv_heads, intermediate, max_pos;
+  float rms_eps;
+  double rope_theta;
+  int32_t max_tokens;        /* default per-input limit (EncodeOpts::max_tokens None -> 512) */
+  int32_t n_dims;            /* number of dense heads loaded (supported_dims) */
+  int32_t dims[8];           /* output dims, dims[0] is default_dim */
+  int32_t max_batch_tokens;  /* workspace capacity in tokens; larger batches are run in pieces */
+  int32_t max_batch_seqs;
+  int32_t fuse_swiglu;       /* 1: SwiGLU fused into the gate/up GEMM epilogue */
+} lg_stella_config_t;
+
+/* The 12 tensors of one layer (crates/encoders/src/stella.rs:326-349), HOST fp32, HF [out, in]. */
+typedef struct lg_stella_layer_weights {
+  const float *norm1, *norm2;
+  const float *wq, *bq, *wk, *bk, *wv, *bv, *wo;
+  const float *w_gate, *w_up, *w_down;
+} lg_stella_layer_weights_t;
+
+typedef struct lg_stella_weights {
+  const float* tok_embed;   /* [vocab, hidden] */
+  const float* final_norm;  /* [hidden] */
+  const lg_stella_layer_weights_t* layers;
+  const float* head_w[8];   /* [dims[i], hidden]  (2_Dense_{dim}/linear.weight) */
+  const float* head_b[8];   /* [dims[i]] */
+} lg_stella_weights_t;
+
+/* StellaModel::load counterpart for in-memory weights: casts to bf16, uploads, sizes the
+ * workspace. All device allocation happens here. Returns LG_EMB_COMPUTE on failure with the
+ * reason available from lg_last_error(). */
+uint32_t lg_stella_create(int32_t device, const lg_stella_config_t* cfg, const lg_stella_weights_t* w,
+                          void** model);
+void lg_stella_destroy(void* model);
+
+/* EmbeddingModel::{default_dim, supported_dims, max_tokens} */
+int32_t lg_stella_default_dim(const void* model);
+int32_t lg_stella_supported_dims(const void* model, int32_t* out, int32_t cap);
+int32_t lg_stella_max_tokens(const void* model);
+
+/* EmbeddingModel::encode_batch at id level. host_ids u32 [cu_seqlens[n_seqs]], host_cu_seqlens
+ * i32 [n_seqs + 1], host_out f32 [n_seqs, dim], unit-norm rows. dim == 0 selects default_dim;
+ * max_tokens == 0 selects the model default. Copies ids to the device, runs the forward, copies
+ * the embeddings back and synchronises. Thread-safe (calls are serialised per model). */
+uint32_t lg_stella_encode_ids_batch(void* model, const uint32_t* host_ids, const int32_t* host_cu_seqlens,
+                                    int32_t n_seqs, int32_t dim, int32_t max_tokens, float* host_out);
+
+/* The same forward with everything already resident: dev_ids u32 [n_tokens], dev_cu_seqlens i32
+ * [n_seqs+1], dev_positions i32 [n_tokens] (position of each token inside its sequence),
+ * dev_out f32 [n_seqs, dim]. Enqueues on `stream` and returns without synchronising.
+ * n_tokens <= max_batch_tokens. causal != 0 runs the decoder-style (causal) variant. */
+uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* dev_cu_seqlens,
+                                  const void* dev_positions, int32_t n_tokens, int32_t n_seqs,
+                                  int32_t max_seqlen, int32_t dim, int32_t causal, void* dev_out, void* stream);
+
+/* StellaEncoder::forward output of the last forward: f32 [n_tokens, hidden] copied to host. */
+uint32_t lg_stella_last_hidden(void* model, int32_t n_tokens, float* host_out);
+/* Number of kernel launches one forward of n_layers issues (for launch accounting). */
+int32_t lg_stella_launches_per_forward(const void* model);
+/* Status word written by kernels with bounded waits / range checks during the last forward. */
+int32_t lg_stella_device_status(void* model);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* lg_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

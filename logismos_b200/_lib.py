@@ -1,0 +1,139 @@
+"""ctypes binding of liblogismos_kernels.so (the C ABI declared in include/*.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liblogismos_kernels.so")
+
+vp, i32, i64, u32, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_float, C.c_size_t
+
+
+class LogismosError(RuntimeError):
+    """A launcher or runtime call returned a non-zero status (kernels::Error::Launch in the
+    reference, crates/kernels/src/error.rs:30-41): carries the raw code and its classified kind."""
+
+    def __init__(self, op: str, code: int, kind: str = "", message: str = ""):
+        self.op, self.code, self.kind = op, code, kind
+        super().__init__(f"{op}: {kind or 'error'} (code {code}) {message}".strip())
+
+
+class NoGpuBuild(LogismosError):
+    """The CUDA library is absent (Error::NoGpuBuild, crates/kernels/src/error.rs:58-64)."""
+
+
+def library_path() -> str:
+    return _SO
+
+
+class _LStella(C.Structure):
+    pass
+
+
+def _declare(l):
+    sig = {
+        # runtime shim
+        "lg_device_count": [C.POINTER(i32)],
+        "lg_device_set_current": [i32],
+        "lg_device_props_get": [i32, vp],
+        "lg_device_mem_info": [i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
+        "lg_device_synchronize": [i32],
+        "lg_malloc": [i32, sz, C.POINTER(vp)],
+        "lg_free": [i32, vp],
+        "lg_memset": [i32, vp, i32, sz],
+        "lg_memcpy_h2d": [i32, vp, vp, sz],
+        "lg_memcpy_d2h": [i32, vp, vp, sz],
+        "lg_memcpy_h2d_async": [i32, vp, vp, sz, vp],
+        "lg_stream_create": [i32, C.POINTER(vp)],
+        "lg_stream_synchronize": [i32, vp],
+        "lg_stream_destroy": [i32, vp],
+        "lg_event_create": [i32, C.POINTER(vp)],
+        "lg_event_record": [i32, vp, vp],
+        "lg_event_synchronize": [i32, vp],
+        "lg_event_elapsed_ms": [vp, vp, C.POINTER(f32)],
+        "lg_event_destroy": [i32, vp],
+        "lg_error_kind_from_raw": [u32],
+        # reference launchers
+        "logismos_launch_matmul_naive_fp16": [vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_matmul_wmma_fp16": [vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_rms_norm_fp16": [vp, vp, vp, i32, i32, f32, vp],
+        "logismos_launch_softmax_fp16": [vp, vp, i32, i32, vp],
+        "logismos_launch_rope_fp16": [vp, vp, i32, i32, i32, i32, vp],
+        # encoder path
+        "logismos_launch_embed_lookup_bf16": [vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_rms_norm_f32": [vp, vp, vp, i32, i32, f32, i32, vp],
+        "logismos_launch_linear_t_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_linear_t_naive_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "logismos_launch_rope_halves_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_swiglu_bf16": [vp, vp, i32, i32, vp],
+        "logismos_launch_varlen_attention_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
+        "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
+        # decode path
+        "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_paged_attention_decode_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
+                                                        i32, i32, i32, i32, i32, vp],
+        "logismos_launch_paged_kv_store_bf16": [vp, vp, i32, vp, vp, vp, i32, i32, i64, vp, vp],
+        "logismos_launch_paged_kv_gather_bf16": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
+        "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
+        "logismos_launch_greedy_argmax": [vp, i32, vp, i32, i32, vp],
+        # model
+        "lg_stella_create": [i32, vp, vp, C.POINTER(vp)],
+        "lg_stella_encode_ids_batch": [vp, vp, vp, i32, i32, i32, vp],
+        "lg_stella_forward_device": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
+        "lg_stella_last_hidden": [vp, i32, vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(l, name)
+        fn.argtypes = args
+        fn.restype = u32
+    l.lg_error_kind_name.argtypes = [u32]
+    l.lg_error_kind_name.restype = C.c_char_p
+    l.lg_error_string.argtypes = [u32]
+    l.lg_error_string.restype = C.c_char_p
+    l.lg_last_error.argtypes = []
+    l.lg_last_error.restype = C.c_char_p
+    l.logismos_paged_decode_scratch_bytes.argtypes = [i32, i32, i32]
+    l.logismos_paged_decode_scratch_bytes.restype = sz
+    l.logismos_build_packing.argtypes = [vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp]
+    l.logismos_build_packing.restype = i64
+    l.logismos_build_decode_chunks.argtypes = [vp, i32, i32, vp]
+    l.logismos_build_decode_chunks.restype = i32
+    l.lg_stella_destroy.argtypes = [vp]
+    l.lg_stella_destroy.restype = None
+    for name in ("lg_stella_default_dim", "lg_stella_max_tokens", "lg_stella_launches_per_forward",
+                 "lg_stella_device_status"):
+        getattr(l, name).argtypes = [vp]
+        getattr(l, name).restype = i32
+    l.lg_stella_supported_dims.argtypes = [vp, C.POINTER(i32), i32]
+    l.lg_stella_supported_dims.restype = i32
+    return l
+
+
+class _Lazy:
+    """Loads the shared library on first use; a missing library is an error, never a fallback."""
+
+    def __init__(self):
+        self._l = None
+
+    def _load(self):
+        if self._l is None:
+            if not os.path.exists(_SO):
+                raise NoGpuBuild("load", 0, "NoGpuBuild",
+                                 f"{_SO} is missing: build it with `python -m logismos_b200.build` "
+                                 "(there is no CPU fallback)")
+            self._l = _declare(C.CDLL(_SO))
+        return self._l
+
+    def __getattr__(self, name):
+        return getattr(self._load(), name)
+
+
+lib = _Lazy()
+
+
+def check(code: int, op: str):
+    """Raise LogismosError for a non-zero launcher / runtime status."""
+    if code:
+        kind = lib.lg_error_kind_name(lib.lg_error_kind_from_raw(code)).decode()
+        raise LogismosError(op, int(code), kind, lib.lg_error_string(code).decode())

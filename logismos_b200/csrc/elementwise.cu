@@ -1,0 +1,279 @@
+// Memory-bound pieces of the encoder/decoder layer: embedding gather, RMSNorm over the fp32
+// residual stream, halves-RoPE on packed q/k, SwiGLU, pooled embedding head, greedy argmax.
+// Each restates one function of crates/kernels/src/cpu_f32/mod.rs (cited per kernel) with
+// 128-bit coalesced accesses and warp-shuffle reductions.
+#include "common.cuh"
+#include "logismos_kernels.h"
+
+namespace {
+
+using namespace lg;
+
+// cpu_f32::embed_lookup (mod.rs:106-127). One warp per token row; 8 bf16 per lane per step.
+__global__ void embed_lookup_kernel(const __nv_bfloat16* __restrict__ table,
+                                    const uint32_t* __restrict__ ids, float* __restrict__ out,
+                                    int n_ids, int hidden, int vocab) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_ids) return;
+  const int lane = threadIdx.x & 31;
+  const uint32_t id = ids[row];
+  float* dst = out + (size_t)row * hidden;
+  if (id >= (uint32_t)vocab) {  // out-of-range id: zero row, not an error (mod.rs:96-104)
+    for (int j = lane * 4; j < hidden; j += 128) *reinterpret_cast<float4*>(dst + j) = make_float4(0, 0, 0, 0);
+    return;
+  }
+  const __nv_bfloat16* src = table + (size_t)id * hidden;
+  for (int j = lane * 8; j < hidden; j += 256) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + j));
+    const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+    *reinterpret_cast<float4*>(dst + j) = make_float4(a.x, a.y, b.x, b.y);
+    *reinterpret_cast<float4*>(dst + j + 4) = make_float4(c.x, c.y, d.x, d.y);
+  }
+}
+
+// cpu_f32::rms_norm (mod.rs:137-159). One CTA per row, the row held in registers between the
+// two passes (n <= 8 * 4 * blockDim).
+template <bool OUT_F32>
+__global__ void rms_norm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                    void* __restrict__ y, int n, float eps) {
+  __shared__ float red[32];
+  const float* row = x + (size_t)blockIdx.x * n;
+  float4 v[8];
+  float ss = 0.0f;
+  int cnt = 0;
+  for (int j = threadIdx.x * 4; j < n && cnt < 8; j += blockDim.x * 4, ++cnt) {
+    v[cnt] = *reinterpret_cast<const float4*>(row + j);
+    ss += v[cnt].x * v[cnt].x + v[cnt].y * v[cnt].y + v[cnt].z * v[cnt].z + v[cnt].w * v[cnt].w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  cnt = 0;
+  for (int j = threadIdx.x * 4; j < n && cnt < 8; j += blockDim.x * 4, ++cnt) {
+    const float4 g = __ldg(reinterpret_cast<const float4*>(w + j));
+    const float o0 = v[cnt].x * inv * g.x, o1 = v[cnt].y * inv * g.y;
+    const float o2 = v[cnt].z * inv * g.z, o3 = v[cnt].w * inv * g.w;
+    if (OUT_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + (size_t)blockIdx.x * n + j) = make_float4(o0, o1, o2, o3);
+    } else {
+      uint2 p;
+      p.x = pack_bf16x2(o0, o1);
+      p.y = pack_bf16x2(o2, o3);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)blockIdx.x * n + j) = p;
+    }
+  }
+}
+
+// cpu_f32::rope_halves_in_place (mod.rs:502-547): y[i] = x[i] c - x[i+d/2] s,
+// y[i+d/2] = x[i] s + x[i+d/2] c, in fp32, on bf16 storage. One thread per (token, head, pair of
+// adjacent i), i.e. bf16x2 accesses in both halves.
+__global__ void rope_halves_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cosT,
+                                   const float* __restrict__ sinT, const int* __restrict__ positions,
+                                   int n_tokens, int n_heads, int head_dim, int row_stride,
+                                   int max_pos, int* __restrict__ status) {
+  const int half = head_dim >> 1, pairs = half >> 1;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)n_tokens * n_heads * pairs;
+  if (idx >= total) return;
+  const int p = (int)(idx % pairs);
+  const int h = (int)((idx / pairs) % n_heads);
+  const int t = (int)(idx / ((int64_t)pairs * n_heads));
+  const int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) {  // RopeTable::gather rejects it (rope.rs:57-66)
+    if (status) atomicExch(status, 1);
+    return;
+  }
+  __nv_bfloat16* base = qk + (size_t)t * row_stride + h * head_dim;
+  const float2 c = *reinterpret_cast<const float2*>(cosT + (size_t)pos * half + 2 * p);
+  const float2 s = *reinterpret_cast<const float2*>(sinT + (size_t)pos * half + 2 * p);
+  uint32_t* lo = reinterpret_cast<uint32_t*>(base + 2 * p);
+  uint32_t* hi = reinterpret_cast<uint32_t*>(base + half + 2 * p);
+  const float2 x0 = unpack_bf16x2(*lo), x1 = unpack_bf16x2(*hi);
+  *lo = pack_bf16x2(x0.x * c.x - x1.x * s.x, x0.y * c.y - x1.y * s.y);
+  *hi = pack_bf16x2(x0.x * s.x + x1.x * c.x, x0.y * s.y + x1.y * c.y);
+}
+
+// cpu_f32::silu (x / (1 + e^-x), mod.rs:349-351) times up (hadamard, :365-374).
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                              int rows, int inter) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // 8 outputs per thread
+  const int per_row = inter >> 3;
+  if (idx >= (int64_t)rows * per_row) return;
+  const int r = (int)(idx / per_row), j = (int)(idx % per_row) * 8;
+  const uint4 g = __ldg(reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * inter + j));
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * inter + inter + j));
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = unpack_bf16x2(gw[i]), b = unpack_bf16x2(uw[i]);
+    ow[i] = pack_bf16x2(a.x / (1.0f + __expf(-a.x)) * b.x, a.y / (1.0f + __expf(-a.y)) * b.y);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)r * inter + j) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+// StellaModel::encode_raw tail (crates/embed/src/stella.rs:231-246): masked mean (mask all
+// ones; zero-length sequence -> denominator 1) -> L2 (clamp 1e-12) -> W p + b -> L2.
+// One CTA (256 threads) per sequence; pooled vector in shared memory (hidden <= 4096).
+__global__ void pool_head_kernel(const float* __restrict__ hs, const int* __restrict__ cu,
+                                 const __nv_bfloat16* __restrict__ hw, const float* __restrict__ hb,
+                                 float* __restrict__ out, int hidden, int dim) {
+  extern __shared__ float sm[];
+  float* pooled = sm;           // [hidden]
+  float* yv = sm + hidden;      // [dim]
+  __shared__ float red[32];
+  const int s0 = cu[blockIdx.x], s1 = cu[blockIdx.x + 1];
+  const int len = s1 - s0;
+  const float inv_den = len > 0 ? 1.0f / (float)len : 1.0f;
+  float sq = 0.0f;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+    float acc = 0.0f;
+    for (int t = s0; t < s1; ++t) acc += hs[(size_t)t * hidden + j];
+    acc *= inv_den;
+    pooled[j] = acc;
+    sq += acc * acc;
+  }
+  sq = block_sum(sq, red);
+  const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) pooled[j] *= inv;
+  __syncthreads();
+  // dense head: one warp per output row, 8 bf16 per lane per step
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float sq2 = 0.0f;
+  for (int o = warp; o < dim; o += nw) {
+    const __nv_bfloat16* wr = hw + (size_t)o * hidden;
+    float acc = 0.0f;
+    for (int j = lane * 8; j < hidden; j += 256) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(wr + j));
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      acc += a.x * pooled[j] + a.y * pooled[j + 1] + b.x * pooled[j + 2] + b.y * pooled[j + 3] +
+             c.x * pooled[j + 4] + c.y * pooled[j + 5] + d.x * pooled[j + 6] + d.y * pooled[j + 7];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      acc += hb[o];
+      yv[o] = acc;
+      sq2 += acc * acc;
+    }
+  }
+  sq2 = block_sum(sq2, red);
+  const float inv2 = 1.0f / fmaxf(sqrtf(sq2), 1e-12f);
+  for (int o = threadIdx.x; o < dim; o += blockDim.x) out[(size_t)blockIdx.x * dim + o] = yv[o] * inv2;
+}
+
+// decode::greedy (crates/decode/src/lib.rs:73-83): strict > from -inf, so the first maximum wins
+// and NaN is never selected. One CTA per row; ties across threads resolve to the lowest index.
+template <typename T>
+__global__ void greedy_argmax_kernel(const T* __restrict__ logits, uint32_t* __restrict__ out, int n) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const T* row = logits + (size_t)blockIdx.x * n;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float v = (float)row[j];
+    if (v > best) { best = v; best_i = j; }
+  }
+  auto better = [](float v, int i, float bvv, int bii) { return v > bvv || (v == bvv && i < bii); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) { bv[warp] = best; bi[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < nw ? bv[lane] : -INFINITY;
+    best_i = lane < nw ? bi[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    // nothing exceeded -inf (all -inf or NaN): the reference returns index 0
+    if (lane == 0) out[blockIdx.x] = (best_i == 0x7fffffff) ? 0u : (uint32_t)best_i;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t logismos_launch_embed_lookup_bf16(const void* table, const void* ids, void* out,
+                                           int32_t n_ids, int32_t hidden, int32_t vocab,
+                                           void* stream) {
+  if (n_ids < 0 || hidden <= 0 || vocab <= 0 || (hidden % 8)) return lg::kInvalidValue;
+  if (n_ids == 0) return 0;
+  const int wpb = 8;
+  embed_lookup_kernel<<<(n_ids + wpb - 1) / wpb, wpb * 32, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)table, (const uint32_t*)ids, (float*)out, n_ids, hidden, vocab);
+  return lg::launch_status();
+}
+
+uint32_t logismos_launch_rms_norm_f32(const void* x, const void* w, void* y, int32_t rows,
+                                      int32_t n, float eps, int32_t out_f32, void* stream) {
+  if (rows < 0 || n <= 0 || (n % 4) || n > 8 * 4 * 256) return lg::kInvalidValue;
+  if (rows == 0) return 0;
+  int bs = 32;
+  while (bs * 4 * 2 < n && bs < 256) bs <<= 1;  // aim for ~2 float4 per thread
+  if (out_f32)
+    rms_norm_f32_kernel<true><<<rows, bs, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)w, y, n, eps);
+  else
+    rms_norm_f32_kernel<false><<<rows, bs, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)w, y, n, eps);
+  return lg::launch_status();
+}
+
+uint32_t logismos_launch_rope_halves_bf16(void* qk, const void* cos_f32, const void* sin_f32,
+                                          const void* positions, int32_t n_tokens,
+                                          int32_t n_rot_heads, int32_t head_dim,
+                                          int32_t row_stride, int32_t max_pos, void* status,
+                                          void* stream) {
+  if (n_tokens < 0 || n_rot_heads <= 0 || head_dim <= 0 || (head_dim % 4) || max_pos <= 0 ||
+      row_stride < n_rot_heads * head_dim || (row_stride % 2))
+    return lg::kInvalidValue;
+  if (n_tokens == 0) return 0;
+  const int64_t total = (int64_t)n_tokens * n_rot_heads * (head_dim / 4);
+  const int bs = 256;
+  rope_halves_kernel<<<(unsigned)((total + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)qk, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions,
+      n_tokens, n_rot_heads, head_dim, row_stride, max_pos, (int*)status);
+  return lg::launch_status();
+}
+
+uint32_t logismos_launch_swiglu_bf16(const void* gu, void* out, int32_t rows, int32_t inter,
+                                     void* stream) {
+  if (rows < 0 || inter <= 0 || (inter % 8)) return lg::kInvalidValue;
+  if (rows == 0) return 0;
+  const int64_t total = (int64_t)rows * (inter / 8);
+  const int bs = 256;
+  swiglu_kernel<<<(unsigned)((total + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, inter);
+  return lg::launch_status();
+}
+
+uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu, const void* head_w,
+                                       const void* head_b, void* out, int32_t n_seqs,
+                                       int32_t hidden, int32_t dim, void* stream) {
+  if (n_seqs < 0 || hidden <= 0 || dim <= 0 || (hidden % 8) || (size_t)(hidden + dim) * 4 > 48 * 1024)
+    return lg::kInvalidValue;
+  if (n_seqs == 0) return 0;
+  pool_head_kernel<<<n_seqs, 256, (size_t)(hidden + dim) * 4, (cudaStream_t)stream>>>(
+      (const float*)hidden_f32, (const int*)cu, (const __nv_bfloat16*)head_w, (const float*)head_b,
+      (float*)out, hidden, dim);
+  return lg::launch_status();
+}
+
+uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, void* out,
+                                       int32_t rows, int32_t n, void* stream) {
+  if (rows < 0 || n <= 0) return lg::kInvalidValue;
+  if (rows == 0) return 0;
+  if (logits_f32)
+    greedy_argmax_kernel<float><<<rows, 256, 0, (cudaStream_t)stream>>>((const float*)logits, (uint32_t*)out, n);
+  else
+    greedy_argmax_kernel<__nv_bfloat16><<<rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, (uint32_t*)out, n);
+  return lg::launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,456 @@
+// C = A W^T (+ bias) on the 5th-generation tensor cores: the GPU form of cpu_f32::linear_t
+// (crates/kernels/src/cpu_f32/mod.rs:271-345) for the encoder / prefill GEMMs, which are the
+// only dense contractions on the path.
+//
+// Design (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor 2-D tiles of A [128 x 64] and W [BN x 64]
+//               (bf16, 128-byte swizzle) into a ring of shared-memory stages
+//   warp 1      allocates TMEM and issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN,
+//               K=16; four per 64-wide stage) with fp32 accumulators in TMEM; two accumulator
+//               buffers so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns per warp step, fused bias /
+//               residual add / SwiGLU, vectorised global stores
+// Synchronisation is by mbarriers only: full/empty per stage (TMA complete_tx, tcgen05.commit)
+// and full/empty per accumulator buffer. Every wait is bounded; on expiry the kernel raises an
+// error word, lets outstanding copies land, frees its TMEM and returns.
+// No cluster launch and no multicast is used: each CTA fetches its own tiles.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "logismos_kernels.h"
+
+namespace {
+
+using namespace lg;
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 bf16 = 128 B = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (200 * 1024) / kStage;  // 256->4, 192->5, 128->6
+  static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;
+  static constexpr size_t kSmem = (size_t)kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+// ---- mbarrier / TMA / tcgen05 wrappers --------------------------------------------------------
+
+LG_DEVINL void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+LG_DEVINL void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes));
+}
+LG_DEVINL void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar));
+}
+LG_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit expired or another role already gave up.
+LG_DEVINL bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+LG_DEVINL void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(smem_dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+LG_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+LG_DEVINL void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+LG_DEVINL void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+               : "memory");
+}
+
+LG_DEVINL void tc_mma_bf16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+LG_DEVINL void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+LG_DEVINL void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 B, 8-row
+// swizzle atoms 1024 B apart (stride byte offset), leading byte offset unused (encoded 1),
+// descriptor version 1, layout type 2 (SWIZZLE_128B). Addresses are encoded >> 4.
+LG_DEVINL uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: D fp32, A and B bf16, both K-major, M=128, N=BN.
+template <int BN>
+__host__ __device__ constexpr uint32_t make_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+LG_DEVINL float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                        const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K,
+                        int ldc, int* __restrict__ status) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + C::kStages * C::kStage;  // full[S], empty[S], tfull[2], tempty[2]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * C::kStages + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::kStages + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kStages * C::kStage + 8 * (2 * C::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kStages * C::kStage + 8 * (2 * C::kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), (uint32_t)C::kStage);
+          const uint32_t sa = smem_base + stage * C::kStage;
+          tma_load_2d(sa, &map_a, full_bar(stage), kb * BK, m_blk * BM);
+          tma_load_2d(sa + C::kStageA, &map_w, full_bar(stage), kb * BK, n_blk * BN);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<BN>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * C::kStage;
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + C::kStageA);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 bf16 along K inside the swizzle row = +32 B = +2 in the encoded address
+            tc_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(tfull_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+      const int buf = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m_blk * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      if (EPI == LG_EPI_SWIGLU) {
+        // W rows interleave 32 gate rows with the 32 matching up rows
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t g[32], u[32];
+          tc_ld32(t_row + c, g);
+          tc_ld32(t_row + c + 32, u);
+          tc_wait_ld();
+          const int ncol = n_blk * BN + c;        // column of the gate block in W-row space
+          const int ocol = ncol >> 1;             // output column
+          if (row < M && ncol < N) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + ocol;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int e = j * 8 + i * 2;
+                float g0 = __uint_as_float(g[e]), g1 = __uint_as_float(g[e + 1]);
+                float u0 = __uint_as_float(u[e]), u1 = __uint_as_float(u[e + 1]);
+                if (bias) { g0 += bias[ncol + e]; g1 += bias[ncol + e + 1]; u0 += bias[ncol + 32 + e]; u1 += bias[ncol + 32 + e + 1]; }
+                w[i] = pack_bf16x2(silu_f(g0) * u0, silu_f(g1) * u1);
+              }
+              *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      } else {
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(t_row + c, r);
+          tc_wait_ld();
+          const int ncol = n_blk * BN + c;
+          if (row < M) {
+            if (EPI == LG_EPI_BF16) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + ncol;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (ncol + j * 8 < N) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const int e = j * 8 + i * 2;
+                    float a = __uint_as_float(r[e]), b = __uint_as_float(r[e + 1]);
+                    if (bias) { a += bias[ncol + e]; b += bias[ncol + e + 1]; }
+                    w[i] = pack_bf16x2(a, b);
+                  }
+                  *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              }
+            } else {  // LG_EPI_RESID_F32
+              float* dst = reinterpret_cast<float*>(out) + (size_t)row * ldc + ncol;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (ncol + j * 4 < N) {
+                  float4 v = *reinterpret_cast<float4*>(dst + j * 4);
+                  const int e = j * 4;
+                  float a0 = __uint_as_float(r[e]), a1 = __uint_as_float(r[e + 1]);
+                  float a2 = __uint_as_float(r[e + 2]), a3 = __uint_as_float(r[e + 3]);
+                  if (bias) { a0 += bias[ncol + e]; a1 += bias[ncol + e + 1]; a2 += bias[ncol + e + 2]; a3 += bias[ncol + e + 3]; }
+                  v.x += a0; v.y += a1; v.z += a2; v.w += a3;
+                  *reinterpret_cast<float4*>(dst + j * 4) = v;
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  __syncwarp();
+  if (*abort_flag) {
+    // a wait expired somewhere: give copies that may still be in flight time to land before the
+    // shared memory and TMEM are released, and report
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
+  }
+}
+
+// One thread per output element, ascending-k fp32 accumulation: the correctness anchor.
+__global__ void linear_t_naive_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w,
+                                      const float* __restrict__ bias, void* __restrict__ out, int M, int N,
+                                      int K, int lda, int ldc, int epi) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.y * blockDim.y + threadIdx.y;
+  if (row >= M || col >= N) return;
+  float acc = 0.0f;
+  const __nv_bfloat16* ar = a + (size_t)row * lda;
+  const __nv_bfloat16* wr = w + (size_t)col * K;
+  for (int k = 0; k < K; ++k) acc += __bfloat162float(ar[k]) * __bfloat162float(wr[k]);
+  if (bias) acc += bias[col];
+  if (epi == LG_EPI_BF16)
+    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)row * ldc + col] = __float2bfloat16_rn(acc);
+  else
+    reinterpret_cast<float*>(out)[(size_t)row * ldc + col] += acc;
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with row stride ld (elements); box = [box_rows, 64 cols]
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n) return n;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (n <= 0) n = 148;
+  return n;
+}
+
+template <int BN, int EPI>
+uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, int m, int n, int k, int lda,
+                    int ldc, int* status, cudaStream_t stream) {
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM)) return lg::kInvalidValue;
+  if (!make_map(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)k, BN)) return lg::kInvalidValue;
+  auto kern = linear_t_tcgen05_kernel<BN, EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmem);
+  if (e != cudaSuccess) return (uint32_t)e;
+  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, bias, out, m, n, k, ldc, status);
+  return lg::launch_status();
+}
+
+template <int EPI>
+uint32_t launch_epi(const void* a, const void* w, const float* bias, void* out, int m, int n, int k, int lda,
+                    int ldc, int* status, cudaStream_t stream) {
+  // tile width by wave quantisation: time ~ waves(BN) * BN; ties go to the wider tile
+  const int sms = sm_count();
+  const int mt = (m + BM - 1) / BM;
+  int best_bn = 256;
+  long best_cost = -1;
+  const int cands[3] = {256, 192, 128};
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cands[i];
+    const long tiles = (long)mt * ((n + bn - 1) / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    const long cost = waves * bn;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+  }
+  if (best_bn == 256) return launch_cfg<256, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
+  if (best_bn == 192) return launch_cfg<192, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
+  return launch_cfg<128, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t logismos_launch_linear_t_bf16(const void* a, const void* w, const void* bias, void* out, int32_t m,
+                                       int32_t n, int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
+                                       void* status_i32, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || (k % BK) || (n % 16) || (lda % 8) || lda < k) return lg::kInvalidValue;
+  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return lg::kInvalidValue;
+  if (epilogue == LG_EPI_SWIGLU && (n % 64)) return lg::kInvalidValue;
+  const int out_cols = epilogue == LG_EPI_SWIGLU ? n / 2 : n;
+  if (ldc < out_cols || (ldc % (epilogue == LG_EPI_RESID_F32 ? 4 : 8))) return lg::kInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const float* b = (const float*)bias;
+  int* st = (int*)status_i32;
+  switch (epilogue) {
+    case LG_EPI_BF16: return launch_epi<LG_EPI_BF16>(a, w, b, out, m, n, k, lda, ldc, st, s);
+    case LG_EPI_RESID_F32: return launch_epi<LG_EPI_RESID_F32>(a, w, b, out, m, n, k, lda, ldc, st, s);
+    case LG_EPI_SWIGLU: return launch_epi<LG_EPI_SWIGLU>(a, w, b, out, m, n, k, lda, ldc, st, s);
+    default: return lg::kInvalidValue;
+  }
+}
+
+uint32_t logismos_launch_linear_t_naive_bf16(const void* a, const void* w, const void* bias, void* out,
+                                             int32_t m, int32_t n, int32_t k, int32_t lda, int32_t ldc,
+                                             int32_t epilogue, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || lda < k || ldc < n) return lg::kInvalidValue;
+  if (epilogue != LG_EPI_BF16 && epilogue != LG_EPI_RESID_F32) return lg::kInvalidValue;
+  dim3 block(32, 8), grid((n + 31) / 32, (m + 7) / 8);
+  linear_t_naive_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (const float*)bias, out, m, n, k, lda, ldc, epilogue);
+  return lg::launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,235 @@
+// int4 group-32 dequant GEMV / skinny GEMM:  y[b,n] = sum_g s[n,g] * sum_{k in g} q[n,k] * x[b,k]
+//
+// Weight layout (anchored on the reference's Turbo4Block nibble order, crates/quant/src/lib.rs
+// :272-301): codes [N, K/2] bytes, value k of a row in byte k/2, low nibble for even k, stored as
+// a two's-complement 4-bit integer; scales [N, K/32] fp16. Activations x [B, K] bf16, output
+// y [B, N] bf16, fp32 accumulation. The weight matrix stays [N, K] like the reference's
+// linear_t (crates/kernels/src/cpu_f32/mod.rs:271-345).
+//
+// The kernel is bound by HBM traffic of the codes (0.5625 B per weight incl. scales), so the
+// design goal is to keep CUDA-core work per weight minimal:
+//   - a warp owns 16 weight rows; lane (g = lane/4, c = lane%4) reads, for rows g and g+8, the
+//     32-bit word c of four consecutive groups, i.e. the warp touches 64 contiguous bytes of
+//     each of its 16 rows per step;
+//   - nibbles become bf16 with one shift + one LOP3 per pair: ((w >> 4i) & 0x000f000f) ^ 0x0008
+//     | 0x4300 is the bf16 number 136 + q (q the signed code), exact;
+//   - the multiply-accumulate runs on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> fp32,
+//     products exact), the 16 k-slots of one instruction all taken from ONE quantisation group, so
+//     the group scale is applied afterwards in fp32: acc += s * (sum (136+q) x - 136 sum x).
+//     The correction 136 * sum_{k in group} x[b,k] is computed once per CTA while x is staged.
+//   - x is staged in shared memory as bf16 in the slot order the fragments want
+//     ([x0,x4,x1,x5,x2,x6,x3,x7] per 8 values), so a lane fetches the B fragments of both
+//     instructions of a group with one 128-bit load.
+#include "common.cuh"
+#include "logismos_kernels.h"
+
+namespace {
+
+using namespace lg;
+
+constexpr int kGroup = 32;
+constexpr int kIterK = 128;  // k covered by one warp step (4 groups)
+
+LG_DEVINL uint32_t nib_pair_bf16(uint32_t w) {
+  uint32_t r;
+  // (w & 0x000f000f) ^ 0x43084308 : LUT (a & b) ^ c = 0x6a
+  asm("lop3.b32 %0, %1, %2, %3, 0x6a;\n" : "=r"(r) : "r"(w), "r"(0x000f000fu), "r"(0x43084308u));
+  return r;
+}
+
+struct Frag {
+  uint32_t w0[4], w1[4];  // word c of groups G0..G0+3 for rows g and g+8
+  uint2 s0, s1;           // 4 fp16 scales each
+};
+
+LG_DEVINL void load_frag(Frag& f, const uint8_t* p0, const uint8_t* p1, const __half* sp0,
+                         const __half* sp1) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f.w0[j] = __ldg(reinterpret_cast<const uint32_t*>(p0 + j * 16));
+    f.w1[j] = __ldg(reinterpret_cast<const uint32_t*>(p1 + j * 16));
+  }
+  f.s0 = __ldg(reinterpret_cast<const uint2*>(sp0));
+  f.s1 = __ldg(reinterpret_cast<const uint2*>(sp1));
+}
+
+// NT = number of 8-wide batch tiles. Block = 32 * rt * ks threads.
+template <int NT>
+__global__ void __launch_bounds__(256)
+gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
+                     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                     int N, int K, int kc, int rt, int ks) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int rt_idx = warp / ks, ks_idx = warp % ks;
+  const int groups_kc = kc / kGroup;
+  const int xrow_stride = groups_kc * 64 + 64;  // bytes; +64 keeps 128-bit fragment loads conflict free
+  uint8_t* xs = smem;
+  float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
+
+  const int row_base = (blockIdx.x * rt + rt_idx) * 16;
+  const int r0 = min(row_base + g, N - 1), r1 = min(row_base + g + 8, N - 1);
+  const int groups_row = K / kGroup;
+  const uint8_t* wp0 = codes + (size_t)r0 * (K / 2) + c * 4;
+  const uint8_t* wp1 = codes + (size_t)r1 * (K / 2) + c * 4;
+  const __half* sp0 = scales + (size_t)r0 * groups_row;
+  const __half* sp1 = scales + (size_t)r1 * groups_row;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+
+  for (int k0 = 0; k0 < K; k0 += kc) {
+    const int kcur = min(kc, K - k0);
+    const int iters = kcur / kIterK;
+    // first weight fragment of this chunk goes in flight before x is staged
+    Frag cur;
+    int it = ks_idx;
+    if (it < iters)
+      load_frag(cur, wp0 + (k0 >> 1) + it * 64, wp1 + (k0 >> 1) + it * 64,
+                sp0 + k0 / kGroup + it * 4, sp1 + k0 / kGroup + it * 4);
+
+    if (k0 > 0) __syncthreads();  // previous chunk fully consumed
+    {
+      const int units_row = kcur / 8;
+      const int total = NT * 8 * units_row;  // multiple of 128: whole warps are in or out
+      for (int u = tid; u < total; u += blockDim.x) {
+        const int n = u / units_row, kk = u % units_row;
+        const int G = kk >> 2, cc = kk & 3;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kk * 8));
+        const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
+        const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
+        float s = ((v01.x + v01.y) + (v23.x + v23.y)) + ((v45.x + v45.y) + (v67.x + v67.y));
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        uint4 perm;  // [x0,x4 | x1,x5 | x2,x6 | x3,x7]
+        perm.x = __byte_perm(raw.x, raw.z, 0x5410);
+        perm.y = __byte_perm(raw.x, raw.z, 0x7632);
+        perm.z = __byte_perm(raw.y, raw.w, 0x5410);
+        perm.w = __byte_perm(raw.y, raw.w, 0x7632);
+        *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
+        if (cc == 0) negcorr[G * (NT * 8) + n] = -136.0f * s;
+      }
+    }
+    __syncthreads();
+
+    while (it < iters) {
+      const int nit = it + ks;
+      Frag nxt;
+      if (nit < iters)
+        load_frag(nxt, wp0 + (k0 >> 1) + nit * 64, wp1 + (k0 >> 1) + nit * 64,
+                  sp0 + k0 / kGroup + nit * 4, sp1 + k0 / kGroup + nit * 4);
+      const __half2 s0a = *reinterpret_cast<const __half2*>(&cur.s0.x);
+      const __half2 s0b = *reinterpret_cast<const __half2*>(&cur.s0.y);
+      const __half2 s1a = *reinterpret_cast<const __half2*>(&cur.s1.x);
+      const __half2 s1b = *reinterpret_cast<const __half2*>(&cur.s1.y);
+      const float sc0[4] = {__low2float(s0a), __high2float(s0a), __low2float(s0b), __high2float(s0b)};
+      const float sc1[4] = {__low2float(s1a), __high2float(s1a), __low2float(s1b), __high2float(s1b)};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int G = it * 4 + j;
+        const uint32_t w0 = cur.w0[j], w1 = cur.w1[j];
+        const uint32_t a_lo[4] = {nib_pair_bf16(w0), nib_pair_bf16(w1), nib_pair_bf16(w0 >> 4),
+                                  nib_pair_bf16(w1 >> 4)};
+        const uint32_t a_hi[4] = {nib_pair_bf16(w0 >> 8), nib_pair_bf16(w1 >> 8),
+                                  nib_pair_bf16(w0 >> 12), nib_pair_bf16(w1 >> 12)};
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 bx = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * xrow_stride +
+                                                           G * 64 + c * 16);
+          const float2 nc = *reinterpret_cast<const float2*>(negcorr + G * (NT * 8) + nt * 8 + 2 * c);
+          float d[4] = {nc.x, nc.y, nc.x, nc.y};
+          const uint32_t b_lo[2] = {bx.x, bx.y}, b_hi[2] = {bx.z, bx.w};
+          mma_bf16_16816(d, a_lo, b_lo, d);
+          mma_bf16_16816(d, a_hi, b_hi, d);
+          acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
+          acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
+          acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
+          acc[nt][3] = fmaf(sc1[j], d[3], acc[nt][3]);
+        }
+      }
+      cur = nxt;
+      it = nit;
+    }
+  }
+
+  // reduce the ks partial sums of each row tile through shared memory, then store bf16
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(smem);  // [warp][NT][4][32]
+  if (ks > 1) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+    __syncthreads();
+  }
+  if (ks_idx == 0) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float v[4] = {acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]};
+      for (int s = 1; s < ks; ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] += red[(((warp + s) * NT + nt) * 4 + i) * 32 + lane];
+      const int b0 = nt * 8 + 2 * c;
+      const int ra = row_base + g, rb = row_base + g + 8;
+      if (ra < N) {
+        if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(v[0]);
+        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(v[1]);
+      }
+      if (rb < N) {
+        if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(v[2]);
+        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(v[3]);
+      }
+    }
+  }
+}
+
+template <int NT>
+uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y, int batch, int N,
+                   int K, cudaStream_t stream) {
+  const int iters_k = K / kIterK;
+  int kc = 4096 / NT;  // x chunk staged per pass: NT * 8 rows * kc * 2 B  (<= 64 KB)
+  if (kc > K) kc = K;
+  const int iters_c = kc / kIterK;
+  int ks = 8;  // warps splitting the k range of one 16-row tile; each should get >= 2 steps
+  while (ks > 1 && (iters_c < 2 * ks || iters_k < 2 * ks)) ks >>= 1;
+  const int row_tiles = (N + 15) / 16;
+  int rt = 8 / ks;  // row tiles per CTA: 8 warps unless that leaves fewer than two CTAs per SM
+  while (rt > 1 && row_tiles / rt < 2 * 148) rt >>= 1;
+  const int threads = 32 * rt * ks;
+  const int groups_kc = kc / kGroup;
+  size_t smem = (size_t)NT * 8 * (groups_kc * 64 + 64) + (size_t)groups_kc * NT * 8 * 4;
+  const size_t red = (size_t)(threads / 32) * NT * 4 * 32 * 4;
+  if (red > smem) smem = red;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_int4_g32_kernel<NT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (uint32_t)e;
+  }
+  const int grid = (row_tiles + rt - 1) / rt;
+  gemv_int4_g32_kernel<NT><<<grid, threads, smem, stream>>>(
+      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+      batch, N, K, kc, rt, ks);
+  return lg::launch_status();
+}
+
+}  // namespace
+
+extern "C" uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes, const void* scales_f16,
+                                                       const void* x_bf16, void* y_bf16,
+                                                       int32_t batch, int32_t n, int32_t k,
+                                                       void* stream) {
+  if (batch <= 0 || batch > 64 || n <= 0 || k <= 0 || (k % kIterK) != 0) return lg::kInvalidValue;
+  if (((uintptr_t)codes & 3) || ((uintptr_t)scales_f16 & 7) || ((uintptr_t)x_bf16 & 15))
+    return lg::kInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nt = (batch + 7) / 8;
+  if (nt == 1) return launch_nt<1>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
+  if (nt == 2) return launch_nt<2>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
+  if (nt <= 4) return launch_nt<4>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
+  return launch_nt<8>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
+}

@@ -1,0 +1,313 @@
+"""Tensor-level ops over the CUDA launchers: the mirror of the reference's op layer
+(crates/praxis/src/{matmul,norm,softmax,rope}.rs) plus the ops this build adds in the same style.
+
+Rules kept from the reference (crates/praxis/src/matmul.rs:31-82, :154-166):
+  * inputs are immutable, the output is freshly allocated;
+  * dtype, rank and contiguity are checked and reported as ``InvalidOp``;
+  * there is no silent transfer: a CPU operand is an ``InvalidOp`` (the GPU build has no CPU arm);
+  * an op synchronises its stream before returning (crates/praxis/src/stream_pool.rs:11-21) unless
+    ``sync=False`` is passed by a caller that times kernels itself.
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, lib
+
+
+class InvalidOp(ValueError):
+    """praxis::Error::Invalid"""
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return C.c_void_p(0) if t is None else C.c_void_p(t.data_ptr())
+
+
+def _req(t, name, dtype, rank=None):
+    if not isinstance(t, torch.Tensor):
+        raise InvalidOp(f"{name}: not a tensor")
+    if t.device.type != "cuda":
+        raise InvalidOp(f"{name}: operands must all be on the same CUDA device (no CPU arm, no implicit transfer)")
+    if t.dtype != dtype:
+        raise InvalidOp(f"{name}: expected {dtype}, got {t.dtype}")
+    if rank is not None and t.dim() != rank:
+        raise InvalidOp(f"{name}: expected rank {rank}, got {t.dim()}")
+    if not t.is_contiguous():
+        raise InvalidOp(f"{name}: must be contiguous")
+
+
+def _same_device(*ts):
+    devs = {t.device for t in ts if t is not None}
+    if len(devs) > 1:
+        raise InvalidOp("operands must be on the same CUDA device")
+
+
+def _done(sync):
+    if sync:
+        torch.cuda.current_stream().synchronize()
+
+
+# ---- the reference's four ops (fp16) ---------------------------------------------------------
+
+def matmul(a, b, sync=True):
+    """praxis::matmul (matmul.rs:30-168): D = A @ B, fp16 rank-2; tensor-core variant when every
+    dim is a multiple of 16, else the naive kernel (:113-117)."""
+    _req(a, "a", torch.float16, 2); _req(b, "b", torch.float16, 2); _same_device(a, b)
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2:
+        raise InvalidOp(f"matmul: inner dims differ ({k} vs {k2})")
+    d = torch.zeros((m, n), dtype=torch.float16, device=a.device)
+    with torch.cuda.device(a.device):
+        fn = lib.logismos_launch_matmul_wmma_fp16 if (m % 16 == 0 and n % 16 == 0 and k % 16 == 0) \
+            else lib.logismos_launch_matmul_naive_fp16
+        check(fn(_p(a), _p(b), _p(d), m, n, k, _stream()), "matmul_fp16")
+        _done(sync)
+    return d
+
+
+def rms_norm(x, w, eps, sync=True):
+    """praxis::rms_norm (norm.rs:28-122)."""
+    _req(x, "x", torch.float16, 2); _req(w, "w", torch.float16, 1); _same_device(x, w)
+    if w.shape[0] != x.shape[1]:
+        raise InvalidOp("rms_norm: weight length != row length")
+    y = torch.zeros_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_rms_norm_fp16(_p(x), _p(w), _p(y), x.shape[0], x.shape[1], float(eps), _stream()), "rms_norm_fp16")
+        _done(sync)
+    return y
+
+
+def softmax(x, sync=True):
+    """praxis::softmax (softmax.rs:25-86): row softmax over the last dim of a rank-2 tensor."""
+    _req(x, "x", torch.float16, 2)
+    y = torch.zeros_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_softmax_fp16(_p(x), _p(y), x.shape[0], x.shape[1], _stream()), "softmax_fp16")
+        _done(sync)
+    return y
+
+
+def rope_apply(x, cos_sin, sync=True):
+    """praxis::rope_apply (rope.rs:102-208): interleaved-pair RoPE on (B,S,H,D) fp16 with an fp32
+    (S,D) table; returns a rotated copy (the input is left untouched)."""
+    _req(x, "x", torch.float16, 4); _req(cos_sin, "cos_sin", torch.float32, 2); _same_device(x, cos_sin)
+    b, s, h, d = x.shape
+    if tuple(cos_sin.shape) != (s, d):
+        raise InvalidOp("rope_apply: table must be (seq, head_dim)")
+    y = x.clone()
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_rope_fp16(_p(y), _p(cos_sin), b, s, h, d, _stream()), "rope_fp16")
+        _done(sync)
+    return y
+
+
+# ---- encoder path ----------------------------------------------------------------------------
+
+EPI_BF16, EPI_RESID_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def embed_lookup(table, ids, sync=True):
+    _req(table, "table", torch.bfloat16, 2); _req(ids, "ids", torch.int32, 1)
+    out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    with torch.cuda.device(table.device):
+        check(lib.logismos_launch_embed_lookup_bf16(_p(table), _p(ids), _p(out), ids.shape[0], table.shape[1], table.shape[0], _stream()), "embed_lookup")
+        _done(sync)
+    return out
+
+
+def rms_norm_f32(x, w, eps, out_f32=False, sync=True):
+    _req(x, "x", torch.float32, 2); _req(w, "w", torch.float32, 1)
+    y = torch.empty(x.shape, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_rms_norm_f32(_p(x), _p(w), _p(y), x.shape[0], x.shape[1], float(eps), int(out_f32), _stream()), "rms_norm_f32")
+        _done(sync)
+    return y
+
+
+def linear_t(a, w, bias=None, residual=None, swiglu=False, naive=False, sync=True):
+    """C = A W^T (+bias). residual: fp32 tensor updated in place (returns it). swiglu: W holds gate/up
+    rows interleaved in blocks of 32; returns silu(gate)*up."""
+    _req(a, "a", torch.bfloat16, 2); _req(w, "w", torch.bfloat16, 2)
+    if bias is not None:
+        _req(bias, "bias", torch.float32, 1)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise InvalidOp("linear_t: inner dims differ")
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    if residual is not None:
+        _req(residual, "residual", torch.float32, 2)
+        out, epi, ldc = residual, EPI_RESID_F32, n
+    elif swiglu:
+        out, epi, ldc = torch.empty((m, n // 2), dtype=torch.bfloat16, device=a.device), EPI_SWIGLU, n // 2
+    else:
+        out, epi, ldc = torch.empty((m, n), dtype=torch.bfloat16, device=a.device), EPI_BF16, n
+    with torch.cuda.device(a.device):
+        if naive:
+            check(lib.logismos_launch_linear_t_naive_bf16(_p(a), _p(w), _p(bias), _p(out), m, n, k, k, ldc, epi, _stream()), "linear_t_naive")
+        else:
+            check(lib.logismos_launch_linear_t_bf16(_p(a), _p(w), _p(bias), _p(out), m, n, k, k, ldc, epi, _p(status), _stream()), "linear_t")
+        _done(sync)
+        if sync and not naive and int(status.item()) != 0:
+            raise InvalidOp(f"linear_t: device status {int(status.item())} (a bounded wait expired)")
+    return out
+
+
+def rope_halves_(qk, cos, sin, positions, n_rot_heads, head_dim, sync=True):
+    """In-place halves-RoPE on the first n_rot_heads heads of each row of qk [tokens, row_stride]."""
+    _req(qk, "qk", torch.bfloat16, 2); _req(cos, "cos", torch.float32, 2); _req(sin, "sin", torch.float32, 2)
+    _req(positions, "positions", torch.int32, 1)
+    status = torch.zeros(1, dtype=torch.int32, device=qk.device)
+    with torch.cuda.device(qk.device):
+        check(lib.logismos_launch_rope_halves_bf16(_p(qk), _p(cos), _p(sin), _p(positions), qk.shape[0], n_rot_heads, head_dim,
+                                                   qk.shape[1], cos.shape[0], _p(status), _stream()), "rope_halves")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("RopeTable::gather: position >= max_seq")
+    return qk
+
+
+def swiglu(gu, sync=True):
+    _req(gu, "gu", torch.bfloat16, 2)
+    inter = gu.shape[1] // 2
+    out = torch.empty((gu.shape[0], inter), dtype=torch.bfloat16, device=gu.device)
+    with torch.cuda.device(gu.device):
+        check(lib.logismos_launch_swiglu_bf16(_p(gu), _p(out), gu.shape[0], inter, _stream()), "swiglu")
+        _done(sync)
+    return out
+
+
+def varlen_attention(qkv, cu_seqlens, n_heads, n_kv_heads, head_dim, causal=False, max_seqlen=None, sync=True):
+    _req(qkv, "qkv", torch.bfloat16, 2); _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    n_seqs = cu_seqlens.shape[0] - 1
+    if max_seqlen is None:
+        max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item()) if n_seqs > 0 else 0
+    out = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        check(lib.logismos_launch_varlen_attention_bf16(_p(qkv), _p(cu_seqlens), _p(out), n_seqs, max_seqlen, n_heads, n_kv_heads,
+                                                        head_dim, qkv.shape[1], n_heads * head_dim,
+                                                        (n_heads + n_kv_heads) * head_dim, int(causal), _stream()), "varlen_attention")
+        _done(sync)
+    return out
+
+
+def pool_head(hidden, cu_seqlens, head_w, head_b, sync=True):
+    _req(hidden, "hidden", torch.float32, 2); _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _req(head_w, "head_w", torch.bfloat16, 2); _req(head_b, "head_b", torch.float32, 1)
+    n_seqs = cu_seqlens.shape[0] - 1
+    out = torch.empty((n_seqs, head_w.shape[0]), dtype=torch.float32, device=hidden.device)
+    with torch.cuda.device(hidden.device):
+        check(lib.logismos_launch_pool_head_f32(_p(hidden), _p(cu_seqlens), _p(head_w), _p(head_b), _p(out), n_seqs, hidden.shape[1],
+                                                head_w.shape[0], _stream()), "pool_head")
+        _done(sync)
+    return out
+
+
+# ---- decode path -----------------------------------------------------------------------------
+
+def gemv_int4(codes, scales, x, out=None, sync=True):
+    """y = x @ dequant(codes, scales)^T. codes u8 [n, k/2], scales f16 [n, k/32], x bf16 [b, k]."""
+    _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2); _req(x, "x", torch.bfloat16, 2)
+    n, k = codes.shape[0], codes.shape[1] * 2
+    if x.shape[1] != k or tuple(scales.shape) != (n, k // 32):
+        raise InvalidOp("gemv_int4: shape mismatch")
+    y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_gemv_int4_g32_bf16(_p(codes), _p(scales), _p(x), _p(y), x.shape[0], n, k, _stream()), "gemv_int4_g32")
+        _done(sync)
+    return y
+
+
+def build_decode_chunks(context_lens_host, chunk_tokens):
+    """Host helper: (chunk_offsets int32 CPU tensor [n+1], total_chunks)."""
+    cl = torch.as_tensor(context_lens_host, dtype=torch.int32).contiguous()
+    off = torch.empty(cl.numel() + 1, dtype=torch.int32)
+    total = lib.logismos_build_decode_chunks(C.c_void_p(cl.data_ptr()), cl.numel(), chunk_tokens, C.c_void_p(off.data_ptr()))
+    if total < 0:
+        raise InvalidOp("build_decode_chunks: bad arguments")
+    return off, int(total)
+
+
+def paged_attention_decode(q, k_pool, v_pool, new_k, new_v, block_tables, context_lens, chunk_offsets, total_chunks,
+                           chunk_tokens, n_heads, n_kv_heads, head_dim, scratch=None, sync=True):
+    _req(q, "q", torch.bfloat16, 2); _req(k_pool, "k_pool", torch.bfloat16, 3); _req(v_pool, "v_pool", torch.bfloat16, 3)
+    _req(block_tables, "block_tables", torch.int32, 2); _req(context_lens, "context_lens", torch.int32, 1)
+    _req(chunk_offsets, "chunk_offsets", torch.int32, 1)
+    n_seqs = q.shape[0]
+    need = lib.logismos_paged_decode_scratch_bytes(total_chunks, n_heads, head_dim)
+    if scratch is None:
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    elif scratch.numel() * scratch.element_size() < need:
+        raise InvalidOp("paged_attention_decode: scratch too small")
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        check(lib.logismos_launch_paged_attention_decode_bf16(
+            _p(q), _p(k_pool), _p(v_pool), _p(new_k), _p(new_v), _p(block_tables), _p(context_lens), _p(chunk_offsets),
+            _p(out), _p(scratch), _p(status), n_seqs, total_chunks, chunk_tokens, block_tables.shape[1], k_pool.shape[0],
+            n_heads, n_kv_heads, head_dim, _stream()), "paged_attention_decode")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("paged_attention_decode: a block id fell outside the pool")
+    return out
+
+
+def paged_kv_store(k, v, k_pool, v_pool, slot_mapping, sync=True):
+    _req(k, "k", torch.bfloat16, 2); _req(v, "v", torch.bfloat16, 2); _req(slot_mapping, "slot_mapping", torch.int64, 1)
+    status = torch.zeros(1, dtype=torch.int32, device=k.device)
+    row = k_pool.shape[-1]
+    with torch.cuda.device(k.device):
+        check(lib.logismos_launch_paged_kv_store_bf16(_p(k), _p(v), k.shape[1], _p(k_pool), _p(v_pool), _p(slot_mapping), k.shape[0], row,
+                                                      k_pool.shape[0] * k_pool.shape[1], _p(status), _stream()), "paged_kv_store")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("paged_kv_store: slot outside the pool")
+
+
+def paged_kv_gather(k_pool, v_pool, block_table, length, sync=True):
+    _req(block_table, "block_table", torch.int32, 1)
+    row = k_pool.shape[-1]
+    ko = torch.empty((length, row), dtype=torch.bfloat16, device=k_pool.device)
+    vo = torch.empty_like(ko)
+    status = torch.zeros(1, dtype=torch.int32, device=k_pool.device)
+    with torch.cuda.device(k_pool.device):
+        check(lib.logismos_launch_paged_kv_gather_bf16(_p(k_pool), _p(v_pool), _p(block_table), block_table.shape[0], length, row,
+                                                       k_pool.shape[0], _p(ko), _p(vo), _p(status), _stream()), "paged_kv_gather")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("paged_kv_gather: block table entry missing or outside the pool")
+    return ko, vo
+
+
+def gdn_decode_step_(state, q, k, v, g, beta, scale, sync=True):
+    """One gated-delta-rule decode step; state f32 [n_seqs, heads, 128, 128] is updated in place."""
+    _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
+    _req(v, "v", torch.bfloat16, 3); _req(g, "g", torch.float32, 2); _req(beta, "beta", torch.float32, 2)
+    if tuple(state.shape[2:]) != (128, 128):
+        raise InvalidOp("gdn: head_dim must be 128")
+    o = torch.empty_like(v)
+    with torch.cuda.device(state.device):
+        check(lib.logismos_launch_gdn_decode_step(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), state.shape[0], state.shape[1],
+                                                  float(scale), _stream()), "gdn_decode_step")
+        _done(sync)
+    return o
+
+
+def greedy(logits, sync=True):
+    """decode::greedy per row: first maximum wins, NaN never selected."""
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        raise InvalidOp("greedy: logits must be f32 or bf16")
+    _req(logits, "logits", logits.dtype, 2)
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        check(lib.logismos_launch_greedy_argmax(_p(logits), int(logits.dtype == torch.float32), _p(out), logits.shape[0], logits.shape[1], _stream()), "greedy_argmax")
+        _done(sync)
+    return out

@@ -56,43 +56,16 @@ int orc_rope_gather(const float* cos_tab, const float* sin_tab, size_t max_seq, 
   return 0;
 }
 
-// attention.rs:122-304. Returns 1 for seq > rope max_seq, 2 for a GQA/shape violation.
-// causal=1 additionally masks key j > query i (this build's decoder variant; the reference
-// forward is bidirectional with a per-key-column padding mask).
-int orc_attention_forward(const orc_attn_t* a, const float* x, const uint8_t* mask, size_t seq,
-                          const float* cos_tab, const float* sin_tab, size_t rope_max_seq,
-                          int causal, float* out) {
-  const size_t hidden = a->hidden, n_h = a->n_heads, n_kv = a->n_kv_heads, d = a->head_dim;
-  const size_t kvw = n_kv * d;
-  if (n_kv == 0 || n_h % n_kv != 0 || d * n_h != hidden) return 2;
-  if (seq > rope_max_seq) return 1;
-  const size_t groups = n_h / n_kv;
-
-  std::vector<float> q(seq * hidden), k(seq * kvw), v(seq * kvw);
-  orc_linear_t(x, seq * hidden, a->wq, hidden * hidden, a->bq, hidden, seq, hidden, hidden, q.data());
-  orc_linear_t(x, seq * hidden, a->wk, kvw * hidden, a->bk, kvw, seq, kvw, hidden, k.data());
-  orc_linear_t(x, seq * hidden, a->wv, kvw * hidden, a->bv, kvw, seq, kvw, hidden, v.data());
-
-  // positions: row r of q is (s = r / n_h); row r of k is (s = r / n_kv)   (attention.rs:203-213)
-  {
-    std::vector<size_t> pos_q(seq * n_h), pos_k(seq * n_kv);
-    for (size_t s = 0; s < seq; ++s) {
-      for (size_t h = 0; h < n_h; ++h) pos_q[s * n_h + h] = s;
-      for (size_t h = 0; h < n_kv; ++h) pos_k[s * n_kv + h] = s;
-    }
-    size_t half = d / 2;
-    std::vector<float> cq(seq * n_h * half), sq(seq * n_h * half);
-    std::vector<float> ck(seq * n_kv * half), sk(seq * n_kv * half);
-    if (orc_rope_gather(cos_tab, sin_tab, rope_max_seq, d, pos_q.data(), pos_q.size(), cq.data(), sq.data())) return 1;
-    if (orc_rope_gather(cos_tab, sin_tab, rope_max_seq, d, pos_k.data(), pos_k.size(), ck.data(), sk.data())) return 1;
-    orc_rope_halves_in_place(q.data(), cq.data(), sq.data(), seq * n_h, d);
-    orc_rope_halves_in_place(k.data(), ck.data(), sk.data(), seq * n_kv, d);
-  }
-
+// attention.rs:217-299: the score / mask / softmax / PV stage on already projected and rotated
+// q [seq, n_h, d], k and v [seq, n_kv, d]; writes the merged heads [seq, n_h * d].
+int orc_sdpa(const float* q, const float* k, const float* v, const uint8_t* mask, size_t seq,
+             size_t n_h, size_t n_kv, size_t d, int causal, float* merged_out) {
+  if (n_kv == 0 || n_h % n_kv != 0) return 2;
+  const size_t hidden = n_h * d, kvw = n_kv * d, groups = n_h / n_kv;
   std::vector<float> q_hsd(seq * hidden), k_hsd(seq * kvw), v_hsd(seq * kvw);
-  orc_transpose_seq_heads(q.data(), seq, n_h, d, q_hsd.data());
-  orc_transpose_seq_heads(k.data(), seq, n_kv, d, k_hsd.data());
-  orc_transpose_seq_heads(v.data(), seq, n_kv, d, v_hsd.data());
+  orc_transpose_seq_heads(q, seq, n_h, d, q_hsd.data());
+  orc_transpose_seq_heads(k, seq, n_kv, d, k_hsd.data());
+  orc_transpose_seq_heads(v, seq, n_kv, d, v_hsd.data());
   std::vector<float> k_exp(n_h * seq * d), v_exp(n_h * seq * d);
   orc_repeat_kv(k_hsd.data(), n_kv, groups, seq, d, k_exp.data());
   orc_repeat_kv(v_hsd.data(), n_kv, groups, seq, d, v_exp.data());
@@ -127,8 +100,45 @@ int orc_attention_forward(const orc_attn_t* a, const float* x, const uint8_t* ma
     orc_linear(scores.data() + h * seq * seq, seq * seq, v_exp.data() + h * seq * d, seq * d,
                nullptr, 0, seq, d, seq, attn.data() + h * seq * d);
 
+  orc_merge_heads(attn.data(), n_h, seq, d, merged_out);
+  return 0;
+}
+
+// attention.rs:122-304. Returns 1 for seq > rope max_seq, 2 for a GQA/shape violation.
+// causal=1 additionally masks key j > query i (this build's decoder variant; the reference
+// forward is bidirectional with a per-key-column padding mask).
+int orc_attention_forward(const orc_attn_t* a, const float* x, const uint8_t* mask, size_t seq,
+                          const float* cos_tab, const float* sin_tab, size_t rope_max_seq,
+                          int causal, float* out) {
+  const size_t hidden = a->hidden, n_h = a->n_heads, n_kv = a->n_kv_heads, d = a->head_dim;
+  const size_t kvw = n_kv * d;
+  if (n_kv == 0 || n_h % n_kv != 0 || d * n_h != hidden) return 2;
+  if (seq > rope_max_seq) return 1;
+  const size_t groups = n_h / n_kv;
+
+  std::vector<float> q(seq * hidden), k(seq * kvw), v(seq * kvw);
+  orc_linear_t(x, seq * hidden, a->wq, hidden * hidden, a->bq, hidden, seq, hidden, hidden, q.data());
+  orc_linear_t(x, seq * hidden, a->wk, kvw * hidden, a->bk, kvw, seq, kvw, hidden, k.data());
+  orc_linear_t(x, seq * hidden, a->wv, kvw * hidden, a->bv, kvw, seq, kvw, hidden, v.data());
+
+  // positions: row r of q is (s = r / n_h); row r of k is (s = r / n_kv)   (attention.rs:203-213)
+  {
+    std::vector<size_t> pos_q(seq * n_h), pos_k(seq * n_kv);
+    for (size_t s = 0; s < seq; ++s) {
+      for (size_t h = 0; h < n_h; ++h) pos_q[s * n_h + h] = s;
+      for (size_t h = 0; h < n_kv; ++h) pos_k[s * n_kv + h] = s;
+    }
+    size_t half = d / 2;
+    std::vector<float> cq(seq * n_h * half), sq(seq * n_h * half);
+    std::vector<float> ck(seq * n_kv * half), sk(seq * n_kv * half);
+    if (orc_rope_gather(cos_tab, sin_tab, rope_max_seq, d, pos_q.data(), pos_q.size(), cq.data(), sq.data())) return 1;
+    if (orc_rope_gather(cos_tab, sin_tab, rope_max_seq, d, pos_k.data(), pos_k.size(), ck.data(), sk.data())) return 1;
+    orc_rope_halves_in_place(q.data(), cq.data(), sq.data(), seq * n_h, d);
+    orc_rope_halves_in_place(k.data(), ck.data(), sk.data(), seq * n_kv, d);
+  }
+
   std::vector<float> merged(seq * hidden);
-  orc_merge_heads(attn.data(), n_h, seq, d, merged.data());
+  orc_sdpa(q.data(), k.data(), v.data(), mask, seq, n_h, n_kv, d, causal, merged.data());
   orc_linear_t(merged.data(), seq * hidden, a->wo, hidden * hidden, nullptr, 0, seq, hidden, hidden, out);
   return 0;
 }

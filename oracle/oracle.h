@@ -64,6 +64,8 @@ int orc_rope_gather(const float* cos_tab, const float* sin_tab, size_t max_seq, 
 int orc_attention_forward(const orc_attn_t* a, const float* x, const uint8_t* mask, size_t seq,
                           const float* cos_tab, const float* sin_tab, size_t rope_max_seq,
                           int causal, float* out);
+int orc_sdpa(const float* q, const float* k, const float* v, const uint8_t* mask, size_t seq,
+             size_t n_h, size_t n_kv, size_t d, int causal, float* merged_out);
 void orc_transpose_seq_heads(const float* x, size_t seq, size_t heads, size_t d, float* out);
 void orc_merge_heads(const float* x, size_t heads, size_t seq, size_t d, float* out);
 void orc_repeat_kv(const float* kv, size_t n_kv, size_t groups, size_t seq, size_t d, float* out);

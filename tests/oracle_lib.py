@@ -166,6 +166,17 @@ def attention_forward(w, hidden, n_heads, n_kv, head_dim, x, mask, cos_tab, sin_
     return out.reshape(seq, hidden)
 
 
+def sdpa(q, k, v, n_heads, n_kv, d, mask=None, causal=False):
+    """attention.rs:217-299 on projected + rotated q [S, n_heads*d], k, v [S, n_kv*d] -> [S, n_heads*d]."""
+    q, k, v = f32(q), f32(k), f32(v)
+    seq = q.size // (n_heads * d)
+    mask = np.ones(seq, np.uint8) if mask is None else np.ascontiguousarray(mask, dtype=np.uint8)
+    out = np.empty((seq, n_heads * d), np.float32)
+    if lib.orc_sdpa(P(q), P(k), P(v), P(mask, u8p), c_sz(seq), c_sz(n_heads), c_sz(n_kv), c_sz(d), C.c_int(int(causal)), P(out)):
+        raise ValueError("sdpa shape error")
+    return out
+
+
 def transpose_seq_heads(x, seq, heads, d):
     x = f32(x); out = np.empty_like(x)
     lib.orc_transpose_seq_heads(P(x), c_sz(seq), c_sz(heads), c_sz(d), P(out))

@@ -10,7 +10,8 @@ STELLA_1_5B = dict(vocab=151646, hidden=1536, n_layers=28, n_heads=12, n_kv_head
                    intermediate=8960, max_pos=32768, head_out_dim=1024, rms_eps=1e-6,
                    rope_theta=1e6)
 
-TINY = dict(vocab=1000, hidden=256, n_layers=2, n_heads=4, n_kv_heads=2, intermediate=512,
+# Stella structure at small dims; head_dim stays 128 (what the GPU kernels support), GQA 2:1
+TINY = dict(vocab=1000, hidden=512, n_layers=2, n_heads=4, n_kv_heads=2, intermediate=1024,
             max_pos=512, head_out_dim=128, rms_eps=1e-6, rope_theta=1e6)
 
 

@@ -1,0 +1,43 @@
+"""Gated delta rule decode step against gated_delta_rule_recurrent_fwd restated in the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as O
+from gpu_util import DEV, bf16_cuda, max_rel, to_np
+from logismos_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def test_multi_step_decode_matches_recurrent_reference():
+    rng = np.random.default_rng(0)
+    n_seqs, heads, steps, D = 3, 4, 5, 128
+    state0 = (rng.standard_normal((n_seqs, heads, D, D)) * 0.1).astype(np.float32)
+    st = torch.from_numpy(state0.copy()).to(DEV)
+    qs, ks, vs, gs, bs, outs = [], [], [], [], [], []
+    for _ in range(steps):
+        q = rng.standard_normal((n_seqs, heads, D)).astype(np.float32); k = rng.standard_normal((n_seqs, heads, D)).astype(np.float32)
+        O.l2_norm_rows(q.reshape(-1), D); O.l2_norm_rows(k.reshape(-1), D)  # q/k L2-normalised per head
+        q_t, q = bf16_cuda(q); k_t, k = bf16_cuda(k); v_t, v = bf16_cuda(rng.standard_normal((n_seqs, heads, D)))
+        a = rng.standard_normal((n_seqs, heads)).astype(np.float32); b = rng.standard_normal((n_seqs, heads)).astype(np.float32)
+        g, beta = O.gdn_gates(a, b, np.zeros(heads, np.float32), np.zeros(heads, np.float32))
+        o = ops.gdn_decode_step_(st, q_t, k_t, v_t, torch.from_numpy(g).to(DEV), torch.from_numpy(beta).to(DEV), D ** -0.5)
+        qs.append(q); ks.append(k); vs.append(v); gs.append(g); bs.append(beta); outs.append(to_np(o))
+    final = to_np(st)
+    for s in range(n_seqs):
+        for h in range(heads):
+            o_ref, s_ref = O.gdn_recurrent_fwd(np.stack([x[s, h] for x in qs]), np.stack([x[s, h] for x in ks]),
+                                               np.stack([x[s, h] for x in vs]), np.array([x[s, h] for x in bs]),
+                                               np.array([x[s, h] for x in gs]), D ** -0.5, state0[s, h], D, D)
+            got = np.stack([x[s, h] for x in outs])
+            assert max_rel(got, o_ref.reshape(steps, D)) <= 2e-2
+            assert max_rel(final[s, h], s_ref.reshape(D, D)) <= 1e-4  # the state stays fp32
+
+
+def test_zero_beta_only_decays_the_state():  # cpu.rs:296-313
+    st0 = np.full((1, 1, 128, 128), 2.0, np.float32)
+    st = torch.from_numpy(st0.copy()).to(DEV)
+    one, _ = bf16_cuda(np.ones((1, 1, 128)))
+    ops.gdn_decode_step_(st, one, one, one, torch.zeros((1, 1), device=DEV), torch.zeros((1, 1), device=DEV), 1.0)
+    assert (to_np(st) == st0).all()

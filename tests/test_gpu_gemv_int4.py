@@ -1,0 +1,94 @@
+"""int4 group-32 dequant GEMV / skinny GEMM against the oracle (the benchmark shapes and batch
+sizes; value distributions of the benchmark configuration)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as O
+from gpu_util import DEV, TOL, bf16_cuda, max_rel, to_np
+from logismos_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(n, k, b, seed):
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(-8, 8, (n, k), dtype=np.int8)
+    scales = np.abs(rng.standard_normal((n, k // 32)) * 0.02).astype(np.float16)
+    x_t, x = bf16_cuda(rng.standard_normal((b, k)))
+    packed = O.int4_pack(codes)
+    return codes, packed, scales, x_t, x
+
+
+def run(packed, scales, x_t):
+    return to_np(ops.gemv_int4(torch.from_numpy(packed).to(DEV), torch.from_numpy(scales).to(DEV), x_t))
+
+
+@pytest.mark.parametrize("n,k", [(1536, 1536), (8960, 1536), (1536, 8960)])
+@pytest.mark.parametrize("b", [1, 4, 16, 64])
+def test_benchmark_shapes(n, k, b):
+    codes, packed, scales, x_t, x = make_case(n, k, b, n + k + b)
+    y = run(packed, scales, x_t)
+    ref = O.int4_gemv(packed, scales.view(np.uint16), x)
+    assert max_rel(y, ref) <= TOL
+    # tighter: the only rounding left is the bf16 store of y
+    assert np.abs(y - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
+
+
+@pytest.mark.parametrize("n,k,b", [(16, 128, 1), (17, 256, 3), (40, 384, 9), (100, 4224, 33), (31, 640, 64)])
+def test_ragged_shapes(n, k, b):
+    codes, packed, scales, x_t, x = make_case(n, k, b, 11 * n + b)
+    assert max_rel(run(packed, scales, x_t), O.int4_gemv(packed, scales.view(np.uint16), x)) <= TOL
+
+
+def test_unpacking_is_bit_exact():
+    """With unit scales and a one-hot activation the output IS the signed code: every nibble
+    position of every row must come back exactly."""
+    n, k = 64, 256
+    rng = np.random.default_rng(7)
+    codes = rng.integers(-8, 8, (n, k), dtype=np.int8)
+    packed = O.int4_pack(codes)
+    scales = np.ones((n, k // 32), np.float16)
+    got = np.empty((n, k), np.float32)
+    for k0 in range(0, k, 64):
+        x = np.zeros((64, k), np.float32); x[np.arange(64), k0 + np.arange(64)] = 1.0
+        x_t, _ = bf16_cuda(x)
+        got[:, k0:k0 + 64] = run(packed, scales, x_t).T
+    assert (got == codes.astype(np.float32)).all()
+    assert (O.int4_unpack(packed) == codes).all()
+
+
+def test_extreme_codes_and_zero_scales():
+    n, k = 32, 256
+    codes = np.full((n, k), -8, np.int8); codes[::2] = 7
+    packed = O.int4_pack(codes)
+    scales = np.full((n, k // 32), 0.5, np.float16); scales[5] = 0
+    x_t, x = bf16_cuda(np.ones((2, k)))
+    y = run(packed, scales, x_t)
+    ref = O.int4_gemv(packed, scales.view(np.uint16), x)
+    assert (y == O.bf16_round(ref)).all() and (y[:, 5] == 0).all()
+
+
+def test_shape_guards():
+    c = torch.zeros((16, 50), dtype=torch.uint8, device=DEV)  # k = 100, not a multiple of 128
+    with pytest.raises(Exception):
+        ops.gemv_int4(c, torch.zeros((16, 3), dtype=torch.float16, device=DEV), torch.zeros((1, 100), dtype=torch.bfloat16, device=DEV))
+
+
+def test_lm_head_shape_linearity_and_sampled_rows():
+    """(151936, 1536), the HBM-bound benchmark shape: sampled rows against the oracle, and the
+    size-independent property y(x1 + x2) = y(x1) + y(x2) over all rows."""
+    n, k = 151936, 1536
+    rng = np.random.default_rng(9)
+    packed = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    scales = np.abs(rng.standard_normal((n, k // 32)) * 0.02).astype(np.float16)
+    p_t = torch.from_numpy(packed).to(DEV); s_t = torch.from_numpy(scales).to(DEV)
+    x1 = np.zeros((1, k), np.float32); x2 = np.zeros((1, k), np.float32)
+    x1[0, ::2] = rng.integers(-4, 5, k // 2); x2[0, 1::2] = rng.integers(-4, 5, k // 2)  # exact in bf16
+    y1 = to_np(ops.gemv_int4(p_t, s_t, bf16_cuda(x1)[0])).astype(np.float64)
+    y2 = to_np(ops.gemv_int4(p_t, s_t, bf16_cuda(x2)[0])).astype(np.float64)
+    y12 = to_np(ops.gemv_int4(p_t, s_t, bf16_cuda(x1 + x2)[0])).astype(np.float64)
+    assert np.abs(y12 - (y1 + y2)).max() <= 3 * 2 ** -8 * np.abs(y12).max()
+    rows = np.concatenate([[0, 1, 15, 16, n - 17, n - 1], rng.integers(0, n, 250)])
+    ref = O.int4_gemv(np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scales[rows]).view(np.uint16), x1 + x2)
+    assert max_rel(y12[:, rows], ref) <= TOL

@@ -1,0 +1,117 @@
+"""End-to-end Stella embedding forward through the C ABI (lg_stella_*), against
+  (1) the committed golden fixture made with the reference's own golden method (HF Qwen2Model
+      fp32, padding-only mask; tests/golden/make_stella_fixture.py), and
+  (2) the CPU oracle on the same seeded weights and ids.
+Bars: embedding cosine >= 0.9999 and max-rel <= 2e-2 per tensor (bf16 storage on the GPU vs fp32
+on the CPU); the reference's own gate for its Rust path is looser (1e-3 abs, cos > 0.999)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from gpu_util import TOL, cosine, max_rel
+from logismos_b200.embed import ComputeError, EncodeOpts, InputTooLong, StellaModel, UnsupportedDim
+from stella_weights import STELLA_1_5B, TINY, make_batch, make_weights
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "stella_tiny_hf.npz")
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    g = np.load(GOLD)
+    w = make_weights(TINY, int(g["seed_w"]))
+    return g, w, O.OracleStella(TINY, w)
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+def test_golden_fixture_and_oracle_parity(tiny, fuse):
+    g, w, oracle = tiny
+    m = StellaModel(TINY, w, max_batch_tokens=512, max_batch_seqs=16, fuse_swiglu=fuse)
+    ids, cu = g["ids"], g["cu_seqlens"]
+    emb = m.encode_ids_batch(ids, cu)
+    assert emb.shape == (len(cu) - 1, TINY["head_out_dim"]) and m.device_status() == 0
+    assert np.abs(np.linalg.norm(emb, axis=1) - 1).max() < 1e-5       # unit-norm rows
+    for i in range(len(cu) - 1):
+        assert cosine(emb[i], g["embeddings"][i]) >= 0.9999
+        assert np.abs(emb[i] - g["embeddings"][i]).max() <= TOL * np.abs(g["embeddings"][i]).max()
+        assert cosine(emb[i], oracle.encode_raw(ids[cu[i]:cu[i + 1]])) >= 0.9999
+    # hidden states of the whole ragged batch against per-sequence oracle forwards
+    hs = m.last_hidden(int(cu[-1]))
+    for i in range(len(cu) - 1):
+        ref = oracle.forward(ids[cu[i]:cu[i + 1]])
+        assert max_rel(hs[cu[i]:cu[i + 1]], ref) <= TOL
+    # a sequence encoded alone equals its row in the batch (packing does not mix sequences)
+    alone = m.encode_ids(ids[cu[1]:cu[2]])
+    assert np.abs(alone - emb[1]).max() < 1e-5
+    m.close()
+
+
+def test_embedding_model_contract(tiny):  # crates/core/src/lib.rs:139-163, crates/embed/src/stella.rs:296-378
+    g, w, _ = tiny
+    rng = np.random.default_rng(0)
+    heads = {128: (w["head_w"], w["head_b"]),
+             64: ((rng.standard_normal((64, TINY["hidden"])) * 0.02).astype(np.float32), np.zeros(64, np.float32))}
+    m = StellaModel(TINY, w, max_batch_tokens=256, max_batch_seqs=4, heads=heads)
+    assert m.default_dim() == 128 and m.supported_dims() == [128, 64] and m.max_tokens() == 512
+    ids = np.arange(20, dtype=np.uint32)
+    assert m.encode_ids(ids, EncodeOpts(dim=64)).shape == (64,)
+    with pytest.raises(UnsupportedDim):
+        m.encode_ids(ids, EncodeOpts(dim=256))
+    with pytest.raises(InputTooLong):      # an error, never truncation
+        m.encode_ids(ids, EncodeOpts(max_tokens=19))
+    with pytest.raises(InputTooLong):
+        m.encode_ids(np.zeros(513, np.uint32))
+    # more sequences / tokens than the workspace holds: run in pieces, same result
+    ids2, cu2 = make_batch(TINY, 5, n_seq=9, lo=20, hi=120)
+    big = m.encode_ids_batch(ids2, cu2)
+    for i in (0, 4, 8):
+        assert np.abs(big[i] - m.encode_ids(ids2[cu2[i]:cu2[i + 1]])).max() < 1e-5
+    # empty batch and out-of-range ids (zero embedding rows, cpu_f32/mod.rs:96-104)
+    assert m.encode_ids_batch(np.zeros(0, np.uint32), np.zeros(1, np.int32)).shape == (0, 128)
+    weird = np.array([1, TINY["vocab"] + 5, 7], np.uint32)
+    assert np.isfinite(m.encode_ids(weird)).all()
+    m.close()
+
+
+def test_causal_variant_matches_oracle(tiny):
+    import torch
+    g, w, oracle = tiny
+    m = StellaModel(TINY, w, max_batch_tokens=256, max_batch_seqs=4)
+    ids, cu = make_batch(TINY, 11, n_seq=2, lo=30, hi=90)
+    T = int(cu[-1])
+    pos = np.concatenate([np.arange(cu[i + 1] - cu[i]) for i in range(2)]).astype(np.int32)
+    d_ids = torch.from_numpy(ids.view(np.int32)).cuda(); d_cu = torch.from_numpy(cu).cuda(); d_pos = torch.from_numpy(pos).cuda()
+    out = torch.empty((2, 128), dtype=torch.float32, device="cuda")
+    m.forward_device(d_ids.data_ptr(), d_cu.data_ptr(), d_pos.data_ptr(), T, 2, int((cu[1:] - cu[:-1]).max()), out.data_ptr(),
+                     torch.cuda.current_stream().cuda_stream, causal=True)
+    hs = m.last_hidden(T)
+    for i in range(2):
+        ref = oracle.forward(ids[cu[i]:cu[i + 1]], causal=True)
+        assert max_rel(hs[cu[i]:cu[i + 1]], ref) <= TOL
+    m.close()
+
+
+def test_full_size_stella_1_5b_parity_on_short_sequences():
+    """The benchmark architecture at full depth and width (28 layers, hidden 1536, 12/2 heads,
+    intermediate 8960, vocab 151646): the oracle runs two short sequences in seconds."""
+    cfg = STELLA_1_5B
+    w = make_weights(cfg, 2024)
+    m = StellaModel(cfg, w, max_batch_tokens=4608, max_batch_seqs=16)
+    oracle = O.OracleStella(cfg, w)
+    ids, cu = make_batch(cfg, 7, n_seq=8, lo=32, hi=512)
+    emb = m.encode_ids_batch(ids, cu)
+    assert m.device_status() == 0 and np.isfinite(emb).all()
+    lens = cu[1:] - cu[:-1]
+    for i in np.argsort(lens)[:2]:
+        ref = oracle.encode_raw(ids[cu[i]:cu[i + 1]])
+        assert cosine(emb[i], ref) >= 0.9999
+        assert np.abs(emb[i] - ref).max() <= TOL * np.abs(ref).max()
+    # size-independent properties over the whole batch: unit norm, permutation equivariance
+    assert np.abs(np.linalg.norm(emb, axis=1) - 1).max() < 1e-4
+    order = np.arange(8)[::-1]
+    ids_p = np.concatenate([ids[cu[i]:cu[i + 1]] for i in order]); cu_p = np.zeros(9, np.int32); cu_p[1:] = np.cumsum(lens[order])
+    emb_p = m.encode_ids_batch(ids_p, cu_p)
+    assert np.abs(emb_p - emb[order]).max() < 1e-4
+    m.close()
