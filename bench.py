@@ -240,12 +240,16 @@ def run_ours(args, cfg, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if rank == 0:  # nvidia-smi needs a moment to start: keep the GPU busy until the first sample arrives
+        t_wait = time.perf_counter()
+        while not sampler.rows and time.perf_counter() - t_wait < 5.0:
+            step(); torch.cuda.synchronize()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):

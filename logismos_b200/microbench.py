@@ -1,0 +1,166 @@
+"""Per-kernel microbenchmarks on one GPU (the quantized GEMV and paged-decode benchmark
+configurations, and the model's GEMM shapes), each launch timed with CUDA events on the launch
+stream, operands rotated over several copies so that every launch reads from HBM.
+
+  python -m logismos_b200.microbench gemv  [--n N --k K --batch B --iters I]
+  python -m logismos_b200.microbench gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
+  python -m logismos_b200.microbench paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
+  python -m logismos_b200.microbench attn  [--seqs S --len L --iters I]
+  python -m logismos_b200.microbench sweep          (every benchmark shape, one JSON line each)
+
+Prints one JSON line per case: achieved GB/s or TFLOP/s, the measured peak it is compared with
+(MEASURED_PEAKS.json next to the package, else the documented fallback) and the fraction.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+from . import ops
+from ._lib import lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm": d["hbm_gbs"], "tf": d["bf16_tflops"], "src": "measured"}
+    return {"hbm": 6650.0, "tf": 1590.0, "src": "fallback"}
+
+
+def timeit(fn, iters, warmup=3):
+    st = torch.cuda.current_stream()
+    for i in range(warmup):
+        fn(i)
+    st.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for i in range(iters):
+        fn(i)
+    e1.record(st)
+    e1.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+def bench_gemv(n, k, batch, iters, copies=None, pk=None):
+    pk = pk or peaks()
+    wbytes = n * k // 2 + n * (k // 32) * 2
+    copies = copies or max(2, min(16, int(300e6 // wbytes) + 1))  # > 256 MB of distinct weights in rotation
+    codes = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+    scales = [(torch.rand((n, k // 32), device="cuda") * 0.02).to(torch.float16) for _ in range(copies)]
+    x = torch.randn((batch, k), device="cuda").to(torch.bfloat16)
+    y = torch.empty((batch, n), dtype=torch.bfloat16, device="cuda")
+    t = timeit(lambda i: ops.gemv_int4(codes[i % copies], scales[i % copies], x, out=y, sync=False), iters)
+    t_l2 = timeit(lambda i: ops.gemv_int4(codes[0], scales[0], x, out=y, sync=False), iters)
+    by = wbytes + batch * k * 2 + batch * n * 2
+    return {"kernel": "gemv_int4_g32", "n": n, "k": k, "batch": batch, "bytes": by, "us": t * 1e6, "GBps": by / t / 1e9,
+            "frac_hbm": by / t / 1e9 / pk["hbm"], "us_l2_resident": t_l2 * 1e6, "GBps_l2_resident": by / t_l2 / 1e9,
+            "TFLOPs": 2.0 * batch * n * k / t / 1e12, "peak": pk["hbm"], "peak_src": pk["src"], "weight_copies": copies}
+
+
+def bench_gemm(m, n, k, epi, iters, pk=None):
+    pk = pk or peaks()
+    a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    copies = 4
+    ws = [(torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    res = torch.zeros((m, n), dtype=torch.float32, device="cuda") if epi == "resid" else None
+
+    def run(i):
+        if epi == "resid":
+            ops.linear_t(a, ws[i % copies], residual=res, sync=False)
+        else:
+            ops.linear_t(a, ws[i % copies], swiglu=(epi == "swiglu"), sync=False)
+    t = timeit(run, iters)
+    fl = 2.0 * m * n * k
+    return {"kernel": "linear_t_tcgen05", "m": m, "n": n, "k": k, "epilogue": epi, "flops": fl, "us": t * 1e6, "TFLOPs": fl / t / 1e12,
+            "frac_tensor": fl / t / 1e12 / pk["tf"], "peak": pk["tf"], "peak_src": pk["src"] + " burst"}
+
+
+def paged_case(seqs, min_ctx, max_ctx, seed=3):
+    rng = np.random.default_rng(seed)
+    ctx = np.exp(rng.uniform(np.log(min_ctx), np.log(max_ctx), seqs)).round().astype(np.int64)
+    nb = (ctx + 15) // 16
+    n_pool = int(nb.sum())
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.zeros((seqs, int(nb.max())), np.int32)
+    o = 0
+    for s in range(seqs):
+        tables[s, :nb[s]] = perm[o:o + nb[s]]
+        o += nb[s]
+    return ctx, tables, n_pool
+
+
+def bench_paged(seqs, min_ctx, max_ctx, chunk, iters, n_heads=16, n_kv=2, pk=None):
+    pk = pk or peaks()
+    d = 128
+    ctx, tables, n_pool = paged_case(seqs, min_ctx, max_ctx)
+    row = n_kv * d
+    kp = torch.randn((n_pool, 16, row), device="cuda").to(torch.bfloat16)
+    vp = torch.randn((n_pool, 16, row), device="cuda").to(torch.bfloat16)
+    q = torch.randn((seqs, n_heads * d), device="cuda").to(torch.bfloat16)
+    nk = torch.randn((seqs, row), device="cuda").to(torch.bfloat16)
+    nv = torch.randn((seqs, row), device="cuda").to(torch.bfloat16)
+    off, total = ops.build_decode_chunks(ctx.astype(np.int32), chunk)
+    d_tab, d_ctx, d_off = torch.from_numpy(tables).cuda(), torch.from_numpy(ctx.astype(np.int32)).cuda(), off.cuda()
+    scratch = torch.empty(int(lib.logismos_paged_decode_scratch_bytes(total, n_heads, d)), dtype=torch.uint8, device="cuda")
+    t = timeit(lambda i: ops.paged_attention_decode(q, kp, vp, nk, nv, d_tab, d_ctx, d_off, total, chunk, n_heads, n_kv, d,
+                                                    scratch=scratch, sync=False), iters)
+    by = float(ctx.sum()) * row * 2 * 2 + seqs * (n_heads * d * 2 * 2 + row * 2 * 2) + tables.size * 4
+    return {"kernel": "paged_attention_decode+merge", "seqs": seqs, "context_tokens": int(ctx.sum()), "pool_blocks": n_pool,
+            "chunk_tokens": chunk, "total_chunks": total, "bytes": by, "us": t * 1e6, "GBps": by / t / 1e9,
+            "frac_hbm": by / t / 1e9 / pk["hbm"], "scratch_bytes": scratch.numel(), "peak": pk["hbm"], "peak_src": pk["src"]}
+
+
+def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
+    d = 128
+    T = seqs * length
+    qkv = torch.randn((T, (n_heads + 2 * n_kv) * d), device="cuda").to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, length, dtype=torch.int32, device="cuda")
+    t = timeit(lambda i: ops.varlen_attention(qkv, cu, n_heads, n_kv, d, max_seqlen=length, sync=False), iters)
+    fl = 4.0 * n_heads * d * length * length * seqs
+    return {"kernel": "varlen_attention", "seqs": seqs, "len": length, "flops": fl, "us": t * 1e6, "TFLOPs": fl / t / 1e12}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="logismos_b200.microbench")
+    ap.add_argument("what", choices=["gemv", "gemm", "paged", "attn", "sweep"])
+    ap.add_argument("--m", type=int, default=2176)
+    ap.add_argument("--n", type=int, default=151936)
+    ap.add_argument("--k", type=int, default=1536)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--epi", default="bf16", choices=["bf16", "resid", "swiglu"])
+    ap.add_argument("--seqs", type=int, default=256)
+    ap.add_argument("--len", type=int, default=512)
+    ap.add_argument("--min-ctx", type=int, default=128)
+    ap.add_argument("--max-ctx", type=int, default=32768)
+    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args(argv)
+    if a.what == "gemv":
+        print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
+    elif a.what == "gemm":
+        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.epi, a.iters)))
+    elif a.what == "paged":
+        print(json.dumps(bench_paged(a.seqs, a.min_ctx, a.max_ctx, a.chunk, a.iters)))
+    elif a.what == "attn":
+        print(json.dumps(bench_attn(a.seqs, a.len, a.iters)))
+    else:
+        pk = peaks()
+        for (n, k) in [(1536, 1536), (8960, 1536), (1536, 8960), (151936, 1536)]:
+            for b in (1, 4, 16, 64):
+                print(json.dumps(bench_gemv(n, k, b, a.iters, pk=pk)), flush=True)
+        print(json.dumps(bench_paged(256, 128, 32768, 512, 10, pk=pk)), flush=True)
+        for (n, k, epi) in [(2048, 1536, "bf16"), (1536, 1536, "resid"), (17920, 1536, "swiglu"), (1536, 8960, "resid")]:
+            print(json.dumps(bench_gemm(a.m, n, k, epi, a.iters, pk=pk)), flush=True)
+        print(json.dumps(bench_attn(8, 512, a.iters)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

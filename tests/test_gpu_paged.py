@@ -38,7 +38,7 @@ def test_store_and_gather_equal_the_flat_cache_bit_for_bit():
         for n in sorted({0, 1, L // 2, L}):
             fk, fv = flat.get(0, n)
             gk, gv = ops.paged_kv_gather(kp, vp, torch.from_numpy(tables[i]).to(DEV), n)
-            assert (bits(gk).view(np.uint8).reshape(n, -1) == fk).all() and (bits(gv).view(np.uint8).reshape(n, -1) == fv).all()
+            assert (bits(gk).view(np.uint8).reshape(n, row * 2) == fk).all() and (bits(gv).view(np.uint8).reshape(n, row * 2) == fv).all()
             ok, ov = O.paged_gather(kp_np.view(np.uint8).reshape(n_blocks, BS, row * 2), vp_np.view(np.uint8).reshape(n_blocks, BS, row * 2), BS, tables[i], n)
             assert (ok == fk).all() and (ov == fv).all()
     with pytest.raises(ops.InvalidOp):  # a slot outside the pool is reported, not written
