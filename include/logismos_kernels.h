@@ -136,6 +136,12 @@ uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes_u8, const void* sc
                                             const void* x_bf16, void* y_bf16, int32_t batch,
                                             int32_t n, int32_t k, void* stream);
 
+/* Expands int4 group-32 weights (same storage as above) to bf16 [n, k]: w = bf16(scale * code).
+ * The prefill side of a mixed step runs its contractions on the tcgen05 GEMM over this expansion.
+ * k % 32 == 0. */
+uint32_t logismos_launch_dequant_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
+                                               void* out_bf16, int32_t n, int32_t k, void* stream);
+
 /* Paged-attention decode with fused KV append. The paged cache keeps the row layout of
  * FlatKvCache (crates/cache/src/flat.rs:36-69: one row = all kv heads of one token, contiguous):
  * k_pool / v_pool bf16 [n_pool_blocks, block_size = 16, n_kv_heads * head_dim]; logical token t
@@ -172,6 +178,13 @@ uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool_bf16, const voi
                                               int32_t len, int32_t row_elems,
                                               int32_t n_pool_blocks, void* k_out_bf16,
                                               void* v_out_bf16, void* status_i32, void* stream);
+
+/* dst[r, :] = src[idx[r], :] for fp32 rows (bit-exact copy): picks the last token row of every
+ * sequence of a packed step before the final norm and the lm_head. An index outside
+ * [0, n_src_rows) yields a zero row and sets *status to 1. width % 4 == 0. */
+uint32_t logismos_launch_gather_rows_f32(const void* src_f32, const void* idx_i32, void* dst_f32,
+                                         int32_t n_rows, int32_t width, int32_t n_src_rows,
+                                         void* status_i32, void* stream);
 
 /* gated_delta_rule_recurrent_fwd (crates/kernels/src/gated_delta_rule/cpu.rs:92-182), one decode
  * step for a batch of sequences and heads: state f32 [n_seqs, heads, K=128, V=128] updated in

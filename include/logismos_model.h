@@ -95,6 +95,62 @@ int32_t lg_stella_launches_per_forward(const void* model);
 /* Status word written by kernels with bounded waits / range checks during the last forward. */
 int32_t lg_stella_device_status(void* model);
 
+/* ====================================================================================
+ * Continuous-batching decoder step over a Qwen2-style layer stack with int4 group-32 weights and
+ * a paged KV cache. The reference has no decoder executor (crates/decoders is an empty scaffold,
+ * src/lib.rs:1-15) and no scheduler (crates/sched/src/lib.rs:1-30); the contract kept is the
+ * reference's only execution semantics, one sequence per call
+ * (crates/transformers/src/attention.rs:13-14): a packed step must equal running every sequence
+ * alone through the causal variant of StellaEncoder::forward, followed by lm_head + decode::greedy
+ * (crates/decode/src/lib.rs:73-83) on its last token.
+ * ==================================================================================== */
+typedef struct lg_decoder_config {
+  int32_t vocab, hidden, n_layers, n_heads, n_kv_heads, intermediate, max_pos;
+  float rms_eps;
+  double rope_theta;
+  int32_t n_pool_blocks;       /* KV blocks of 16 tokens per layer */
+  int32_t max_blocks_per_seq;  /* width of a block-table row */
+  int32_t max_step_tokens;     /* capacity of one packed step */
+  int32_t max_step_seqs;
+} lg_decoder_config_t;
+
+/* int4 group-32 matrix on the HOST: codes u8 [n, k/2], scales fp16 bits [n, k/32]
+ * (storage contract of logismos_launch_gemv_int4_g32_bf16). */
+typedef struct lg_int4_matrix { const uint8_t* codes; const uint16_t* scales; } lg_int4_matrix_t;
+typedef struct lg_decoder_layer_weights {
+  const float *norm1, *norm2, *bq, *bk, *bv;            /* fp32 */
+  lg_int4_matrix_t wq, wk, wv, wo, w_gate, w_up, w_down;  /* HF [out, in] */
+} lg_decoder_layer_weights_t;
+typedef struct lg_decoder_weights {
+  const float* tok_embed;  /* fp32 [vocab, hidden], stored bf16 on the device */
+  const float* final_norm;
+  const lg_decoder_layer_weights_t* layers;
+  lg_int4_matrix_t lm_head;  /* [vocab, hidden] */
+} lg_decoder_weights_t;
+
+uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const lg_decoder_weights_t* w, void** model);
+void lg_decoder_destroy(void* model);
+
+/* One packed step. Sequence i brings new_lens[i] new tokens (ids packed in sequence order in
+ * host_ids) on top of cached_lens[i] tokens already in the paged cache; its block-table row
+ * host_block_tables[i, :] must cover cached + new tokens. new_lens[i] == 1 is a decode token,
+ * > 1 a prefill chunk, which must start its sequence (cached_lens[i] == 0). All K/V rows of the new
+ * tokens are written to the cache; host_next_tokens[i] receives the greedy token after the last
+ * new token of sequence i. Synchronises before returning. Status codes as lg_embedding_status. */
+uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* host_cached_lens,
+                         const int32_t* host_new_lens, int32_t n_seqs, const int32_t* host_block_tables,
+                         uint32_t* host_next_tokens);
+/* Re-runs the device work of the last lg_decoder_step (same indices, same ids; the cache rows are
+ * rewritten with the same values) on `stream` without host transfers or synchronisation: for
+ * kernel-only timing. */
+uint32_t lg_decoder_replay_device(void* model, void* stream);
+/* fp32 [n_seqs, hidden]: final-norm output of each sequence's last new token in the last step. */
+uint32_t lg_decoder_last_hidden(void* model, int32_t n_seqs, float* host_out);
+/* bf16 logits of the last step as fp32 [n_seqs, vocab]. */
+uint32_t lg_decoder_last_logits(void* model, int32_t n_seqs, float* host_out);
+int32_t lg_decoder_launches_last_step(const void* model);
+int32_t lg_decoder_device_status(void* model);
+
 /* Message of the last failure on the calling thread ("" if none). */
 const char* lg_last_error(void);
 

@@ -71,10 +71,12 @@ def _declare(l):
         "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_paged_attention_decode_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
                                                         i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_kv_store_bf16": [vp, vp, i32, vp, vp, vp, i32, i32, i64, vp, vp],
         "logismos_launch_paged_kv_gather_bf16": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
+        "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],
         "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
         "logismos_launch_greedy_argmax": [vp, i32, vp, i32, i32, vp],
         # model
@@ -82,6 +84,11 @@ def _declare(l):
         "lg_stella_encode_ids_batch": [vp, vp, vp, i32, i32, i32, vp],
         "lg_stella_forward_device": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "lg_stella_last_hidden": [vp, i32, vp],
+        "lg_decoder_create": [i32, vp, vp, C.POINTER(vp)],
+        "lg_decoder_step": [vp, vp, vp, vp, i32, vp, vp],
+        "lg_decoder_replay_device": [vp, vp],
+        "lg_decoder_last_hidden": [vp, i32, vp],
+        "lg_decoder_last_logits": [vp, i32, vp],
     }
     for name, args in sig.items():
         fn = getattr(l, name)
@@ -101,6 +108,11 @@ def _declare(l):
     l.logismos_build_decode_chunks.restype = i32
     l.lg_stella_destroy.argtypes = [vp]
     l.lg_stella_destroy.restype = None
+    l.lg_decoder_destroy.argtypes = [vp]
+    l.lg_decoder_destroy.restype = None
+    for name in ("lg_decoder_launches_last_step", "lg_decoder_device_status"):
+        getattr(l, name).argtypes = [vp]
+        getattr(l, name).restype = i32
     for name in ("lg_stella_default_dim", "lg_stella_max_tokens", "lg_stella_launches_per_forward",
                  "lg_stella_device_status"):
         getattr(l, name).argtypes = [vp]

@@ -494,6 +494,7 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv, const void* cu_s
                                                int32_t max_seqlen, int32_t n_heads, int32_t n_kv_heads,
                                                int32_t head_dim, int32_t row_stride, int32_t k_off, int32_t v_off,
                                                int32_t causal, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim != D || (n_heads % n_kv_heads) ||
       (row_stride % 8) || (k_off % 8) || (v_off % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
     return lg::kInvalidValue;
@@ -526,6 +527,7 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
     const void* context_lens, const void* chunk_offsets, void* out, void* scratch, void* status, int32_t n_seqs,
     int32_t total_chunks, int32_t chunk_tokens, int32_t max_blocks, int32_t n_pool_blocks, int32_t n_heads,
     int32_t n_kv_heads, int32_t head_dim, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_seqs < 0 || total_chunks < 0 || chunk_tokens <= 0 || (chunk_tokens % 64) || max_blocks <= 0 ||
       n_pool_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim != D || (n_heads % n_kv_heads) ||
       n_heads / n_kv_heads > 16 || (new_k == nullptr) != (new_v == nullptr))
@@ -557,6 +559,7 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
 uint32_t logismos_launch_paged_kv_store_bf16(const void* k, const void* v, int32_t src_row_stride, void* k_pool,
                                              void* v_pool, const void* slot_mapping, int32_t n_tokens,
                                              int32_t row_elems, int64_t n_pool_slots, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_tokens < 0 || row_elems <= 0 || (row_elems % 8) || (src_row_stride % 8) || src_row_stride < row_elems)
     return lg::kInvalidValue;
   if (n_tokens == 0) return 0;
@@ -571,6 +574,7 @@ uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool, const void* v_
                                               int32_t table_len, int32_t len, int32_t row_elems,
                                               int32_t n_pool_blocks, void* k_out, void* v_out, void* status,
                                               void* stream) {
+  lg::LaunchScope launch_scope_;
   if (table_len < 0 || len < 0 || row_elems <= 0 || (row_elems % 8)) return lg::kInvalidValue;
   if (len == 0) return 0;
   const int64_t total = (int64_t)len * (row_elems / 8);

@@ -13,6 +13,13 @@ namespace lg {
 // runtime status of the launch, read right after it.
 inline uint32_t launch_status() { return (uint32_t)cudaGetLastError(); }
 
+// The runtime keeps the status of the last failed call until someone reads it, whoever made that
+// call (an earlier API call of this process that was allowed to fail, another library). A launcher
+// reports only its own launch, so it drops such a leftover before launching.
+struct LaunchScope {
+  LaunchScope() { (void)cudaGetLastError(); }
+};
+
 // Shape-guard failures are reported as cudaErrorInvalidValue (1) without launching.
 constexpr uint32_t kInvalidValue = 1u;
 

@@ -8,7 +8,13 @@
 #include "logismos_cudacore.h"
 
 namespace {
-inline uint32_t make_current(int32_t ordinal) { return (uint32_t)cudaSetDevice(ordinal); }
+// Every entry point returns its status explicitly, so a failure must not also stay behind in the
+// runtime's "last error" slot, where the next kernel launch of the process would pick it up.
+inline uint32_t done(cudaError_t e) {
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return (uint32_t)e;
+}
+inline uint32_t make_current(int32_t ordinal) { return done(cudaSetDevice(ordinal)); }
 }  // namespace
 
 #define LG_CURRENT(ord)                          \
@@ -23,7 +29,7 @@ uint32_t lg_device_count(int32_t* count) {
   int c = 0;
   cudaError_t e = cudaGetDeviceCount(&c);
   if (count) *count = (e == cudaSuccess) ? c : 0;
-  return (uint32_t)e;
+  return done(e);
 }
 
 uint32_t lg_device_set_current(int32_t ordinal) { return make_current(ordinal); }
@@ -32,7 +38,7 @@ uint32_t lg_device_props_get(int32_t ordinal, lg_device_props_t* out) {
   if (!out) return (uint32_t)cudaErrorInvalidValue;
   cudaDeviceProp p;
   cudaError_t e = cudaGetDeviceProperties(&p, ordinal);
-  if (e != cudaSuccess) return (uint32_t)e;
+  if (e != cudaSuccess) return done(e);
   std::memset(out, 0, sizeof(*out));
   std::snprintf(out->isa, sizeof(out->isa), "sm_%d%d", p.major, p.minor);
   std::snprintf(out->name, sizeof(out->name), "%s", p.name);
@@ -54,46 +60,46 @@ uint32_t lg_device_mem_info(int32_t ordinal, uint64_t* free_bytes, uint64_t* tot
   cudaError_t e = cudaMemGetInfo(&f, &t);
   if (free_bytes) *free_bytes = f;
   if (total_bytes) *total_bytes = t;
-  return (uint32_t)e;
+  return done(e);
 }
 
 uint32_t lg_device_synchronize(int32_t ordinal) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaDeviceSynchronize();
+  return done(cudaDeviceSynchronize());
 }
 
 uint32_t lg_malloc(int32_t ordinal, size_t bytes, void** dev_ptr) {
   if (!dev_ptr) return (uint32_t)cudaErrorInvalidValue;
   *dev_ptr = nullptr;
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaMalloc(dev_ptr, bytes);
+  return done(cudaMalloc(dev_ptr, bytes));
 }
 
 uint32_t lg_free(int32_t ordinal, void* dev_ptr) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaFree(dev_ptr);
+  return done(cudaFree(dev_ptr));
 }
 
 uint32_t lg_memset(int32_t ordinal, void* dev_ptr, int32_t value, size_t bytes) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaMemset(dev_ptr, value, bytes);
+  return done(cudaMemset(dev_ptr, value, bytes));
 }
 
 uint32_t lg_memcpy_h2d(int32_t ordinal, void* dev_dst, const void* host_src, size_t bytes) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaMemcpy(dev_dst, host_src, bytes, cudaMemcpyHostToDevice);
+  return done(cudaMemcpy(dev_dst, host_src, bytes, cudaMemcpyHostToDevice));
 }
 
 uint32_t lg_memcpy_d2h(int32_t ordinal, void* host_dst, const void* dev_src, size_t bytes) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaMemcpy(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost);
+  return done(cudaMemcpy(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost));
 }
 
 uint32_t lg_memcpy_h2d_async(int32_t ordinal, void* dev_dst, const void* host_src, size_t bytes,
                              void* stream) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice,
-                                   (cudaStream_t)stream);
+  return done(cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice,
+                                   (cudaStream_t)stream));
 }
 
 uint32_t lg_stream_create(int32_t ordinal, void** stream) {
@@ -103,17 +109,17 @@ uint32_t lg_stream_create(int32_t ordinal, void** stream) {
   cudaStream_t s;
   cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
   if (e == cudaSuccess) *stream = (void*)s;
-  return (uint32_t)e;
+  return done(e);
 }
 
 uint32_t lg_stream_synchronize(int32_t ordinal, void* stream) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaStreamSynchronize((cudaStream_t)stream);
+  return done(cudaStreamSynchronize((cudaStream_t)stream));
 }
 
 uint32_t lg_stream_destroy(int32_t ordinal, void* stream) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaStreamDestroy((cudaStream_t)stream);
+  return done(cudaStreamDestroy((cudaStream_t)stream));
 }
 
 uint32_t lg_event_create(int32_t ordinal, void** event) {
@@ -123,27 +129,27 @@ uint32_t lg_event_create(int32_t ordinal, void** event) {
   cudaEvent_t ev;
   cudaError_t e = cudaEventCreate(&ev);
   if (e == cudaSuccess) *event = (void*)ev;
-  return (uint32_t)e;
+  return done(e);
 }
 
 uint32_t lg_event_record(int32_t ordinal, void* event, void* stream) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream);
+  return done(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
 }
 
 uint32_t lg_event_synchronize(int32_t ordinal, void* event) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaEventSynchronize((cudaEvent_t)event);
+  return done(cudaEventSynchronize((cudaEvent_t)event));
 }
 
 uint32_t lg_event_elapsed_ms(void* start, void* end, float* ms) {
   if (!ms) return (uint32_t)cudaErrorInvalidValue;
-  return (uint32_t)cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)end);
+  return done(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)end));
 }
 
 uint32_t lg_event_destroy(int32_t ordinal, void* event) {
   LG_CURRENT(ordinal);
-  return (uint32_t)cudaEventDestroy((cudaEvent_t)event);
+  return done(cudaEventDestroy((cudaEvent_t)event));
 }
 
 uint32_t lg_error_kind_from_raw(uint32_t code) {

@@ -1,0 +1,412 @@
+// Host-side executor of one continuous-batching step over a Qwen2-style decoder stack with int4
+// group-32 weights and a paged KV cache (block 16). The reference has neither a decoder executor
+// (crates/decoders/src/lib.rs:1-15) nor a scheduler (crates/sched/src/lib.rs:1-30); the contract
+// kept is "a packed step equals running every sequence alone" through the causal variant of
+// StellaLayer::forward (crates/encoders/src/stella.rs:190-206), lm_head and decode::greedy
+// (crates/decode/src/lib.rs:73-83).
+//
+// A step packs decode tokens (one per sequence) first and prefill chunks after them:
+//   embed -> per layer [ rms_norm -> QKV (int4 weights) + bias -> RoPE at each token's position ->
+//   K/V rows scattered into the paged cache by slot mapping -> attention: paged decode kernel for
+//   the decode rows, ragged causal attention for the prefill rows -> o_proj + residual ->
+//   rms_norm -> gate/up -> SwiGLU -> down + residual ] -> last token rows -> final norm ->
+//   lm_head (int4 GEMV) -> greedy argmax.
+// Contractions over the packed rows run on the tcgen05 GEMM over a per-layer bf16 expansion of the
+// int4 codes; the lm_head, whose batch is the number of sequences, runs on the int4 GEMV kernel.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "logismos_kernels.h"
+#include "logismos_model.h"
+
+namespace lgm {
+void set_error(const std::string& s);
+}
+
+namespace {
+
+using lgm::set_error;
+
+inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+struct Buf {
+  void* p = nullptr;
+  bool alloc(size_t n) { return cudaMalloc(&p, n ? n : 1) == cudaSuccess; }
+  bool upload(const void* src, size_t n) { return alloc(n) && cudaMemcpy(p, src, n, cudaMemcpyHostToDevice) == cudaSuccess; }
+  void release() { if (p) cudaFree(p); p = nullptr; }
+};
+
+struct QMat { Buf codes, scales; int n = 0, k = 0; };
+
+struct DLayer {
+  Buf norm1, norm2, bqkv, kpool, vpool;
+  QMat wqkv, wo, wgu, wdown;
+};
+
+constexpr int kChunkTokens = 512;
+constexpr int kBlock = 16;
+
+struct Decoder {
+  lg_decoder_config_t cfg{};
+  int device = 0, head_dim = 0, qkv_dim = 0, kv_dim = 0;
+  Buf tok_embed, final_norm, cos, sin;
+  QMat lm_head;
+  std::vector<DLayer> layers;
+  // workspace
+  Buf x, h, qkv, attn, qdec, gu, act, wscratch, last, last_bf16, logits, tokens, status;
+  Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch;
+  // pinned staging (one block)
+  uint8_t* pinned = nullptr;
+  size_t pinned_bytes = 0;
+  cudaStream_t stream = nullptr;
+  std::mutex mu;
+  // description of the last step (for replay and diagnostics)
+  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, pre_tokens = 0, max_pre_len = 0, total_chunks = 0, launches = 0;
+  std::vector<int> order;  // internal slot -> caller's sequence index
+  size_t max_chunks = 0;
+};
+
+bool upload_q(QMat& q, const std::vector<const lg_int4_matrix_t*>& parts, const std::vector<int>& rows, int k) {
+  size_t n = 0;
+  for (int r : rows) n += (size_t)r;
+  std::vector<uint8_t> codes(n * (k / 2));
+  std::vector<uint16_t> scales(n * (k / 32));
+  size_t o = 0;
+  for (size_t i = 0; i < parts.size(); ++i) {
+    std::memcpy(codes.data() + o * (k / 2), parts[i]->codes, (size_t)rows[i] * (k / 2));
+    std::memcpy(scales.data() + o * (k / 32), parts[i]->scales, (size_t)rows[i] * (k / 32) * 2);
+    o += (size_t)rows[i];
+  }
+  q.n = (int)n;
+  q.k = k;
+  return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
+}
+
+#define LG_TRY(expr, what)                                                                         \
+  do {                                                                                             \
+    uint32_t rc_ = (uint32_t)(expr);                                                               \
+    if (rc_ != 0) {                                                                                \
+      char buf_[192];                                                                              \
+      std::snprintf(buf_, sizeof(buf_), "%s failed: %s (code %u)", what, cudaGetErrorString((cudaError_t)rc_), rc_); \
+      set_error(buf_);                                                                             \
+      return LG_EMB_COMPUTE;                                                                       \
+    }                                                                                              \
+  } while (0)
+
+// C = A W^T with int4 weights: expand to bf16, then the tcgen05 GEMM with the requested epilogue
+uint32_t qlinear(Decoder* m, const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc,
+                 int epi, cudaStream_t s) {
+  LG_TRY(logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, m->wscratch.p, w.n, w.k, s), "dequant_int4");
+  LG_TRY(logismos_launch_linear_t_bf16(a, m->wscratch.p, bias, out, T, w.n, w.k, lda, ldc, epi, m->status.p, s), "linear_t");
+  m->launches += 2;
+  return 0;
+}
+
+uint32_t run_device(Decoder* m, cudaStream_t s) {
+  const lg_decoder_config_t& c = m->cfg;
+  const int H = c.hidden, I = c.intermediate, D = m->head_dim, QKV = m->qkv_dim, KV = m->kv_dim, T = m->T;
+  void* st = m->status.p;
+  m->launches = 0;
+  LG_TRY(logismos_launch_embed_lookup_bf16(m->tok_embed.p, m->ids.p, m->x.p, T, H, c.vocab, s), "embed_lookup");
+  m->launches += 1;
+  for (int l = 0; l < c.n_layers; ++l) {
+    DLayer& L = m->layers[l];
+    LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm1.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
+    if (uint32_t rc = qlinear(m, m->h.p, L.wqkv, L.bqkv.p, m->qkv.p, T, H, QKV, LG_EPI_BF16, s)) return rc;
+    LG_TRY(logismos_launch_rope_halves_bf16(m->qkv.p, m->cos.p, m->sin.p, m->pos.p, T, c.n_heads + c.n_kv_heads, D, QKV,
+                                            c.max_pos, st, s), "rope");
+    const uint16_t* qkv16 = (const uint16_t*)m->qkv.p;
+    LG_TRY(logismos_launch_paged_kv_store_bf16(qkv16 + H, qkv16 + H + KV, QKV, L.kpool.p, L.vpool.p, m->slots.p, T, KV,
+                                               (int64_t)c.n_pool_blocks * kBlock, st, s), "paged_kv_store");
+    m->launches += 3;
+    if (m->n_dec > 0) {
+      // decode rows are the first n_dec rows of the packed batch: gather their q heads contiguously
+      LG_TRY(cudaMemcpy2DAsync(m->qdec.p, (size_t)H * 2, m->qkv.p, (size_t)QKV * 2, (size_t)H * 2, m->n_dec,
+                               cudaMemcpyDeviceToDevice, s), "q gather");
+      LG_TRY(logismos_launch_paged_attention_decode_bf16(m->qdec.p, L.kpool.p, L.vpool.p, nullptr, nullptr, m->dec_tables.p,
+                                                         m->dec_ctx.p, m->dec_chunks.p, m->attn.p, m->dec_scratch.p, st, m->n_dec,
+                                                         m->total_chunks, kChunkTokens, c.max_blocks_per_seq, c.n_pool_blocks,
+                                                         c.n_heads, c.n_kv_heads, D, s), "paged_attention_decode");
+      m->launches += 2;
+    }
+    if (m->n_pre > 0) {
+      LG_TRY(logismos_launch_varlen_attention_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
+                                                   (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->n_pre, m->max_pre_len,
+                                                   c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, s), "varlen_attention");
+      m->launches += 1;
+    }
+    if (uint32_t rc = qlinear(m, m->attn.p, L.wo, nullptr, m->x.p, T, H, H, LG_EPI_RESID_F32, s)) return rc;
+    LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
+    if (uint32_t rc = qlinear(m, m->h.p, L.wgu, nullptr, m->gu.p, T, H, 2 * I, LG_EPI_BF16, s)) return rc;
+    LG_TRY(logismos_launch_swiglu_bf16(m->gu.p, m->act.p, T, I, s), "swiglu");
+    if (uint32_t rc = qlinear(m, m->act.p, L.wdown, nullptr, m->x.p, T, I, H, LG_EPI_RESID_F32, s)) return rc;
+    m->launches += 2;
+  }
+  LG_TRY(logismos_launch_gather_rows_f32(m->x.p, m->last_idx.p, m->last.p, m->n_seqs, H, T, st, s), "gather_rows");
+  LG_TRY(logismos_launch_rms_norm_f32(m->last.p, m->final_norm.p, m->last_bf16.p, m->n_seqs, H, c.rms_eps, 0, s), "final_norm");
+  m->launches += 2;
+  for (int b0 = 0; b0 < m->n_seqs; b0 += 64) {
+    const int nb = m->n_seqs - b0 < 64 ? m->n_seqs - b0 : 64;
+    LG_TRY(logismos_launch_gemv_int4_g32_bf16(m->lm_head.codes.p, m->lm_head.scales.p, (uint16_t*)m->last_bf16.p + (size_t)b0 * H,
+                                              (uint16_t*)m->logits.p + (size_t)b0 * c.vocab, nb, c.vocab, H, s), "lm_head");
+    m->launches += 1;
+  }
+  LG_TRY(logismos_launch_greedy_argmax(m->logits.p, 0, m->tokens.p, m->n_seqs, c.vocab, s), "greedy");
+  m->launches += 1;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const lg_decoder_weights_t* w, void** model) {
+  if (!cfg || !w || !model) { set_error("null argument"); return LG_EMB_COMPUTE; }
+  *model = nullptr;
+  const lg_decoder_config_t& c = *cfg;
+  if (c.hidden <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.hidden % c.n_heads || c.n_heads % c.n_kv_heads ||
+      c.hidden / c.n_heads != 128 || c.hidden % 128 || c.intermediate % 128 || c.n_layers < 0 || c.n_pool_blocks <= 0 ||
+      c.max_blocks_per_seq <= 0 || c.max_step_tokens <= 0 || c.max_step_seqs <= 0 || c.max_pos <= 0 || c.vocab <= 0 ||
+      c.n_heads / c.n_kv_heads > 16) {
+    set_error("unsupported decoder config (head_dim must be 128; hidden and intermediate multiples of 128)");
+    return LG_EMB_COMPUTE;
+  }
+  if (cudaSetDevice(device) != cudaSuccess) { set_error("cudaSetDevice failed"); return LG_EMB_COMPUTE; }
+  Decoder* m = new Decoder();
+  m->cfg = c;
+  m->device = device;
+  m->head_dim = c.hidden / c.n_heads;
+  m->kv_dim = c.n_kv_heads * m->head_dim;
+  m->qkv_dim = c.hidden + 2 * m->kv_dim;
+  const size_t H = c.hidden, I = c.intermediate, KV = m->kv_dim, QKV = m->qkv_dim;
+  bool ok = true;
+  {
+    std::vector<uint16_t> tmp((size_t)c.vocab * H);
+    for (size_t i = 0; i < tmp.size(); ++i) tmp[i] = f32_to_bf16(w->tok_embed[i]);
+    ok = ok && m->tok_embed.upload(tmp.data(), tmp.size() * 2);
+  }
+  ok = ok && m->final_norm.upload(w->final_norm, H * 4);
+  ok = ok && upload_q(m->lm_head, {&w->lm_head}, {c.vocab}, (int)H);
+  m->layers.resize(c.n_layers);
+  const size_t pool_bytes = (size_t)c.n_pool_blocks * kBlock * KV * 2;
+  for (int l = 0; l < c.n_layers && ok; ++l) {
+    const lg_decoder_layer_weights_t& lw = w->layers[l];
+    DLayer& L = m->layers[l];
+    ok = ok && L.norm1.upload(lw.norm1, H * 4) && L.norm2.upload(lw.norm2, H * 4);
+    std::vector<float> b(QKV);
+    std::memcpy(b.data(), lw.bq, H * 4);
+    std::memcpy(b.data() + H, lw.bk, KV * 4);
+    std::memcpy(b.data() + H + KV, lw.bv, KV * 4);
+    ok = ok && L.bqkv.upload(b.data(), QKV * 4);
+    ok = ok && upload_q(L.wqkv, {&lw.wq, &lw.wk, &lw.wv}, {(int)H, (int)KV, (int)KV}, (int)H);
+    ok = ok && upload_q(L.wo, {&lw.wo}, {(int)H}, (int)H);
+    ok = ok && upload_q(L.wgu, {&lw.w_gate, &lw.w_up}, {(int)I, (int)I}, (int)H);
+    ok = ok && upload_q(L.wdown, {&lw.w_down}, {(int)H}, (int)I);
+    ok = ok && L.kpool.alloc(pool_bytes) && L.vpool.alloc(pool_bytes);
+    ok = ok && cudaMemset(L.kpool.p, 0, pool_bytes) == cudaSuccess && cudaMemset(L.vpool.p, 0, pool_bytes) == cudaSuccess;
+  }
+  if (ok) {  // RoPE table in f64 then f32 (cpu_f32/mod.rs:599-619)
+    const size_t half = m->head_dim / 2;
+    std::vector<float> cs((size_t)c.max_pos * half), sn((size_t)c.max_pos * half);
+    for (int p = 0; p < c.max_pos; ++p)
+      for (size_t i = 0; i < half; ++i) {
+        const double ang = (double)p * std::pow(c.rope_theta, -(2.0 * (double)i) / (double)m->head_dim);
+        cs[p * half + i] = (float)std::cos(ang);
+        sn[p * half + i] = (float)std::sin(ang);
+      }
+    ok = ok && m->cos.upload(cs.data(), cs.size() * 4) && m->sin.upload(sn.data(), sn.size() * 4);
+  }
+  const size_t T = c.max_step_tokens, S = c.max_step_seqs, MB = c.max_blocks_per_seq;
+  size_t wmax = QKV * H;
+  if (2 * I * H > wmax) wmax = 2 * I * H;
+  // every sequence of a step may be a decode sequence of up to max_blocks_per_seq blocks
+  m->max_chunks = S * ((MB * kBlock + kChunkTokens - 1) / kChunkTokens);
+  ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
+       m->qdec.alloc(S * H * 2) && m->gu.alloc(T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) &&
+       m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) && m->logits.alloc(S * (size_t)c.vocab * 2) &&
+       m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->slots.alloc(T * 8) &&
+       m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&
+       m->dec_chunks.alloc((S + 1) * 4) &&
+       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim));
+  ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
+  m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4;
+  ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
+  if (!ok) {
+    set_error(std::string("lg_decoder_create: allocation or upload failed: ") + cudaGetErrorString(cudaGetLastError()));
+    lg_decoder_destroy(m);
+    return LG_EMB_COMPUTE;
+  }
+  *model = m;
+  return LG_EMB_OK;
+}
+
+void lg_decoder_destroy(void* model) {
+  if (!model) return;
+  Decoder* m = static_cast<Decoder*>(model);
+  cudaSetDevice(m->device);
+  Buf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->qkv,
+                 &m->attn, &m->qdec, &m->gu, &m->act, &m->wscratch, &m->last, &m->last_bf16, &m->logits, &m->tokens, &m->status,
+                 &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch};
+  for (Buf* b : bufs) b->release();
+  for (auto& L : m->layers) {
+    Buf* lb[] = {&L.norm1, &L.norm2, &L.bqkv, &L.kpool, &L.vpool, &L.wqkv.codes, &L.wqkv.scales, &L.wo.codes, &L.wo.scales,
+                 &L.wgu.codes, &L.wgu.scales, &L.wdown.codes, &L.wdown.scales};
+    for (Buf* b : lb) b->release();
+  }
+  if (m->pinned) cudaFreeHost(m->pinned);
+  if (m->stream) cudaStreamDestroy(m->stream);
+  delete m;
+}
+
+uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* cached, const int32_t* newl, int32_t n_seqs,
+                         const int32_t* tables, uint32_t* next_tokens) {
+  Decoder* m = static_cast<Decoder*>(model);
+  const lg_decoder_config_t& c = m->cfg;
+  if (n_seqs <= 0 || n_seqs > c.max_step_seqs || !host_ids || !cached || !newl || !tables || !next_tokens) {
+    set_error("lg_decoder_step: bad arguments or too many sequences for the workspace");
+    return LG_EMB_COMPUTE;
+  }
+  std::lock_guard<std::mutex> lock(m->mu);
+  if (cudaSetDevice(m->device) != cudaSuccess) { set_error("cudaSetDevice failed"); return LG_EMB_COMPUTE; }
+  const int MB = c.max_blocks_per_seq;
+  // internal order: decode sequences first, then prefill chunks
+  std::vector<int> order;
+  std::vector<int64_t> src_off(n_seqs);
+  int64_t off = 0, total = 0;
+  for (int i = 0; i < n_seqs; ++i) {
+    if (newl[i] <= 0 || cached[i] < 0) { set_error("lg_decoder_step: every sequence needs >= 1 new token"); return LG_EMB_COMPUTE; }
+    if (newl[i] > 1 && cached[i] != 0) { set_error("lg_decoder_step: a prefill chunk must start its sequence (cached_len == 0)"); return LG_EMB_COMPUTE; }
+    if ((int64_t)cached[i] + newl[i] > c.max_pos || (int64_t)cached[i] + newl[i] > (int64_t)MB * kBlock) {
+      set_error("lg_decoder_step: sequence exceeds max_pos or its block table");
+      return LG_EMB_INPUT_TOO_LONG;
+    }
+    src_off[i] = off;
+    off += newl[i];
+    total += newl[i];
+  }
+  if (total > c.max_step_tokens) { set_error("lg_decoder_step: step exceeds max_step_tokens"); return LG_EMB_COMPUTE; }
+  for (int i = 0; i < n_seqs; ++i) if (newl[i] == 1) order.push_back(i);
+  const int n_dec = (int)order.size();
+  for (int i = 0; i < n_seqs; ++i) if (newl[i] > 1) order.push_back(i);
+  const int n_pre = n_seqs - n_dec;
+  // carve the pinned block
+  uint8_t* pp = m->pinned;
+  uint32_t* h_ids = (uint32_t*)pp; pp += (size_t)total * 4;
+  int32_t* h_pos = (int32_t*)pp; pp += (size_t)total * 4;
+  int64_t* h_slots = (int64_t*)pp; pp += (size_t)total * 8;
+  int32_t* h_cu = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
+  int32_t* h_cu_pre = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
+  int32_t* h_last = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
+  int32_t* h_chunks = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
+  int32_t* h_tables = (int32_t*)pp; pp += (size_t)n_seqs * MB * 4;
+  int32_t* h_ctx = (int32_t*)pp;
+  std::vector<int32_t> o_cached(n_seqs), o_new(n_seqs), o_seqids((size_t)total);
+  int64_t t = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    const int i = order[s];
+    o_cached[s] = cached[i];
+    o_new[s] = newl[i];
+    std::memcpy(h_tables + (size_t)s * MB, tables + (size_t)i * MB, (size_t)MB * 4);
+    std::memcpy(h_ids + t, host_ids + src_off[i], (size_t)newl[i] * 4);
+    t += newl[i];
+  }
+  const int64_t built = logismos_build_packing(o_cached.data(), o_new.data(), n_seqs, h_tables, MB, kBlock, c.n_pool_blocks, h_cu,
+                                               h_pos, h_slots, o_seqids.data());
+  if (built != total) { set_error("lg_decoder_step: a block table entry is missing or outside the pool"); return LG_EMB_COMPUTE; }
+  int max_pre = 0;
+  h_cu_pre[0] = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    h_last[s] = h_cu[s + 1] - 1;
+    if (s < n_dec) h_ctx[s] = o_cached[s] + 1;
+    else {
+      h_cu_pre[s - n_dec + 1] = h_cu[s + 1] - n_dec;
+      if (o_new[s] > max_pre) max_pre = o_new[s];
+    }
+  }
+  const int total_chunks = n_dec > 0 ? logismos_build_decode_chunks(h_ctx, n_dec, kChunkTokens, h_chunks) : 0;
+  if (total_chunks < 0 || (size_t)total_chunks > m->max_chunks) { set_error("lg_decoder_step: decode chunk count exceeds the scratch"); return LG_EMB_COMPUTE; }
+  m->T = (int)total; m->n_dec = n_dec; m->n_pre = n_pre; m->n_seqs = n_seqs; m->max_pre_len = max_pre; m->total_chunks = total_chunks;
+  m->order = order;
+  cudaStream_t s = m->stream;
+  LG_TRY(cudaMemcpyAsync(m->ids.p, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D ids");
+  LG_TRY(cudaMemcpyAsync(m->pos.p, h_pos, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D positions");
+  LG_TRY(cudaMemcpyAsync(m->slots.p, h_slots, (size_t)total * 8, cudaMemcpyHostToDevice, s), "H2D slots");
+  LG_TRY(cudaMemcpyAsync(m->cu_prefill.p, h_cu_pre, (size_t)(n_pre + 1) * 4, cudaMemcpyHostToDevice, s), "H2D cu_seqlens");
+  LG_TRY(cudaMemcpyAsync(m->last_idx.p, h_last, (size_t)n_seqs * 4, cudaMemcpyHostToDevice, s), "H2D last rows");
+  if (n_dec > 0) {
+    LG_TRY(cudaMemcpyAsync(m->dec_ctx.p, h_ctx, (size_t)n_dec * 4, cudaMemcpyHostToDevice, s), "H2D context lens");
+    LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)n_dec * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
+    LG_TRY(cudaMemcpyAsync(m->dec_chunks.p, h_chunks, (size_t)(n_dec + 1) * 4, cudaMemcpyHostToDevice, s), "H2D chunk offsets");
+  }
+  if (uint32_t rc = run_device(m, s)) return rc;
+  std::vector<uint32_t> toks(n_seqs);
+  LG_TRY(cudaMemcpyAsync(toks.data(), m->tokens.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, s), "D2H tokens");
+  LG_TRY(cudaStreamSynchronize(s), "stream synchronize");
+  for (int k = 0; k < n_seqs; ++k) next_tokens[order[k]] = toks[k];
+  if (lg_decoder_device_status(m) != 0) { set_error("a device-side range check or bounded wait failed"); return LG_EMB_COMPUTE; }
+  return LG_EMB_OK;
+}
+
+uint32_t lg_decoder_replay_device(void* model, void* stream) {
+  Decoder* m = static_cast<Decoder*>(model);
+  if (m->T <= 0) { set_error("lg_decoder_replay_device: no step has run"); return LG_EMB_COMPUTE; }
+  if (cudaSetDevice(m->device) != cudaSuccess) { set_error("cudaSetDevice failed"); return LG_EMB_COMPUTE; }
+  return run_device(m, (cudaStream_t)stream);
+}
+
+uint32_t lg_decoder_last_hidden(void* model, int32_t n_seqs, float* host_out) {
+  Decoder* m = static_cast<Decoder*>(model);
+  if (n_seqs != m->n_seqs) { set_error("lg_decoder_last_hidden: n_seqs differs from the last step"); return LG_EMB_COMPUTE; }
+  cudaSetDevice(m->device);
+  const size_t H = m->cfg.hidden;
+  std::vector<uint16_t> tmp((size_t)n_seqs * H);
+  LG_TRY(cudaDeviceSynchronize(), "device synchronize");
+  LG_TRY(cudaMemcpy(tmp.data(), m->last_bf16.p, tmp.size() * 2, cudaMemcpyDeviceToHost), "D2H hidden");
+  for (int k = 0; k < n_seqs; ++k)
+    for (size_t j = 0; j < H; ++j) {
+      const uint32_t u = (uint32_t)tmp[(size_t)k * H + j] << 16;
+      std::memcpy(&host_out[(size_t)m->order[k] * H + j], &u, 4);
+    }
+  return LG_EMB_OK;
+}
+
+uint32_t lg_decoder_last_logits(void* model, int32_t n_seqs, float* host_out) {
+  Decoder* m = static_cast<Decoder*>(model);
+  if (n_seqs != m->n_seqs) { set_error("lg_decoder_last_logits: n_seqs differs from the last step"); return LG_EMB_COMPUTE; }
+  cudaSetDevice(m->device);
+  const size_t V = m->cfg.vocab;
+  std::vector<uint16_t> tmp((size_t)n_seqs * V);
+  LG_TRY(cudaDeviceSynchronize(), "device synchronize");
+  LG_TRY(cudaMemcpy(tmp.data(), m->logits.p, tmp.size() * 2, cudaMemcpyDeviceToHost), "D2H logits");
+  for (int k = 0; k < n_seqs; ++k)
+    for (size_t j = 0; j < V; ++j) {
+      const uint32_t u = (uint32_t)tmp[(size_t)k * V + j] << 16;
+      std::memcpy(&host_out[(size_t)m->order[k] * V + j], &u, 4);
+    }
+  return LG_EMB_OK;
+}
+
+int32_t lg_decoder_launches_last_step(const void* model) { return static_cast<const Decoder*>(model)->launches; }
+
+int32_t lg_decoder_device_status(void* model) {
+  Decoder* m = static_cast<Decoder*>(model);
+  int32_t v = -1;
+  cudaSetDevice(m->device);
+  if (cudaMemcpy(&v, m->status.p, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // extern "C"

@@ -204,6 +204,7 @@ extern "C" {
 uint32_t logismos_launch_embed_lookup_bf16(const void* table, const void* ids, void* out,
                                            int32_t n_ids, int32_t hidden, int32_t vocab,
                                            void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_ids < 0 || hidden <= 0 || vocab <= 0 || (hidden % 8)) return lg::kInvalidValue;
   if (n_ids == 0) return 0;
   const int wpb = 8;
@@ -214,6 +215,7 @@ uint32_t logismos_launch_embed_lookup_bf16(const void* table, const void* ids, v
 
 uint32_t logismos_launch_rms_norm_f32(const void* x, const void* w, void* y, int32_t rows,
                                       int32_t n, float eps, int32_t out_f32, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (rows < 0 || n <= 0 || (n % 4) || n > 8 * 4 * 256) return lg::kInvalidValue;
   if (rows == 0) return 0;
   int bs = 32;
@@ -230,6 +232,7 @@ uint32_t logismos_launch_rope_halves_bf16(void* qk, const void* cos_f32, const v
                                           int32_t n_rot_heads, int32_t head_dim,
                                           int32_t row_stride, int32_t max_pos, void* status,
                                           void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_tokens < 0 || n_rot_heads <= 0 || head_dim <= 0 || (head_dim % 4) || max_pos <= 0 ||
       row_stride < n_rot_heads * head_dim || (row_stride % 2))
     return lg::kInvalidValue;
@@ -244,6 +247,7 @@ uint32_t logismos_launch_rope_halves_bf16(void* qk, const void* cos_f32, const v
 
 uint32_t logismos_launch_swiglu_bf16(const void* gu, void* out, int32_t rows, int32_t inter,
                                      void* stream) {
+  lg::LaunchScope launch_scope_;
   if (rows < 0 || inter <= 0 || (inter % 8)) return lg::kInvalidValue;
   if (rows == 0) return 0;
   const int64_t total = (int64_t)rows * (inter / 8);
@@ -256,6 +260,7 @@ uint32_t logismos_launch_swiglu_bf16(const void* gu, void* out, int32_t rows, in
 uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu, const void* head_w,
                                        const void* head_b, void* out, int32_t n_seqs,
                                        int32_t hidden, int32_t dim, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_seqs < 0 || hidden <= 0 || dim <= 0 || (hidden % 8) || (size_t)(hidden + dim) * 4 > 48 * 1024)
     return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
@@ -267,6 +272,7 @@ uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu, c
 
 uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, void* out,
                                        int32_t rows, int32_t n, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (rows < 0 || n <= 0) return lg::kInvalidValue;
   if (rows == 0) return 0;
   if (logits_f32)
@@ -277,3 +283,33 @@ uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, v
 }
 
 }  // extern "C"
+
+// ---- row gather (last token of each sequence before the final norm / lm_head) -------------------
+namespace {
+__global__ void gather_rows_f32_kernel(const float* __restrict__ src, const int* __restrict__ idx,
+                                       float* __restrict__ dst, int n_rows, int width, int n_src_rows,
+                                       int* __restrict__ status) {
+  const int r = blockIdx.x;
+  const int s = idx[r];
+  if (s < 0 || s >= n_src_rows) {
+    if (threadIdx.x == 0 && status) atomicExch(status, 1);
+    for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4)
+      *reinterpret_cast<float4*>(dst + (size_t)r * width + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4)
+    *reinterpret_cast<float4*>(dst + (size_t)r * width + j) = *reinterpret_cast<const float4*>(src + (size_t)s * width + j);
+}
+}  // namespace
+
+extern "C" uint32_t logismos_launch_gather_rows_f32(const void* src_f32, const void* idx_i32, void* dst_f32,
+                                                    int32_t n_rows, int32_t width, int32_t n_src_rows,
+                                                    void* status_i32, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (n_rows < 0 || width <= 0 || (width % 4) || n_src_rows < 0) return lg::kInvalidValue;
+  if (n_rows == 0) return 0;
+  gather_rows_f32_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const float*)src_f32, (const int*)idx_i32,
+                                                                  (float*)dst_f32, n_rows, width, n_src_rows,
+                                                                  (int*)status_i32);
+  return lg::launch_status();
+}

@@ -78,6 +78,7 @@ gdn_decode_step_kernel(float* __restrict__ state, const __nv_bfloat16* __restric
 extern "C" uint32_t logismos_launch_gdn_decode_step(void* state, const void* q, const void* k, const void* v,
                                                     const void* g, const void* beta, void* o, int32_t n_seqs,
                                                     int32_t heads, float scale, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (n_seqs < 0 || heads <= 0) return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
   if (((uintptr_t)state & 15) || ((uintptr_t)v & 7) || ((uintptr_t)o & 7)) return lg::kInvalidValue;

@@ -426,6 +426,7 @@ extern "C" {
 uint32_t logismos_launch_linear_t_bf16(const void* a, const void* w, const void* bias, void* out, int32_t m,
                                        int32_t n, int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
                                        void* status_i32, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (m <= 0 || n <= 0 || k <= 0 || (k % BK) || (n % 16) || (lda % 8) || lda < k) return lg::kInvalidValue;
   if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return lg::kInvalidValue;
   if (epilogue == LG_EPI_SWIGLU && (n % 64)) return lg::kInvalidValue;
@@ -445,6 +446,7 @@ uint32_t logismos_launch_linear_t_bf16(const void* a, const void* w, const void*
 uint32_t logismos_launch_linear_t_naive_bf16(const void* a, const void* w, const void* bias, void* out,
                                              int32_t m, int32_t n, int32_t k, int32_t lda, int32_t ldc,
                                              int32_t epilogue, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (m <= 0 || n <= 0 || k <= 0 || lda < k || ldc < n) return lg::kInvalidValue;
   if (epilogue != LG_EPI_BF16 && epilogue != LG_EPI_RESID_F32) return lg::kInvalidValue;
   dim3 block(32, 8), grid((n + 31) / 32, (m + 7) / 8);

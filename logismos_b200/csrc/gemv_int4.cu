@@ -188,9 +188,203 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
   }
 }
 
+
+// ---- streaming variant ---------------------------------------------------------------------------
+// For tall weight matrices (many 16-row tiles per SM) the kernel above spends most of its
+// instructions re-staging x and reducing across warps. Here a CTA stages x ONCE (all of K) and every
+// warp then streams whole row tiles on its own: the weights of one step (16 rows x 64 B) and their
+// scales (16 rows x 8 B) travel global -> shared with cp.async through a per-warp ring of STAGES
+// slots that runs ahead across row-tile boundaries; ldmatrix.x4 hands lane (g, c) exactly "word c of
+// groups 0..3 of row g"; no block-wide barrier and no cross-warp reduction in the loop.
+constexpr int kWPitch = 80;                       // row pitch of a staged weight step: conflict-free ldmatrix
+constexpr int kSlotBytes = 16 * kWPitch + 16 * 8;  // 16 rows of codes + 16 rows of 4 fp16 scales
+
+template <int NT, int STAGES>
+__global__ void __launch_bounds__(512)
+gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
+                            const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                            int N, int K) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int groups = K / kGroup, iters = K / kIterK;
+  const int xrow_stride = groups * 64 + 64;
+  uint8_t* xs = smem;
+  float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
+  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kSlotBytes;
+  const uint32_t ring = smem_u32(ring_gen);
+
+  // stage x (bf16, fragment order) and the per-group corrections, once
+  {
+    const int units_row = K / 8;
+    const int total = NT * 8 * units_row;
+    for (int u = tid; u < total; u += blockDim.x) {
+      const int n = u / units_row, kk = u % units_row;
+      const int G = kk >> 2, cc = kk & 3;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + kk * 8));
+      const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
+      const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
+      float s = ((v01.x + v01.y) + (v23.x + v23.y)) + ((v45.x + v45.y) + (v67.x + v67.y));
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      uint4 perm;
+      perm.x = __byte_perm(raw.x, raw.z, 0x5410);
+      perm.y = __byte_perm(raw.x, raw.z, 0x7632);
+      perm.z = __byte_perm(raw.y, raw.w, 0x5410);
+      perm.w = __byte_perm(raw.y, raw.w, 0x7632);
+      *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
+      if (cc == 0) negcorr[G * (NT * 8) + n] = -136.0f * s;
+    }
+  }
+  __syncthreads();
+
+  const int row_tiles = (N + 15) / 16;
+  const int tile_stride = gridDim.x * nwarps;
+  const int first_tile = blockIdx.x * nwarps + warp;
+  const int my_tiles = first_tile < row_tiles ? (row_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+  const int total_steps = my_tiles * iters;
+
+  // producer state: flattened step -> (tile, it)
+  int p_step = 0, p_tile = first_tile, p_it = 0;
+  auto issue = [&]() {
+    if (p_step < total_steps) {
+      const uint32_t slot = ring + (uint32_t)(p_step % STAGES) * kSlotBytes;
+      const int row_base = p_tile * 16;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int rl = g + 8 * h;
+        const int r = min(row_base + rl, N - 1);
+        cp_async16(slot + rl * kWPitch + c * 16, codes + (size_t)r * (K / 2) + p_it * 64 + c * 16);
+      }
+      if (lane < 16) {
+        const int r = min(row_base + lane, N - 1);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(slot + 16 * kWPitch + lane * 8),
+                     "l"(scales + (size_t)r * groups + p_it * 4));
+      }
+      ++p_step;
+      if (++p_it == iters) { p_it = 0; p_tile += tile_stride; }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) issue();
+
+  float acc[NT][4];
+  int c_tile = first_tile, c_it = 0;
+  const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: lanes 8j..8j+7 address the rows of matrix j (= group j)
+  for (int step = 0; step < total_steps; ++step) {
+    if (c_it == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+    }
+    issue();
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const uint32_t slot = ring + (uint32_t)(step % STAGES) * kSlotBytes;
+    uint32_t w0[4], w1[4];
+    ldmatrix_x4(w0, slot + mr * kWPitch + mat * 16);
+    ldmatrix_x4(w1, slot + (8 + mr) * kWPitch + mat * 16);
+    const uint8_t* sgen = ring_gen + (size_t)(step % STAGES) * kSlotBytes + 16 * kWPitch;
+    const uint2 s0r = *reinterpret_cast<const uint2*>(sgen + g * 8);
+    const uint2 s1r = *reinterpret_cast<const uint2*>(sgen + (g + 8) * 8);
+    const float2 s0a = __half22float2(*reinterpret_cast<const __half2*>(&s0r.x));
+    const float2 s0b = __half22float2(*reinterpret_cast<const __half2*>(&s0r.y));
+    const float2 s1a = __half22float2(*reinterpret_cast<const __half2*>(&s1r.x));
+    const float2 s1b = __half22float2(*reinterpret_cast<const __half2*>(&s1r.y));
+    const float sc0[4] = {s0a.x, s0a.y, s0b.x, s0b.y};
+    const float sc1[4] = {s1a.x, s1a.y, s1b.x, s1b.y};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int G = c_it * 4 + j;
+      const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0[j] >> 4), nib_pair_bf16(w1[j] >> 4)};
+      const uint32_t a_hi[4] = {nib_pair_bf16(w0[j] >> 8), nib_pair_bf16(w1[j] >> 8), nib_pair_bf16(w0[j] >> 12), nib_pair_bf16(w1[j] >> 12)};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 bx = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * xrow_stride + G * 64 + c * 16);
+        const float2 nc = *reinterpret_cast<const float2*>(negcorr + G * (NT * 8) + nt * 8 + 2 * c);
+        float d[4] = {nc.x, nc.y, nc.x, nc.y};
+        const uint32_t b_lo[2] = {bx.x, bx.y}, b_hi[2] = {bx.z, bx.w};
+        mma_bf16_16816(d, a_lo, b_lo, d);
+        mma_bf16_16816(d, a_hi, b_hi, d);
+        acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
+        acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
+        acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
+        acc[nt][3] = fmaf(sc1[j], d[3], acc[nt][3]);
+      }
+    }
+    __syncwarp();  // every lane is done with the slot before a later issue() refills it
+    if (++c_it == iters) {
+      const int ra = c_tile * 16 + g, rb = ra + 8;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b0 = nt * 8 + 2 * c;
+        if (ra < N) {
+          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[nt][0]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[nt][1]);
+        }
+        if (rb < N) {
+          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[nt][2]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[nt][3]);
+        }
+      }
+      c_it = 0;
+      c_tile += tile_stride;
+    }
+  }
+  cp_async_wait<0>();
+}
+
+int gemv_sm_count() {
+  static int n = 0;
+  if (n) return n;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (n <= 0) n = 148;
+  return n;
+}
+
+// Returns true (and the status in *rc) when the streaming variant applies and was launched.
+template <int NT>
+bool try_launch_stream(const void* codes, const void* scales, const void* x, void* y, int batch, int N, int K,
+                       cudaStream_t stream, uint32_t* rc) {
+  const int sms = gemv_sm_count();
+  const int row_tiles = (N + 15) / 16;
+  if (row_tiles < 2 * sms) return false;  // too few row tiles per SM: the k-split kernel spreads better
+  const int groups = K / kGroup;
+  const size_t xbytes = (size_t)NT * 8 * (groups * 64 + 64) + (size_t)groups * NT * 8 * 4;
+  int warps = (row_tiles + sms - 1) / sms;
+  warps = warps < 2 ? 2 : (warps > 16 ? 16 : warps);
+  const bool deep = warps <= 8;
+  const int stages = deep ? 8 : 4;
+  size_t smem = xbytes + (size_t)warps * stages * kSlotBytes;
+  while (smem > 200 * 1024 && warps > 2) { --warps; smem = xbytes + (size_t)warps * stages * kSlotBytes; }
+  if (smem > 200 * 1024) return false;  // x does not fit: chunked kernel
+  const int grid = (row_tiles + warps - 1) / warps < sms ? (row_tiles + warps - 1) / warps : sms;
+  cudaError_t e;
+  if (deep) {
+    e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
+    gemv_int4_g32_stream_kernel<NT, 8><<<grid, warps * 32, smem, stream>>>(
+        (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
+  } else {
+    e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
+    gemv_int4_g32_stream_kernel<NT, 4><<<grid, warps * 32, smem, stream>>>(
+        (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
+  }
+  *rc = lg::launch_status();
+  return true;
+}
+
 template <int NT>
 uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y, int batch, int N,
                    int K, cudaStream_t stream) {
+  uint32_t src = 0;
+  if (try_launch_stream<NT>(codes, scales, x, y, batch, N, K, stream, &src)) return src;
   const int iters_k = K / kIterK;
   int kc = 4096 / NT;  // x chunk staged per pass: NT * 8 rows * kc * 2 B  (<= 64 KB)
   if (kc > K) kc = K;
@@ -223,8 +417,9 @@ extern "C" uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes, const 
                                                        const void* x_bf16, void* y_bf16,
                                                        int32_t batch, int32_t n, int32_t k,
                                                        void* stream) {
+  lg::LaunchScope launch_scope_;
   if (batch <= 0 || batch > 64 || n <= 0 || k <= 0 || (k % kIterK) != 0) return lg::kInvalidValue;
-  if (((uintptr_t)codes & 3) || ((uintptr_t)scales_f16 & 7) || ((uintptr_t)x_bf16 & 15))
+  if (((uintptr_t)codes & 15) || ((uintptr_t)scales_f16 & 7) || ((uintptr_t)x_bf16 & 15))
     return lg::kInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const int nt = (batch + 7) / 8;

@@ -121,6 +121,7 @@ extern "C" {
 
 uint32_t logismos_launch_matmul_naive_fp16(const void* a, const void* b, void* d, int32_t m,
                                            int32_t n, int32_t k, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (!matmul_shape_ok(m, n, k)) return lg::kInvalidValue;
   dim3 block(16, 16), grid((n + 15) / 16, (m + 15) / 16);
   matmul_naive_fp16_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
@@ -130,6 +131,7 @@ uint32_t logismos_launch_matmul_naive_fp16(const void* a, const void* b, void* d
 
 uint32_t logismos_launch_matmul_wmma_fp16(const void* a, const void* b, void* d, int32_t m,
                                           int32_t n, int32_t k, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (!matmul_shape_ok(m, n, k) || (m % 16) || (n % 16) || (k % 16)) return lg::kInvalidValue;
   dim3 block(128), grid((n + 31) / 32, (m + 31) / 32);
   matmul_tc_fp16_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
@@ -139,6 +141,7 @@ uint32_t logismos_launch_matmul_wmma_fp16(const void* a, const void* b, void* d,
 
 uint32_t logismos_launch_rms_norm_fp16(const void* x, const void* w, void* y, int32_t m, int32_t n,
                                        float eps, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (m <= 0 || n <= 0) return lg::kInvalidValue;
   int bs = 32;
   while (bs < n && bs < 256) bs <<= 1;
@@ -148,6 +151,7 @@ uint32_t logismos_launch_rms_norm_fp16(const void* x, const void* w, void* y, in
 }
 
 uint32_t logismos_launch_softmax_fp16(const void* x, void* y, int32_t m, int32_t n, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (m <= 0 || n <= 0) return lg::kInvalidValue;
   int bs = 32;
   while (bs < n && bs < 256) bs <<= 1;
@@ -159,6 +163,7 @@ uint32_t logismos_launch_softmax_fp16(const void* x, void* y, int32_t m, int32_t
 // four extents within i32 (overflow of the 64-bit product is a rejection, not a wrap).
 uint32_t logismos_launch_rope_fp16(void* qk, const void* cos_sin, int32_t batch, int32_t seq,
                                    int32_t heads, int32_t head_dim, void* stream) {
+  lg::LaunchScope launch_scope_;
   if (batch <= 0 || seq <= 0 || heads <= 0 || head_dim <= 0 || (head_dim & 1)) return lg::kInvalidValue;
   int64_t total = 1;
   const int32_t dims[4] = {batch, seq, heads, head_dim};

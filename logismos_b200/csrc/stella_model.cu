@@ -24,6 +24,14 @@ namespace {
 thread_local std::string g_last_error;
 
 void set_error(const std::string& s) { g_last_error = s; }
+}  // namespace
+
+// shared with the other executors of the library
+namespace lgm {
+void set_error(const std::string& s) { g_last_error = s; }
+}  // namespace lgm
+
+namespace {
 
 inline uint16_t f32_to_bf16(float f) {
   uint32_t u;

@@ -35,18 +35,40 @@ def peaks():
     return {"hbm": 6650.0, "tf": 1590.0, "src": "fallback"}
 
 
+USE_GRAPH = True
+
+
 def timeit(fn, iters, warmup=3):
-    st = torch.cuda.current_stream()
+    """Seconds per launch. The `iters` launches are captured into one CUDA graph and the graph is
+    replayed, so that host-side launch cost (Python, descriptor encoding) is not what is timed; a
+    kernel of a few microseconds is otherwise hidden behind ~15 us of host work per call."""
     for i in range(warmup):
         fn(i)
-    st.synchronize()
+    torch.cuda.synchronize()
+    if not USE_GRAPH:
+        st = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for i in range(iters):
+            fn(i)
+        e1.record(st)
+        e1.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / iters
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    st = torch.cuda.current_stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
     e0.record(st)
-    for i in range(iters):
-        fn(i)
+    for _ in range(reps):
+        g.replay()
     e1.record(st)
     e1.synchronize()
-    return e0.elapsed_time(e1) * 1e-3 / iters
+    return e0.elapsed_time(e1) * 1e-3 / (iters * reps)
 
 
 def bench_gemv(n, k, batch, iters, copies=None, pk=None):
@@ -142,7 +164,10 @@ def main(argv=None):
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--chunk", type=int, default=512)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-graph", action="store_true", help="time back-to-back launches from Python instead of a CUDA graph")
     a = ap.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = not a.no_graph
     if a.what == "gemv":
         print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
     elif a.what == "gemm":

@@ -226,6 +226,17 @@ def gemv_int4(codes, scales, x, out=None, sync=True):
     return y
 
 
+def dequant_int4(codes, scales, sync=True):
+    """codes u8 [n, k/2], scales f16 [n, k/32] -> bf16 [n, k] = bf16(scale * code)."""
+    _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2)
+    n, k = codes.shape[0], codes.shape[1] * 2
+    out = torch.empty((n, k), dtype=torch.bfloat16, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(lib.logismos_launch_dequant_int4_g32_bf16(_p(codes), _p(scales), _p(out), n, k, _stream()), "dequant_int4_g32")
+        _done(sync)
+    return out
+
+
 def build_decode_chunks(context_lens_host, chunk_tokens):
     """Host helper: (chunk_offsets int32 CPU tensor [n+1], total_chunks)."""
     cl = torch.as_tensor(context_lens_host, dtype=torch.int32).contiguous()

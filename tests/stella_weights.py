@@ -43,3 +43,30 @@ def make_batch(cfg, seed, n_seq=8, lo=32, hi=512):
     cu[1:] = np.cumsum(lens)
     ids = rng.integers(0, cfg["vocab"], size=int(cu[-1]), dtype=np.uint32)
     return ids, cu
+
+
+def quantize_weights(cfg, w, seed_lm=5):
+    """int4 group-32 version of a Stella-architecture weight dict, for the decoder executor.
+
+    Returns (qw, deq): ``qw`` in the layout logismos_b200.decoder.DecoderModel takes, and ``deq``, the
+    fp32 weight dict holding exactly the dequantised values (what the CPU oracle runs on), plus
+    ``deq['lm_head']`` fp32 [vocab, hidden]."""
+    import oracle_lib as O
+    rng = np.random.Generator(np.random.PCG64(seed_lm))
+    lm = rng.standard_normal((cfg["vocab"], cfg["hidden"]), dtype=np.float32) * np.float32(0.02)
+    qw = {"tok_embed": w["tok_embed"], "final_norm": w["final_norm"], "layers": []}
+    deq = {"tok_embed": O.bf16_round(w["tok_embed"]), "final_norm": w["final_norm"], "layers": [],
+           "head_w": w["head_w"], "head_b": w["head_b"]}
+    c, s = O.int4_quantize(lm)
+    qw["lm_head"] = (c, s)
+    deq["lm_head"] = O.int4_dequant(c, s)
+    for lw in w["layers"]:
+        ql = {n: lw[n] for n in ("norm1", "norm2", "bq", "bk", "bv")}
+        dl = dict(ql)
+        for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down"):
+            c, s = O.int4_quantize(lw[n])
+            ql[n] = (c, s)
+            dl[n] = O.int4_dequant(c, s)
+        qw["layers"].append(ql)
+        deq["layers"].append(dl)
+    return qw, deq

@@ -57,6 +57,22 @@ def test_launcher_shape_guards_reject_without_launching():  # matmul/mod.rs:213-
     assert lib.logismos_launch_paged_attention_decode_bf16(z, z, z, z, z, z, z, z, z, z, z, 1, 1, 100, 4, 4, 16, 2, 128, z) == 1
 
 
+def test_runtime_shim_returns_a_status_on_a_machine_without_a_gpu():
+    """Every lg_* call must come back with a status (never spin or abort), device or not: on a box
+    without a driver the calls fail with a classified code, on a GPU box they succeed."""
+    n = C.c_int32(-1)
+    rc = lib.lg_device_count(C.byref(n))
+    assert (rc == 0 and n.value >= 1) or (rc != 0 and n.value == 0)
+    d = C.c_void_p(123)
+    rc = lib.lg_malloc(2**31 - 1, 64, C.byref(d))  # an ordinal no machine has: fails before allocating
+    assert rc != 0 and d.value is None
+    assert lib.lg_device_set_current(2**31 - 1) != 0
+    s = C.c_void_p(77)
+    assert lib.lg_stream_create(2**31 - 1, C.byref(s)) != 0 and s.value is None
+    ms = C.c_float(0)
+    assert lib.lg_event_elapsed_ms(None, None, None) == 1  # null out-pointer: InvalidValue
+
+
 def test_error_kind_names_need_no_device():
     name = lambda c: lib.lg_error_kind_name(lib.lg_error_kind_from_raw(c)).decode()
     assert name(2) == "OutOfMemory" and name(700) == "IllegalAddress" and name(719) == "LaunchFailure"
