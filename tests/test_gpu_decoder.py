@@ -74,14 +74,14 @@ def test_mixed_prefill_and_decode_steps_equal_per_sequence_execution(setup):
 
 def test_step_rejects_what_it_cannot_run(setup):
     qw, _, _ = setup
-    model = DecoderModel(TINY, qw, n_pool_blocks=8, max_blocks_per_seq=4, max_step_tokens=64, max_step_seqs=2)
-    tab = np.array([[0, 1, 2, 3]], np.int32)
+    model = DecoderModel(TINY, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2)
+    tab = np.array([[0, 1, 2, 3, 4, 5, 6, 7]], np.int32)
     with pytest.raises(ComputeError):   # a prefill chunk continuing a cached sequence
         model.step([1, 2, 3], [4], [3], tab)
     with pytest.raises(ComputeError):   # block table row with a missing entry
-        model.step([1] * 20, [0], [20], np.array([[0, -1, -1, -1]], np.int32))
+        model.step([1] * 20, [0], [20], np.array([[0, -1, -1, -1, -1, -1, -1, -1]], np.int32))
     with pytest.raises(ComputeError):   # more tokens than the step workspace
         model.step([1] * 65, [0], [65], tab)
     with pytest.raises(Exception):      # beyond the block table
-        model.step([1], [64], [1], tab)
+        model.step([1], [128], [1], tab)
     model.close()
