@@ -163,6 +163,30 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
     int32_t total_chunks, int32_t chunk_tokens, int32_t max_blocks, int32_t n_pool_blocks,
     int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, void* stream);
 
+/* Paged-attention decode for callers that cannot allocate device memory where they decode (an
+ * engine that has given all free HBM to its KV pool, a thread where an allocation's device-wide
+ * synchronisation is unacceptable). It has no counterpart in the reference. Same arguments and
+ * results as logismos_launch_paged_attention_decode_bf16 minus `scratch`: the per-chunk partials
+ * go to a buffer of LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES built into the library image (each
+ * GPU that loads the library holds it until exit). The call allocates nothing.
+ *   - Limit: logismos_paged_decode_scratch_bytes(total_chunks, n_heads, head_dim) must not exceed
+ *     the constant (8 MiB: e.g. 1008 chunks at 16 heads x 128); beyond it the call returns
+ *     cudaErrorMemoryAllocation (2) without launching and says why on stderr.
+ *   - The first call on each device looks up the buffer's device address (that device must be
+ *     current, as for any launch) and caches it; make that first call before starting any stream
+ *     capture on the device.
+ *   - All calls share the one buffer and it keeps the previous call's contents; nothing in it needs
+ *     clearing, since a launch only reads partials it wrote itself. For the same reason two calls
+ *     whose kernels can overlap on the GPU (different streams, or threads) race on it: serialise
+ *     them, or use the entry point with caller scratch. */
+#define LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+uint32_t logismos_launch_paged_attention_decode_noalloc_bf16(
+    const void* q_bf16, void* k_pool_bf16, void* v_pool_bf16, const void* new_k_bf16,
+    const void* new_v_bf16, const void* block_tables_i32, const void* context_lens_i32,
+    const void* chunk_offsets_i32, void* out_bf16, void* status_i32, int32_t n_seqs,
+    int32_t total_chunks, int32_t chunk_tokens, int32_t max_blocks, int32_t n_pool_blocks,
+    int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, void* stream);
+
 /* KvCache::put for a ragged batch (crates/cache/src/lib.rs:57-82): row i of k/v bf16
  * [n_tokens, row_elems] is stored at physical slot slot_mapping[i] (i64: block * 16 + offset).
  * A slot outside the pool is skipped and sets *status to 1. */

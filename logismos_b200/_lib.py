@@ -74,6 +74,8 @@ def _declare(l):
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_paged_attention_decode_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
                                                         i32, i32, i32, i32, i32, vp],
+        "logismos_launch_paged_attention_decode_noalloc_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
+                                                                i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_kv_store_bf16": [vp, vp, i32, vp, vp, vp, i32, i32, i64, vp, vp],
         "logismos_launch_paged_kv_gather_bf16": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
         "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],

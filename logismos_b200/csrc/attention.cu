@@ -11,6 +11,9 @@
 // (running max / running sum) softmax in fp32, exp2 domain.
 // Scores are scaled after the dot product (attention.rs:239-241); the GQA mapping is
 // q head j -> kv head j / (n_heads / n_kv_heads) (attention.rs:366-382).
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 #include "logismos_kernels.h"
 
@@ -585,3 +588,65 @@ uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool, const void* v_
 }
 
 }  // extern "C"
+
+// ================================ paged decode without caller scratch ==========================
+//
+// Some hosts of this library may not allocate device memory at the point where they decode: an
+// engine that has already handed every free byte of HBM to its KV pool and weight buffers, or a
+// decode thread in which the implicit device-wide synchronisation of an allocation call is not
+// acceptable. For them the per-chunk partial results live in a fixed buffer inside the library
+// image instead of a caller-provided scratch buffer. Every GPU that loads the library holds these
+// LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES until the process exits.
+namespace {
+
+static __device__ __align__(256) unsigned char g_paged_decode_static_scratch[LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[kMaxStaticDevices] = {nullptr};
+
+// The array's name is a host-side handle, not a device address: the address on the CURRENT device
+// is looked up once per device and cached. Returns cudaSuccess and the pointer, or the error.
+cudaError_t static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxStaticDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_paged_decode_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" uint32_t logismos_launch_paged_attention_decode_noalloc_bf16(
+    const void* q, void* k_pool, void* v_pool, const void* new_k, const void* new_v, const void* block_tables,
+    const void* context_lens, const void* chunk_offsets, void* out, void* status, int32_t n_seqs,
+    int32_t total_chunks, int32_t chunk_tokens, int32_t max_blocks, int32_t n_pool_blocks, int32_t n_heads,
+    int32_t n_kv_heads, int32_t head_dim, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (total_chunks < 0 || n_heads <= 0 || head_dim <= 0) return lg::kInvalidValue;
+  const size_t need = logismos_paged_decode_scratch_bytes(total_chunks, n_heads, head_dim);
+  if (need > (size_t)LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES) {
+    std::fprintf(stderr,
+                 "logismos_launch_paged_attention_decode_noalloc_bf16: %d chunks x %d heads need %zu bytes of "
+                 "scratch, the built-in buffer holds %zu; use more tokens per chunk, fewer sequences per call, or "
+                 "the entry point that takes caller scratch\n",
+                 total_chunks, n_heads, need, (size_t)LOGISMOS_PAGED_DECODE_STATIC_SCRATCH_BYTES);
+    return (uint32_t)cudaErrorMemoryAllocation;
+  }
+  void* scratch = nullptr;
+  cudaError_t e = static_scratch_for_current_device(&scratch);
+  if (e != cudaSuccess) return (uint32_t)e;
+  // Nothing in the buffer has to start at zero: every partial a launch reads, the same launch wrote.
+  return logismos_launch_paged_attention_decode_bf16(q, k_pool, v_pool, new_k, new_v, block_tables, context_lens,
+                                                     chunk_offsets, out, scratch, status, n_seqs, total_chunks,
+                                                     chunk_tokens, max_blocks, n_pool_blocks, n_heads, n_kv_heads,
+                                                     head_dim, stream);
+}
