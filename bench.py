@@ -298,6 +298,70 @@ def run_ours(args, cfg, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_ragged_step(args, rank, world, local_rank):
+    """Continuous-batching step of the benchmark's third configuration: a 28-layer Stella-dim causal
+    stack with int4 group-32 weights, 64 decode sequences (contexts uniform in [256, 8192]) plus 4
+    prefill chunks of 512 tokens, paged KV cache with 16-token blocks. Weights are random int4 codes
+    with |N(0, 0.02)| scales; the cache rows of the claimed contexts hold zeros (only their traffic
+    matters for timing). One step = 2112 tokens."""
+    import torch
+    from logismos_b200.decoder import BlockAllocator, DecoderModel
+    torch.cuda.set_device(local_rank)
+    cfg = dict(STELLA_1_5B, vocab=151936)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    rng = np.random.Generator(np.random.PCG64(11 + rank))
+    h, inter, kv = cfg["hidden"], cfg["intermediate"], 256
+
+    def qmat(n, k):
+        return (rng.integers(0, 256, (n, k // 2), dtype=np.uint8), np.abs(rng.standard_normal((n, k // 32), dtype=np.float32) * 0.02).astype(np.float16))
+
+    layer = {"norm1": np.ones(h, np.float32), "norm2": np.ones(h, np.float32), "bq": np.zeros(h, np.float32),
+             "bk": np.zeros(kv, np.float32), "bv": np.zeros(kv, np.float32), "wq": qmat(h, h), "wk": qmat(kv, h), "wv": qmat(kv, h),
+             "wo": qmat(h, h), "w_gate": qmat(inter, h), "w_up": qmat(inter, h), "w_down": qmat(h, inter)}
+    w = {"tok_embed": (rng.standard_normal((cfg["vocab"], h), dtype=np.float32) * np.float32(0.02)), "final_norm": np.ones(h, np.float32),
+         "layers": [layer] * cfg["n_layers"], "lm_head": qmat(cfg["vocab"], h)}
+    ctx = rng.integers(256, 8193, 64)
+    cached = np.concatenate([ctx, np.zeros(4, np.int64)]).astype(np.int32)
+    new = np.concatenate([np.ones(64, np.int64), np.full(4, 512)]).astype(np.int32)
+    max_blocks = 520
+    n_pool = int(((cached + new + 15) // 16).sum()) + 8
+    alloc = BlockAllocator(n_pool, max_blocks, seed=1)
+    tables = np.stack([alloc.ensure(i, int(cached[i] + new[i])) for i in range(68)])
+    ids = rng.integers(0, cfg["vocab"], int(new.sum()), dtype=np.uint32)
+    model = DecoderModel(cfg, w, n_pool_blocks=n_pool, max_blocks_per_seq=max_blocks, max_step_tokens=2112, max_step_seqs=68, device=local_rank)
+    toks = model.step(ids, cached, new, tables)
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        model.replay_device(stream.cuda_stream)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        model.replay_device(stream.cuda_stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    dt = e0.elapsed_time(e1) * 1e-3
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        toks = model.step(ids, cached, new, tables)
+    dt_e2e = time.perf_counter() - t0
+    T = int(new.sum())
+    kv_bytes = float(ctx.sum() + 64) * 1024 * cfg["n_layers"]
+    w_bytes = (h * h * 2 + 2 * kv * h + 3 * h * inter) * 0.5625 * cfg["n_layers"]
+    if rank == 0:
+        print(json.dumps({"metric": "ragged_step_tokens_per_s", "value": T * args.steps / dt, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16 activations, int4-g32 weights", "data": "synthetic",
+                          "config": {"workload": "ragged continuous-batching step: 64 decode seqs (ctx U[256,8192]) + 4 x 512-token prefill chunks, 28 layers, int4-g32 weights, paged KV block 16",
+                                     "tokens_per_step": T, "decode_context_tokens": int(ctx.sum()), "n_layers": cfg["n_layers"]},
+                          "e2e": {"value": T * args.steps / dt_e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(T * 16 + 68 * (max_blocks + 4) * 4), "d2h_bytes_per_step": 68 * 4},
+                          "gpu_launches": model.launches_last_step() * args.steps, "device_status": model.device_status(),
+                          "algorithmic": {"linear_tflop_per_step": 2.0 * T * (h * h * 2 + 2 * kv * h + 3 * h * inter) * cfg["n_layers"] / 1e12,
+                                          "decode_kv_gb_per_step": kv_bytes / 1e9, "int4_weight_gb_per_step": w_bytes / 1e9},
+                          "next_tokens_sample": [int(t) for t in toks[:4]]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -308,12 +372,15 @@ def main():
     ap.add_argument("--no-micro", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
+    ap.add_argument("--workload", default="stella", choices=["stella", "ragged_step"])
     args = ap.parse_args()
     cfg = dict(STELLA_1_5B)
     if args.layers:
         cfg["n_layers"] = args.layers
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.workload == "ragged_step":
+        run_ragged_step(args, rank, world, local)
+    elif args.impl == "reference":
         run_reference(args, cfg, rank, world)
     else:
         run_ours(args, cfg, rank, world, local)

@@ -115,13 +115,14 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv_bf16, const void*
                                                int32_t v_off, int32_t causal, void* stream);
 
 /* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
- * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), one CTA per
- * sequence, mask all ones. hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden];
- * head_b f32 [dim]; out f32 [n_seqs, dim]. A sequence of length 0 pools to zeros. */
+ * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), mask all ones.
+ * hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden]; head_b f32 [dim]; out f32
+ * [n_seqs, dim]; scratch_f32 [n_seqs, hidden] receives the pooled means. A sequence of length 0
+ * pools to zeros. Three launches. */
 uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu_seqlens_i32,
                                        const void* head_w_bf16, const void* head_b_f32,
-                                       void* out_f32, int32_t n_seqs, int32_t hidden, int32_t dim,
-                                       void* stream);
+                                       void* out_f32, void* scratch_f32, int32_t n_seqs,
+                                       int32_t hidden, int32_t dim, void* stream);
 
 /* ====================================================================================
  * Decode path. No reference GPU or CPU implementation exists for these; the anchors are the

@@ -112,52 +112,67 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
 }
 
 // StellaModel::encode_raw tail (crates/embed/src/stella.rs:231-246): masked mean (mask all
-// ones; zero-length sequence -> denominator 1) -> L2 (clamp 1e-12) -> W p + b -> L2.
-// One CTA (256 threads) per sequence; pooled vector in shared memory (hidden <= 4096).
-__global__ void pool_head_kernel(const float* __restrict__ hs, const int* __restrict__ cu,
-                                 const __nv_bfloat16* __restrict__ hw, const float* __restrict__ hb,
-                                 float* __restrict__ out, int hidden, int dim) {
-  extern __shared__ float sm[];
-  float* pooled = sm;           // [hidden]
-  float* yv = sm + hidden;      // [dim]
-  __shared__ float red[32];
+// ones; zero-length sequence -> denominator 1) -> L2 (clamp 1e-12) -> W p + b -> L2, as three
+// small kernels so that the token rows and the head weights are read by many CTAs:
+//   pool_mean: CTA = (sequence, 128 columns), tokens summed in order (the reference's order)
+//   head_rows: CTA = (sequence, 64 output rows), normalises the pooled vector on the fly
+//   l2_rows:   CTA = sequence
+__global__ void pool_mean_kernel(const float* __restrict__ hs, const int* __restrict__ cu,
+                                 float* __restrict__ pooled, int hidden) {
   const int s0 = cu[blockIdx.x], s1 = cu[blockIdx.x + 1];
-  const int len = s1 - s0;
-  const float inv_den = len > 0 ? 1.0f / (float)len : 1.0f;
-  float sq = 0.0f;
-  for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-    float acc = 0.0f;
-    for (int t = s0; t < s1; ++t) acc += hs[(size_t)t * hidden + j];
-    acc *= inv_den;
-    pooled[j] = acc;
-    sq += acc * acc;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= hidden) return;
+  const float* p = hs + (size_t)s0 * hidden + j;
+  float acc = 0.0f;
+  int t = s0;
+  for (; t + 8 <= s1; t += 8) {  // eight rows in flight, added in token order
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = p[(size_t)i * hidden];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += v[i];
+    p += (size_t)8 * hidden;
   }
+  for (; t < s1; ++t) { acc += *p; p += hidden; }
+  const int len = s1 - s0;
+  pooled[(size_t)blockIdx.x * hidden + j] = acc * (len > 0 ? 1.0f / (float)len : 1.0f);
+}
+
+__global__ void head_rows_kernel(const float* __restrict__ pooled, const __nv_bfloat16* __restrict__ hw,
+                                 const float* __restrict__ hb, float* __restrict__ out, int hidden, int dim) {
+  extern __shared__ float pn[];  // normalised pooled vector
+  __shared__ float red[32];
+  const float* pv = pooled + (size_t)blockIdx.x * hidden;
+  float sq = 0.0f;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) { const float v = pv[j]; pn[j] = v; sq += v * v; }
   sq = block_sum(sq, red);
   const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
-  for (int j = threadIdx.x; j < hidden; j += blockDim.x) pooled[j] *= inv;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) pn[j] *= inv;
   __syncthreads();
-  // dense head: one warp per output row, 8 bf16 per lane per step
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  float sq2 = 0.0f;
-  for (int o = warp; o < dim; o += nw) {
+  const int o_end = min(dim, (int)(blockIdx.y + 1) * 64);
+  for (int o = blockIdx.y * 64 + warp; o < o_end; o += nw) {
     const __nv_bfloat16* wr = hw + (size_t)o * hidden;
     float acc = 0.0f;
     for (int j = lane * 8; j < hidden; j += 256) {
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(wr + j));
       const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
-      acc += a.x * pooled[j] + a.y * pooled[j + 1] + b.x * pooled[j + 2] + b.y * pooled[j + 3] +
-             c.x * pooled[j + 4] + c.y * pooled[j + 5] + d.x * pooled[j + 6] + d.y * pooled[j + 7];
+      acc += a.x * pn[j] + a.y * pn[j + 1] + b.x * pn[j + 2] + b.y * pn[j + 3] +
+             c.x * pn[j + 4] + c.y * pn[j + 5] + d.x * pn[j + 6] + d.y * pn[j + 7];
     }
     acc = warp_sum(acc);
-    if (lane == 0) {
-      acc += hb[o];
-      yv[o] = acc;
-      sq2 += acc * acc;
-    }
+    if (lane == 0) out[(size_t)blockIdx.x * dim + o] = acc + hb[o];
   }
-  sq2 = block_sum(sq2, red);
-  const float inv2 = 1.0f / fmaxf(sqrtf(sq2), 1e-12f);
-  for (int o = threadIdx.x; o < dim; o += blockDim.x) out[(size_t)blockIdx.x * dim + o] = yv[o] * inv2;
+}
+
+__global__ void l2_rows_kernel(float* __restrict__ y, int dim) {
+  __shared__ float red[32];
+  float* row = y + (size_t)blockIdx.x * dim;
+  float sq = 0.0f;
+  for (int j = threadIdx.x; j < dim; j += blockDim.x) sq += row[j] * row[j];
+  sq = block_sum(sq, red);
+  const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
+  for (int j = threadIdx.x; j < dim; j += blockDim.x) row[j] *= inv;
 }
 
 // decode::greedy (crates/decode/src/lib.rs:73-83): strict > from -inf, so the first maximum wins
@@ -258,15 +273,22 @@ uint32_t logismos_launch_swiglu_bf16(const void* gu, void* out, int32_t rows, in
 }
 
 uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu, const void* head_w,
-                                       const void* head_b, void* out, int32_t n_seqs,
+                                       const void* head_b, void* out, void* scratch_f32, int32_t n_seqs,
                                        int32_t hidden, int32_t dim, void* stream) {
   lg::LaunchScope launch_scope_;
-  if (n_seqs < 0 || hidden <= 0 || dim <= 0 || (hidden % 8) || (size_t)(hidden + dim) * 4 > 48 * 1024)
+  if (n_seqs < 0 || hidden <= 0 || dim <= 0 || (hidden % 8) || (size_t)hidden * 4 > 48 * 1024 || !scratch_f32)
     return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
-  pool_head_kernel<<<n_seqs, 256, (size_t)(hidden + dim) * 4, (cudaStream_t)stream>>>(
-      (const float*)hidden_f32, (const int*)cu, (const __nv_bfloat16*)head_w, (const float*)head_b,
-      (float*)out, hidden, dim);
+  cudaStream_t s = (cudaStream_t)stream;
+  pool_mean_kernel<<<dim3(n_seqs, (hidden + 127) / 128), 128, 0, s>>>((const float*)hidden_f32, (const int*)cu,
+                                                                      (float*)scratch_f32, hidden);
+  uint32_t rc = lg::launch_status();
+  if (rc) return rc;
+  head_rows_kernel<<<dim3(n_seqs, (dim + 63) / 64), 256, (size_t)hidden * 4, s>>>(
+      (const float*)scratch_f32, (const __nv_bfloat16*)head_w, (const float*)head_b, (float*)out, hidden, dim);
+  rc = lg::launch_status();
+  if (rc) return rc;
+  l2_rows_kernel<<<n_seqs, 256, 0, s>>>((float*)out, dim);
   return lg::launch_status();
 }
 

@@ -8,8 +8,10 @@
 //   warp 1      allocates TMEM and issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN,
 //               K=16; four per 64-wide stage) with fp32 accumulators in TMEM; two accumulator
 //               buffers so the epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns per warp step, fused bias /
-//               residual add / SwiGLU, vectorised global stores
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns per warp step; bf16 outputs (bias,
+//               SwiGLU fused in registers) go out as 64-byte-per-thread vector stores; the fp32
+//               residual update x += acc is staged as 32 x 32 slabs in shared memory (128-byte
+//               swizzle) and applied by a TMA bulk tensor reduce-add, so x is never read into the SM
 // Synchronisation is by mbarriers only: full/empty per stage (TMA complete_tx, tcgen05.commit)
 // and full/empty per accumulator buffer. Every wait is bounded; on expiry the kernel raises an
 // error word, lets outstanding copies land, frees its TMEM and returns.
@@ -34,9 +36,10 @@ struct Cfg {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (200 * 1024) / kStage;  // 256->4, 192->5, 128->6
+  static constexpr int kStages = (192 * 1024) / kStage;  // 256->4, 192->4, 128->6
   static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;
-  static constexpr size_t kSmem = (size_t)kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 staging slabs of 32 rows x 128 B
+  static constexpr size_t kSmem = (size_t)kStages * kStage + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 // ---- mbarrier / TMA / tcgen05 wrappers --------------------------------------------------------
@@ -79,6 +82,29 @@ LG_DEVINL void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t b
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
       ::"r"(smem_dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+
+// shared -> global bulk tensor store / reduce-add of one staged slab (box given by the tensor map)
+LG_DEVINL void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(map), "r"(smem_src),
+               "r"(x), "r"(y)
+               : "memory");
+}
+LG_DEVINL void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n" ::"l"(map),
+               "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+LG_DEVINL void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+template <int N>
+LG_DEVINL void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory"); }
+LG_DEVINL void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+LG_DEVINL void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// One 32-row slab of 128 bytes per row in the 128-byte-swizzle layout the tensor map expects: the
+// 16-byte chunk j of row r sits at chunk position j ^ (r & 7). `slab` is 1024-byte aligned.
+LG_DEVINL void slab_write(uint8_t* slab, int row, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(slab + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
 }
 
 LG_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -137,20 +163,22 @@ LG_DEVINL float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K,
-                        int ldc, int* __restrict__ status) {
+                        const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
+                        void* __restrict__ out, int M, int N, int K, int ldc, int* __restrict__ status) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bars = smem_base + C::kStages * C::kStage;  // full[S], empty[S], tfull[2], tempty[2]
+  const uint32_t epi_base = smem_base + C::kStages * C::kStage;  // 8 staging slabs of 4 KB (1024-aligned)
+  const uint32_t bars = epi_base + C::kEpiBytes;  // full[S], empty[S], tfull[2], tempty[2]
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
   auto tfull_bar = [&](int b) { return bars + 8u * (2 * C::kStages + b); };
   auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::kStages + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kStages * C::kStage + 8 * (2 * C::kStages + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kStages * C::kStage + 8 * (2 * C::kStages + 4) + 8);
+  uint8_t* bars_gen = smem_gen + C::kStages * C::kStage + C::kEpiBytes;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * (2 * C::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * (2 * C::kStages + 4) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -224,17 +252,79 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
-    int it = 0;
+    uint8_t* slabs = smem_gen + C::kStages * C::kStage + q * 2 * 4096;
+    const uint32_t slabs_a = epi_base + q * 2 * 4096;
+    int it = 0, n_store = 0;
     bool ok = true;
+    // hands the slab just written to the TMA engine; the slab used two stores ago must have been read
+    auto slab_acquire = [&]() -> int {
+      const int b = n_store & 1;
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+      return b;
+    };
+    auto slab_release = [&](int b, int x, int y, bool in_range) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        if (in_range) {
+          if (EPI == LG_EPI_RESID_F32) tma_reduce_add_2d(&map_out, slabs_a + b * 4096, x, y);
+          else tma_store_2d(&map_out, slabs_a + b * 4096, x, y);
+        }
+        bulk_commit();
+      }
+      ++n_store;
+    };
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
       const int buf = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int row = m_blk * BM + q * 32 + lane;
+      const int row0 = m_blk * BM + q * 32;  // first output row of this warp's slab
+      const int row = row0 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-      if (EPI == LG_EPI_SWIGLU) {
+      if (EPI == LG_EPI_RESID_F32) {
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(t_row + c, r);
+          tc_wait_ld();
+          const int ncol = n_blk * BN + c;
+          const int b = slab_acquire();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float a0 = __uint_as_float(r[4 * j]), a1 = __uint_as_float(r[4 * j + 1]);
+            float a2 = __uint_as_float(r[4 * j + 2]), a3 = __uint_as_float(r[4 * j + 3]);
+            if (bias && ncol + 4 * j < N) { a0 += bias[ncol + 4 * j]; a1 += bias[ncol + 4 * j + 1]; a2 += bias[ncol + 4 * j + 2]; a3 += bias[ncol + 4 * j + 3]; }
+            slab_write(slabs + b * 4096, lane, j, make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3)));
+          }
+          slab_release(b, ncol, row0, ncol < N && row0 < M);
+        }
+      } else if (EPI == LG_EPI_BF16) {
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(t_row + c, r);
+          tc_wait_ld();
+          const int ncol = n_blk * BN + c;
+          if (row < M) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + ncol;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (ncol + j * 8 < N) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const int e = j * 8 + i * 2;
+                    float a = __uint_as_float(r[e]), b = __uint_as_float(r[e + 1]);
+                    if (bias) { a += bias[ncol + e]; b += bias[ncol + e + 1]; }
+                    w[i] = pack_bf16x2(a, b);
+                  }
+                  *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              }
+          }
+        }
+      } else {  // LG_EPI_SWIGLU
         // W rows interleave 32 gate rows with the 32 matching up rows
         for (int c = 0; c < BN; c += 64) {
           uint32_t g[32], u[32];
@@ -260,51 +350,12 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             }
           }
         }
-      } else {
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tc_ld32(t_row + c, r);
-          tc_wait_ld();
-          const int ncol = n_blk * BN + c;
-          if (row < M) {
-            if (EPI == LG_EPI_BF16) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + ncol;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (ncol + j * 8 < N) {
-                  uint32_t w[4];
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const int e = j * 8 + i * 2;
-                    float a = __uint_as_float(r[e]), b = __uint_as_float(r[e + 1]);
-                    if (bias) { a += bias[ncol + e]; b += bias[ncol + e + 1]; }
-                    w[i] = pack_bf16x2(a, b);
-                  }
-                  *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-              }
-            } else {  // LG_EPI_RESID_F32
-              float* dst = reinterpret_cast<float*>(out) + (size_t)row * ldc + ncol;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (ncol + j * 4 < N) {
-                  float4 v = *reinterpret_cast<float4*>(dst + j * 4);
-                  const int e = j * 4;
-                  float a0 = __uint_as_float(r[e]), a1 = __uint_as_float(r[e + 1]);
-                  float a2 = __uint_as_float(r[e + 2]), a3 = __uint_as_float(r[e + 3]);
-                  if (bias) { a0 += bias[ncol + e]; a1 += bias[ncol + e + 1]; a2 += bias[ncol + e + 2]; a3 += bias[ncol + e + 3]; }
-                  v.x += a0; v.y += a1; v.z += a2; v.w += a3;
-                  *reinterpret_cast<float4*>(dst + j * 4) = v;
-                }
-              }
-            }
-          }
-        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
     }
+    if (lane == 0) bulk_wait_all();  // every slab has left shared memory and landed before the CTA retires
   }
 
   // ---------------- teardown ----------------
@@ -360,16 +411,19 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows, cols] with row stride ld (elements); box = [box_rows, 64 cols]
-bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+// 2-D tensor [rows, cols] with row stride ld (elements); box = [box_rows, 128 bytes of columns],
+// 128-byte swizzle. Operands are bf16 (64 columns per box row); the fp32 output map has 32.
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+              bool f32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
+  const uint64_t esz = f32 ? 4 : 2;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint64_t strides[1] = {ld * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -386,15 +440,20 @@ int sm_count() {
 template <int BN, int EPI>
 uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, int m, int n, int k, int lda,
                     int ldc, int* status, cudaStream_t stream) {
-  CUtensorMap ma, mw;
+  CUtensorMap ma, mw, mo;
   if (!make_map(&ma, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM)) return lg::kInvalidValue;
   if (!make_map(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)k, BN)) return lg::kInvalidValue;
+  if (EPI == LG_EPI_RESID_F32) {  // fp32 [m, n] in 32 x 32 boxes for the reduce-add epilogue
+    if (!make_map(&mo, out, (uint64_t)m, (uint64_t)n, (uint64_t)ldc, 32, true)) return lg::kInvalidValue;
+  } else {
+    mo = ma;  // unused by the direct-store epilogues
+  }
   auto kern = linear_t_tcgen05_kernel<BN, EPI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmem);
   if (e != cudaSuccess) return (uint32_t)e;
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, bias, out, m, n, k, ldc, status);
+  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, mo, bias, out, m, n, k, ldc, status);
   return lg::launch_status();
 }
 

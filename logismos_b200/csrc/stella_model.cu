@@ -66,7 +66,7 @@ struct Stella {
   std::vector<Layer> layers;
   DevBuf head_w[8], head_b[8];
   // workspace
-  DevBuf x, h, qkv, attn, gu, act, hidden_out, ids, pos, cu, out, status;
+  DevBuf x, h, qkv, attn, gu, act, hidden_out, pooled, ids, pos, cu, out, status;
   // pinned staging
   uint32_t* h_ids = nullptr;
   int32_t* h_pos = nullptr;
@@ -131,8 +131,8 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
     LG_TRY(logismos_launch_linear_t_bf16(m->act.p, L.wdown.p, nullptr, m->x.p, T, H, I, I, H, LG_EPI_RESID_F32, st, s), "down_proj");
   }
   LG_TRY(logismos_launch_rms_norm_f32(m->x.p, m->final_norm.p, m->hidden_out.p, T, H, c.rms_eps, 1, s), "final_norm");
-  LG_TRY(logismos_launch_pool_head_f32(m->hidden_out.p, cu, m->head_w[dim_idx].p, m->head_b[dim_idx].p, out, n_seqs, H,
-                                       c.dims[dim_idx], s), "pool_head");
+  LG_TRY(logismos_launch_pool_head_f32(m->hidden_out.p, cu, m->head_w[dim_idx].p, m->head_b[dim_idx].p, out, m->pooled.p,
+                                       n_seqs, H, c.dims[dim_idx], s), "pool_head");
   return LG_EMB_OK;
 }
 
@@ -217,7 +217,7 @@ uint32_t lg_stella_create(int32_t device, const lg_stella_config_t* cfg, const l
   int max_dim = 0;
   for (int i = 0; i < c.n_dims; ++i) max_dim = c.dims[i] > max_dim ? c.dims[i] : max_dim;
   ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
-       m->gu.alloc(c.fuse_swiglu ? 16 : T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->hidden_out.alloc(T * H * 4) &&
+       m->gu.alloc(c.fuse_swiglu ? 16 : T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->hidden_out.alloc(T * H * 4) && m->pooled.alloc(S * H * 4) &&
        m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->cu.alloc((S + 1) * 4) && m->out.alloc(S * max_dim * 4) &&
        m->status.alloc(4);
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
@@ -239,7 +239,7 @@ void lg_stella_destroy(void* model) {
   Stella* m = static_cast<Stella*>(model);
   cudaSetDevice(m->device);
   DevBuf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->x, &m->h, &m->qkv, &m->attn, &m->gu,
-                    &m->act, &m->hidden_out, &m->ids, &m->pos, &m->cu, &m->out, &m->status};
+                    &m->act, &m->hidden_out, &m->pooled, &m->ids, &m->pos, &m->cu, &m->out, &m->status};
   for (DevBuf* b : bufs) b->release();
   for (auto& L : m->layers) {
     L.norm1.release(); L.norm2.release(); L.wqkv.release(); L.bqkv.release(); L.wo.release(); L.wgu.release(); L.wdown.release();
@@ -262,7 +262,7 @@ int32_t lg_stella_supported_dims(const void* model, int32_t* out, int32_t cap) {
 int32_t lg_stella_max_tokens(const void* model) { return static_cast<const Stella*>(model)->cfg.max_tokens; }
 int32_t lg_stella_launches_per_forward(const void* model) {
   const Stella* m = static_cast<const Stella*>(model);
-  return 1 + m->cfg.n_layers * (m->cfg.fuse_swiglu ? 8 : 9) + 2;
+  return 1 + m->cfg.n_layers * (m->cfg.fuse_swiglu ? 8 : 9) + 4;
 }
 
 uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* dev_cu, const void* dev_pos,

@@ -204,8 +204,9 @@ def pool_head(hidden, cu_seqlens, head_w, head_b, sync=True):
     _req(head_w, "head_w", torch.bfloat16, 2); _req(head_b, "head_b", torch.float32, 1)
     n_seqs = cu_seqlens.shape[0] - 1
     out = torch.empty((n_seqs, head_w.shape[0]), dtype=torch.float32, device=hidden.device)
+    scratch = torch.empty((n_seqs, hidden.shape[1]), dtype=torch.float32, device=hidden.device)
     with torch.cuda.device(hidden.device):
-        check(lib.logismos_launch_pool_head_f32(_p(hidden), _p(cu_seqlens), _p(head_w), _p(head_b), _p(out), n_seqs, hidden.shape[1],
+        check(lib.logismos_launch_pool_head_f32(_p(hidden), _p(cu_seqlens), _p(head_w), _p(head_b), _p(out), _p(scratch), n_seqs, hidden.shape[1],
                                                 head_w.shape[0], _stream()), "pool_head")
         _done(sync)
     return out
