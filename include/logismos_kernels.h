@@ -220,6 +220,23 @@ uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, co
                                          const void* beta_f32, void* o_bf16, int32_t n_seqs,
                                          int32_t heads, float scale, void* stream);
 
+/* gated_delta_rule_chunk_fwd / recurrent_fwd over a ragged batch (cpu.rs:92-249): sequence i owns
+ * token rows cu_seqlens[i] .. cu_seqlens[i+1] of q, k, v bf16 [n_tokens, heads, 128], g, beta f32
+ * [n_tokens, heads]; state f32 [n_seqs, heads, 128, 128] is the initial state on entry and the
+ * final state on return; o bf16 [n_tokens, heads, 128]. Tokens are processed in order. */
+uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const void* k_bf16,
+                                     const void* v_bf16, const void* g_f32, const void* beta_f32,
+                                     void* o_bf16, const void* cu_seqlens_i32, int32_t n_seqs,
+                                     int32_t heads, float scale, void* stream);
+/* Inputs of the recurrence from the layer's projections (no reference code; the formulas are
+ * those of research/14-gdn-aiter-preflight.md:190-198, :209-219): q, k bf16 [n_tokens, heads, 128]
+ * are L2-normalised per head row in place (l2_norm_in_place, cpu.rs:19-34);
+ * g = -exp(A_log[h]) * softplus(a + dt_bias[h]) (softplus(x) = x for x > 20), beta = sigmoid(b),
+ * a, b, g, beta f32 [n_tokens, heads], A_log, dt_bias f32 [heads]. */
+uint32_t logismos_launch_gdn_prepare(void* q_bf16, void* k_bf16, const void* a_f32, const void* b_f32,
+                                     const void* A_log_f32, const void* dt_bias_f32, void* g_f32,
+                                     void* beta_f32, int32_t n_tokens, int32_t heads, void* stream);
+
 /* decode::greedy (crates/decode/src/lib.rs:73-83): argmax per row, first maximum wins, NaN
  * never selected. logits bf16 or f32 [rows, n]; out u32 [rows]. */
 uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, void* out_u32,

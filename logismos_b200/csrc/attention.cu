@@ -141,7 +141,7 @@ LG_DEVINL void stage_rows(uint32_t sbase, uint8_t* sgen, const __nv_bfloat16* sr
 }
 
 template <bool CAUSAL>
-__global__ void __launch_bounds__(kVarlenThreads)
+__global__ void __launch_bounds__(kVarlenThreads, 3)
 varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu,
                         __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int row_stride,
                         int k_off, int v_off, float sl2) {
@@ -154,9 +154,11 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
 
-  uint8_t* sq = smem;                       // 16 KB
-  uint8_t* sk[2] = {smem + 16384, smem + 49152};
-  uint8_t* sv[2] = {smem + 32768, smem + 65536};
+  // two K/V tile buffers of 16 KB + 16 KB; the query tile is staged in the second buffer's K half
+  // and lives in registers from then on, so 64 KB per CTA (three CTAs per SM)
+  uint8_t* sk[2] = {smem, smem + 32768};
+  uint8_t* sv[2] = {smem + 16384, smem + 49152};
+  uint8_t* sq = sk[1];
   const uint32_t sq_a = smem_u32(sq);
   const uint32_t sk_a[2] = {smem_u32(sk[0]), smem_u32(sk[1])};
   const uint32_t sv_a[2] = {smem_u32(sv[0]), smem_u32(sv[1])};
@@ -181,6 +183,11 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
     for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
+  cp_async_wait<0>();
+  __syncthreads();
+  load_q_frags(sq_a + warp * 16 * kRowBytes, lane, qf);
+  __syncthreads();  // the query tile's buffer is free for K/V tile 1 from here on
+
   for (int it = 0; it < n_tiles; ++it) {
     const int buf = it & 1;
     if (it + 1 < n_tiles) {
@@ -192,7 +199,6 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (it == 0) load_q_frags(sq_a + warp * 16 * kRowBytes, lane, qf);
 
     float s[8][4];
     qk_tile<8>(qf, sk_a[buf], 0, lane, s);
@@ -502,7 +508,7 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv, const void* cu_s
       (row_stride % 8) || (k_off % 8) || (v_off % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
     return lg::kInvalidValue;
   if (n_seqs == 0 || max_seqlen == 0) return 0;
-  const size_t smem = 16384 + 4 * 16384;
+  const size_t smem = 4 * 16384;
   const float sl2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid((max_seqlen + kQTile - 1) / kQTile, n_heads, n_seqs);
   cudaError_t e;

@@ -9,7 +9,7 @@
 //   embed -> per layer [ rms_norm -> QKV (int4 weights) + bias -> RoPE at each token's position ->
 //   K/V rows scattered into the paged cache by slot mapping -> attention: paged decode kernel for
 //   the decode rows, ragged causal attention for the prefill rows -> o_proj + residual ->
-//   rms_norm -> gate/up -> SwiGLU -> down + residual ] -> last token rows -> final norm ->
+//   rms_norm -> gate/up with SwiGLU fused in the GEMM epilogue -> down + residual ] -> last token rows -> final norm ->
 //   lm_head (int4 GEMV) -> greedy argmax.
 // Contractions over the packed rows run on the tcgen05 GEMM over a per-layer bf16 expansion of the
 // int4 codes; the lm_head, whose batch is the number of sequences, runs on the int4 GEMV kernel.
@@ -77,6 +77,23 @@ struct Decoder {
   std::vector<int> order;  // internal slot -> caller's sequence index
   size_t max_chunks = 0;
 };
+
+// gate and up rows interleaved in blocks of 32 (32 gate rows, then the 32 matching up rows), the
+// row order the fused SwiGLU epilogue of the GEMM expects
+bool upload_q_gate_up(QMat& q, const lg_int4_matrix_t& gate, const lg_int4_matrix_t& up, int inter, int k) {
+  const size_t cb = (size_t)32 * (k / 2), sb = (size_t)32 * (k / 32);
+  std::vector<uint8_t> codes((size_t)2 * inter * (k / 2));
+  std::vector<uint16_t> scales((size_t)2 * inter * (k / 32));
+  for (int b = 0; b < inter / 32; ++b) {
+    std::memcpy(codes.data() + (size_t)(2 * b) * cb, gate.codes + (size_t)b * cb, cb);
+    std::memcpy(codes.data() + (size_t)(2 * b + 1) * cb, up.codes + (size_t)b * cb, cb);
+    std::memcpy(scales.data() + (size_t)(2 * b) * sb, gate.scales + (size_t)b * sb, sb * 2);
+    std::memcpy(scales.data() + (size_t)(2 * b + 1) * sb, up.scales + (size_t)b * sb, sb * 2);
+  }
+  q.n = 2 * inter;
+  q.k = k;
+  return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
+}
 
 bool upload_q(QMat& q, const std::vector<const lg_int4_matrix_t*>& parts, const std::vector<int>& rows, int k) {
   size_t n = 0;
@@ -149,10 +166,9 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
     }
     if (uint32_t rc = qlinear(m, m->attn.p, L.wo, nullptr, m->x.p, T, H, H, LG_EPI_RESID_F32, s)) return rc;
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
-    if (uint32_t rc = qlinear(m, m->h.p, L.wgu, nullptr, m->gu.p, T, H, 2 * I, LG_EPI_BF16, s)) return rc;
-    LG_TRY(logismos_launch_swiglu_bf16(m->gu.p, m->act.p, T, I, s), "swiglu");
+    if (uint32_t rc = qlinear(m, m->h.p, L.wgu, nullptr, m->act.p, T, H, I, LG_EPI_SWIGLU, s)) return rc;
     if (uint32_t rc = qlinear(m, m->act.p, L.wdown, nullptr, m->x.p, T, I, H, LG_EPI_RESID_F32, s)) return rc;
-    m->launches += 2;
+    m->launches += 1;
   }
   LG_TRY(logismos_launch_gather_rows_f32(m->x.p, m->last_idx.p, m->last.p, m->n_seqs, H, T, st, s), "gather_rows");
   LG_TRY(logismos_launch_rms_norm_f32(m->last.p, m->final_norm.p, m->last_bf16.p, m->n_seqs, H, c.rms_eps, 0, s), "final_norm");
@@ -212,7 +228,7 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
     ok = ok && L.bqkv.upload(b.data(), QKV * 4);
     ok = ok && upload_q(L.wqkv, {&lw.wq, &lw.wk, &lw.wv}, {(int)H, (int)KV, (int)KV}, (int)H);
     ok = ok && upload_q(L.wo, {&lw.wo}, {(int)H}, (int)H);
-    ok = ok && upload_q(L.wgu, {&lw.w_gate, &lw.w_up}, {(int)I, (int)I}, (int)H);
+    ok = ok && upload_q_gate_up(L.wgu, lw.w_gate, lw.w_up, (int)I, (int)H);
     ok = ok && upload_q(L.wdown, {&lw.w_down}, {(int)H}, (int)I);
     ok = ok && L.kpool.alloc(pool_bytes) && L.vpool.alloc(pool_bytes);
     ok = ok && cudaMemset(L.kpool.p, 0, pool_bytes) == cudaSuccess && cudaMemset(L.vpool.p, 0, pool_bytes) == cudaSuccess;
@@ -234,7 +250,7 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
   // every sequence of a step may be a decode sequence of up to max_blocks_per_seq blocks
   m->max_chunks = S * ((MB * kBlock + kChunkTokens - 1) / kChunkTokens);
   ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
-       m->qdec.alloc(S * H * 2) && m->gu.alloc(T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) &&
+       m->qdec.alloc(S * H * 2) && m->gu.alloc(16) && m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) &&
        m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) && m->logits.alloc(S * (size_t)c.vocab * 2) &&
        m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->slots.alloc(T * 8) &&
        m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&

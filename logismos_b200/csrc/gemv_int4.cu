@@ -244,94 +244,109 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
   const int first_tile = blockIdx.x * nwarps + warp;
   const int my_tiles = first_tile < row_tiles ? (row_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
   const int total_steps = my_tiles * iters;
+  const uint32_t ring_end = ring + STAGES * kSlotBytes;
 
-  // producer state: flattened step -> (tile, it)
-  int p_step = 0, p_tile = first_tile, p_it = 0;
+  // ---- producer: runs STAGES-1 steps ahead of the consumer, across row-tile boundaries. All
+  // addresses advance by constants inside a tile; they are rebuilt only when the tile changes.
+  int p_left = total_steps, p_it = 0, p_tile = first_tile;
+  uint32_t p_slot = ring;
+  const uint8_t *pw0, *pw1;
+  const __half* ps;
+  auto producer_tile = [&](int tile) {
+    const int rb = tile * 16;
+    pw0 = codes + (size_t)min(rb + g, N - 1) * (K / 2) + c * 16;
+    pw1 = codes + (size_t)min(rb + g + 8, N - 1) * (K / 2) + c * 16;
+    ps = scales + (size_t)min(rb + (lane & 15), N - 1) * groups;
+  };
+  producer_tile(p_tile);
+  const uint32_t dst_w = (uint32_t)(g * kWPitch + c * 16), dst_s = (uint32_t)(16 * kWPitch + (lane & 15) * 8);
   auto issue = [&]() {
-    if (p_step < total_steps) {
-      const uint32_t slot = ring + (uint32_t)(p_step % STAGES) * kSlotBytes;
-      const int row_base = p_tile * 16;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int rl = g + 8 * h;
-        const int r = min(row_base + rl, N - 1);
-        cp_async16(slot + rl * kWPitch + c * 16, codes + (size_t)r * (K / 2) + p_it * 64 + c * 16);
-      }
-      if (lane < 16) {
-        const int r = min(row_base + lane, N - 1);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(slot + 16 * kWPitch + lane * 8),
-                     "l"(scales + (size_t)r * groups + p_it * 4));
-      }
-      ++p_step;
-      if (++p_it == iters) { p_it = 0; p_tile += tile_stride; }
+    if (p_left > 0) {
+      cp_async16(p_slot + dst_w, pw0);
+      cp_async16(p_slot + dst_w + 8 * kWPitch, pw1);
+      if (lane < 16) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(p_slot + dst_s), "l"(ps));
+      pw0 += 64; pw1 += 64; ps += 4;
+      p_slot += kSlotBytes;
+      if (p_slot == ring_end) p_slot = ring;
+      --p_left;
+      if (++p_it == iters) { p_it = 0; p_tile += tile_stride; producer_tile(p_tile); }
     }
     cp_async_commit();
   };
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) issue();
 
-  float acc[NT][4];
-  int c_tile = first_tile, c_it = 0;
+  // ---- consumer
   const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: lanes 8j..8j+7 address the rows of matrix j (= group j)
-  for (int step = 0; step < total_steps; ++step) {
-    if (c_it == 0) {
+  const uint32_t ld_off0 = (uint32_t)(mr * kWPitch + mat * 16), ld_off1 = ld_off0 + 8 * kWPitch;
+  const uint32_t sc_off0 = (uint32_t)(16 * kWPitch + g * 8), sc_off1 = sc_off0 + 64;
+  const uint32_t xs_a = smem_u32(xs) + (uint32_t)(g * xrow_stride + c * 16);
+  const uint32_t nc_a = smem_u32(negcorr) + (uint32_t)(2 * c * 4);
+  uint32_t c_slot = ring;
+  int c_tile = first_tile;
+  for (int t = 0; t < my_tiles; ++t, c_tile += tile_stride) {
+    float acc[NT][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
-    }
-    issue();
-    cp_async_wait<STAGES - 1>();
-    __syncwarp();
-    const uint32_t slot = ring + (uint32_t)(step % STAGES) * kSlotBytes;
-    uint32_t w0[4], w1[4];
-    ldmatrix_x4(w0, slot + mr * kWPitch + mat * 16);
-    ldmatrix_x4(w1, slot + (8 + mr) * kWPitch + mat * 16);
-    const uint8_t* sgen = ring_gen + (size_t)(step % STAGES) * kSlotBytes + 16 * kWPitch;
-    const uint2 s0r = *reinterpret_cast<const uint2*>(sgen + g * 8);
-    const uint2 s1r = *reinterpret_cast<const uint2*>(sgen + (g + 8) * 8);
-    const float2 s0a = __half22float2(*reinterpret_cast<const __half2*>(&s0r.x));
-    const float2 s0b = __half22float2(*reinterpret_cast<const __half2*>(&s0r.y));
-    const float2 s1a = __half22float2(*reinterpret_cast<const __half2*>(&s1r.x));
-    const float2 s1b = __half22float2(*reinterpret_cast<const __half2*>(&s1r.y));
-    const float sc0[4] = {s0a.x, s0a.y, s0b.x, s0b.y};
-    const float sc1[4] = {s1a.x, s1a.y, s1b.x, s1b.y};
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+    uint32_t xa = xs_a, na = nc_a;
+    for (int it = 0; it < iters; ++it) {
+      issue();
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+      uint32_t w0[4], w1[4];
+      ldmatrix_x4(w0, c_slot + ld_off0);
+      ldmatrix_x4(w1, c_slot + ld_off1);
+      uint32_t s0x, s0y, s1x, s1y;
+      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(s0x), "=r"(s0y) : "r"(c_slot + sc_off0));
+      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(s1x), "=r"(s1y) : "r"(c_slot + sc_off1));
+      const float2 s0a = __half22float2(*reinterpret_cast<const __half2*>(&s0x));
+      const float2 s0b = __half22float2(*reinterpret_cast<const __half2*>(&s0y));
+      const float2 s1a = __half22float2(*reinterpret_cast<const __half2*>(&s1x));
+      const float2 s1b = __half22float2(*reinterpret_cast<const __half2*>(&s1y));
+      const float sc0[4] = {s0a.x, s0a.y, s0b.x, s0b.y};
+      const float sc1[4] = {s1a.x, s1a.y, s1b.x, s1b.y};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int G = c_it * 4 + j;
-      const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0[j] >> 4), nib_pair_bf16(w1[j] >> 4)};
-      const uint32_t a_hi[4] = {nib_pair_bf16(w0[j] >> 8), nib_pair_bf16(w1[j] >> 8), nib_pair_bf16(w0[j] >> 12), nib_pair_bf16(w1[j] >> 12)};
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0[j] >> 4), nib_pair_bf16(w1[j] >> 4)};
+        const uint32_t a_hi[4] = {nib_pair_bf16(w0[j] >> 8), nib_pair_bf16(w1[j] >> 8), nib_pair_bf16(w0[j] >> 12), nib_pair_bf16(w1[j] >> 12)};
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const uint4 bx = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * xrow_stride + G * 64 + c * 16);
-        const float2 nc = *reinterpret_cast<const float2*>(negcorr + G * (NT * 8) + nt * 8 + 2 * c);
-        float d[4] = {nc.x, nc.y, nc.x, nc.y};
-        const uint32_t b_lo[2] = {bx.x, bx.y}, b_hi[2] = {bx.z, bx.w};
-        mma_bf16_16816(d, a_lo, b_lo, d);
-        mma_bf16_16816(d, a_hi, b_hi, d);
-        acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
-        acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
-        acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
-        acc[nt][3] = fmaf(sc1[j], d[3], acc[nt][3]);
-      }
-    }
-    __syncwarp();  // every lane is done with the slot before a later issue() refills it
-    if (++c_it == iters) {
-      const int ra = c_tile * 16 + g, rb = ra + 8;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int b0 = nt * 8 + 2 * c;
-        if (ra < N) {
-          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[nt][0]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[nt][1]);
-        }
-        if (rb < N) {
-          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[nt][2]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[nt][3]);
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t b_lo[2], b_hi[2];
+          float d[4];
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                       : "=r"(b_lo[0]), "=r"(b_lo[1]), "=r"(b_hi[0]), "=r"(b_hi[1])
+                       : "r"(xa + (uint32_t)(nt * 8 * xrow_stride + j * 64)));
+          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];\n" : "=f"(d[0]), "=f"(d[1]) : "r"(na + (uint32_t)((j * NT * 8 + nt * 8) * 4)));
+          d[2] = d[0];
+          d[3] = d[1];
+          mma_bf16_16816(d, a_lo, b_lo, d);
+          mma_bf16_16816(d, a_hi, b_hi, d);
+          acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
+          acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
+          acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
+          acc[nt][3] = fmaf(sc1[j], d[3], acc[nt][3]);
         }
       }
-      c_it = 0;
-      c_tile += tile_stride;
+      __syncwarp();  // every lane is done with the slot before a later issue() refills it
+      c_slot += kSlotBytes;
+      if (c_slot == ring_end) c_slot = ring;
+      xa += 4 * 64;
+      na += 4 * NT * 8 * 4;
+    }
+    const int ra = c_tile * 16 + g, rb = ra + 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int b0 = nt * 8 + 2 * c;
+      if (ra < N) {
+        if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[nt][0]);
+        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[nt][1]);
+      }
+      if (rb < N) {
+        if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[nt][2]);
+        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[nt][3]);
+      }
     }
   }
   cp_async_wait<0>();
@@ -356,8 +371,21 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
   if (row_tiles < 2 * sms) return false;  // too few row tiles per SM: the k-split kernel spreads better
   const int groups = K / kGroup;
   const size_t xbytes = (size_t)NT * 8 * (groups * 64 + 64) + (size_t)groups * NT * 8 * 4;
+  // warps per CTA: enough to keep ~48 KB of weights in flight per SM, and among those counts the one
+  // that leaves the least idle tail (every warp gets floor or ceil of tiles / (grid * warps))
   int warps = (row_tiles + sms - 1) / sms;
   warps = warps < 2 ? 2 : (warps > 16 ? 16 : warps);
+  if (warps > 8) {
+    double best_eff = -1.0;
+    int best_w = warps;
+    for (int wv = 16; wv >= 10; --wv) {
+      const long slots = (long)sms * wv;
+      const long per = (row_tiles + slots - 1) / slots;
+      const double eff = (double)row_tiles / (double)(per * slots);
+      if (eff > best_eff + 1e-9) { best_eff = eff; best_w = wv; }
+    }
+    warps = best_w;
+  }
   const bool deep = warps <= 8;
   const int stages = deep ? 8 : 4;
   size_t smem = xbytes + (size_t)warps * stages * kSlotBytes;

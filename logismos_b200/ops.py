@@ -313,6 +313,33 @@ def gdn_decode_step_(state, q, k, v, g, beta, scale, sync=True):
     return o
 
 
+def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, sync=True):
+    """Gated delta rule over a ragged batch; q, k, v bf16 [T, heads, 128]; state updated in place."""
+    _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
+    _req(v, "v", torch.bfloat16, 3); _req(g, "g", torch.float32, 2); _req(beta, "beta", torch.float32, 2)
+    _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    if tuple(state.shape[2:]) != (128, 128) or state.shape[0] != cu_seqlens.shape[0] - 1:
+        raise InvalidOp("gdn_prefill: state must be [n_seqs, heads, 128, 128]")
+    o = torch.empty_like(v)
+    with torch.cuda.device(state.device):
+        check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(cu_seqlens), state.shape[0],
+                                              state.shape[1], float(scale), _stream()), "gdn_prefill")
+        _done(sync)
+    return o
+
+
+def gdn_prepare_(q, k, a, b, A_log, dt_bias, sync=True):
+    """L2-normalises q, k head rows in place and returns (g, beta) fp32 [T, heads]."""
+    _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3); _req(a, "a", torch.float32, 2); _req(b, "b", torch.float32, 2)
+    _req(A_log, "A_log", torch.float32, 1); _req(dt_bias, "dt_bias", torch.float32, 1)
+    g = torch.empty_like(a); beta = torch.empty_like(a)
+    with torch.cuda.device(q.device):
+        check(lib.logismos_launch_gdn_prepare(_p(q), _p(k), _p(a), _p(b), _p(A_log), _p(dt_bias), _p(g), _p(beta), q.shape[0], q.shape[1],
+                                              _stream()), "gdn_prepare")
+        _done(sync)
+    return g, beta
+
+
 def greedy(logits, sync=True):
     """decode::greedy per row: first maximum wins, NaN never selected."""
     if logits.dtype not in (torch.float32, torch.bfloat16):

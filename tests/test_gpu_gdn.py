@@ -41,3 +41,33 @@ def test_zero_beta_only_decays_the_state():  # cpu.rs:296-313
     one, _ = bf16_cuda(np.ones((1, 1, 128)))
     ops.gdn_decode_step_(st, one, one, one, torch.zeros((1, 1), device=DEV), torch.zeros((1, 1), device=DEV), 1.0)
     assert (to_np(st) == st0).all()
+
+
+def test_ragged_prefill_matches_chunk_reference_and_continues_into_decode():
+    rng = np.random.default_rng(3)
+    heads, D = 3, 128
+    lens = [37, 1, 130]
+    T = sum(lens)
+    cu = np.zeros(4, np.int32); cu[1:] = np.cumsum(lens)
+    q_t, _ = bf16_cuda(rng.standard_normal((T, heads, D))); k_t, _ = bf16_cuda(rng.standard_normal((T, heads, D)))
+    v_t, v = bf16_cuda(rng.standard_normal((T, heads, D)))
+    a = rng.standard_normal((T, heads)).astype(np.float32); b = rng.standard_normal((T, heads)).astype(np.float32)
+    A_log = rng.uniform(-1, 0.5, heads).astype(np.float32); dt_bias = rng.standard_normal(heads).astype(np.float32)
+    # gates and q/k normalisation on the GPU against the oracle
+    g_t, beta_t = ops.gdn_prepare_(q_t, k_t, torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV),
+                                   torch.from_numpy(A_log).to(DEV), torch.from_numpy(dt_bias).to(DEV))
+    g_ref, beta_ref = O.gdn_gates(a, b, A_log, dt_bias)
+    assert np.abs(to_np(g_t) - g_ref).max() <= 1e-5 * max(1, np.abs(g_ref).max()) and np.abs(to_np(beta_t) - beta_ref).max() <= 1e-6
+    q, k = to_np(q_t), to_np(k_t)
+    assert np.abs(np.linalg.norm(q, axis=-1) - 1).max() < 1e-2
+    state0 = (rng.standard_normal((3, heads, D, D)) * 0.05).astype(np.float32)
+    st = torch.from_numpy(state0.copy()).to(DEV)
+    o = to_np(ops.gdn_prefill_(st, q_t, k_t, v_t, g_t, beta_t, torch.from_numpy(cu).to(DEV), D ** -0.5))
+    g_np, beta_np = to_np(g_t), to_np(beta_t)
+    final = to_np(st)
+    for s in range(3):
+        sl = slice(cu[s], cu[s + 1])
+        for h in range(heads):
+            o_ref, states = O.gdn_chunk_fwd(q[sl, h], k[sl, h], v[sl, h], beta_np[sl, h], g_np[sl, h], D ** -0.5, state0[s, h], D, D, 64)
+            assert max_rel(o[sl, h], o_ref.reshape(-1, D)) <= 2e-2
+            assert max_rel(final[s, h], states[-1].reshape(D, D)) <= 1e-4
