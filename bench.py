@@ -362,23 +362,137 @@ def run_ragged_step(args, rank, world, local_rank):
                           "next_tokens_sample": [int(t) for t in toks[:4]]}))
 
 
+def run_serving_sweep(args, rank, world, local_rank):
+    """Serving sweep of the hybrid decoder (the benchmark's last configuration): 48 layers, three
+    gated-delta-rule linear-attention layers (16 heads of 128, fp32 state) per gated full-attention
+    layer (16 query / 2 KV heads of 256, paged KV cache), hidden 2048, SwiGLU 6144, vocab 151936, int4
+    group-32 random weights. Requests: prompt lengths lognormal (median 1024, sigma 1, capped at
+    16384), output lengths uniform in [64, 1024], seeded Poisson arrivals; request-sharded round-robin
+    over the ranks (every rank holds a full replica; no data-path collective). --requests is the
+    number of requests PER GPU (the full configuration has 4096 in total; the default is a bounded
+    sample of the same distributions so the run ends within minutes). One step = one scheduler
+    step (every running sequence decodes one token, admitted prompts are prefilled whole); the value
+    is generated tokens per second over the timed steps through the host-buffer entry point (each
+    step copies its ids and index arrays to the device and its tokens back)."""
+    import torch
+    import torch.distributed as dist
+    from hybrid_weights import HYBRID_SERVING
+    from logismos_b200.hybrid import HybridModel
+    from logismos_b200.serving import Scheduler, shard_requests, synthetic_load
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = dict(HYBRID_SERVING)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    rng = np.random.Generator(np.random.PCG64(17))
+    H, I, GH = cfg["hidden"], cfg["intermediate"], cfg["gdn_heads"]
+    QW, KW, GW = cfg["n_heads"] * cfg["attn_head_dim"], cfg["n_kv_heads"] * cfg["attn_head_dim"], GH * 128
+
+    def qmat(n, k):
+        return (rng.integers(0, 256, (n, k // 2), dtype=np.uint8),
+                np.abs(rng.standard_normal((n, k // 32), dtype=np.float32) * (0.25 / np.sqrt(k))).astype(np.float16))
+
+    mlp = {"w_gate": qmat(I, H), "w_up": qmat(I, H), "w_down": qmat(H, I), "norm1": np.ones(H, np.float32), "norm2": np.ones(H, np.float32)}
+    full = dict(mlp, wq=qmat(QW, H), wgate=qmat(QW, H), wk=qmat(KW, H), wv=qmat(KW, H), wo=qmat(H, QW))
+    lin = dict(mlp, wq=qmat(GW, H), wk=qmat(GW, H), wv=qmat(GW, H), wgate=qmat(GW, H), wo=qmat(H, GW), wa=qmat(GH, H), wb=qmat(GH, H),
+               A_log=np.log(rng.uniform(0.5, 4.0, GH)).astype(np.float32), dt_bias=rng.uniform(-3.0, 0.0, GH).astype(np.float32))
+    w = {"tok_embed": rng.standard_normal((cfg["vocab"], H), dtype=np.float32) * np.float32(0.5), "final_norm": np.ones(H, np.float32),
+         "lm_head": qmat(cfg["vocab"], H),
+         "layers": [full if (l + 1) % cfg["full_attn_interval"] == 0 else lin for l in range(cfg["n_layers"])]}
+    n_req = args.requests
+    reqs = shard_requests(synthetic_load(n_req * world, 4096, cfg["vocab"], rate_per_s=args.arrival_rate * world), world, rank)
+    max_seqs = min(args.max_seqs, n_req)
+    max_blocks = (16384 + 1024 + 15) // 16
+    lifetime = sorted((-(-(len(r.prompt) + r.max_new) // 16) for r in reqs), reverse=True)
+    n_pool = int(sum(lifetime[:max_seqs])) + 8
+    step_tokens = 16384 + max_seqs
+    model = HybridModel(cfg, w, n_pool_blocks=n_pool, max_blocks_per_seq=max_blocks, max_step_tokens=step_tokens, max_step_seqs=max_seqs,
+                        n_state_slots=max_seqs, device=local_rank)
+    sched = Scheduler(n_pool, max_blocks, max_seqs, step_tokens, max_seqs, prefill_token_budget=args.prefill_budget)
+    for r in reqs:
+        sched.add(r)
+    launches = h2d = 0
+    steps = dec_tokens = pre_tokens = gen = 0
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_start = time.perf_counter()
+    t_timed = None
+    step_ms = []
+    while not sched.idle() and (args.steps <= 0 or steps < warm + args.steps):
+        if steps == warm:
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t_timed = time.perf_counter()
+            gen = dec_tokens = pre_tokens = launches = h2d = 0
+        now = time.perf_counter() - t_start
+        plan = sched.plan(now)
+        if plan is None:
+            continue
+        t0 = time.perf_counter()
+        toks = model.step(plan.ids, plan.cached, plan.new, plan.tables, plan.slots)
+        step_ms.append((1e3 * (time.perf_counter() - t0), plan.n_decode, plan.n_prefill_tokens))
+        sched.commit(plan, toks, time.perf_counter() - t_start)
+        steps += 1
+        gen += len(plan.rids); dec_tokens += plan.n_decode; pre_tokens += plan.n_prefill_tokens
+        launches += model.launches_last_step()
+        h2d += int(plan.ids.size * 16 + len(plan.rids) * (max_blocks + 6) * 4)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - (t_timed if t_timed is not None else t_start)
+    timed_steps = max(steps - warm, 0) if t_timed is not None else steps
+    clocks = sampler.stop() if rank == 0 else None
+    status = model.device_status()
+    tt = torch.tensor([dt, float(gen), float(pre_tokens), float(timed_steps), float(launches)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        mx = tt.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tt, op=dist.ReduceOp.SUM)
+        dt = float(mx[0])
+    gen_all, pre_all, steps_all, launches_all = float(tt[1]), float(tt[2]), float(tt[3]), float(tt[4])
+    if rank == 0:
+        dec_only = [m for m, nd, npre in step_ms[warm:] if npre == 0]
+        line = {"metric": "hybrid_decoder_generated_tokens_per_s", "value": gen_all / dt, "unit": "tokens/s", "n_gpus": world,
+                "steps": int(steps_all / world), "warmup": warm, "ms_per_step": 1e3 * dt / max(timed_steps, 1), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, int4-g32 weights, fp32 recurrent state", "data": "synthetic",
+                "config": {"workload": "hybrid decoder serving sweep, %d requests per GPU (prompts lognormal median 1024 cap 16384, outputs U[64,1024], Poisson %.0f req/s per GPU), %d layers 3:1 linear:full attention" % (n_req, args.arrival_rate, cfg["n_layers"]),
+                           "max_concurrent_per_gpu": max_seqs, "kv_pool_blocks": n_pool, "inputs": "every step's working set (int4 weights, KV pool, recurrent states) exceeds L2"},
+                "e2e": {"value": gen_all / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / max(timed_steps, 1)), "d2h_bytes_per_step": int(4 * gen / max(timed_steps, 1))},
+                "gpu_launches": int(launches_all), "clocks": clocks, "device_status": status,
+                "prefill_tokens_per_s": pre_all / dt, "total_tokens_per_s": (pre_all + gen_all) / dt,
+                "decode_only_step_ms_median": float(np.median(dec_only)) if dec_only else None,
+                "requests_finished_rank0": len(sched.done), "sweep_complete": sched.idle()}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 20; serving_sweep: 0 = the whole sweep)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override depth (development only; the reported config is 28)")
     ap.add_argument("--no-micro", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
-    ap.add_argument("--workload", default="stella", choices=["stella", "ragged_step"])
+    ap.add_argument("--workload", default="stella", choices=["stella", "ragged_step", "serving_sweep"])
+    ap.add_argument("--requests", type=int, default=96, help="serving_sweep: requests per GPU")
+    ap.add_argument("--max-seqs", type=int, default=256, help="serving_sweep: concurrent sequences per GPU")
+    ap.add_argument("--arrival-rate", type=float, default=64.0, help="serving_sweep: Poisson arrivals per second per GPU")
+    ap.add_argument("--prefill-budget", type=int, default=8192, help="serving_sweep: prompt tokens admitted per step")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 0 if args.workload == "serving_sweep" else 20
     cfg = dict(STELLA_1_5B)
     if args.layers:
         cfg["n_layers"] = args.layers
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "ragged_step":
+    if args.workload == "serving_sweep":
+        run_serving_sweep(args, rank, world, local)
+    elif args.workload == "ragged_step":
         run_ragged_step(args, rank, world, local)
     elif args.impl == "reference":
         run_reference(args, cfg, rank, world)

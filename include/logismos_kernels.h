@@ -223,19 +223,32 @@ uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, co
 /* gated_delta_rule_chunk_fwd / recurrent_fwd over a ragged batch (cpu.rs:92-249): sequence i owns
  * token rows cu_seqlens[i] .. cu_seqlens[i+1] of q, k, v bf16 [n_tokens, heads, 128], g, beta f32
  * [n_tokens, heads]; state f32 [n_seqs, heads, 128, 128] is the initial state on entry and the
- * final state on return; o bf16 [n_tokens, heads, 128]. Tokens are processed in order. */
+ * final state on return; o bf16 [n_tokens, heads, 128]. Tokens are processed in order.
+ * q, k, v may be column blocks of a wider projection output: token t, head h starts at
+ * t * qkv_stride + h * 128 (elements). state_slots i32 [n_seqs] (may be NULL = identity) selects
+ * each sequence's slot in a state pool [n_slots, heads, 128, 128]; fresh u8 [n_seqs] (may be NULL)
+ * marks sequences that start here and therefore begin from the zero state. */
 uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const void* k_bf16,
                                      const void* v_bf16, const void* g_f32, const void* beta_f32,
-                                     void* o_bf16, const void* cu_seqlens_i32, int32_t n_seqs,
-                                     int32_t heads, float scale, void* stream);
+                                     void* o_bf16, const void* cu_seqlens_i32,
+                                     const void* state_slots_i32, const void* fresh_u8, int32_t n_seqs,
+                                     int32_t heads, int32_t qkv_stride, float scale, void* stream);
 /* Inputs of the recurrence from the layer's projections (no reference code; the formulas are
  * those of research/14-gdn-aiter-preflight.md:190-198, :209-219): q, k bf16 [n_tokens, heads, 128]
  * are L2-normalised per head row in place (l2_norm_in_place, cpu.rs:19-34);
  * g = -exp(A_log[h]) * softplus(a + dt_bias[h]) (softplus(x) = x for x > 20), beta = sigmoid(b),
- * a, b, g, beta f32 [n_tokens, heads], A_log, dt_bias f32 [heads]. */
+ * g, beta f32 [n_tokens, heads], A_log, dt_bias f32 [heads]. q, k rows start at
+ * t * qk_stride + h * 128; a, b are read at t * ab_stride + h (f32). */
 uint32_t logismos_launch_gdn_prepare(void* q_bf16, void* k_bf16, const void* a_f32, const void* b_f32,
                                      const void* A_log_f32, const void* dt_bias_f32, void* g_f32,
-                                     void* beta_f32, int32_t n_tokens, int32_t heads, void* stream);
+                                     void* beta_f32, int32_t n_tokens, int32_t heads,
+                                     int32_t qk_stride, int32_t ab_stride, void* stream);
+/* x[t, j] *= sigmoid(gate[t, j]) (mode 0) or silu(gate[t, j]) (mode 1), bf16 in place, fp32 math;
+ * rows of x and gate have their own strides (elements). The output gates of the hybrid decoder's
+ * attention and linear-attention layers. n % 8 == 0. */
+uint32_t logismos_launch_gated_mul_bf16(void* x_bf16, int32_t x_stride, const void* gate_bf16,
+                                        int32_t gate_stride, int32_t rows, int32_t n, int32_t mode,
+                                        void* stream);
 
 /* decode::greedy (crates/decode/src/lib.rs:73-83): argmax per row, first maximum wins, NaN
  * never selected. logits bf16 or f32 [rows, n]; out u32 [rows]. */

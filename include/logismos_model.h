@@ -151,6 +151,64 @@ uint32_t lg_decoder_last_logits(void* model, int32_t n_seqs, float* host_out);
 int32_t lg_decoder_launches_last_step(const void* model);
 int32_t lg_decoder_device_status(void* model);
 
+/* ====================================================================================
+ * Hybrid decoder step: a stack that mixes gated-delta-rule linear-attention layers (fp32 recurrent
+ * state per sequence, crates/kernels/src/gated_delta_rule/cpu.rs:92-182) with gated full-attention
+ * layers (paged KV cache, head_dim 128 or 256), SwiGLU MLPs, int4 group-32 weights. No reference
+ * counterpart (crates/decoders/src/lib.rs:1-15 is an empty scaffold); the layer formulas are those
+ * of research/14-gdn-aiter-preflight.md:190-198, :209-219 and the contract is the same as
+ * lg_decoder_step: a packed step equals running every sequence alone.
+ *   block:  x += mixer(rms_norm(x, norm1));  x += swiglu(rms_norm(x, norm2))
+ *   full attention (layer l with (l + 1) % full_attn_interval == 0), no biases:
+ *     q, gate [n_heads * d], k, v [n_kv_heads * d] = h W^T; RoPE(halves) on q, k; causal attention;
+ *     out *= sigmoid(gate); o_proj
+ *   linear attention (all other layers), gdn_heads heads of key = value dim 128:
+ *     q, k, v, z [gdn_heads * 128] = h W^T; a, b [gdn_heads] = h W^T (fp32 outputs);
+ *     q, k L2-normalised per head; g = -exp(A_log) softplus(a + dt_bias); beta = sigmoid(b);
+ *     o = gated delta rule (scale 1/sqrt(128)); o *= silu(z); out_proj
+ * ==================================================================================== */
+typedef struct lg_hybrid_config {
+  int32_t vocab, hidden, n_layers, n_heads, n_kv_heads, attn_head_dim, gdn_heads, intermediate, max_pos;
+  int32_t full_attn_interval;  /* 4 = three linear-attention layers, then one full-attention layer */
+  float rms_eps;
+  double rope_theta;
+  int32_t n_pool_blocks;       /* KV blocks of 16 tokens per full-attention layer */
+  int32_t max_blocks_per_seq;
+  int32_t max_step_tokens;
+  int32_t max_step_seqs;
+  int32_t n_state_slots;       /* recurrent-state slots per linear-attention layer */
+} lg_hybrid_config_t;
+
+typedef struct lg_hybrid_layer_weights {
+  const float *norm1, *norm2;
+  /* full attention: wq, wgate [n_heads*d, hidden], wk, wv [n_kv_heads*d, hidden], wo [hidden, n_heads*d]
+   * linear attention: wq, wk, wv, wgate(= z) [gdn_heads*128, hidden], wo [hidden, gdn_heads*128],
+   *                   wa, wb [gdn_heads, hidden], A_log, dt_bias fp32 [gdn_heads] */
+  lg_int4_matrix_t wq, wk, wv, wgate, wo, wa, wb;
+  const float *A_log, *dt_bias;
+  lg_int4_matrix_t w_gate, w_up, w_down;
+} lg_hybrid_layer_weights_t;
+typedef struct lg_hybrid_weights {
+  const float* tok_embed;
+  const float* final_norm;
+  const lg_hybrid_layer_weights_t* layers;
+  lg_int4_matrix_t lm_head;
+} lg_hybrid_weights_t;
+
+uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const lg_hybrid_weights_t* w, void** model);
+void lg_hybrid_destroy(void* model);
+/* As lg_decoder_step, plus host_state_slots i32 [n_seqs]: the recurrent-state slot of each
+ * sequence (distinct within a step, < n_state_slots). A sequence with cached_lens[i] == 0 starts
+ * from the zero state; otherwise its slot must hold the state its previous step left. */
+uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* host_cached_lens,
+                        const int32_t* host_new_lens, int32_t n_seqs, const int32_t* host_block_tables,
+                        const int32_t* host_state_slots, uint32_t* host_next_tokens);
+uint32_t lg_hybrid_replay_device(void* model, void* stream);
+uint32_t lg_hybrid_last_hidden(void* model, int32_t n_seqs, float* host_out);
+uint32_t lg_hybrid_last_logits(void* model, int32_t n_seqs, float* host_out);
+int32_t lg_hybrid_launches_last_step(const void* model);
+int32_t lg_hybrid_device_status(void* model);
+
 /* Message of the last failure on the calling thread ("" if none). */
 const char* lg_last_error(void);
 

@@ -80,8 +80,9 @@ def _declare(l):
         "logismos_launch_paged_kv_gather_bf16": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
         "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],
         "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
-        "logismos_launch_gdn_prefill": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
-        "logismos_launch_gdn_prepare": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp],
+        "logismos_launch_gdn_prefill": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp],
+        "logismos_launch_gdn_prepare": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
+        "logismos_launch_gated_mul_bf16": [vp, i32, vp, i32, i32, i32, i32, vp],
         "logismos_launch_greedy_argmax": [vp, i32, vp, i32, i32, vp],
         # model
         "lg_stella_create": [i32, vp, vp, C.POINTER(vp)],
@@ -93,6 +94,11 @@ def _declare(l):
         "lg_decoder_replay_device": [vp, vp],
         "lg_decoder_last_hidden": [vp, i32, vp],
         "lg_decoder_last_logits": [vp, i32, vp],
+        "lg_hybrid_create": [i32, vp, vp, C.POINTER(vp)],
+        "lg_hybrid_step": [vp, vp, vp, vp, i32, vp, vp, vp],
+        "lg_hybrid_replay_device": [vp, vp],
+        "lg_hybrid_last_hidden": [vp, i32, vp],
+        "lg_hybrid_last_logits": [vp, i32, vp],
     }
     for name, args in sig.items():
         fn = getattr(l, name)
@@ -114,7 +120,10 @@ def _declare(l):
     l.lg_stella_destroy.restype = None
     l.lg_decoder_destroy.argtypes = [vp]
     l.lg_decoder_destroy.restype = None
-    for name in ("lg_decoder_launches_last_step", "lg_decoder_device_status"):
+    l.lg_hybrid_destroy.argtypes = [vp]
+    l.lg_hybrid_destroy.restype = None
+    for name in ("lg_decoder_launches_last_step", "lg_decoder_device_status", "lg_hybrid_launches_last_step",
+                 "lg_hybrid_device_status"):
         getattr(l, name).argtypes = [vp]
         getattr(l, name).restype = i32
     for name in ("lg_stella_default_dim", "lg_stella_max_tokens", "lg_stella_launches_per_forward",

@@ -21,37 +21,39 @@ namespace {
 
 using namespace lg;
 
-constexpr int D = 128;              // head_dim supported by these kernels
-constexpr int kRowBytes = D * 2;    // one head row in shared memory
+// The kernels are templates on the head dimension HD (128 or 256): a head row is HD bf16 values,
+// i.e. HD/8 chunks of 16 bytes in shared memory, HD/16 k-steps for Q.K^T and HD/8 output tiles for P.V.
 constexpr float kLog2e = 1.4426950408889634f;
 
-// shared-memory address of 16-byte chunk `chunk` of row `row` in a [rows][128] bf16 tile
+// shared-memory address of 16-byte chunk `chunk` of row `row` in a [rows][HD] bf16 tile
+template <int HD>
 LG_DEVINL uint32_t tile_addr(uint32_t base, int row, int chunk) {
-  return base + (uint32_t)row * kRowBytes + (uint32_t)((chunk ^ (row & 7)) << 4);
+  return base + (uint32_t)row * (HD * 2) + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
 
-// A fragments (16 rows x 128) of a query tile staged at `qbase`: qf[ks] covers k = 16ks..16ks+15
-LG_DEVINL void load_q_frags(uint32_t qbase, int lane, uint32_t (&qf)[8][4]) {
+// A fragments (16 rows x HD) of a query tile staged at `qbase`: qf[ks] covers k = 16ks..16ks+15
+template <int HD>
+LG_DEVINL void load_q_frags(uint32_t qbase, int lane, uint32_t (&qf)[HD / 16][4]) {
   const int mat = lane >> 3, r = lane & 7;
   const int row = r + 8 * (mat & 1);
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qf[ks], tile_addr(qbase, row, 2 * ks + (mat >> 1)));
+  for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[ks], tile_addr<HD>(qbase, row, 2 * ks + (mat >> 1)));
 }
 
-// s[t][:] = Q(16x128) . K(tokens tok0+8t .. +7)^T for NT 8-token tiles of the K tile at kbase
-template <int NT>
-LG_DEVINL void qk_tile(const uint32_t (&qf)[8][4], uint32_t kbase, int tok0, int lane, float (&s)[NT][4]) {
+// s[t][:] = Q(16xHD) . K(tokens tok0+8t .. +7)^T for NT 8-token tiles of the K tile at kbase
+template <int NT, int HD>
+LG_DEVINL void qk_tile(const uint32_t (&qf)[HD / 16][4], uint32_t kbase, int tok0, int lane, float (&s)[NT][4]) {
   const int mat = lane >> 3, r = lane & 7;
 #pragma unroll
   for (int t = 0; t < NT; ++t)
 #pragma unroll
     for (int i = 0; i < 4; ++i) s[t][i] = 0.0f;
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
     for (int t = 0; t < NT; t += 2) {
       uint32_t b[4];
-      ldmatrix_x4(b, tile_addr(kbase, tok0 + 8 * (t + (mat >> 1)) + r, 2 * ks + (mat & 1)));
+      ldmatrix_x4(b, tile_addr<HD>(kbase, tok0 + 8 * (t + (mat >> 1)) + r, 2 * ks + (mat & 1)));
       const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
       mma_bf16_16816(s[t], qf[ks], b0, s[t]);
       mma_bf16_16816(s[t + 1], qf[ks], b1, s[t + 1]);
@@ -59,9 +61,9 @@ LG_DEVINL void qk_tile(const uint32_t (&qf)[8][4], uint32_t kbase, int tok0, int
   }
 }
 
-// o(16x128) += P(16 x 8NT tokens) . V(tokens tok0.. , 128)
-template <int NT>
-LG_DEVINL void pv_tile(const float (&p)[NT][4], uint32_t vbase, int tok0, int lane, float (&o)[16][4]) {
+// o(16xHD) += P(16 x 8NT tokens) . V(tokens tok0.. , HD)
+template <int NT, int HD>
+LG_DEVINL void pv_tile(const float (&p)[NT][4], uint32_t vbase, int tok0, int lane, float (&o)[HD / 8][4]) {
   const int mat = lane >> 3, r = lane & 7;
 #pragma unroll
   for (int kt = 0; kt < NT / 2; ++kt) {
@@ -71,9 +73,9 @@ LG_DEVINL void pv_tile(const float (&p)[NT][4], uint32_t vbase, int tok0, int la
     a[2] = pack_bf16x2(p[2 * kt + 1][0], p[2 * kt + 1][1]);
     a[3] = pack_bf16x2(p[2 * kt + 1][2], p[2 * kt + 1][3]);
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) {
+    for (int j = 0; j < HD / 8; j += 2) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, tile_addr(vbase, tok0 + 16 * kt + 8 * (mat & 1) + r, j + (mat >> 1)));
+      ldmatrix_x4_trans(b, tile_addr<HD>(vbase, tok0 + 16 * kt + 8 * (mat & 1) + r, j + (mat >> 1)));
       const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
       mma_bf16_16816(o[j], a, b0, o[j]);
       mma_bf16_16816(o[j + 1], a, b1, o[j + 1]);
@@ -84,8 +86,8 @@ LG_DEVINL void pv_tile(const float (&p)[NT][4], uint32_t vbase, int tok0, int la
 // Online softmax step over s (raw scores, -inf where masked) for the two rows a lane owns
 // (g and g+8). m/l are running max (raw domain) and running sum; o is rescaled in place and
 // s is overwritten with the probabilities exp2((s - m) * sl2).
-template <int NT>
-LG_DEVINL void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[16][4], float sl2) {
+template <int NT, int DT>
+LG_DEVINL void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[DT][4], float sl2) {
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
@@ -114,7 +116,7 @@ LG_DEVINL void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], flo
   m[0] = mn0;
   m[1] = mn1;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = 0; j < DT; ++j) {
     o[j][0] *= a0; o[j][1] *= a0;
     o[j][2] *= a1; o[j][3] *= a1;
   }
@@ -122,16 +124,20 @@ LG_DEVINL void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], flo
 
 // ================================ varlen (encoder / prefill) ===================================
 
-constexpr int kQTile = 64, kKvTile = 64, kVarlenThreads = 128;
+constexpr int kQTile = 64, kVarlenThreads = 128;
+// key/value tile: 64 tokens at head_dim 128, 32 at head_dim 256 (same bytes, same register budget)
+template <int HD> struct KvTile { static constexpr int value = HD == 128 ? 64 : 32; };
 
-// stage rows [t0, t0+64) of one head (128 bf16 per row) into a swizzled tile; rows >= limit are zeroed
+// stage ROWS rows [t0, t0+ROWS) of one head (HD bf16 per row) into a swizzled tile; rows >= limit are zeroed
+template <int HD, int ROWS>
 LG_DEVINL void stage_rows(uint32_t sbase, uint8_t* sgen, const __nv_bfloat16* src, int64_t row_stride,
                           int t0, int limit, int tid) {
+  constexpr int CH = HD / 8;
 #pragma unroll
-  for (int i = 0; i < (64 * 16) / kVarlenThreads; ++i) {
+  for (int i = 0; i < (ROWS * CH) / kVarlenThreads; ++i) {
     const int u = tid + i * kVarlenThreads;
-    const int row = u >> 4, chunk = u & 15;
-    const uint32_t dst = tile_addr(sbase, row, chunk);
+    const int row = u / CH, chunk = u % CH;
+    const uint32_t dst = tile_addr<HD>(sbase, row, chunk);
     if (t0 + row < limit) {
       cp_async16(dst, src + (int64_t)(t0 + row) * row_stride + chunk * 8);
     } else {
@@ -140,8 +146,8 @@ LG_DEVINL void stage_rows(uint32_t sbase, uint8_t* sgen, const __nv_bfloat16* sr
   }
 }
 
-template <bool CAUSAL>
-__global__ void __launch_bounds__(kVarlenThreads, 3)
+template <bool CAUSAL, int HD>
+__global__ void __launch_bounds__(kVarlenThreads, HD == 128 ? 3 : 1)
 varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu,
                         __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int row_stride,
                         int k_off, int v_off, float sl2) {
@@ -153,11 +159,13 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
   const int kvh = h / (n_heads / n_kv);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
+  constexpr int D = HD, kRowBytes = HD * 2, kKvTile = KvTile<HD>::value, NT = kKvTile / 8, DT = HD / 8;
+  constexpr int KTB = kKvTile * kRowBytes;  // bytes of one K (or V) tile: 16 KB
 
-  // two K/V tile buffers of 16 KB + 16 KB; the query tile is staged in the second buffer's K half
-  // and lives in registers from then on, so 64 KB per CTA (three CTAs per SM)
-  uint8_t* sk[2] = {smem, smem + 32768};
-  uint8_t* sv[2] = {smem + 16384, smem + 49152};
+  // two K/V tile buffers of 16 KB + 16 KB; the query tile is staged in the second buffer (all of
+  // it at head_dim 256) and lives in registers from then on, so 64 KB per CTA
+  uint8_t* sk[2] = {smem, smem + 2 * KTB};
+  uint8_t* sv[2] = {smem + KTB, smem + 3 * KTB};
   uint8_t* sq = sk[1];
   const uint32_t sq_a = smem_u32(sq);
   const uint32_t sk_a[2] = {smem_u32(sk[0]), smem_u32(sk[1])};
@@ -170,29 +178,29 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
   const int kv_end = CAUSAL ? min(len, q0 + kQTile) : len;
   const int n_tiles = (kv_end + kKvTile - 1) / kKvTile;
 
-  stage_rows(sq_a, sq, qsrc, row_stride, q0, len, tid);
-  stage_rows(sk_a[0], sk[0], ksrc, row_stride, 0, len, tid);
-  stage_rows(sv_a[0], sv[0], vsrc, row_stride, 0, len, tid);
+  stage_rows<HD, kQTile>(sq_a, sq, qsrc, row_stride, q0, len, tid);
+  stage_rows<HD, kKvTile>(sk_a[0], sk[0], ksrc, row_stride, 0, len, tid);
+  stage_rows<HD, kKvTile>(sv_a[0], sv[0], vsrc, row_stride, 0, len, tid);
   cp_async_commit();
 
-  uint32_t qf[8][4];
-  float o[16][4];
+  uint32_t qf[HD / 16][4];
+  float o[DT][4];
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
+  for (int j = 0; j < DT; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
   cp_async_wait<0>();
   __syncthreads();
-  load_q_frags(sq_a + warp * 16 * kRowBytes, lane, qf);
+  load_q_frags<HD>(sq_a + warp * 16 * kRowBytes, lane, qf);
   __syncthreads();  // the query tile's buffer is free for K/V tile 1 from here on
 
   for (int it = 0; it < n_tiles; ++it) {
     const int buf = it & 1;
     if (it + 1 < n_tiles) {
-      stage_rows(sk_a[buf ^ 1], sk[buf ^ 1], ksrc, row_stride, (it + 1) * kKvTile, len, tid);
-      stage_rows(sv_a[buf ^ 1], sv[buf ^ 1], vsrc, row_stride, (it + 1) * kKvTile, len, tid);
+      stage_rows<HD, kKvTile>(sk_a[buf ^ 1], sk[buf ^ 1], ksrc, row_stride, (it + 1) * kKvTile, len, tid);
+      stage_rows<HD, kKvTile>(sv_a[buf ^ 1], sv[buf ^ 1], vsrc, row_stride, (it + 1) * kKvTile, len, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -200,14 +208,14 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
     }
     __syncthreads();
 
-    float s[8][4];
-    qk_tile<8>(qf, sk_a[buf], 0, lane, s);
+    float s[NT][4];
+    qk_tile<NT, HD>(qf, sk_a[buf], 0, lane, s);
     // mask keys beyond the sequence and (causal) beyond the query position
     const int kbase = it * kKvTile;
     const int qrow0 = q0 + warp * 16 + g, qrow1 = qrow0 + 8;
     if (kbase + kKvTile > len || (CAUSAL && kbase + kKvTile > q0 + warp * 16)) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
+      for (int t = 0; t < NT; ++t) {
         const int k0 = kbase + 8 * t + 2 * c, k1 = k0 + 1;
         if (k0 >= len || (CAUSAL && k0 > qrow0)) s[t][0] = -INFINITY;
         if (k1 >= len || (CAUSAL && k1 > qrow0)) s[t][1] = -INFINITY;
@@ -215,8 +223,8 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
         if (k1 >= len || (CAUSAL && k1 > qrow1)) s[t][3] = -INFINITY;
       }
     }
-    softmax_step<8>(s, m, l, o, sl2);
-    pv_tile<8>(s, sv_a[buf], 0, lane, o);
+    softmax_step<NT, DT>(s, m, l, o, sl2);
+    pv_tile<NT, HD>(s, sv_a[buf], 0, lane, o);
     __syncthreads();  // tile fully consumed before it is overwritten two iterations later
   }
 
@@ -228,7 +236,7 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
   const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
   const int64_t ostride = (int64_t)n_heads * D;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = 0; j < DT; ++j) {
     const int d = 8 * j + 2 * c;
     if (r0 < len)
       *reinterpret_cast<uint32_t*>(out + (int64_t)(s0 + r0) * ostride + h * D + d) = pack_bf16x2(o[j][0] * inv0, o[j][1] * inv0);
@@ -242,23 +250,30 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
 constexpr int kBlock = 16;          // tokens per KV block
 constexpr int kDecWarps = 4;
 constexpr int kDecStages = 3;
-constexpr int kDecStageBytes = 2 * kBlock * kRowBytes;  // K block + V block of one kv head = 8 KB
-constexpr int kDecSmem = kDecWarps * kDecStages * kDecStageBytes + 16 * kRowBytes;  // + Q tile
+template <int HD>
+struct DecCfg {
+  static constexpr int kRowBytes = HD * 2;
+  static constexpr int kStageBytes = 2 * kBlock * kRowBytes;  // K block + V block of one kv head: 8 KB at head_dim 128
+  static constexpr int kSmem = kDecWarps * kDecStages * kStageBytes + 16 * kRowBytes;  // + Q tile
+};
 
 // issue the cp.async copies of one 16-token block (K then V) of kv head `kvh` into a warp's stage
+template <int HD>
 LG_DEVINL void stage_block(uint32_t sbase, const __nv_bfloat16* kpool, const __nv_bfloat16* vpool,
                            int64_t phys_block, int row_elems, int kvh, int lane) {
-  const __nv_bfloat16* kb = kpool + (phys_block * kBlock) * (int64_t)row_elems + kvh * D;
-  const __nv_bfloat16* vb = vpool + (phys_block * kBlock) * (int64_t)row_elems + kvh * D;
+  constexpr int CH = HD / 8;
+  const __nv_bfloat16* kb = kpool + (phys_block * kBlock) * (int64_t)row_elems + kvh * HD;
+  const __nv_bfloat16* vb = vpool + (phys_block * kBlock) * (int64_t)row_elems + kvh * HD;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < (kBlock * CH) / 32; ++i) {
     const int u = lane + 32 * i;
-    const int row = u >> 4, chunk = u & 15;
-    cp_async16(tile_addr(sbase, row, chunk), kb + (int64_t)row * row_elems + chunk * 8);
-    cp_async16(tile_addr(sbase + kBlock * kRowBytes, row, chunk), vb + (int64_t)row * row_elems + chunk * 8);
+    const int row = u / CH, chunk = u % CH;
+    cp_async16(tile_addr<HD>(sbase, row, chunk), kb + (int64_t)row * row_elems + chunk * 8);
+    cp_async16(tile_addr<HD>(sbase + kBlock * HD * 2, row, chunk), vb + (int64_t)row * row_elems + chunk * 8);
   }
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ kpool,
                     __nv_bfloat16* __restrict__ vpool, const __nv_bfloat16* __restrict__ new_k,
@@ -272,6 +287,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int n_rep = n_heads / n_kv;
+  constexpr int D = HD, kRowBytes = HD * 2, DT = HD / 8, CH = HD / 8;
+  constexpr int kDecStageBytes = DecCfg<HD>::kStageBytes;
   const int row_elems = n_kv * D;
 
   // which sequence owns this chunk: largest s with chunk_offsets[s] <= chunk_id
@@ -293,11 +310,11 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     const int pos = ctx - 1;
     const int pb = (pos / kBlock) < max_blocks ? table[pos / kBlock] : -1;
     if (pb >= 0 && pb < n_pool_blocks) {
-      if (tid < 32) {
+      if (tid < 2 * CH) {
         const int64_t dst = ((int64_t)pb * kBlock + pos % kBlock) * row_elems + kvh * D;
         const int64_t src = (int64_t)seq * row_elems + kvh * D;
-        const int chunk = tid & 15;
-        if (tid < 16)
+        const int chunk = tid % CH;
+        if (tid < CH)
           *reinterpret_cast<uint4*>(kpool + dst + chunk * 8) = __ldg(reinterpret_cast<const uint4*>(new_k + src + chunk * 8));
         else
           *reinterpret_cast<uint4*>(vpool + dst + chunk * 8) = __ldg(reinterpret_cast<const uint4*>(new_v + src + chunk * 8));
@@ -311,19 +328,19 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
   // ---- stage the query rows of this kv head's group (rows >= n_rep are zero) ----
   uint8_t* sq = smem + kDecWarps * kDecStages * kDecStageBytes;
   const uint32_t sq_a = smem_u32(sq);
-  for (int u = tid; u < 16 * 16; u += kDecWarps * 32) {
-    const int row = u >> 4, chunk = u & 15;
+  for (int u = tid; u < 16 * CH; u += kDecWarps * 32) {
+    const int row = u / CH, chunk = u % CH;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row < n_rep) v = __ldg(reinterpret_cast<const uint4*>(q + ((int64_t)seq * n_heads + kvh * n_rep + row) * D + chunk * 8));
-    *reinterpret_cast<uint4*>(sq + (tile_addr(sq_a, row, chunk) - sq_a)) = v;
+    *reinterpret_cast<uint4*>(sq + (tile_addr<HD>(sq_a, row, chunk) - sq_a)) = v;
   }
   __syncthreads();
-  uint32_t qf[8][4];
-  load_q_frags(sq_a, lane, qf);
+  uint32_t qf[HD / 16][4];
+  load_q_frags<HD>(sq_a, lane, qf);
 
-  float o[16][4];
+  float o[DT][4];
 #pragma unroll
-  for (int j = 0; j < 16; ++j)
+  for (int j = 0; j < DT; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
@@ -339,7 +356,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
       const int bidx = my_first + i * kDecWarps;
       const int pb = bidx < max_blocks ? table[bidx] : -1;
       if (pb >= 0 && pb < n_pool_blocks) {
-        stage_block(wbase + (i % kDecStages) * kDecStageBytes, kpool, vpool, pb, row_elems, kvh, lane);
+        stage_block<HD>(wbase + (i % kDecStages) * kDecStageBytes, kpool, vpool, pb, row_elems, kvh, lane);
       } else if (lane == 0 && status) {
         atomicExch(status, 1);
       }
@@ -359,7 +376,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     const uint32_t sb = wbase + (i % kDecStages) * kDecStageBytes;
     float s[2][4];
     if (valid_block) {
-      qk_tile<2>(qf, sb, 0, lane, s);
+      qk_tile<2, HD>(qf, sb, 0, lane, s);
     } else {
 #pragma unroll
       for (int t = 0; t < 2; ++t)
@@ -375,19 +392,19 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         if (k0 + 1 >= tok_end) { s[t][1] = -INFINITY; s[t][3] = -INFINITY; }
       }
     }
-    softmax_step<2>(s, m, l, o, sl2);
+    softmax_step<2, DT>(s, m, l, o, sl2);
     if (valid_block) {
       // rows of a partially filled block beyond the context may hold stale data: P is 0 there,
       // but 0 * NaN is NaN, so such rows are cleared before the product
       if (tbase + kBlock > tok_end) {
-        for (int u = lane; u < kBlock * 16; u += 32) {
-          const int row = u >> 4, chunk = u & 15;
+        for (int u = lane; u < kBlock * CH; u += 32) {
+          const int row = u / CH, chunk = u % CH;
           if (tbase + row >= tok_end)
-            *reinterpret_cast<uint4*>(smem + (tile_addr(sb + kBlock * kRowBytes, row, chunk) - smem_u32(smem))) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(smem + (tile_addr<HD>(sb + kBlock * kRowBytes, row, chunk) - smem_u32(smem))) = make_uint4(0u, 0u, 0u, 0u);
         }
         __syncwarp();
       }
-      pv_tile<2>(s, sb + kBlock * kRowBytes, 0, lane, o);
+      pv_tile<2, HD>(s, sb + kBlock * kRowBytes, 0, lane, o);
     }
     __syncwarp();
   }
@@ -402,7 +419,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
   float* so = reinterpret_cast<float*>(smem);                 // [warp][16][128]
   float* sml = so + kDecWarps * 16 * D;                       // [warp][16][2]
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = 0; j < DT; ++j) {
     const int d = 8 * j + 2 * c;
     *reinterpret_cast<float2*>(so + ((warp * 16 + g) * D + d)) = make_float2(o[j][0], o[j][1]);
     *reinterpret_cast<float2*>(so + ((warp * 16 + g + 8) * D + d)) = make_float2(o[j][2], o[j][3]);
@@ -412,28 +429,30 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     sml[(warp * 16 + g + 8) * 2] = m[1]; sml[(warp * 16 + g + 8) * 2 + 1] = l[1];
   }
   __syncthreads();
-  // thread t owns column d = t; loops over the group's query heads
+  // thread t owns columns d = t, t + 128, ...; loops over the group's query heads
   for (int r = 0; r < n_rep; ++r) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
-    float L = 0.0f, acc = 0.0f;
+    float L = 0.0f, f[kDecWarps];
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) {
       const float mw = sml[(w * 16 + r) * 2];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f((mw - M) * sl2);
-      L += sml[(w * 16 + r) * 2 + 1] * f;
-      acc += so[(w * 16 + r) * D + tid] * f;
+      f[w] = (mw == -INFINITY) ? 0.0f : exp2f((mw - M) * sl2);
+      L += sml[(w * 16 + r) * 2 + 1] * f[w];
     }
     const int head = kvh * n_rep + r;
-    if (n_chunks == 1) {
-      out[((int64_t)seq * n_heads + head) * D + tid] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
-    } else {
-      part_o[((int64_t)chunk_id * n_heads + head) * D + tid] = acc;
-      if (tid == 0) {
-        part_ml[((int64_t)chunk_id * n_heads + head) * 2] = M;
-        part_ml[((int64_t)chunk_id * n_heads + head) * 2 + 1] = L;
-      }
+#pragma unroll
+    for (int d = tid; d < D; d += kDecWarps * 32) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kDecWarps; ++w) acc += so[(w * 16 + r) * D + d] * f[w];
+      if (n_chunks == 1) out[((int64_t)seq * n_heads + head) * D + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+      else part_o[((int64_t)chunk_id * n_heads + head) * D + d] = acc;
+    }
+    if (n_chunks != 1 && tid == 0) {
+      part_ml[((int64_t)chunk_id * n_heads + head) * 2] = M;
+      part_ml[((int64_t)chunk_id * n_heads + head) * 2 + 1] = L;
     }
   }
 }
@@ -441,7 +460,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
 // merges the per-chunk partial results of sequences that were split into several chunks
 __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           const int* __restrict__ chunk_offsets, __nv_bfloat16* __restrict__ out,
-                                          int n_heads, float sl2) {
+                                          int n_heads, int D, float sl2) {
   const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int c0 = chunk_offsets[seq], c1 = chunk_offsets[seq + 1];
   if (c1 - c0 <= 1) return;  // single-chunk sequences were finished by the main kernel
@@ -504,26 +523,22 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv, const void* cu_s
                                                int32_t head_dim, int32_t row_stride, int32_t k_off, int32_t v_off,
                                                int32_t causal, void* stream) {
   lg::LaunchScope launch_scope_;
-  if (n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim != D || (n_heads % n_kv_heads) ||
+  if (n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || (head_dim != 128 && head_dim != 256) || (n_heads % n_kv_heads) ||
       (row_stride % 8) || (k_off % 8) || (v_off % 8) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
     return lg::kInvalidValue;
   if (n_seqs == 0 || max_seqlen == 0) return 0;
   const size_t smem = 4 * 16384;
   const float sl2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid((max_seqlen + kQTile - 1) / kQTile, n_heads, n_seqs);
-  cudaError_t e;
-  if (causal) {
-    e = cudaFuncSetAttribute(varlen_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto launch = [&](auto kern) -> uint32_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    varlen_attention_kernel<true><<<grid, kVarlenThreads, smem, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, (__nv_bfloat16*)out, n_heads, n_kv_heads, row_stride, k_off, v_off, sl2);
-  } else {
-    e = cudaFuncSetAttribute(varlen_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (uint32_t)e;
-    varlen_attention_kernel<false><<<grid, kVarlenThreads, smem, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, (__nv_bfloat16*)out, n_heads, n_kv_heads, row_stride, k_off, v_off, sl2);
-  }
-  return lg::launch_status();
+    kern<<<grid, kVarlenThreads, smem, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, (__nv_bfloat16*)out,
+                                                             n_heads, n_kv_heads, row_stride, k_off, v_off, sl2);
+    return lg::launch_status();
+  };
+  if (head_dim == 128) return causal ? launch(varlen_attention_kernel<true, 128>) : launch(varlen_attention_kernel<false, 128>);
+  return causal ? launch(varlen_attention_kernel<true, 256>) : launch(varlen_attention_kernel<false, 256>);
 }
 
 size_t logismos_paged_decode_scratch_bytes(int32_t total_chunks, int32_t n_heads, int32_t head_dim) {
@@ -538,28 +553,31 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
     int32_t n_kv_heads, int32_t head_dim, void* stream) {
   lg::LaunchScope launch_scope_;
   if (n_seqs < 0 || total_chunks < 0 || chunk_tokens <= 0 || (chunk_tokens % 64) || max_blocks <= 0 ||
-      n_pool_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim != D || (n_heads % n_kv_heads) ||
+      n_pool_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || (head_dim != 128 && head_dim != 256) || (n_heads % n_kv_heads) ||
       n_heads / n_kv_heads > 16 || (new_k == nullptr) != (new_v == nullptr))
     return lg::kInvalidValue;
   if (n_seqs == 0 || total_chunks == 0) return 0;
   if (scratch == nullptr || ((uintptr_t)scratch & 15)) return lg::kInvalidValue;
   float* part_o = (float*)scratch;
-  float* part_ml = part_o + (size_t)total_chunks * n_heads * D;
+  float* part_ml = part_o + (size_t)total_chunks * n_heads * head_dim;
   const float sl2 = kLog2e / sqrtf((float)head_dim);
-  cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-  if (e != cudaSuccess) return (uint32_t)e;
   dim3 grid(total_chunks, n_kv_heads);
-  paged_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)new_k,
-      (const __nv_bfloat16*)new_v, (const int*)block_tables, (const int*)context_lens, (const int*)chunk_offsets,
-      (__nv_bfloat16*)out, part_o, part_ml, (int*)status, n_seqs, chunk_tokens, max_blocks, n_pool_blocks, n_heads,
-      n_kv_heads, sl2);
-  uint32_t rc = lg::launch_status();
+  auto launch = [&](auto kern, int smem) -> uint32_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (uint32_t)e;
+    kern<<<grid, kDecWarps * 32, smem, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)new_k,
+        (const __nv_bfloat16*)new_v, (const int*)block_tables, (const int*)context_lens, (const int*)chunk_offsets,
+        (__nv_bfloat16*)out, part_o, part_ml, (int*)status, n_seqs, chunk_tokens, max_blocks, n_pool_blocks, n_heads,
+        n_kv_heads, sl2);
+    return lg::launch_status();
+  };
+  uint32_t rc = head_dim == 128 ? launch(paged_decode_kernel<128>, DecCfg<128>::kSmem) : launch(paged_decode_kernel<256>, DecCfg<256>::kSmem);
   if (rc) return rc;
   if (total_chunks > n_seqs) {  // at least one sequence spans several chunks
     dim3 mgrid(n_seqs, n_heads);
-    paged_decode_merge_kernel<<<mgrid, D, 0, (cudaStream_t)stream>>>(part_o, part_ml, (const int*)chunk_offsets,
-                                                                    (__nv_bfloat16*)out, n_heads, sl2);
+    paged_decode_merge_kernel<<<mgrid, head_dim, 0, (cudaStream_t)stream>>>(part_o, part_ml, (const int*)chunk_offsets,
+                                                                           (__nv_bfloat16*)out, n_heads, head_dim, sl2);
     rc = lg::launch_status();
   }
   return rc;

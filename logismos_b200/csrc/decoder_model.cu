@@ -25,30 +25,11 @@
 #include "logismos_kernels.h"
 #include "logismos_model.h"
 
-namespace lgm {
-void set_error(const std::string& s);
-}
+#include "model_util.h"
 
 namespace {
 
-using lgm::set_error;
-
-inline uint16_t f32_to_bf16(float f) {
-  uint32_t u;
-  std::memcpy(&u, &f, 4);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
-  u += 0x7fffu + ((u >> 16) & 1u);
-  return (uint16_t)(u >> 16);
-}
-
-struct Buf {
-  void* p = nullptr;
-  bool alloc(size_t n) { return cudaMalloc(&p, n ? n : 1) == cudaSuccess; }
-  bool upload(const void* src, size_t n) { return alloc(n) && cudaMemcpy(p, src, n, cudaMemcpyHostToDevice) == cudaSuccess; }
-  void release() { if (p) cudaFree(p); p = nullptr; }
-};
-
-struct QMat { Buf codes, scales; int n = 0, k = 0; };
+using namespace lgm;
 
 struct DLayer {
   Buf norm1, norm2, bqkv, kpool, vpool;
@@ -77,50 +58,6 @@ struct Decoder {
   std::vector<int> order;  // internal slot -> caller's sequence index
   size_t max_chunks = 0;
 };
-
-// gate and up rows interleaved in blocks of 32 (32 gate rows, then the 32 matching up rows), the
-// row order the fused SwiGLU epilogue of the GEMM expects
-bool upload_q_gate_up(QMat& q, const lg_int4_matrix_t& gate, const lg_int4_matrix_t& up, int inter, int k) {
-  const size_t cb = (size_t)32 * (k / 2), sb = (size_t)32 * (k / 32);
-  std::vector<uint8_t> codes((size_t)2 * inter * (k / 2));
-  std::vector<uint16_t> scales((size_t)2 * inter * (k / 32));
-  for (int b = 0; b < inter / 32; ++b) {
-    std::memcpy(codes.data() + (size_t)(2 * b) * cb, gate.codes + (size_t)b * cb, cb);
-    std::memcpy(codes.data() + (size_t)(2 * b + 1) * cb, up.codes + (size_t)b * cb, cb);
-    std::memcpy(scales.data() + (size_t)(2 * b) * sb, gate.scales + (size_t)b * sb, sb * 2);
-    std::memcpy(scales.data() + (size_t)(2 * b + 1) * sb, up.scales + (size_t)b * sb, sb * 2);
-  }
-  q.n = 2 * inter;
-  q.k = k;
-  return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
-}
-
-bool upload_q(QMat& q, const std::vector<const lg_int4_matrix_t*>& parts, const std::vector<int>& rows, int k) {
-  size_t n = 0;
-  for (int r : rows) n += (size_t)r;
-  std::vector<uint8_t> codes(n * (k / 2));
-  std::vector<uint16_t> scales(n * (k / 32));
-  size_t o = 0;
-  for (size_t i = 0; i < parts.size(); ++i) {
-    std::memcpy(codes.data() + o * (k / 2), parts[i]->codes, (size_t)rows[i] * (k / 2));
-    std::memcpy(scales.data() + o * (k / 32), parts[i]->scales, (size_t)rows[i] * (k / 32) * 2);
-    o += (size_t)rows[i];
-  }
-  q.n = (int)n;
-  q.k = k;
-  return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
-}
-
-#define LG_TRY(expr, what)                                                                         \
-  do {                                                                                             \
-    uint32_t rc_ = (uint32_t)(expr);                                                               \
-    if (rc_ != 0) {                                                                                \
-      char buf_[192];                                                                              \
-      std::snprintf(buf_, sizeof(buf_), "%s failed: %s (code %u)", what, cudaGetErrorString((cudaError_t)rc_), rc_); \
-      set_error(buf_);                                                                             \
-      return LG_EMB_COMPUTE;                                                                       \
-    }                                                                                              \
-  } while (0)
 
 // C = A W^T with int4 weights: expand to bf16, then the tcgen05 GEMM with the requested epilogue
 uint32_t qlinear(Decoder* m, const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc,
@@ -173,8 +110,9 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
   LG_TRY(logismos_launch_gather_rows_f32(m->x.p, m->last_idx.p, m->last.p, m->n_seqs, H, T, st, s), "gather_rows");
   LG_TRY(logismos_launch_rms_norm_f32(m->last.p, m->final_norm.p, m->last_bf16.p, m->n_seqs, H, c.rms_eps, 0, s), "final_norm");
   m->launches += 2;
-  for (int b0 = 0; b0 < m->n_seqs; b0 += 64) {
-    const int nb = m->n_seqs - b0 < 64 ? m->n_seqs - b0 : 64;
+  // batches of 32 keep the staged activations of the streaming GEMV within one CTA's shared memory
+  for (int b0 = 0; b0 < m->n_seqs; b0 += 32) {
+    const int nb = m->n_seqs - b0 < 32 ? m->n_seqs - b0 : 32;
     LG_TRY(logismos_launch_gemv_int4_g32_bf16(m->lm_head.codes.p, m->lm_head.scales.p, (uint16_t*)m->last_bf16.p + (size_t)b0 * H,
                                               (uint16_t*)m->logits.p + (size_t)b0 * c.vocab, nb, c.vocab, H, s), "lm_head");
     m->launches += 1;

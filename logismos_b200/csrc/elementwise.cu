@@ -184,9 +184,23 @@ __global__ void greedy_argmax_kernel(const T* __restrict__ logits, uint32_t* __r
   const T* row = logits + (size_t)blockIdx.x * n;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const float v = (float)row[j];
-    if (v > best) { best = v; best_i = j; }
+  constexpr int V = 16 / (int)sizeof(T);  // elements per 128-bit load
+  if ((n % V) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // a thread walks its own ascending index sequence, so strict > keeps its first maximum
+    for (int j = threadIdx.x * V; j < n; j += blockDim.x * V) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + j));
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float v = (float)e[i];
+        if (v > best) { best = v; best_i = j + i; }
+      }
+    }
+  } else {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      const float v = (float)row[j];
+      if (v > best) { best = v; best_i = j; }
+    }
   }
   auto better = [](float v, int i, float bvv, int bii) { return v > bvv || (v == bvv && i < bii); };
 #pragma unroll
@@ -298,9 +312,9 @@ uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, v
   if (rows < 0 || n <= 0) return lg::kInvalidValue;
   if (rows == 0) return 0;
   if (logits_f32)
-    greedy_argmax_kernel<float><<<rows, 256, 0, (cudaStream_t)stream>>>((const float*)logits, (uint32_t*)out, n);
+    greedy_argmax_kernel<float><<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, (uint32_t*)out, n);
   else
-    greedy_argmax_kernel<__nv_bfloat16><<<rows, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, (uint32_t*)out, n);
+    greedy_argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, (uint32_t*)out, n);
   return lg::launch_status();
 }
 
@@ -333,5 +347,39 @@ extern "C" uint32_t logismos_launch_gather_rows_f32(const void* src_f32, const v
   gather_rows_f32_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const float*)src_f32, (const int*)idx_i32,
                                                                   (float*)dst_f32, n_rows, width, n_src_rows,
                                                                   (int*)status_i32);
+  return lg::launch_status();
+}
+
+// ---- output gates of the hybrid decoder layers -----------------------------------------------------
+namespace {
+__global__ void gated_mul_kernel(__nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ gate,
+                                 int gate_stride, int rows, int n, int mode) {
+  const int per_row = n >> 3;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)rows * per_row) return;
+  const int r = (int)(idx / per_row), j = (int)(idx % per_row) * 8;
+  uint4* xp = reinterpret_cast<uint4*>(x + (size_t)r * x_stride + j);
+  const uint4 xv = *xp;
+  const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate + (size_t)r * gate_stride + j));
+  const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = unpack_bf16x2(xw[i]), g = unpack_bf16x2(gw[i]);
+    const float s0 = 1.0f / (1.0f + __expf(-g.x)), s1 = 1.0f / (1.0f + __expf(-g.y));
+    ow[i] = mode ? pack_bf16x2(a.x * g.x * s0, a.y * g.y * s1) : pack_bf16x2(a.x * s0, a.y * s1);
+  }
+  *xp = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+}  // namespace
+
+extern "C" uint32_t logismos_launch_gated_mul_bf16(void* x, int32_t x_stride, const void* gate, int32_t gate_stride,
+                                                   int32_t rows, int32_t n, int32_t mode, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (rows < 0 || n <= 0 || (n % 8) || (x_stride % 8) || (gate_stride % 8) || x_stride < n || gate_stride < n) return lg::kInvalidValue;
+  if (rows == 0) return 0;
+  const int64_t total = (int64_t)rows * (n / 8);
+  gated_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate, gate_stride, rows, n, mode);
   return lg::launch_status();
 }

@@ -11,14 +11,19 @@
 //   - a warp owns 16 weight rows; lane (g = lane/4, c = lane%4) reads, for rows g and g+8, the
 //     32-bit word c of four consecutive groups, i.e. the warp touches 64 contiguous bytes of
 //     each of its 16 rows per step;
-//   - nibbles become bf16 with one shift + one LOP3 per pair: ((w >> 4i) & 0x000f000f) ^ 0x0008
-//     | 0x4300 is the bf16 number 136 + q (q the signed code), exact;
-//   - the multiply-accumulate runs on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> fp32,
-//     products exact), the 16 k-slots of one instruction all taken from ONE quantisation group, so
-//     the group scale is applied afterwards in fp32: acc += s * (sum (136+q) x - 136 sum x).
-//     The correction 136 * sum_{k in group} x[b,k] is computed once per CTA while x is staged.
-//   - x is staged in shared memory as bf16 in the slot order the fragments want
-//     ([x0,x4,x1,x5,x2,x6,x3,x7] per 8 values), so a lane fetches the B fragments of both
+//   - nibbles become 16-bit floats with one LOP3 per pair and one shift per 32-bit word: the low
+//     nibble of each byte, (w & 0x000f000f) ^ 0x0008 | 0x4300, is the bf16 number 136 + q (q the
+//     signed code); the high nibble is used IN PLACE, (w & 0x00f000f0) ^ 0x0080 | 0x6400, which is
+//     the fp16 number 1152 + 16 q; both exact;
+//   - the multiply-accumulate runs on the tensor cores (mma.sync m16n8k16, fp32 accumulate, exact
+//     products): one bf16 instruction for the low nibbles against x, one fp16 instruction for the
+//     high nibbles against x/16, all 16 k-slots of an instruction taken from ONE quantisation
+//     group, so the group scale is applied afterwards in fp32:
+//       acc += s * (sum_lo (136+q) x + sum_hi (1152+16q) x/16 - 136 sum_lo x - 72 sum_hi x).
+//     The correction term is computed once per CTA while x is staged. x/16 is held in fp16: exact
+//     for |x| in [2^-10, 2^20); activations beyond 2^20 in magnitude are outside this kernel's range;
+//   - x is staged in shared memory in the slot order the fragments want (per 8 values:
+//     bf16 [x0,x4,x2,x6] then fp16 [x1,x5,x3,x7]/16), so a lane fetches the B fragments of both
 //     instructions of a group with one 128-bit load.
 #include "common.cuh"
 #include "logismos_kernels.h"
@@ -35,6 +40,38 @@ LG_DEVINL uint32_t nib_pair_bf16(uint32_t w) {
   // (w & 0x000f000f) ^ 0x43084308 : LUT (a & b) ^ c = 0x6a
   asm("lop3.b32 %0, %1, %2, %3, 0x6a;\n" : "=r"(r) : "r"(w), "r"(0x000f000fu), "r"(0x43084308u));
   return r;
+}
+
+LG_DEVINL uint32_t nib_pair_f16_hi(uint32_t w) {
+  uint32_t r;
+  // (w & 0x00f000f0) ^ 0x64806480 : the high nibble of each byte, in place, as fp16 1152 + 16 q
+  asm("lop3.b32 %0, %1, %2, %3, 0x6a;\n" : "=r"(r) : "r"(w), "r"(0x00f000f0u), "r"(0x64806480u));
+  return r;
+}
+
+LG_DEVINL void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2], const float (&c)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// One 16-byte unit of staged activations from 8 consecutive bf16 values x0..x7 of one batch row:
+// bf16 (x0,x4) (x2,x6) for the low-nibble instruction, fp16 (x1,x5)/16 (x3,x7)/16 for the
+// high-nibble instruction. Returns the unit's share of the group correction.
+LG_DEVINL float stage_unit(uint4 raw, uint4& out) {
+  const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
+  const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
+  out.x = __byte_perm(raw.x, raw.z, 0x5410);  // (x0, x4) bf16
+  out.y = __byte_perm(raw.y, raw.w, 0x5410);  // (x2, x6) bf16
+  const __half2 h15 = __floats2half2_rn(v01.y * 0.0625f, v45.y * 0.0625f);
+  const __half2 h37 = __floats2half2_rn(v23.y * 0.0625f, v67.y * 0.0625f);
+  out.z = *reinterpret_cast<const uint32_t*>(&h15);
+  out.w = *reinterpret_cast<const uint32_t*>(&h37);
+  const float2 f15 = __half22float2(h15), f37 = __half22float2(h37);
+  const float lo = (v01.x + v45.x) + (v23.x + v67.x);
+  const float hi = (f15.x + f15.y) + (f37.x + f37.y);  // sum of x/16 as the tensor core will see it
+  return 136.0f * lo + 1152.0f * hi;
 }
 
 struct Frag {
@@ -101,18 +138,12 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
         const int G = kk >> 2, cc = kk & 3;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kk * 8));
-        const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
-        const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
-        float s = ((v01.x + v01.y) + (v23.x + v23.y)) + ((v45.x + v45.y) + (v67.x + v67.y));
+        uint4 perm;
+        float s = stage_unit(raw, perm);
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
-        uint4 perm;  // [x0,x4 | x1,x5 | x2,x6 | x3,x7]
-        perm.x = __byte_perm(raw.x, raw.z, 0x5410);
-        perm.y = __byte_perm(raw.x, raw.z, 0x7632);
-        perm.z = __byte_perm(raw.y, raw.w, 0x5410);
-        perm.w = __byte_perm(raw.y, raw.w, 0x7632);
         *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
-        if (cc == 0) negcorr[G * (NT * 8) + n] = -136.0f * s;
+        if (cc == 0) negcorr[G * (NT * 8) + n] = -s;
       }
     }
     __syncthreads();
@@ -133,10 +164,9 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
       for (int j = 0; j < 4; ++j) {
         const int G = it * 4 + j;
         const uint32_t w0 = cur.w0[j], w1 = cur.w1[j];
-        const uint32_t a_lo[4] = {nib_pair_bf16(w0), nib_pair_bf16(w1), nib_pair_bf16(w0 >> 4),
-                                  nib_pair_bf16(w1 >> 4)};
-        const uint32_t a_hi[4] = {nib_pair_bf16(w0 >> 8), nib_pair_bf16(w1 >> 8),
-                                  nib_pair_bf16(w0 >> 12), nib_pair_bf16(w1 >> 12)};
+        const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+        const uint32_t a_lo[4] = {nib_pair_bf16(w0), nib_pair_bf16(w1), nib_pair_bf16(w0s), nib_pair_bf16(w1s)};
+        const uint32_t a_hi[4] = {nib_pair_f16_hi(w0), nib_pair_f16_hi(w1), nib_pair_f16_hi(w0s), nib_pair_f16_hi(w1s)};
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const uint4 bx = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * xrow_stride +
@@ -145,7 +175,7 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
           float d[4] = {nc.x, nc.y, nc.x, nc.y};
           const uint32_t b_lo[2] = {bx.x, bx.y}, b_hi[2] = {bx.z, bx.w};
           mma_bf16_16816(d, a_lo, b_lo, d);
-          mma_bf16_16816(d, a_hi, b_hi, d);
+          mma_f16_16816(d, a_hi, b_hi, d);
           acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
           acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
           acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
@@ -197,7 +227,7 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
 // slots that runs ahead across row-tile boundaries; ldmatrix.x4 hands lane (g, c) exactly "word c of
 // groups 0..3 of row g"; no block-wide barrier and no cross-warp reduction in the loop.
 constexpr int kWPitch = 80;                       // row pitch of a staged weight step: conflict-free ldmatrix
-constexpr int kSlotBytes = 16 * kWPitch + 16 * 8;  // 16 rows of codes + 16 rows of 4 fp16 scales
+constexpr int kSlotBytes = 16 * kWPitch + 16 * 8 + 16 * 16;  // codes, 16 x 4 fp16 scales, the same as fp32
 
 template <int NT, int STAGES>
 __global__ void __launch_bounds__(512)
@@ -223,18 +253,12 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
       const int G = kk >> 2, cc = kk & 3;
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + kk * 8));
-      const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
-      const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
-      float s = ((v01.x + v01.y) + (v23.x + v23.y)) + ((v45.x + v45.y) + (v67.x + v67.y));
+      uint4 perm;
+      float s = stage_unit(raw, perm);
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
-      uint4 perm;
-      perm.x = __byte_perm(raw.x, raw.z, 0x5410);
-      perm.y = __byte_perm(raw.x, raw.z, 0x7632);
-      perm.z = __byte_perm(raw.y, raw.w, 0x5410);
-      perm.w = __byte_perm(raw.y, raw.w, 0x7632);
       *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
-      if (cc == 0) negcorr[G * (NT * 8) + n] = -136.0f * s;
+      if (cc == 0) negcorr[G * (NT * 8) + n] = -s;
     }
   }
   __syncthreads();
@@ -279,7 +303,7 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
   // ---- consumer
   const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: lanes 8j..8j+7 address the rows of matrix j (= group j)
   const uint32_t ld_off0 = (uint32_t)(mr * kWPitch + mat * 16), ld_off1 = ld_off0 + 8 * kWPitch;
-  const uint32_t sc_off0 = (uint32_t)(16 * kWPitch + g * 8), sc_off1 = sc_off0 + 64;
+  const uint32_t sc_off0 = (uint32_t)(16 * kWPitch + 128 + g * 16), sc_off1 = sc_off0 + 128;
   const uint32_t xs_a = smem_u32(xs) + (uint32_t)(g * xrow_stride + c * 16);
   const uint32_t nc_a = smem_u32(negcorr) + (uint32_t)(2 * c * 4);
   uint32_t c_slot = ring;
@@ -298,19 +322,21 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
       uint32_t w0[4], w1[4];
       ldmatrix_x4(w0, c_slot + ld_off0);
       ldmatrix_x4(w1, c_slot + ld_off1);
-      uint32_t s0x, s0y, s1x, s1y;
-      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(s0x), "=r"(s0y) : "r"(c_slot + sc_off0));
-      asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(s1x), "=r"(s1y) : "r"(c_slot + sc_off1));
-      const float2 s0a = __half22float2(*reinterpret_cast<const __half2*>(&s0x));
-      const float2 s0b = __half22float2(*reinterpret_cast<const __half2*>(&s0y));
-      const float2 s1a = __half22float2(*reinterpret_cast<const __half2*>(&s1x));
-      const float2 s1b = __half22float2(*reinterpret_cast<const __half2*>(&s1y));
-      const float sc0[4] = {s0a.x, s0a.y, s0b.x, s0b.y};
-      const float sc1[4] = {s1a.x, s1a.y, s1b.x, s1b.y};
+      {  // each lane widens two of the step's 64 scales to fp32 (instead of every lane widening eight)
+        uint32_t sh;
+        asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(sh) : "r"(c_slot + (uint32_t)(16 * kWPitch + lane * 4)));
+        const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sh));
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(c_slot + (uint32_t)(16 * kWPitch + 128 + lane * 8)), "f"(sf.x), "f"(sf.y));
+      }
+      __syncwarp();
+      float sc0[4], sc1[4];
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(sc0[0]), "=f"(sc0[1]), "=f"(sc0[2]), "=f"(sc0[3]) : "r"(c_slot + sc_off0));
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(sc1[0]), "=f"(sc1[1]), "=f"(sc1[2]), "=f"(sc1[3]) : "r"(c_slot + sc_off1));
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0[j] >> 4), nib_pair_bf16(w1[j] >> 4)};
-        const uint32_t a_hi[4] = {nib_pair_bf16(w0[j] >> 8), nib_pair_bf16(w1[j] >> 8), nib_pair_bf16(w0[j] >> 12), nib_pair_bf16(w1[j] >> 12)};
+        const uint32_t w0s = w0[j] >> 8, w1s = w1[j] >> 8;
+        const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0s), nib_pair_bf16(w1s)};
+        const uint32_t a_hi[4] = {nib_pair_f16_hi(w0[j]), nib_pair_f16_hi(w1[j]), nib_pair_f16_hi(w0s), nib_pair_f16_hi(w1s)};
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           uint32_t b_lo[2], b_hi[2];
@@ -322,7 +348,7 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
           d[2] = d[0];
           d[3] = d[1];
           mma_bf16_16816(d, a_lo, b_lo, d);
-          mma_bf16_16816(d, a_hi, b_hi, d);
+          mma_f16_16816(d, a_hi, b_hi, d);
           acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
           acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
           acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);

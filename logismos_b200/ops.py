@@ -322,8 +322,8 @@ def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, sync=True):
         raise InvalidOp("gdn_prefill: state must be [n_seqs, heads, 128, 128]")
     o = torch.empty_like(v)
     with torch.cuda.device(state.device):
-        check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(cu_seqlens), state.shape[0],
-                                              state.shape[1], float(scale), _stream()), "gdn_prefill")
+        check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(cu_seqlens), _p(None), _p(None),
+                                              state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale), _stream()), "gdn_prefill")
         _done(sync)
     return o
 
@@ -335,7 +335,7 @@ def gdn_prepare_(q, k, a, b, A_log, dt_bias, sync=True):
     g = torch.empty_like(a); beta = torch.empty_like(a)
     with torch.cuda.device(q.device):
         check(lib.logismos_launch_gdn_prepare(_p(q), _p(k), _p(a), _p(b), _p(A_log), _p(dt_bias), _p(g), _p(beta), q.shape[0], q.shape[1],
-                                              _stream()), "gdn_prepare")
+                                              q.shape[1] * q.shape[2], a.shape[1], _stream()), "gdn_prepare")
         _done(sync)
     return g, beta
 

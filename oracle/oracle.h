@@ -101,6 +101,26 @@ int orc_stella_encode_batch(void* model, const uint32_t* ids, const int32_t* cu_
 size_t orc_physical_cores(void);
 size_t orc_count_physical_cores_text(const char* cpuinfo_text);
 
+/* ---- [NEW] hybrid decoder stack (no reference model; see hybrid.cpp) --------- */
+typedef struct {
+  int kind; /* 0 = gated full attention, 1 = gated delta rule linear attention */
+  const float *norm1, *norm2;
+  const float* w_mix_in;  /* kind 0: [2*nq*ad + 2*nkv*ad, hidden] rows q|gate|k|v; kind 1: [4*gh*128, hidden] rows q|k|v|z */
+  const float* w_mix_out; /* [hidden, nq*ad] or [hidden, gh*128] */
+  const float *w_ab, *A_log, *dt_bias; /* kind 1: [2*gh, hidden], [gh], [gh] */
+  const float *w_gate, *w_up, *w_down;
+} orc_hybrid_layer_t;
+typedef struct {
+  size_t vocab, hidden, n_layers, n_heads, n_kv_heads, attn_head_dim, gdn_heads, intermediate, max_pos;
+  float rms_eps;
+  double rope_theta;
+  const float *tok_embed, *final_norm, *lm_head;
+  const orc_hybrid_layer_t* layers;
+} orc_hybrid_t;
+void* orc_hybrid_create(const orc_hybrid_t* desc);
+void orc_hybrid_destroy(void* model);
+int orc_hybrid_forward(void* model, const uint32_t* ids, size_t seq, float* hidden_out, float* logits_last);
+
 /* ---- crates/kernels/src/gated_delta_rule/cpu.rs -------------------------- */
 void orc_l2_norm_rows(float* x, size_t len, size_t k);
 void orc_cumsum(const float* g, size_t n, float* out);

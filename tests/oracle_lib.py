@@ -541,3 +541,61 @@ def from_bf16_bits(x):
 def bf16_round(x):
     """fp32 -> bf16 (round to nearest even) -> fp32."""
     return from_bf16_bits(to_bf16_bits(x))
+
+
+class HybridLayerW(C.Structure):
+    _fields_ = [("kind", C.c_int)] + [(n, f32p) for n in ("norm1", "norm2", "w_mix_in", "w_mix_out", "w_ab", "A_log", "dt_bias",
+                                                          "w_gate", "w_up", "w_down")]
+
+
+class HybridT(C.Structure):
+    _fields_ = [(n, c_sz) for n in ("vocab", "hidden", "n_layers", "n_heads", "n_kv_heads", "attn_head_dim", "gdn_heads",
+                                    "intermediate", "max_pos")] + [
+        ("rms_eps", C.c_float), ("rope_theta", C.c_double), ("tok_embed", f32p), ("final_norm", f32p), ("lm_head", f32p),
+        ("layers", C.POINTER(HybridLayerW))]
+
+
+lib.orc_hybrid_create.restype = C.c_void_p
+lib.orc_hybrid_create.argtypes = [C.c_void_p]
+lib.orc_hybrid_destroy.argtypes = [C.c_void_p]
+lib.orc_hybrid_destroy.restype = None
+lib.orc_hybrid_forward.argtypes = [C.c_void_p, u32p, c_sz, f32p, f32p]
+lib.orc_hybrid_forward.restype = C.c_int
+
+
+class OracleHybrid:
+    """The hybrid decoder stack on the CPU, one sequence per call, full recomputation.
+
+    ``weights``: tok_embed, final_norm, lm_head (fp32) and ``layers``: dicts with kind (0 full
+    attention, 1 linear attention), norm1, norm2, w_mix_in, w_mix_out, w_gate, w_up, w_down and, for
+    kind 1, w_ab, A_log, dt_bias (row layouts as in oracle.h)."""
+
+    def __init__(self, cfg, weights):
+        self.cfg, self._keep = cfg, weights
+        L = (HybridLayerW * cfg["n_layers"])()
+        for i, lw in enumerate(weights["layers"]):
+            L[i].kind = int(lw["kind"])
+            for n, _ in HybridLayerW._fields_[1:]:
+                if n in lw:
+                    assert lw[n].dtype == np.float32 and lw[n].flags["C_CONTIGUOUS"]
+                    setattr(L[i], n, P(lw[n]))
+        self._layers = L
+        d = HybridT(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["attn_head_dim"],
+                    cfg["gdn_heads"], cfg["intermediate"], cfg["max_pos"], cfg["rms_eps"], cfg["rope_theta"],
+                    P(weights["tok_embed"]), P(weights["final_norm"]), P(weights["lm_head"]), L)
+        self._h = C.c_void_p(lib.orc_hybrid_create(C.byref(d)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.orc_hybrid_destroy(self._h)
+            self._h = None
+
+    def forward(self, ids, logits=True):
+        """(hidden [seq, hidden] after the final norm, logits [vocab] of the last token)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        hid = np.empty((ids.size, self.cfg["hidden"]), np.float32)
+        lg = np.empty(self.cfg["vocab"], np.float32) if logits else None
+        rc = lib.orc_hybrid_forward(self._h, P(ids, u32p), c_sz(ids.size), P(hid), P(lg) if logits else None)
+        if rc:
+            raise ValueError(f"hybrid forward: error {rc}")
+        return hid, lg

@@ -11,8 +11,7 @@ from logismos_b200 import ops
 pytestmark = pytest.mark.gpu
 
 
-def run_case(lens, nh, nkv, causal, seed):
-    d = 128
+def run_case(lens, nh, nkv, causal, seed, d=128):
     rng = np.random.default_rng(seed)
     T = int(sum(lens))
     stride = (nh + 2 * nkv) * d
@@ -38,6 +37,12 @@ def test_stella_head_layout_ragged_lengths(causal):  # 12 q heads / 2 kv heads, 
 def test_other_gqa_layouts(nh, nkv):
     run_case([100, 17, 300], nh, nkv, False, nh)
     run_case([70, 260], nh, nkv, True, nh + 1)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_head_dim_256(causal):  # the hybrid decoder's full-attention layers: 16 q / 2 kv heads of 256
+    run_case([70, 1, 33, 200, 64], 16, 2, causal, 21, d=256)
+    run_case([129], 4, 4, causal, 22, d=256)
 
 
 def test_rejects_unsupported_head_dim():

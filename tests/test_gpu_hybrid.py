@@ -1,0 +1,81 @@
+"""The hybrid decoder step (linear-attention layers with recurrent state slots, gated full-attention
+layers over the paged KV cache, int4 weights, mixed prefill + decode) against per-sequence
+execution on the CPU oracle: every sequence of a packed step must come out as if its whole history
+had been run alone through the stack, lm_head and greedy argmax."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from gpu_util import TOL, max_rel
+from hybrid_weights import TINY_HYBRID, TINY_HYBRID_128, make_hybrid
+from logismos_b200.decoder import BlockAllocator
+from logismos_b200.embed import ComputeError
+from logismos_b200.hybrid import HybridModel, SlotAllocator
+
+pytestmark = pytest.mark.gpu
+
+
+def drive(cfg, seed, n_decode_steps):
+    qw, deq = make_hybrid(cfg, seed)
+    oracle = O.OracleHybrid(cfg, deq)
+    rng = np.random.default_rng(seed)
+    blocks, slots = BlockAllocator(64, 16, seed=3), SlotAllocator(8)
+    model = HybridModel(cfg, qw, n_pool_blocks=64, max_blocks_per_seq=16, max_step_tokens=512, max_step_seqs=8, n_state_slots=8)
+    hist = {}
+
+    def run(entries):
+        ids, cached, new, tabs, sl, order = [], [], [], [], [], []
+        for sid, toks in entries:
+            prev = hist.setdefault(sid, [])
+            cached.append(len(prev)); new.append(len(toks)); ids.extend(toks)
+            prev.extend(int(t) for t in toks)
+            tabs.append(blocks.ensure(sid, len(prev))); sl.append(slots.get(sid)); order.append(sid)
+        toks = model.step(ids, cached, new, np.stack(tabs), sl)
+        assert model.device_status() == 0
+        hs, lg = model.last_hidden(), model.last_logits()
+        for row, sid in enumerate(order):
+            h_ref, l_ref = oracle.forward(np.asarray(hist[sid], np.uint32))
+            assert max_rel(hs[row], h_ref[-1]) <= TOL, (sid, len(hist[sid]))
+            assert max_rel(lg[row], l_ref) <= TOL
+            assert toks[row] == O.greedy(lg[row])
+            assert l_ref[toks[row]] >= l_ref.max() - TOL * np.abs(l_ref).max()
+        return dict(zip(order, toks.tolist()))
+
+    V = cfg["vocab"]
+    nxt = run([(0, rng.integers(0, V, 40)), (1, rng.integers(0, V, 7)), (2, rng.integers(0, V, 100))])
+    nxt = run([(0, [nxt[0]]), (3, rng.integers(0, V, 33)), (1, [nxt[1]]), (2, [nxt[2]])])
+    for _ in range(n_decode_steps):
+        nxt = run([(sid, [nxt[sid]]) for sid in (2, 0, 3, 1)])
+    # a finished sequence gives its slot and blocks to a new one, which must start from the zero state
+    slots.release(1); blocks.release(1)
+    nxt.update(run([(7, rng.integers(0, V, 21)), (0, [nxt[0]])]))
+    run([(7, [nxt[7]]), (2, [nxt[2]])])
+    # a single-token sequence is a decode against an empty cache and a zero state
+    run([(9, [5])])
+    assert model.launches_last_step() > 0
+    model.close()
+
+
+def test_mixed_steps_equal_per_sequence_execution_head_dim_256():
+    drive(TINY_HYBRID, 21, 8)
+
+
+def test_mixed_steps_equal_per_sequence_execution_head_dim_128():
+    drive(TINY_HYBRID_128, 22, 4)
+
+
+def test_step_rejects_what_it_cannot_run():
+    qw, _ = make_hybrid(TINY_HYBRID_128, 3)
+    model = HybridModel(TINY_HYBRID_128, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2, n_state_slots=2)
+    tab = np.array([[0, 1, 2, 3, 4, 5, 6, 7]], np.int32)
+    with pytest.raises(ComputeError):   # a prefill continuing a cached sequence
+        model.step([1, 2, 3], [4], [3], tab, [0])
+    with pytest.raises(ComputeError):   # state slot outside the pool
+        model.step([1], [0], [1], tab, [2])
+    with pytest.raises(ComputeError):   # one slot for two sequences
+        model.step([1, 2], [0, 0], [1, 1], np.concatenate([tab, tab]), [1, 1])
+    with pytest.raises(ComputeError):   # more tokens than the step workspace
+        model.step([1] * 65, [0], [65], tab, [0])
+    with pytest.raises(Exception):      # beyond the block table
+        model.step([1], [128], [1], tab, [0])
+    model.close()

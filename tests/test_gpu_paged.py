@@ -47,8 +47,7 @@ def test_store_and_gather_equal_the_flat_cache_bit_for_bit():
         ops.paged_kv_gather(kp, vp, torch.tensor([-1], dtype=torch.int32, device=DEV), 3)
 
 
-def decode_case(ctx_lens, nh, nkv, chunk, seed, append=True):
-    d = 128
+def decode_case(ctx_lens, nh, nkv, chunk, seed, append=True, d=128):
     rng = np.random.default_rng(seed)
     n = len(ctx_lens)
     row = nkv * d
@@ -96,6 +95,11 @@ def test_decode_without_append_and_other_layouts():
     decode_case([40, 1025], 12, 2, 512, 5)   # Stella layout, 6 q heads per kv head
     decode_case([33, 200], 8, 8, 128, 6)     # no grouping
     decode_case([90], 16, 1, 64, 7)          # 16 q heads on one kv head
+
+
+def test_decode_head_dim_256():  # 16 q / 2 kv heads of 256, the hybrid decoder's full-attention layout
+    decode_case([1, 16, 17, 300, 1100, 64], 16, 2, 256, 31, d=256)
+    decode_case([45, 513], 8, 2, 512, 32, append=False, d=256)
 
 
 def test_block_id_outside_the_pool_is_reported_not_dereferenced():
