@@ -143,6 +143,24 @@ uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes_u8, const void* sc
 uint32_t logismos_launch_dequant_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
                                                void* out_bf16, int32_t n, int32_t k, void* stream);
 
+/* acc[m, n] += A[m, k] * dequant(W)[n, k]^T for 1 <= m <= 256 tokens, int4 group-32 weights (storage
+ * as above), dequantisation fused into the tensor-core operand pipeline. The linear of decode and
+ * small mixed steps: linear_t (cpu_f32/mod.rs:271-345) on the dequantised matrix. a bf16 [m, k]
+ * rows lda apart; acc fp32 [m, n] rows ldc apart (the fp32 residual stream itself for the output
+ * projections, or a zeroed workspace finished by the call below). Weights enter the MMA as
+ * bf16(code) * bf16(scale). k % 256 == 0. Slices of k meet in fp32 reductions: with several slices
+ * the last bits of acc may differ between runs. status_i32 as for logismos_launch_linear_t_bf16. */
+uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a_bf16, const void* codes_u8,
+                                                  const void* scales_f16, void* acc_f32, int32_t m,
+                                                  int32_t n, int32_t k, int32_t lda, int32_t ldc,
+                                                  void* status_i32, void* stream);
+/* Finishes an accumulation workspace: out bf16 [m, n] = acc (+ bias), or with swiglu != 0,
+ * out bf16 [m, n/2] = silu(gate) * up over columns interleaved in blocks of 32 (the LG_EPI_SWIGLU
+ * row order); acc is left zeroed for the next accumulation. n % 4 == 0 (n % 64 == 0 for swiglu). */
+uint32_t logismos_launch_qlinear_finish_bf16(void* acc_f32, const void* bias_f32, void* out_bf16,
+                                             int32_t m, int32_t n, int32_t ld_acc, int32_t ldc,
+                                             int32_t swiglu, void* stream);
+
 /* Paged-attention decode with fused KV append. The paged cache keeps the row layout of
  * FlatKvCache (crates/cache/src/flat.rs:36-69: one row = all kv heads of one token, contiguous):
  * k_pool / v_pool bf16 [n_pool_blocks, block_size = 16, n_kv_heads * head_dim]; logical token t
@@ -249,6 +267,10 @@ uint32_t logismos_launch_gdn_prepare(void* q_bf16, void* k_bf16, const void* a_f
 uint32_t logismos_launch_gated_mul_bf16(void* x_bf16, int32_t x_stride, const void* gate_bf16,
                                         int32_t gate_stride, int32_t rows, int32_t n, int32_t mode,
                                         void* stream);
+
+/* x[i] += d[i], fp32, n % 4 == 0: joins a partial sum that was reduced across tensor-parallel ranks
+ * into the residual stream (no reference counterpart: the reference has no tensor parallelism). */
+uint32_t logismos_launch_add_f32(void* x_f32, const void* d_f32, int64_t n, void* stream);
 
 /* decode::greedy (crates/decode/src/lib.rs:73-83): argmax per row, first maximum wins, NaN
  * never selected. logits bf16 or f32 [rows, n]; out u32 [rows]. */

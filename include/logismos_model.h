@@ -203,6 +203,16 @@ void lg_hybrid_destroy(void* model);
 uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* host_cached_lens,
                         const int32_t* host_new_lens, int32_t n_seqs, const int32_t* host_block_tables,
                         const int32_t* host_state_slots, uint32_t* host_next_tokens);
+/* Tensor-parallel form. A model created from a 1/tp slice of the heads and of the MLP (n_heads,
+ * n_kv_heads, gdn_heads, intermediate divided by tp; input projections sliced by rows, output
+ * projections by columns; embeddings, norms and lm_head replicated) produces partial sums in its
+ * output projections. With a reduction installed, each partial sum [tokens, hidden] is computed into
+ * a zeroed fp32 buffer, handed to `fn`, which must leave the sum over all ranks in place, ordered on
+ * `stream` (an NCCL all-reduce enqueued on it; it need not synchronise), and is then added to the
+ * residual stream. fn returns 0 on success. fn == NULL removes the reduction. No reference
+ * counterpart (the reference has no tensor parallelism). */
+typedef uint32_t (*lg_allreduce_f32_fn)(void* user, void* dev_buf_f32, uint64_t count, void* stream);
+uint32_t lg_hybrid_set_allreduce(void* model, lg_allreduce_f32_fn fn, void* user);
 uint32_t lg_hybrid_replay_device(void* model, void* stream);
 uint32_t lg_hybrid_last_hidden(void* model, int32_t n_seqs, float* host_out);
 uint32_t lg_hybrid_last_logits(void* model, int32_t n_seqs, float* host_out);

@@ -72,6 +72,8 @@ def _declare(l):
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
+        "logismos_launch_qlinear_int4_g32_acc_f32": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_qlinear_finish_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_attention_decode_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
                                                         i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_attention_decode_noalloc_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
@@ -94,6 +96,8 @@ def _declare(l):
         "lg_decoder_replay_device": [vp, vp],
         "lg_decoder_last_hidden": [vp, i32, vp],
         "lg_decoder_last_logits": [vp, i32, vp],
+        "logismos_launch_add_f32": [vp, vp, i64, vp],
+        "lg_hybrid_set_allreduce": [vp, vp, vp],
         "lg_hybrid_create": [i32, vp, vp, C.POINTER(vp)],
         "lg_hybrid_step": [vp, vp, vp, vp, i32, vp, vp, vp],
         "lg_hybrid_replay_device": [vp, vp],

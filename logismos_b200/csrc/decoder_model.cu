@@ -46,7 +46,7 @@ struct Decoder {
   QMat lm_head;
   std::vector<DLayer> layers;
   // workspace
-  Buf x, h, qkv, attn, qdec, gu, act, wscratch, last, last_bf16, logits, tokens, status;
+  Buf x, h, qkv, attn, qdec, gu, act, wscratch, accws, last, last_bf16, logits, tokens, status;
   Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch;
   // pinned staging (one block)
   uint8_t* pinned = nullptr;
@@ -54,17 +54,14 @@ struct Decoder {
   cudaStream_t stream = nullptr;
   std::mutex mu;
   // description of the last step (for replay and diagnostics)
-  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, pre_tokens = 0, max_pre_len = 0, total_chunks = 0, launches = 0;
+  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, pre_tokens = 0, max_pre_len = 0, total_chunks = 0, launches = 0, logits_f32 = 0;
   std::vector<int> order;  // internal slot -> caller's sequence index
   size_t max_chunks = 0;
 };
 
-// C = A W^T with int4 weights: expand to bf16, then the tcgen05 GEMM with the requested epilogue
 uint32_t qlinear(Decoder* m, const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc,
                  int epi, cudaStream_t s) {
-  LG_TRY(logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, m->wscratch.p, w.n, w.k, s), "dequant_int4");
-  LG_TRY(logismos_launch_linear_t_bf16(a, m->wscratch.p, bias, out, T, w.n, w.k, lda, ldc, epi, m->status.p, s), "linear_t");
-  m->launches += 2;
+  LG_TRY(qlinear_any(a, w, bias, out, T, lda, ldc, epi, m->wscratch.p, m->accws.p, m->status.p, &m->launches, s), "int4 linear");
   return 0;
 }
 
@@ -110,15 +107,13 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
   LG_TRY(logismos_launch_gather_rows_f32(m->x.p, m->last_idx.p, m->last.p, m->n_seqs, H, T, st, s), "gather_rows");
   LG_TRY(logismos_launch_rms_norm_f32(m->last.p, m->final_norm.p, m->last_bf16.p, m->n_seqs, H, c.rms_eps, 0, s), "final_norm");
   m->launches += 2;
-  // batches of 32 keep the staged activations of the streaming GEMV within one CTA's shared memory
-  for (int b0 = 0; b0 < m->n_seqs; b0 += 32) {
-    const int nb = m->n_seqs - b0 < 32 ? m->n_seqs - b0 : 32;
-    LG_TRY(logismos_launch_gemv_int4_g32_bf16(m->lm_head.codes.p, m->lm_head.scales.p, (uint16_t*)m->last_bf16.p + (size_t)b0 * H,
-                                              (uint16_t*)m->logits.p + (size_t)b0 * c.vocab, nb, c.vocab, H, s), "lm_head");
-    m->launches += 1;
+  if (uint32_t rc = lm_head_and_greedy(m->lm_head, m->last_bf16.p, m->logits.p, m->tokens.p, m->n_seqs, H, st, &m->logits_f32,
+                                       &m->launches, s)) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "lm_head / greedy failed: %s (code %u)", cudaGetErrorString((cudaError_t)rc), rc);
+    set_error(buf);
+    return LG_EMB_COMPUTE;
   }
-  LG_TRY(logismos_launch_greedy_argmax(m->logits.p, 0, m->tokens.p, m->n_seqs, c.vocab, s), "greedy");
-  m->launches += 1;
   return 0;
 }
 
@@ -187,14 +182,16 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
   if (2 * I * H > wmax) wmax = 2 * I * H;
   // every sequence of a step may be a decode sequence of up to max_blocks_per_seq blocks
   m->max_chunks = S * ((MB * kBlock + kChunkTokens - 1) / kChunkTokens);
+  const size_t acc_n = QKV > 2 * I ? QKV : 2 * I;
   ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
        m->qdec.alloc(S * H * 2) && m->gu.alloc(16) && m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) &&
-       m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) && m->logits.alloc(S * (size_t)c.vocab * 2) &&
+       m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) && m->logits.alloc(S * (size_t)c.vocab * 4) && m->accws.alloc((size_t)kFusedDequantMaxRows * acc_n * 4) &&
        m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->slots.alloc(T * 8) &&
        m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&
        m->dec_chunks.alloc((S + 1) * 4) &&
        m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim));
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
+  ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4;
   ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -212,7 +209,7 @@ void lg_decoder_destroy(void* model) {
   Decoder* m = static_cast<Decoder*>(model);
   cudaSetDevice(m->device);
   Buf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->qkv,
-                 &m->attn, &m->qdec, &m->gu, &m->act, &m->wscratch, &m->last, &m->last_bf16, &m->logits, &m->tokens, &m->status,
+                 &m->attn, &m->qdec, &m->gu, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens, &m->status,
                  &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
@@ -342,8 +339,14 @@ uint32_t lg_decoder_last_logits(void* model, int32_t n_seqs, float* host_out) {
   if (n_seqs != m->n_seqs) { set_error("lg_decoder_last_logits: n_seqs differs from the last step"); return LG_EMB_COMPUTE; }
   cudaSetDevice(m->device);
   const size_t V = m->cfg.vocab;
-  std::vector<uint16_t> tmp((size_t)n_seqs * V);
   LG_TRY(cudaDeviceSynchronize(), "device synchronize");
+  if (m->logits_f32) {
+    std::vector<float> tmp((size_t)n_seqs * V);
+    LG_TRY(cudaMemcpy(tmp.data(), m->logits.p, tmp.size() * 4, cudaMemcpyDeviceToHost), "D2H logits");
+    for (int k = 0; k < n_seqs; ++k) std::memcpy(host_out + (size_t)m->order[k] * V, tmp.data() + (size_t)k * V, V * 4);
+    return LG_EMB_OK;
+  }
+  std::vector<uint16_t> tmp((size_t)n_seqs * V);
   LG_TRY(cudaMemcpy(tmp.data(), m->logits.p, tmp.size() * 2, cudaMemcpyDeviceToHost), "D2H logits");
   for (int k = 0; k < n_seqs; ++k)
     for (size_t j = 0; j < V; ++j) {

@@ -383,3 +383,23 @@ extern "C" uint32_t logismos_launch_gated_mul_bf16(void* x, int32_t x_stride, co
       (__nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate, gate_stride, rows, n, mode);
   return lg::launch_status();
 }
+
+// ---- x += d (fp32): joins an all-reduced partial sum into the residual stream ------------------
+namespace {
+__global__ void add_f32_kernel(float* __restrict__ x, const float* __restrict__ d, int64_t n4) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 a = reinterpret_cast<float4*>(x)[i];
+  const float4 b = __ldg(reinterpret_cast<const float4*>(d) + i);
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  reinterpret_cast<float4*>(x)[i] = a;
+}
+}  // namespace
+
+extern "C" uint32_t logismos_launch_add_f32(void* x, const void* d, int64_t n, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (n < 0 || (n % 4) || ((uintptr_t)x & 15) || ((uintptr_t)d & 15)) return lg::kInvalidValue;
+  if (n == 0) return 0;
+  add_f32_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)x, (const float*)d, n / 4);
+  return lg::launch_status();
+}

@@ -50,21 +50,38 @@ struct Hybrid {
   Buf tok_embed, final_norm, cos, sin;
   QMat lm_head;
   std::vector<HLayer> layers;
-  Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, last, last_bf16, logits, tokens, status;
+  Buf delta;  // partial sum of an output projection when a cross-rank reduction is installed
+  lg_allreduce_f32_fn allreduce = nullptr;
+  void* allreduce_user = nullptr;
+  Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
   Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, state_slots, fresh;
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
   cudaStream_t stream = nullptr;
   std::mutex mu;
-  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, max_pre_len = 0, total_chunks = 0, launches = 0;
+  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, max_pre_len = 0, total_chunks = 0, launches = 0, logits_f32 = 0;
   std::vector<int> order;
   size_t max_chunks = 0;
 };
 
 uint32_t qlinear(Hybrid* m, const void* a, const QMat& w, void* out, int T, int lda, int ldc, int epi, cudaStream_t s) {
-  LG_TRY(logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, m->wscratch.p, w.n, w.k, s), "dequant_int4");
-  LG_TRY(logismos_launch_linear_t_bf16(a, m->wscratch.p, nullptr, out, T, w.n, w.k, lda, ldc, epi, m->status.p, s), "linear_t");
-  m->launches += 2;
+  LG_TRY(qlinear_any(a, w, nullptr, out, T, lda, ldc, epi, m->wscratch.p, m->accws.p, m->status.p, &m->launches, s), "int4 linear");
+  return 0;
+}
+
+// x += A W^T for an output projection; with a cross-rank reduction installed the local partial sum
+// is reduced over the ranks before it joins the residual stream
+uint32_t out_proj(Hybrid* m, const void* a, const QMat& w, int T, int lda, cudaStream_t s) {
+  const int H = m->cfg.hidden;
+  if (!m->allreduce) return qlinear(m, a, w, m->x.p, T, lda, H, LG_EPI_RESID_F32, s);
+  LG_TRY(cudaMemsetAsync(m->delta.p, 0, (size_t)T * H * 4, s), "memset partial sum");
+  if (uint32_t rc = qlinear(m, a, w, m->delta.p, T, lda, H, LG_EPI_RESID_F32, s)) return rc;
+  if (m->allreduce(m->allreduce_user, m->delta.p, (uint64_t)T * H, (void*)s) != 0) {
+    set_error("the installed all-reduce reported a failure");
+    return LG_EMB_COMPUTE;
+  }
+  LG_TRY(logismos_launch_add_f32(m->x.p, m->delta.p, (int64_t)T * H, s), "add partial sum");
+  m->launches += 1;
   return 0;
 }
 
@@ -106,7 +123,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       }
       LG_TRY(logismos_launch_gated_mul_bf16(m->mix.p, QW, p16 + QW + 2 * KW, AN, T, QW, 0, s), "attention gate");
       m->launches += 1;
-      if (uint32_t rc = qlinear(m, m->mix.p, L.w_out, m->x.p, T, QW, H, LG_EPI_RESID_F32, s)) return rc;
+      if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, QW, s)) return rc;
     } else {
       // columns: q [GW] | k [GW] | v [GW] | z [GW]; a | b as fp32 [T, 2 GH] through the accumulate epilogue
       if (uint32_t rc = qlinear(m, m->h.p, L.w_in, m->proj.p, T, H, GN, LG_EPI_BF16, s)) return rc;
@@ -119,24 +136,23 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
              "gdn recurrence");
       LG_TRY(logismos_launch_gated_mul_bf16(m->mix.p, GW, p16 + 3 * GW, GN, T, GW, 1, s), "linear-attention gate");
       m->launches += 4;
-      if (uint32_t rc = qlinear(m, m->mix.p, L.w_out, m->x.p, T, GW, H, LG_EPI_RESID_F32, s)) return rc;
+      if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
     }
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
     m->launches += 1;
     if (uint32_t rc = qlinear(m, m->h.p, L.wgu, m->act.p, T, H, I, LG_EPI_SWIGLU, s)) return rc;
-    if (uint32_t rc = qlinear(m, m->act.p, L.wdown, m->x.p, T, I, H, LG_EPI_RESID_F32, s)) return rc;
+    if (uint32_t rc = out_proj(m, m->act.p, L.wdown, T, I, s)) return rc;
   }
   LG_TRY(logismos_launch_gather_rows_f32(m->x.p, m->last_idx.p, m->last.p, m->n_seqs, H, T, st, s), "gather_rows");
   LG_TRY(logismos_launch_rms_norm_f32(m->last.p, m->final_norm.p, m->last_bf16.p, m->n_seqs, H, c.rms_eps, 0, s), "final_norm");
   m->launches += 2;
-  for (int b0 = 0; b0 < m->n_seqs; b0 += 32) {
-    const int nb = m->n_seqs - b0 < 32 ? m->n_seqs - b0 : 32;
-    LG_TRY(logismos_launch_gemv_int4_g32_bf16(m->lm_head.codes.p, m->lm_head.scales.p, (uint16_t*)m->last_bf16.p + (size_t)b0 * H,
-                                              (uint16_t*)m->logits.p + (size_t)b0 * c.vocab, nb, c.vocab, H, s), "lm_head");
-    m->launches += 1;
+  if (uint32_t rc = lm_head_and_greedy(m->lm_head, m->last_bf16.p, m->logits.p, m->tokens.p, m->n_seqs, H, st, &m->logits_f32,
+                                       &m->launches, s)) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "lm_head / greedy failed: %s (code %u)", cudaGetErrorString((cudaError_t)rc), rc);
+    set_error(buf);
+    return LG_EMB_COMPUTE;
   }
-  LG_TRY(logismos_launch_greedy_argmax(m->logits.p, 0, m->tokens.p, m->n_seqs, c.vocab, s), "greedy");
-  m->launches += 1;
   return 0;
 }
 
@@ -192,20 +208,17 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
   m->layers.resize(c.n_layers);
   const size_t pool_bytes = (size_t)c.n_pool_blocks * kBlock * KW * 2;
   const size_t state_bytes = (size_t)c.n_state_slots * GH * kGdnDim * kGdnDim * 4;
-  bool any_full = false, any_lin = false;
   for (int l = 0; l < c.n_layers && ok; ++l) {
     const lg_hybrid_layer_weights_t& lw = w->layers[l];
     HLayer& L = m->layers[l];
     L.full = (l + 1) % c.full_attn_interval == 0;
     ok = ok && L.norm1.upload(lw.norm1, (size_t)H * 4) && L.norm2.upload(lw.norm2, (size_t)H * 4);
     if (L.full) {
-      any_full = true;
       ok = ok && upload_q(L.w_in, {&lw.wq, &lw.wk, &lw.wv, &lw.wgate}, {QW, KW, KW, QW}, H);
       ok = ok && upload_q(L.w_out, {&lw.wo}, {H}, QW);
       ok = ok && L.kpool.alloc(pool_bytes) && L.vpool.alloc(pool_bytes);
       ok = ok && cudaMemset(L.kpool.p, 0, pool_bytes) == cudaSuccess && cudaMemset(L.vpool.p, 0, pool_bytes) == cudaSuccess;
     } else {
-      any_lin = true;
       if (!lw.A_log || !lw.dt_bias) { ok = false; break; }
       ok = ok && upload_q(L.w_in, {&lw.wq, &lw.wk, &lw.wv, &lw.wgate}, {GW, GW, GW, GW}, H);
       ok = ok && upload_q(L.w_ab, {&lw.wa, &lw.wb}, {GH, GH}, H);
@@ -227,23 +240,23 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
       }
     ok = ok && m->cos.upload(cs.data(), cs.size() * 4) && m->sin.upload(sn.data(), sn.size() * 4);
   }
-  (void)any_full;
-  (void)any_lin;
   const size_t T = c.max_step_tokens, S = c.max_step_seqs, MB = c.max_blocks_per_seq;
   const size_t pn = (size_t)(m->attn_n > m->gdn_n ? m->attn_n : m->gdn_n);
   size_t wmax = pn * H;
   if ((size_t)2 * I * H > wmax) wmax = (size_t)2 * I * H;
   if ((size_t)m->mix_w * H > wmax) wmax = (size_t)m->mix_w * H;
   m->max_chunks = S * ((MB * kBlock + kChunkTokens - 1) / kChunkTokens);
-  ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->proj.alloc(T * pn * 2) && m->mix.alloc(T * m->mix_w * 2) &&
+  const size_t acc_n = pn > (size_t)2 * I ? pn : (size_t)2 * I;
+  ok = ok && m->x.alloc(T * H * 4) && m->delta.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->proj.alloc(T * pn * 2) && m->mix.alloc(T * m->mix_w * 2) &&
        m->qdec.alloc(S * QW * 2) && m->ab.alloc(T * 2 * GH * 4) && m->g.alloc(T * GH * 4) && m->beta.alloc(T * GH * 4) &&
        m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) && m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) &&
-       m->logits.alloc(S * (size_t)c.vocab * 2) && m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) &&
+       m->logits.alloc(S * (size_t)c.vocab * 4) && m->accws.alloc((size_t)kFusedDequantMaxRows * acc_n * 4) && m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) &&
        m->pos.alloc(T * 4) && m->slots.alloc(T * 8) && m->cu_all.alloc((S + 1) * 4) && m->cu_prefill.alloc((S + 1) * 4) &&
        m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) && m->dec_chunks.alloc((S + 1) * 4) &&
        m->state_slots.alloc(S * 4) && m->fresh.alloc(S) &&
        m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim));
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
+  ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4 + S + 64;
   ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -260,8 +273,8 @@ void lg_hybrid_destroy(void* model) {
   if (!model) return;
   Hybrid* m = static_cast<Hybrid*>(model);
   cudaSetDevice(m->device);
-  Buf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
-                 &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->last, &m->last_bf16, &m->logits, &m->tokens,
+  Buf* bufs[] = {&m->delta, &m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
+                 &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens,
                  &m->status, &m->ids, &m->pos, &m->slots, &m->cu_all, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables,
                  &m->dec_chunks, &m->dec_scratch, &m->state_slots, &m->fresh};
   for (Buf* b : bufs) b->release();
@@ -377,6 +390,15 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
   return LG_EMB_OK;
 }
 
+uint32_t lg_hybrid_set_allreduce(void* model, lg_allreduce_f32_fn fn, void* user) {
+  Hybrid* m = static_cast<Hybrid*>(model);
+  if (!m) { set_error("lg_hybrid_set_allreduce: null model"); return LG_EMB_COMPUTE; }
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->allreduce = fn;
+  m->allreduce_user = user;
+  return LG_EMB_OK;
+}
+
 uint32_t lg_hybrid_replay_device(void* model, void* stream) {
   Hybrid* m = static_cast<Hybrid*>(model);
   if (!m || m->T <= 0) { set_error("lg_hybrid_replay_device: no step has run"); return LG_EMB_COMPUTE; }
@@ -391,7 +413,15 @@ uint32_t lg_hybrid_last_hidden(void* model, int32_t n_seqs, float* host_out) {
 
 uint32_t lg_hybrid_last_logits(void* model, int32_t n_seqs, float* host_out) {
   Hybrid* m = static_cast<Hybrid*>(model);
-  return read_rows_bf16(m, m->logits, n_seqs, (size_t)m->cfg.vocab, host_out, "lg_hybrid_last_logits");
+  if (!m->logits_f32) return read_rows_bf16(m, m->logits, n_seqs, (size_t)m->cfg.vocab, host_out, "lg_hybrid_last_logits");
+  if (n_seqs != m->n_seqs) { set_error("lg_hybrid_last_logits: n_seqs differs from the last step"); return LG_EMB_COMPUTE; }
+  cudaSetDevice(m->device);
+  const size_t V = (size_t)m->cfg.vocab;
+  std::vector<float> tmp((size_t)n_seqs * V);
+  LG_TRY(cudaDeviceSynchronize(), "device synchronize");
+  LG_TRY(cudaMemcpy(tmp.data(), m->logits.p, tmp.size() * 4, cudaMemcpyDeviceToHost), "D2H logits");
+  for (int k = 0; k < n_seqs; ++k) std::memcpy(host_out + (size_t)m->order[k] * V, tmp.data() + (size_t)k * V, V * 4);
+  return LG_EMB_OK;
 }
 
 int32_t lg_hybrid_launches_last_step(const void* model) { return static_cast<const Hybrid*>(model)->launches; }

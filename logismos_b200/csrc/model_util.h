@@ -8,6 +8,7 @@
 #include <string>
 #include <vector>
 
+#include "logismos_kernels.h"
 #include "logismos_model.h"
 
 namespace lgm {
@@ -62,6 +63,61 @@ inline bool upload_q(QMat& q, const std::vector<const lg_int4_matrix_t*>& parts,
   q.n = (int)n;
   q.k = k;
   return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
+}
+
+// C = A W^T with int4 weights, epilogue as for logismos_launch_linear_t_bf16. Up to 256 rows the
+// dequantisation is fused into the tensor-core kernel (fp32 accumulation into the residual stream
+// itself, or into the zeroed workspace `accws` finished to bf16); above that the weights are
+// expanded to bf16 once into `wscratch` and the dense GEMM runs with its fused epilogues.
+constexpr int kFusedDequantMaxRows = 256;
+inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc, int epi,
+                            void* wscratch, void* accws, void* status, int* launches, cudaStream_t s) {
+  uint32_t rc;
+  if (T <= kFusedDequantMaxRows && w.k % 256 == 0) {
+    if (epi == LG_EPI_RESID_F32 && !bias) {
+      *launches += 1;
+      return logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);
+    }
+    if (epi != LG_EPI_RESID_F32) {
+      rc = logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, accws, T, w.n, w.k, lda, w.n, status, s);
+      if (rc) return rc;
+      *launches += 2;
+      return logismos_launch_qlinear_finish_bf16(accws, bias, out, T, w.n, w.n, ldc, epi == LG_EPI_SWIGLU ? 1 : 0, s);
+    }
+  }
+  rc = logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, wscratch, w.n, w.k, s);
+  if (rc) return rc;
+  *launches += 2;
+  return logismos_launch_linear_t_bf16(a, wscratch, bias, out, T, w.n, w.k, lda, ldc, epi, status, s);
+}
+
+// logits = hidden W^T over the vocabulary and decode::greedy (crates/decode/src/lib.rs:73-83) on
+// them. Up to 16 rows the streaming int4 GEMV writes bf16 logits; above that the fused-dequant
+// tensor-core kernel accumulates fp32 logits into the zeroed buffer (which must hold rows * vocab
+// floats). *logits_f32 tells the caller which it was.
+inline uint32_t lm_head_and_greedy(const QMat& lm_head, const void* hidden_bf16, void* logits, void* tokens, int rows, int hidden,
+                                   void* status, int* logits_f32, int* launches, cudaStream_t s) {
+  uint32_t rc;
+  const int vocab = lm_head.n;
+  if (rows > 16 && hidden % 256 == 0) {
+    *logits_f32 = 1;
+    for (int b0 = 0; b0 < rows; b0 += kFusedDequantMaxRows) {
+      const int nb = rows - b0 < kFusedDequantMaxRows ? rows - b0 : kFusedDequantMaxRows;
+      float* dst = (float*)logits + (size_t)b0 * vocab;
+      if (cudaMemsetAsync(dst, 0, (size_t)nb * vocab * 4, s) != cudaSuccess) return (uint32_t)cudaGetLastError();
+      rc = logismos_launch_qlinear_int4_g32_acc_f32((const uint16_t*)hidden_bf16 + (size_t)b0 * hidden, lm_head.codes.p,
+                                                    lm_head.scales.p, dst, nb, vocab, hidden, hidden, vocab, status, s);
+      if (rc) return rc;
+      *launches += 1;
+    }
+  } else {
+    *logits_f32 = 0;
+    rc = logismos_launch_gemv_int4_g32_bf16(lm_head.codes.p, lm_head.scales.p, hidden_bf16, logits, rows, vocab, hidden, s);
+    if (rc) return rc;
+    *launches += 1;
+  }
+  *launches += 1;
+  return logismos_launch_greedy_argmax(logits, *logits_f32, tokens, rows, vocab, s);
 }
 
 }  // namespace lgm

@@ -111,6 +111,13 @@ class HybridModel:
         self._n = n
         return out
 
+    def set_allreduce(self, fn):
+        """Installs (or with None removes) the cross-rank reduction of the output projections' partial
+        sums: a ``tp.ALLREDUCE_FN`` callback (kept alive by this object)."""
+        self._allreduce = fn
+        if lib.lg_hybrid_set_allreduce(self._h, C.cast(fn, C.c_void_p) if fn is not None else None, None):
+            raise ComputeError(lib.lg_last_error().decode())
+
     def replay_device(self, stream_ptr: int):
         if lib.lg_hybrid_replay_device(self._h, C.c_void_p(stream_ptr)):
             raise ComputeError(lib.lg_last_error().decode())
@@ -132,3 +139,29 @@ class HybridModel:
 
     def device_status(self) -> int:
         return int(lib.lg_hybrid_device_status(self._h))
+
+
+# the serving-sweep architecture: 48 layers, three linear-attention layers per full-attention layer
+HYBRID_SERVING = dict(vocab=151936, hidden=2048, n_layers=48, n_heads=16, n_kv_heads=2, attn_head_dim=256, gdn_heads=16,
+                      intermediate=6144, max_pos=32768, full_attn_interval=4, rms_eps=1e-6, rope_theta=1e7)
+
+
+def random_int4_weights(cfg: dict, seed: int) -> dict:
+    """Seeded random int4 group-32 weights of the hybrid architecture for benchmarks (uniform codes,
+    half-normal scales of 0.25 / sqrt(k)). Layers of one kind share their host arrays; every layer
+    still gets its own copy on the device."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    H, I, GH = cfg["hidden"], cfg["intermediate"], cfg["gdn_heads"]
+    QW, KW, GW = cfg["n_heads"] * cfg["attn_head_dim"], cfg["n_kv_heads"] * cfg["attn_head_dim"], GH * 128
+
+    def qmat(n, k):
+        return (rng.integers(0, 256, (n, k // 2), dtype=np.uint8),
+                np.abs(rng.standard_normal((n, k // 32), dtype=np.float32) * (0.25 / np.sqrt(k))).astype(np.float16))
+
+    mlp = {"w_gate": qmat(I, H), "w_up": qmat(I, H), "w_down": qmat(H, I), "norm1": np.ones(H, np.float32), "norm2": np.ones(H, np.float32)}
+    full = dict(mlp, wq=qmat(QW, H), wgate=qmat(QW, H), wk=qmat(KW, H), wv=qmat(KW, H), wo=qmat(H, QW))
+    lin = dict(mlp, wq=qmat(GW, H), wk=qmat(GW, H), wv=qmat(GW, H), wgate=qmat(GW, H), wo=qmat(H, GW), wa=qmat(GH, H), wb=qmat(GH, H),
+               A_log=np.log(rng.uniform(0.5, 4.0, GH)).astype(np.float32), dt_bias=rng.uniform(-3.0, 0.0, GH).astype(np.float32))
+    return {"tok_embed": rng.standard_normal((cfg["vocab"], H), dtype=np.float32) * np.float32(0.5), "final_norm": np.ones(H, np.float32),
+            "lm_head": qmat(cfg["vocab"], H),
+            "layers": [full if is_full_attention(l, cfg["full_attn_interval"]) else lin for l in range(cfg["n_layers"])]}

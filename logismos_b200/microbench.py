@@ -4,6 +4,7 @@ stream, operands rotated over several copies so that every launch reads from HBM
 
   python -m logismos_b200.microbench gemv  [--n N --k K --batch B --iters I]
   python -m logismos_b200.microbench gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
+  python -m logismos_b200.microbench qlinear [--m M --n N --k K --iters I]   (m <= 256, fused int4 dequant)
   python -m logismos_b200.microbench paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
   python -m logismos_b200.microbench attn  [--seqs S --len L --iters I]
   python -m logismos_b200.microbench sweep          (every benchmark shape, one JSON line each)
@@ -87,6 +88,29 @@ def bench_gemv(n, k, batch, iters, copies=None, pk=None):
             "TFLOPs": 2.0 * batch * n * k / t / 1e12, "peak": pk["hbm"], "peak_src": pk["src"], "weight_copies": copies}
 
 
+def bench_qlinear(m, n, k, iters, copies=None, pk=None):
+    """Fused-dequant tensor-core linear for m <= 256 tokens, accumulating into fp32."""
+    pk = pk or peaks()
+    wbytes = n * k // 2 + n * (k // 32) * 2
+    copies = copies or max(2, min(16, int(300e6 // wbytes) + 1))
+    codes = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+    scales = [(torch.rand((n, k // 32), device="cuda") * 0.02).to(torch.float16) for _ in range(copies)]
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    acc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run(i):
+        ops.check(lib.logismos_launch_qlinear_int4_g32_acc_f32(x.data_ptr(), codes[i % copies].data_ptr(), scales[i % copies].data_ptr(),
+                                                               acc.data_ptr(), m, n, k, k, n, status.data_ptr(),
+                                                               torch.cuda.current_stream().cuda_stream), "qlinear")
+    t = timeit(run, iters)
+    by = wbytes + m * k * 2 + m * n * 4
+    fl = 2.0 * m * n * k
+    return {"kernel": "qlinear_int4_tcgen05", "m": m, "n": n, "k": k, "bytes": by, "us": t * 1e6, "GBps": by / t / 1e9,
+            "frac_hbm": by / t / 1e9 / pk["hbm"], "TFLOPs": fl / t / 1e12, "frac_tensor": fl / t / 1e12 / pk["tf"],
+            "device_status": int(status.item()), "peak_src": pk["src"], "weight_copies": copies}
+
+
 def bench_gemm(m, n, k, epi, iters, pk=None):
     pk = pk or peaks()
     a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
@@ -152,7 +176,7 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="logismos_b200.microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "paged", "attn", "sweep"])
+    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "paged", "attn", "sweep"])
     ap.add_argument("--m", type=int, default=2176)
     ap.add_argument("--n", type=int, default=151936)
     ap.add_argument("--k", type=int, default=1536)
@@ -172,6 +196,8 @@ def main(argv=None):
         print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
     elif a.what == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.epi, a.iters)))
+    elif a.what == "qlinear":
+        print(json.dumps(bench_qlinear(a.m, a.n, a.k, a.iters)))
     elif a.what == "paged":
         print(json.dumps(bench_paged(a.seqs, a.min_ctx, a.max_ctx, a.chunk, a.iters)))
     elif a.what == "attn":
@@ -181,6 +207,9 @@ def main(argv=None):
         for (n, k) in [(1536, 1536), (8960, 1536), (1536, 8960), (151936, 1536)]:
             for b in (1, 4, 16, 64):
                 print(json.dumps(bench_gemv(n, k, b, a.iters, pk=pk)), flush=True)
+        for (n, k) in [(8192, 2048), (2048, 2048), (12288, 2048), (2048, 6144), (151936, 2048)]:
+            for m in (16, 64, 128, 256):
+                print(json.dumps(bench_qlinear(m, n, k, a.iters, pk=pk)), flush=True)
         print(json.dumps(bench_paged(256, 128, 32768, 512, 10, pk=pk)), flush=True)
         for (n, k, epi) in [(2048, 1536, "bf16"), (1536, 1536, "resid"), (17920, 1536, "swiglu"), (1536, 8960, "resid")]:
             print(json.dumps(bench_gemm(a.m, n, k, epi, a.iters, pk=pk)), flush=True)

@@ -30,7 +30,7 @@ def _p(t):
     return C.c_void_p(0) if t is None else C.c_void_p(t.data_ptr())
 
 
-def _req(t, name, dtype, rank=None):
+def _req(t, name, dtype, rank=None, contiguous=True):
     if not isinstance(t, torch.Tensor):
         raise InvalidOp(f"{name}: not a tensor")
     if t.device.type != "cuda":
@@ -39,7 +39,7 @@ def _req(t, name, dtype, rank=None):
         raise InvalidOp(f"{name}: expected {dtype}, got {t.dtype}")
     if rank is not None and t.dim() != rank:
         raise InvalidOp(f"{name}: expected rank {rank}, got {t.dim()}")
-    if not t.is_contiguous():
+    if contiguous and not t.is_contiguous():
         raise InvalidOp(f"{name}: must be contiguous")
 
 
@@ -234,6 +234,37 @@ def dequant_int4(codes, scales, sync=True):
     out = torch.empty((n, k), dtype=torch.bfloat16, device=codes.device)
     with torch.cuda.device(codes.device):
         check(lib.logismos_launch_dequant_int4_g32_bf16(_p(codes), _p(scales), _p(out), n, k, _stream()), "dequant_int4_g32")
+        _done(sync)
+    return out
+
+
+def qlinear_int4_acc_(acc, a, codes, scales, sync=True):
+    """acc f32 [m, n] += a bf16 [m, k] @ dequant(codes, scales)[n, k]^T for m <= 256 (fused dequant on
+    the tensor cores). Rows of a and acc may be strided. Returns the device status word's tensor."""
+    _req(a, "a", torch.bfloat16, 2, contiguous=False); _req(acc, "acc", torch.float32, 2, contiguous=False)
+    _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2)
+    m, k = a.shape
+    n = codes.shape[0]
+    if codes.shape[1] * 2 != k or scales.shape != (n, k // 32) or acc.shape != (m, n) or a.stride(1) != 1 or acc.stride(1) != 1:
+        raise InvalidOp("qlinear_int4_acc_: shape mismatch")
+    if not (1 <= m <= 256) or k % 256:
+        raise InvalidOp("qlinear_int4_acc_: needs 1 <= m <= 256 and k % 256 == 0")
+    status = torch.zeros(1, dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        check(lib.logismos_launch_qlinear_int4_g32_acc_f32(_p(a), _p(codes), _p(scales), _p(acc), m, n, k, a.stride(0), acc.stride(0),
+                                                           _p(status), _stream()), "qlinear_int4_g32")
+        _done(sync)
+    return status
+
+
+def qlinear_finish(acc, bias=None, swiglu=False, sync=True):
+    """bf16 [m, n] = acc (+ bias), or SwiGLU over the 32-interleaved gate/up columns -> [m, n/2]; zeroes acc."""
+    _req(acc, "acc", torch.float32, 2)
+    m, n = acc.shape
+    out = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=acc.device)
+    with torch.cuda.device(acc.device):
+        check(lib.logismos_launch_qlinear_finish_bf16(_p(acc), _p(bias) if bias is not None else None, _p(out), m, n, n, out.shape[1],
+                                                      int(swiglu), _stream()), "qlinear_finish")
         _done(sync)
     return out
 
