@@ -7,18 +7,24 @@
 //
 // The weights, not the tokens, fill the 128 rows of the MMA (D[128 weight rows, NT tokens]), so the
 // tensor work scales with the real token count and the kernel stays bound by the int4 stream up to
-// about 64 tokens. The work is cut into units (128 weight rows x 256 values of k); persistent CTAs
-// (two per SM up to 64 tokens) each take a contiguous, equal span of units, and consecutive units of
-// one weight tile form one accumulation with one epilogue. 16 warps:
+// about 64 tokens. The work is cut into units (128 weight rows x 256 values of k); one persistent
+// CTA per SM takes a contiguous, equal span of units, and consecutive units of one weight tile form
+// one accumulation with one epilogue. 24 warps:
 //   warp 0      TMA producer of the raw int4 tiles: codes [128 rows x 128 B] (128-byte swizzle) and
-//               fp16 scales [128 rows x 8] per 256 values of k, ring of 2
-//   warp 1      TMA producer of the activation tiles [NT x 64] bf16 (128-byte swizzle), ring of 3
-//   warp 2      allocates TMEM, issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=NT, K=16)
-//               with fp32 accumulators in TMEM, two accumulator buffers
-//   warps 4-11  dequantise: thread = (weight row, 32-value group); nibble pairs -> bf16 by byte
-//               permute + one logic op (exact 136 + q), minus 136, times the group scale in bf16x2,
-//               written as the 128-byte-swizzled K-major tile the MMA descriptor expects
-//   warps 12-15 epilogue: read the accumulator from TMEM (lane = weight row, column = token) and add
+//               fp16 scales [128 rows x 8] per 256 values of k, ring of 3
+//   warp 1      TMA producer of the activation tiles [NT x 64] bf16 (128-byte swizzle), its own ring
+//               of three 32 KB stages so that their L2 latency stays off the critical path
+//   warps 2, 3  one thread each issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=NT, K=16) for two
+//               of the four k blocks of every unit, the weight operand read from TMEM and the
+//               activations from shared memory, into its own fp32 accumulators in TMEM (warp 2 also
+//               allocates the tensor memory)
+//   warps 4-19  dequantise: four groups of four warps, group g owns k block g of every unit; thread =
+//               one weight row x 64 values; the raw stage is released as soon as it is in registers;
+//               nibble pairs -> bf16 by byte permute + one logic op (exact 136 + q), minus 136, times
+//               the group scale in bf16x2, stored with one tcgen05.st into the tensor-memory tile the
+//               MMA reads as its row operand (lane = weight row, column = two values of k), so the
+//               expanded weights never pass through shared memory
+//   warps 20-23 epilogue: read the accumulator from TMEM (lane = weight row, column = token) and add
 //               it to acc with fire-and-forget fp32 reductions, one coalesced 128-byte row segment
 //               per instruction, while the other accumulator buffer is being filled
 // Spans that split a weight tile meet in the fp32 reductions; the order of those additions, and
@@ -38,24 +44,45 @@ using namespace lg::tc;
 constexpr int kWRows = 128;        // weight rows per CTA = MMA M
 constexpr int kKB = 64;            // k per MMA stage (one 128-byte swizzle row of bf16)
 constexpr int kRawK = 256;         // k per raw stage: 128 B of codes, 8 scales per row
-constexpr int kRawStages = 2;
-constexpr int kMmaStages = 3;
+constexpr int kGroups = kRawK / kKB;  // 4 k blocks per raw block = 4 MMA stages = 4 dequantising warp groups
+constexpr int kRawStages = 5;
 constexpr int kRawCodes = kWRows * 128;           // 16 KB
 constexpr int kRawScales = kWRows * 16;           // 2 KB
 constexpr int kRawStage = kRawCodes + kRawScales; // 18 KB (codes first: 1024-aligned)
-constexpr int kWdStage = kWRows * 128;            // 16 KB dequantised tile
-constexpr int kDqWarps = 8;
+constexpr int kWdCols = kKB / 2;                  // TMEM columns of one dequantised k block: 128 lanes x 32 columns x 2 bf16
+constexpr int kDqWarps = 4 * kGroups;             // 16
+constexpr int kIssuers = 2;                       // MMA-issuing threads (warps 2 and 3), two k blocks of every unit each
 constexpr int kEpiWarps = 4;
-constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps);  // 512
+constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps);  // 768
 
 template <int NT>
 struct QCfg {
-  static constexpr int kAStage = NT * 128;
-  static constexpr int kMmaStage = kWdStage + kAStage;
-  static constexpr int kBarBytes = 256;
-  static constexpr size_t kSmem = (size_t)kRawStages * kRawStage + (size_t)kMmaStages * kMmaStage + 1024 + kBarBytes;
-  static constexpr int kCtasPerSm = kSmem <= 113 * 1024 ? 2 : 1;
+  static constexpr int kABlock = NT * 128;             // activation tile of one k block
+  static constexpr int kABlocksPerStage = NT <= 64 ? 4 : 2;  // activation stage: a whole unit (NT <= 64) or half of one
+  static constexpr int kAStage = kABlocksPerStage * kABlock;
+  static constexpr int kAStages = 3;
+  static constexpr int kBarBytes = 512;
+  static constexpr size_t kSmem = (size_t)kRawStages * kRawStage + (size_t)kAStages * kAStage + 1024 + kBarBytes;
+  // TMEM: two buffers of dequantised weight tiles (four k blocks each; operand A of the MMA), then two
+  // accumulators. One CTA per SM, so the whole tensor memory is this CTA's.
+  static constexpr int kWBufCols = kGroups * kWdCols;  // 128
+  static constexpr int kAccCol = 2 * kWBufCols;
+  static constexpr int kAccBufs = NT <= 64 ? 2 : 1;   // accumulator buffers per issuing thread
+  static constexpr int kTmemCols = 512;
+  static_assert(kAccCol + kIssuers * kAccBufs * NT <= 512, "tensor memory budget");
 };
+
+// Waits of roles that are idle most of the time (producers, epilogue) poll rarely, so that their
+// polling does not take issue slots from the dequantising warps. Bounded like mbar_wait.
+LG_DEVINL bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    __nanosleep(i < 8 ? 100 : 400);
+  }
+  *abort_flag = 1;
+  return false;
+}
 
 // two nibbles of one byte (k even in the low nibble) -> bf16x2 {136 + q_even, 136 + q_odd}
 LG_DEVINL uint32_t nib_pair_136(uint32_t lo, uint32_t hi, uint32_t sel) {
@@ -73,8 +100,52 @@ LG_DEVINL uint32_t bf16x2_sub_mul(uint32_t v, uint32_t c136, uint32_t s2) {
   return *reinterpret_cast<uint32_t*>(&a);
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]^T: the weight operand is read from tensor memory, where the
+// dequantising warps put it (lane = row, one 32-bit column = two consecutive values of k)
+LG_DEVINL void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// registers -> tensor memory: the 32 lanes of this warp's quarter, 32 consecutive columns
+LG_DEVINL void tc_st32(uint32_t taddr, const uint4 (&v)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w),
+        "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w),
+        "r"(v[4].x), "r"(v[4].y), "r"(v[4].z), "r"(v[4].w), "r"(v[5].x), "r"(v[5].y), "r"(v[5].z), "r"(v[5].w),
+        "r"(v[6].x), "r"(v[6].y), "r"(v[6].z), "r"(v[6].w), "r"(v[7].x), "r"(v[7].y), "r"(v[7].z), "r"(v[7].w)
+      : "memory");
+}
+LG_DEVINL void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// 8 codes of one 32-bit word -> 8 bf16 (one 16-byte chunk of the operand tile), scaled
+LG_DEVINL uint4 dequant_word(uint32_t w, uint32_t s2) {
+  const uint32_t c136 = 0x43084308u;
+  const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+  uint4 o;
+  o.x = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0400u), c136, s2);  // bytes {lo.b0, x, hi.b0, x}
+  o.y = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0501u), c136, s2);
+  o.z = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0602u), c136, s2);
+  o.w = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0703u), c136, s2);
+  return o;
+}
+
+LG_DEVINL uint32_t scale_bf16x2(uint32_t packed_f16, int which) {
+  const __half h = __ushort_as_half((unsigned short)(which ? (packed_f16 >> 16) : (packed_f16 & 0xffffu)));
+  const __nv_bfloat16 sb = __float2bfloat16_rn(__half2float(h));
+  const __nv_bfloat162 sb2 = __halves2bfloat162(sb, sb);
+  return *reinterpret_cast<const uint32_t*>(&sb2);
+}
+
 template <int NT>
-__global__ void __launch_bounds__(kQThreads, QCfg<NT>::kCtasPerSm)
+__global__ void __launch_bounds__(kQThreads, 1)
 qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_codes,
                             const __grid_constant__ CUtensorMap map_scales, float* __restrict__ acc, int M, int N, int ldc,
                             int n_raw, int total_units, int* __restrict__ status) {
@@ -83,36 +154,44 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t raw_base = smem_base;
-  const uint32_t mma_base = smem_base + kRawStages * kRawStage;   // kRawStage is a multiple of 1024
-  const uint32_t bars = mma_base + kMmaStages * C::kMmaStage;
-  uint8_t* bars_gen = smem_gen + kRawStages * kRawStage + kMmaStages * C::kMmaStage;
+  const uint32_t a_base = smem_base + kRawStages * kRawStage;   // kRawStage is a multiple of 1024
+  constexpr int kTileBytes = kRawStages * kRawStage + C::kAStages * C::kAStage;
+  const uint32_t bars = smem_base + kTileBytes;
+  uint8_t* bars_gen = smem_gen + kTileBytes;
   auto raw_full = [&](int s) { return bars + 8u * s; };
   auto raw_empty = [&](int s) { return bars + 8u * (kRawStages + s); };
-  auto a_full = [&](int s) { return bars + 8u * (2 * kRawStages + s); };
-  auto wd_full = [&](int s) { return bars + 8u * (2 * kRawStages + kMmaStages + s); };
-  auto mma_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kMmaStages + s); };
-  auto tfull = [&](int b) { return bars + 8u * (2 * kRawStages + 3 * kMmaStages + b); };
-  auto tempty = [&](int b) { return bars + 8u * (2 * kRawStages + 3 * kMmaStages + 2 + b); };
-  constexpr int kNumBars = 2 * kRawStages + 3 * kMmaStages + 4;
+  auto wd_full = [&](int wb, int g) { return bars + 8u * (2 * kRawStages + wb * kGroups + g); };
+  auto wd_empty = [&](int wb) { return bars + 8u * (2 * kRawStages + 2 * kGroups + wb); };
+  auto tfull = [&](int is, int b) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 2 + is * 2 + b); };
+  auto tempty = [&](int b) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 6 + b); };
+  auto a_full = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 8 + s); };
+  auto a_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 8 + C::kAStages + s); };
+  constexpr int kNumBars = 2 * kRawStages + 2 * kGroups + 8 + 2 * C::kAStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * kNumBars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // this CTA's contiguous span of units; unit u = (weight tile u / n_raw, raw block u % n_raw). Units of
-  // one tile that fall into one span are one accumulation ("segment") with one epilogue.
+  // one tile that fall into one span are one accumulation ("segment") with one epilogue. The weight
+  // tiles of a unit go to tensor-memory buffer (unit count & 1).
   const int u0 = (int)((long long)total_units * blockIdx.x / gridDim.x);
   const int u1 = (int)((long long)total_units * (blockIdx.x + 1) / gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), kDqWarps); }
-    for (int s = 0; s < kMmaStages; ++s) { mbar_init(a_full(s), 1); mbar_init(wd_full(s), kDqWarps); mbar_init(mma_empty(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull(b), 1); mbar_init(tempty(b), kEpiWarps); }
+    for (int wb = 0; wb < 2; ++wb) {
+      for (int g = 0; g < kGroups; ++g) mbar_init(wd_full(wb, g), 4);
+      mbar_init(wd_empty(wb), kIssuers);
+    }
+    // an activation stage of a whole unit is read by both issuing threads, one of half a unit by one
+    for (int s = 0; s < C::kAStages; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), C::kABlocksPerStage == kGroups ? kIssuers : 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull(0, b), 1); mbar_init(tfull(1, b), 1); mbar_init(tempty(b), kEpiWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)(2 * NT)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   tc_fence_before();
@@ -136,94 +215,104 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       }
     }
   } else if (warp == 1) {
-    // ---------------- activation producer ----------------
+    // ---------------- activation producer: its own ring of 32 KB stages (one barrier per stage), so
+    // that the L2 latency of the activations stays off the critical path ----------------
     if (lane == 0) {
-      int s = 0;
-      uint32_t phase = 0;
+      int as = 0;
+      uint32_t aphase = 0;
       bool ok = true;
       for (int u = u0; u < u1 && ok; ++u) {
         const int kk = (u % n_raw) * kRawK;
-        for (int j = 0; j < kRawK / kKB; ++j) {
-          if (!mbar_wait(mma_empty(s), phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(a_full(s), (uint32_t)C::kAStage);
-          tma_load_2d(mma_base + s * C::kMmaStage + kWdStage, &map_a, a_full(s), kk + j * kKB, 0);
-          if (++s == kMmaStages) { s = 0; phase ^= 1u; }
+#pragma unroll
+        for (int h = 0; h < kGroups / C::kABlocksPerStage; ++h) {
+          if (!mbar_wait(a_empty(as), aphase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(a_full(as), (uint32_t)C::kAStage);
+#pragma unroll
+          for (int b = 0; b < C::kABlocksPerStage; ++b)
+            tma_load_2d(a_base + as * C::kAStage + b * C::kABlock, &map_a, a_full(as), kk + (h * C::kABlocksPerStage + b) * kKB, 0);
+          if (++as == C::kAStages) { as = 0; aphase ^= 1u; }
         }
       }
     }
-  } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 2 || warp == 3) {
+    // ---------------- MMA issuers: thread `is` takes k blocks 2 is and 2 is + 1 of every unit into its
+    // own accumulators (the epilogue adds the two). Issuing an MMA or a commit costs a thread tens of
+    // cycles whatever the tile size, because it shares its scheduler with busy dequantising warps; two
+    // issuers halve that serial cost, and descriptors are built from constants and one add.
     if (lane == 0) {
+      const int is = warp - 2;
       constexpr uint32_t idesc = make_idesc<NT>();
-      int s = 0, seg = 0;
-      uint32_t phase = 0;
+      constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
+      constexpr int per = C::kABlocksPerStage;          // k blocks per activation stage: 4 or 2
+      constexpr int kMine = kGroups / kIssuers;         // 2
+      const uint32_t a_lo0 = ((a_base & 0x3ffffu) >> 4) | (1u << 16);
+      int seg = 0, n_unit = 0;
+      // activation stages in the order this thread meets them: every stage (per == 4) or every second one
+      int ai = per == kGroups ? 0 : is;
       bool ok = true;
-      for (int u = u0; u < u1 && ok; ++u) {
+      for (int u = u0; u < u1 && ok; ++u, ++n_unit) {
         const int rb = u % n_raw;
         const bool seg_start = (u == u0) || rb == 0, seg_end = (u + 1 == u1) || rb == n_raw - 1;
-        const int buf = seg & 1;
+        const int buf = seg % C::kAccBufs, wb = n_unit & 1;
+        const uint32_t tphase = (uint32_t)(seg / C::kAccBufs) & 1u;
+        const uint32_t wphase = ((uint32_t)n_unit >> 1) & 1u;
         if (seg_start) {
-          if (!mbar_wait(tempty(buf), (((uint32_t)seg >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(tempty(buf), tphase ^ 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
         }
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NT);
-        for (int j = 0; j < kRawK / kKB; ++j) {
-          if (!mbar_wait(wd_full(s), phase, abort_flag) || !mbar_wait(a_full(s), phase, abort_flag)) { ok = false; break; }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(C::kAccCol + (is * C::kAccBufs + buf) * NT);
+        const int as = ai % C::kAStages;
+        if (!mbar_wait(a_full(as), (uint32_t)(ai / C::kAStages) & 1u, abort_flag)) { ok = false; break; }
+#pragma unroll
+        for (int j = 0; j < kMine; ++j) {
+          const int g = is * kMine + j;
+          if (!mbar_wait(wd_full(wb, g), wphase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sw = mma_base + s * C::kMmaStage;
-          const uint64_t dw = make_smem_desc(sw), da = make_smem_desc(sw + kWdStage);
+          const uint32_t w_tmem = tmem_base + (uint32_t)(wb * C::kWBufCols + g * kWdCols);  // 8 columns per 16 values of k
+          const uint32_t a_lo = a_lo0 + (uint32_t)(as * (C::kAStage >> 4) + (g % per) * (C::kABlock >> 4));
 #pragma unroll
           for (int k = 0; k < kKB / 16; ++k)
-            tc_mma_bf16(d_tmem, dw + (uint64_t)(2 * k), da + (uint64_t)(2 * k), idesc, (!seg_start || j || k) ? 1u : 0u);
-          tc_commit(mma_empty(s));
-          if (++s == kMmaStages) { s = 0; phase ^= 1u; }
+            tc_mma_bf16_ts(d_tmem, w_tmem + 8u * k, ((uint64_t)desc_hi << 32) | (a_lo + 2u * k), idesc, (!seg_start || j || k) ? 1u : 0u);
         }
-        if (ok && seg_end) { tc_commit(tfull(buf)); ++seg; }
+        if (!ok) break;
+        tc_commit(a_empty(as));
+        tc_commit(wd_empty(wb));
+        ai += per == kGroups ? 1 : kIssuers;
+        if (seg_end) { tc_commit(tfull(is, buf)); ++seg; }
       }
     }
   } else if (warp >= 4 && warp < 4 + kDqWarps) {
-    // ---------------- dequantise ----------------
+    // ---------------- dequantise: warp group g owns k block g of every unit ----------------
     const int wd = warp - 4;
+    const int g = wd >> 2;
     const int row = (wd & 3) * 32 + lane;   // weight row of the tile
-    const int half = wd >> 2;                // which 32-value group of a 64-wide k block
-    int rs = 0, s = 0;
-    uint32_t rphase = 0, phase = 0;
+    int rs = 0, n_unit = 0;
+    uint32_t rphase = 0;
     bool ok = true;
-    const uint32_t c136 = 0x43084308u;
-    for (int u = u0; u < u1 && ok; ++u) {
+    const uint32_t wt0 = tmem_base + ((uint32_t)((wd & 3) * 32) << 16) + (uint32_t)(g * kWdCols);  // this warp's lane quarter
+    for (int u = u0; u < u1 && ok; ++u, ++n_unit) {
+      const int wb = n_unit & 1;
+      const uint32_t wphase = ((uint32_t)n_unit >> 1) & 1u;
       if (!mbar_wait(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
       const uint8_t* raw = smem_gen + rs * kRawStage;
-      const uint16_t* sc = reinterpret_cast<const uint16_t*>(raw + kRawCodes) + row * 8;
-#pragma unroll 1
-      for (int j = 0; j < kRawK / kKB; ++j) {
-        const int g = 2 * j + half;  // group inside the raw block = 16-byte chunk of the row's codes
-        const uint4 cw = *reinterpret_cast<const uint4*>(raw + row * 128 + ((g ^ (row & 7)) << 4));
-        const float sf = __half2float(__ushort_as_half(sc[g]));
-        const __nv_bfloat16 sb = __float2bfloat16_rn(sf);
-        const __nv_bfloat162 sb2 = __halves2bfloat162(sb, sb);
-        const uint32_t s2 = *reinterpret_cast<const uint32_t*>(&sb2);
-        uint4 o[4];
-        const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t lo = words[i] & 0x0f0f0f0fu, hi = (words[i] >> 4) & 0x0f0f0f0fu;
-          o[i].x = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0400u), c136, s2);  // bytes {lo.b0, x, hi.b0, x}
-          o[i].y = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0501u), c136, s2);
-          o[i].z = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0602u), c136, s2);
-          o[i].w = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0703u), c136, s2);
-        }
-        if (!mbar_wait(mma_empty(s), phase ^ 1u, abort_flag)) { ok = false; break; }
-        uint8_t* wt = smem_gen + kRawStages * kRawStage + s * C::kMmaStage + row * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(wt + (((half * 4 + i) ^ (row & 7)) << 4)) = o[i];
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(wd_full(s));
-        if (++s == kMmaStages) { s = 0; phase ^= 1u; }
-      }
+      // this row's 64 codes of k block g (two 16-byte chunks, swizzled by the TMA) and their two scales
+      const uint4 c0 = *reinterpret_cast<const uint4*>(raw + row * 128 + (((2 * g) ^ (row & 7)) << 4));
+      const uint4 c1 = *reinterpret_cast<const uint4*>(raw + row * 128 + (((2 * g + 1) ^ (row & 7)) << 4));
+      const uint32_t sc = *reinterpret_cast<const uint32_t*>(raw + kRawCodes + row * 16 + g * 4);
       __syncwarp();
-      if (lane == 0) mbar_arrive(raw_empty(rs));
+      if (lane == 0) mbar_arrive(raw_empty(rs));  // the raw stage is in registers: hand it back
       if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+      const uint32_t s0 = scale_bf16x2(sc, 0), s1 = scale_bf16x2(sc, 1);
+      uint4 o[8];
+      o[0] = dequant_word(c0.x, s0); o[1] = dequant_word(c0.y, s0); o[2] = dequant_word(c0.z, s0); o[3] = dequant_word(c0.w, s0);
+      o[4] = dequant_word(c1.x, s1); o[5] = dequant_word(c1.y, s1); o[6] = dequant_word(c1.z, s1); o[7] = dequant_word(c1.w, s1);
+      if (!mbar_wait(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      tc_st32(wt0 + (uint32_t)(wb * C::kWBufCols), o);  // lane = weight row, 32 columns = its 64 bf16 in k order
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wd_full(wb, g));
     }
   } else if (warp >= 4 + kDqWarps) {
     // ---------------- epilogue: TMEM (lane = weight row, column = token) -> fp32 reductions ----------------
@@ -233,21 +322,23 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     for (int u = u0; u < u1 && ok; ++u) {
       const int rb = u % n_raw;
       if (!((u + 1 == u1) || rb == n_raw - 1)) continue;  // not the end of a segment
-      const int buf = seg & 1;
-      if (!mbar_wait(tfull(buf), ((uint32_t)seg >> 1) & 1u, abort_flag)) { ok = false; break; }
+      const int buf = seg % C::kAccBufs;
+      const uint32_t tphase = (uint32_t)(seg / C::kAccBufs) & 1u;
+      if (!mbar_wait_relaxed(tfull(0, buf), tphase, abort_flag) || !mbar_wait_relaxed(tfull(1, buf), tphase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int f = (u / n_raw) * kWRows + q * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < NT; c += 32) {
         if (c >= M) break;
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NT + c), r);
+        uint32_t r[32], r1[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + buf * NT + c), r);
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + (C::kAccBufs + buf) * NT + c), r1);
         tc_wait_ld();
         if (f < N) {
           float* dst = acc + (size_t)c * ldc + f;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (c + j < M) atomicAdd(dst + (size_t)j * ldc, __uint_as_float(r[j]));
+            if (c + j < M) atomicAdd(dst + (size_t)j * ldc, __uint_as_float(r[j]) + __uint_as_float(r1[j]));
         }
       }
       tc_fence_before();
@@ -267,7 +358,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)(2 * NT)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols) : "memory");
   }
 }
 
@@ -341,7 +432,7 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
   const int n_tiles = (n + kWRows - 1) / kWRows, n_raw = k / kRawK;
   const long total = (long)n_tiles * n_raw;
   if (total > 2147483647l) return lg::kInvalidValue;
-  const int slots = sm_count() * QCfg<NT>::kCtasPerSm;
+  const int slots = sm_count();
   const int grid = total < slots ? (int)total : slots;
   kern<<<grid, kQThreads, QCfg<NT>::kSmem, stream>>>(ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, status);
   return lg::launch_status();
@@ -360,10 +451,18 @@ uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a, const void* cod
   if ((k / 2) % 16 || ((k / 32) * 2) % 16) return lg::kInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   int* st = (int*)status_i32;
-  float* o = (float*)acc;
-  if (m <= 64) return launch_q<64>(a, codes, scales, o, m, n, k, lda, ldc, st, s);
-  if (m <= 128) return launch_q<128>(a, codes, scales, o, m, n, k, lda, ldc, st, s);
-  return launch_q<256>(a, codes, scales, o, m, n, k, lda, ldc, st, s);
+  // token tiles of at most 128: beyond that the weights are streamed once per tile (the second pass
+  // is served by L2 for the per-layer matrices)
+  for (int t0 = 0; t0 < m; t0 += 128) {
+    const int mt = m - t0 < 128 ? m - t0 : 128;
+    const void* at = (const uint16_t*)a + (size_t)t0 * lda;
+    float* o = (float*)acc + (size_t)t0 * ldc;
+    const uint32_t rc = mt <= 32   ? launch_q<32>(at, codes, scales, o, mt, n, k, lda, ldc, st, s)
+                        : mt <= 64 ? launch_q<64>(at, codes, scales, o, mt, n, k, lda, ldc, st, s)
+                                   : launch_q<128>(at, codes, scales, o, mt, n, k, lda, ldc, st, s);
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 uint32_t logismos_launch_qlinear_finish_bf16(void* acc, const void* bias, void* out, int32_t m, int32_t n, int32_t ld_acc,
