@@ -376,8 +376,7 @@ def run_serving_sweep(args, rank, world, local_rank):
     step copies its ids and index arrays to the device and its tokens back)."""
     import torch
     import torch.distributed as dist
-    from hybrid_weights import HYBRID_SERVING
-    from logismos_b200.hybrid import HybridModel
+    from logismos_b200.hybrid import HYBRID_SERVING, HybridModel, random_int4_weights
     from logismos_b200.serving import Scheduler, shard_requests, synthetic_load
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -385,30 +384,31 @@ def run_serving_sweep(args, rank, world, local_rank):
     cfg = dict(HYBRID_SERVING)
     if args.layers:
         cfg["n_layers"] = args.layers
-    rng = np.random.Generator(np.random.PCG64(17))
-    H, I, GH = cfg["hidden"], cfg["intermediate"], cfg["gdn_heads"]
-    QW, KW, GW = cfg["n_heads"] * cfg["attn_head_dim"], cfg["n_kv_heads"] * cfg["attn_head_dim"], GH * 128
-
-    def qmat(n, k):
-        return (rng.integers(0, 256, (n, k // 2), dtype=np.uint8),
-                np.abs(rng.standard_normal((n, k // 32), dtype=np.float32) * (0.25 / np.sqrt(k))).astype(np.float16))
-
-    mlp = {"w_gate": qmat(I, H), "w_up": qmat(I, H), "w_down": qmat(H, I), "norm1": np.ones(H, np.float32), "norm2": np.ones(H, np.float32)}
-    full = dict(mlp, wq=qmat(QW, H), wgate=qmat(QW, H), wk=qmat(KW, H), wv=qmat(KW, H), wo=qmat(H, QW))
-    lin = dict(mlp, wq=qmat(GW, H), wk=qmat(GW, H), wv=qmat(GW, H), wgate=qmat(GW, H), wo=qmat(H, GW), wa=qmat(GH, H), wb=qmat(GH, H),
-               A_log=np.log(rng.uniform(0.5, 4.0, GH)).astype(np.float32), dt_bias=rng.uniform(-3.0, 0.0, GH).astype(np.float32))
-    w = {"tok_embed": rng.standard_normal((cfg["vocab"], H), dtype=np.float32) * np.float32(0.5), "final_norm": np.ones(H, np.float32),
-         "lm_head": qmat(cfg["vocab"], H),
-         "layers": [full if (l + 1) % cfg["full_attn_interval"] == 0 else lin for l in range(cfg["n_layers"])]}
+    w = random_int4_weights(cfg, 17)
+    tp = args.tp
+    if tp > 1:
+        # tensor parallel: the ranks form ONE replica; every rank sees every request and must plan the
+        # same steps, so arrivals are not clocked (everything has arrived at time 0)
+        if world != tp:
+            raise SystemExit("--tp %d needs exactly %d ranks" % (tp, tp))
+        from logismos_b200.tp import nccl_allreduce_hook, slice_hybrid_weights
+        cfg_local, w = slice_hybrid_weights(cfg, w, tp, rank)
+    else:
+        cfg_local = cfg
     n_req = args.requests
-    reqs = shard_requests(synthetic_load(n_req * world, 4096, cfg["vocab"], rate_per_s=args.arrival_rate * world), world, rank)
+    if tp > 1:
+        reqs = synthetic_load(n_req, 4096, cfg["vocab"], rate_per_s=0.0)
+    else:
+        reqs = shard_requests(synthetic_load(n_req * world, 4096, cfg["vocab"], rate_per_s=args.arrival_rate * world), world, rank)
     max_seqs = min(args.max_seqs, n_req)
     max_blocks = (16384 + 1024 + 15) // 16
     lifetime = sorted((-(-(len(r.prompt) + r.max_new) // 16) for r in reqs), reverse=True)
     n_pool = int(sum(lifetime[:max_seqs])) + 8
     step_tokens = 16384 + max_seqs
-    model = HybridModel(cfg, w, n_pool_blocks=n_pool, max_blocks_per_seq=max_blocks, max_step_tokens=step_tokens, max_step_seqs=max_seqs,
+    model = HybridModel(cfg_local, w, n_pool_blocks=n_pool, max_blocks_per_seq=max_blocks, max_step_tokens=step_tokens, max_step_seqs=max_seqs,
                         n_state_slots=max_seqs, device=local_rank)
+    if tp > 1:
+        model.set_allreduce(nccl_allreduce_hook())
     sched = Scheduler(n_pool, max_blocks, max_seqs, step_tokens, max_seqs, prefill_token_budget=args.prefill_budget)
     for r in reqs:
         sched.add(r)
@@ -451,12 +451,15 @@ def run_serving_sweep(args, rank, world, local_rank):
         dist.all_reduce(tt, op=dist.ReduceOp.SUM)
         dt = float(mx[0])
     gen_all, pre_all, steps_all, launches_all = float(tt[1]), float(tt[2]), float(tt[3]), float(tt[4])
+    if tp > 1:  # one replica: its tokens count once
+        gen_all, pre_all = gen_all / tp, pre_all / tp
     if rank == 0:
         dec_only = [m for m, nd, npre in step_ms[warm:] if npre == 0]
         line = {"metric": "hybrid_decoder_generated_tokens_per_s", "value": gen_all / dt, "unit": "tokens/s", "n_gpus": world,
                 "steps": int(steps_all / world), "warmup": warm, "ms_per_step": 1e3 * dt / max(timed_steps, 1), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, int4-g32 weights, fp32 recurrent state", "data": "synthetic",
                 "config": {"workload": "hybrid decoder serving sweep, %d requests per GPU (prompts lognormal median 1024 cap 16384, outputs U[64,1024], Poisson %.0f req/s per GPU), %d layers 3:1 linear:full attention" % (n_req, args.arrival_rate, cfg["n_layers"]),
+                           "parallelism": ("tp%d (all-reduce of the output projections over NCCL)" % tp) if tp > 1 else ("request-sharded x%d" % world),
                            "max_concurrent_per_gpu": max_seqs, "kv_pool_blocks": n_pool, "inputs": "every step's working set (int4 weights, KV pool, recurrent states) exceeds L2"},
                 "e2e": {"value": gen_all / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / max(timed_steps, 1)), "d2h_bytes_per_step": int(4 * gen / max(timed_steps, 1))},
                 "gpu_launches": int(launches_all), "clocks": clocks, "device_status": status,
@@ -482,6 +485,7 @@ def main():
     ap.add_argument("--requests", type=int, default=96, help="serving_sweep: requests per GPU")
     ap.add_argument("--max-seqs", type=int, default=256, help="serving_sweep: concurrent sequences per GPU")
     ap.add_argument("--arrival-rate", type=float, default=64.0, help="serving_sweep: Poisson arrivals per second per GPU")
+    ap.add_argument("--tp", type=int, default=1, help="serving_sweep: tensor-parallel degree (ranks form one replica)")
     ap.add_argument("--prefill-budget", type=int, default=8192, help="serving_sweep: prompt tokens admitted per step")
     args = ap.parse_args()
     if args.steps is None:

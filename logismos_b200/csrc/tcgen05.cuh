@@ -9,7 +9,7 @@
 namespace lg {
 namespace tc {
 
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
 // ---- mbarrier / TMA / tcgen05 wrappers --------------------------------------------------------
 
@@ -22,14 +22,16 @@ LG_DEVINL void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 LG_DEVINL void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar));
 }
+// The suspend-time hint lets a waiting thread sleep in hardware until the phase completes (or the
+// hint expires) instead of re-issuing the test, which would take issue slots from working warps.
 LG_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }

@@ -11,9 +11,7 @@ TINY_HYBRID = dict(vocab=1000, hidden=512, n_layers=4, n_heads=4, n_kv_heads=2, 
 # alternating layers, head_dim 128, grouped-query ratio 4
 TINY_HYBRID_128 = dict(vocab=1000, hidden=512, n_layers=2, n_heads=8, n_kv_heads=2, attn_head_dim=128, gdn_heads=8,
                        intermediate=512, max_pos=512, full_attn_interval=2, rms_eps=1e-6, rope_theta=1e4)
-# the serving-sweep architecture (48 layers, 3:1), for the benchmark
-HYBRID_SERVING = dict(vocab=151936, hidden=2048, n_layers=48, n_heads=16, n_kv_heads=2, attn_head_dim=256, gdn_heads=16,
-                      intermediate=6144, max_pos=32768, full_attn_interval=4, rms_eps=1e-6, rope_theta=1e7)
+from logismos_b200.hybrid import HYBRID_SERVING  # noqa: E402,F401  (the serving-sweep architecture)
 
 
 def make_hybrid(cfg, seed):
