@@ -158,6 +158,14 @@ def time_kernel(fn, iters, stream):
     return e0.elapsed_time(e1) / iters * 1e-3
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (same kernels; where the capture ran a smaller case the traffic is scaled by the units
+# processed, as the summaries state). bytes per unit: gate/up GEMM at M=2176 (read 61.97 + write 7.44 MB,
+# the bf16 output lands in L2 first); GEMV lm_head (131.30 + 5.89 MB); paged decode 1027 B per context
+# token + 7.09 MB of partials per 328868 tokens.
+NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 137.19e6, "paged_per_context_token": (337.73e6 + 7.09e6) / 328868}
+
+
 def micro_rooflines(peaks, T, cfg):
     """Per-launch rooflines of the dominant GEMM and the two HBM-bound decode kernels, timed with
     CUDA events on the launch stream, operands rotated so that each launch reads from HBM."""
@@ -173,7 +181,8 @@ def micro_rooflines(peaks, T, cfg):
     t = time_kernel(lambda i: ops.linear_t(a, ws[i % 4], swiglu=True, sync=False), 20, st)
     fl = 2.0 * T * i2 * h
     out["gemm"] = {"kernel": "linear_t_tcgen05 (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": fl / t / 1e12,
-                   "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": fl / t / 1e12 / peaks["tf_burst"], "traffic": None,
+                   "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": fl / t / 1e12 / peaks["tf_burst"],
+                   "traffic": NCU_TRAFFIC["gemm_m2176"] * T / 2176.0, "traffic_note": "ncu capture at M=2176 scaled by tokens (A and output grow with M; W 55 MB does not, so this over-states slightly above 2176)",
                    "flops_per_launch": fl, "us_per_launch": t * 1e6, "peak_source": peaks["src"] + " burst"}
     del ws
     # int4 GEMV, lm_head shape, batch 1
@@ -185,9 +194,22 @@ def micro_rooflines(peaks, T, cfg):
     t = time_kernel(lambda i: ops.gemv_int4(codes[i % 3], scales[i % 3], x, out=y, sync=False), 30, st)
     by = n * k / 2 + n * (k // 32) * 2 + k * 2 + n * 2
     out["gemv"] = {"kernel": "gemv_int4_g32 (151936 x 1536, batch 1)", "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"],
-                   "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"], "traffic": None, "bytes_per_launch": by, "us_per_launch": t * 1e6,
+                   "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"], "traffic": NCU_TRAFFIC["gemv_lm_head"], "bytes_per_launch": by, "us_per_launch": t * 1e6,
                    "peak_source": peaks["src"]}
-    del codes, scales
+    # the same stream through the fused-dequant tensor-core linear (decode of 64 tokens, hybrid lm_head shape)
+    k2 = 2048
+    codes2 = [torch.randint(0, 256, (n, k2 // 2), dtype=torch.uint8, device=dev) for _ in range(2)]
+    scales2 = [(torch.rand((n, k2 // 32), device=dev) * 0.02).to(torch.float16) for _ in range(2)]
+    x2 = torch.randn((64, k2), device=dev).to(torch.bfloat16)
+    acc = torch.zeros((64, n), dtype=torch.float32, device=dev)
+    stw = torch.zeros(1, dtype=torch.int32, device=dev)
+    t = time_kernel(lambda i: ops.check(ops.lib.logismos_launch_qlinear_int4_g32_acc_f32(
+        x2.data_ptr(), codes2[i % 2].data_ptr(), scales2[i % 2].data_ptr(), acc.data_ptr(), 64, n, k2, k2, n, stw.data_ptr(), st.cuda_stream), "qlinear"), 20, st)
+    by2 = n * k2 / 2 + n * (k2 // 32) * 2 + 64 * k2 * 2 + 64 * n * 4
+    out["qlinear"] = {"kernel": "qlinear_int4_tcgen05 (151936 x 2048, 64 tokens, fp32 accumulate)", "bound": "hbm", "achieved": by2 / t / 1e9,
+                      "peak": peaks["hbm"], "unit": "GB/s", "frac": by2 / t / 1e9 / peaks["hbm"], "traffic": None, "bytes_per_launch": by2,
+                      "us_per_launch": t * 1e6, "tflops": 2.0 * 64 * n * k2 / t / 1e12, "device_status": int(stw.item()), "peak_source": peaks["src"]}
+    del codes, scales, codes2, scales2, acc
     # paged-attention decode: 256 sequences, contexts log-uniform in [128, 32768], block 16, fused append
     rng = np.random.default_rng(3)
     ctx = np.exp(rng.uniform(np.log(128), np.log(32768), 256)).round().astype(np.int64)
@@ -208,7 +230,8 @@ def micro_rooflines(peaks, T, cfg):
     by = float(ctx.sum()) * 1024 + 256 * (2048 * 2 * 2 + 512 * 2) + tables.size * 4
     out["paged"] = {"kernel": "paged_attention_decode (256 seqs, ctx log-U[128,32768], GQA 16/2, fused append) incl. merge kernel",
                     "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"],
-                    "traffic": None, "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()),
+                    "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences scaled by context tokens",
+                    "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()),
                     "peak_source": peaks["src"]}
     return out
 
@@ -285,7 +308,7 @@ def run_ours(args, cfg, rank, world, local_rank):
         if world == 1 and not args.no_micro:
             mr = micro_rooflines(peaks, T, cfg)
             line["roofline"] = mr["gemm"]
-            line["extra_rooflines"] = [mr["gemv"], mr["paged"]]
+            line["extra_rooflines"] = [mr["gemv"], mr["paged"], mr["qlinear"]]
         else:
             line["roofline"] = {"bound": "tensor", "achieved": fl * args.steps / dt / 1e12 / 1.0, "peak": peaks["tf_sust"], "unit": "TFLOP/s",
                                 "frac": fl * args.steps / dt / 1e12 / peaks["tf_sust"], "traffic": None,

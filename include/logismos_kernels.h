@@ -261,6 +261,14 @@ uint32_t logismos_launch_gdn_prepare(void* q_bf16, void* k_bf16, const void* a_f
                                      const void* A_log_f32, const void* dt_bias_f32, void* g_f32,
                                      void* beta_f32, int32_t n_tokens, int32_t heads,
                                      int32_t qk_stride, int32_t ab_stride, void* stream);
+/* logismos_launch_gdn_prepare fused with the finishing of the input projection's fp32 accumulation
+ * workspace (logismos_launch_qlinear_int4_g32_acc_f32 into acc f32 [n_tokens, ld_acc], columns
+ * q | k | v | z [heads * 128 each] | a | b [heads each]): q and k are L2-normalised in fp32, q, k, v, z
+ * are rounded to bf16 once into proj [n_tokens, ld_proj] (columns q | k | v | z), g and beta f32
+ * [n_tokens, heads] are computed from a and b, and the workspace is left zeroed. */
+uint32_t logismos_launch_gdn_finish(void* acc_f32, int32_t ld_acc, const void* A_log_f32, const void* dt_bias_f32,
+                                    void* proj_bf16, int32_t ld_proj, void* g_f32, void* beta_f32,
+                                    int32_t n_tokens, int32_t heads, void* stream);
 /* x[t, j] *= sigmoid(gate[t, j]) (mode 0) or silu(gate[t, j]) (mode 1), bf16 in place, fp32 math;
  * rows of x and gate have their own strides (elements). The output gates of the hybrid decoder's
  * attention and linear-attention layers. n % 8 == 0. */

@@ -97,6 +97,7 @@ def _declare(l):
         "lg_decoder_last_hidden": [vp, i32, vp],
         "lg_decoder_last_logits": [vp, i32, vp],
         "logismos_launch_add_f32": [vp, vp, i64, vp],
+        "logismos_launch_gdn_finish": [vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, vp],
         "lg_hybrid_set_allreduce": [vp, vp, vp],
         "lg_hybrid_create": [i32, vp, vp, C.POINTER(vp)],
         "lg_hybrid_step": [vp, vp, vp, vp, i32, vp, vp, vp],

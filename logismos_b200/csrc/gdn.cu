@@ -195,7 +195,64 @@ __global__ void gdn_prepare_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16*
   }
 }
 
+// The same preparation straight from the fp32 accumulation workspace of the input projection
+// (columns q | k | v | z | a | b of every token row): one warp per (token, head) normalises q and k in
+// fp32, rounds q, k, v, z to bf16 once, computes the gates, and leaves the workspace zeroed.
+__global__ void gdn_finish_kernel(float* __restrict__ acc, int64_t ld_acc, const float* __restrict__ A_log,
+                                  const float* __restrict__ dt_bias, __nv_bfloat16* __restrict__ proj, int64_t ld_proj,
+                                  float* __restrict__ g, float* __restrict__ beta, int64_t rows, int heads) {
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = r / heads;
+  const int h = (int)(r % heads);
+  const int w = heads * KD;
+  float* arow = acc + t * ld_acc + h * KD + lane * 4;
+  __nv_bfloat16* prow = proj + t * ld_proj + h * KD + lane * 4;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int which = 0; which < 4; ++which) {  // q, k, v, z
+    float4* src = reinterpret_cast<float4*>(arow + which * w);
+    float4 x = *src;
+    *src = zero;
+    if (which < 2) {
+      const float sq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+      const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
+      x.x *= inv; x.y *= inv; x.z *= inv; x.w *= inv;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(x.x, x.y);
+    o.y = pack_bf16x2(x.z, x.w);
+    *reinterpret_cast<uint2*>(prow + which * w) = o;
+  }
+  if (lane == 0) {
+    float* ab = acc + t * ld_acc + 4 * w;
+    const float x = ab[h] + dt_bias[h];
+    const float sp = x > 20.0f ? x : log1pf(expf(x));
+    g[r] = -expf(A_log[h]) * sp;
+    beta[r] = 1.0f / (1.0f + expf(-ab[heads + h]));
+    ab[h] = 0.0f;
+    ab[heads + h] = 0.0f;
+  }
+}
+
 }  // namespace
+
+extern "C" uint32_t logismos_launch_gdn_finish(void* acc, int32_t ld_acc, const void* A_log, const void* dt_bias, void* proj,
+                                               int32_t ld_proj, void* g, void* beta, int32_t n_tokens, int32_t heads,
+                                               void* stream) {
+  lg::LaunchScope launch_scope_;
+  const int w = heads * KD;
+  if (n_tokens < 0 || heads <= 0 || ld_acc < 4 * w + 2 * heads || (ld_acc % 4) || ld_proj < 4 * w || (ld_proj % 4)) return lg::kInvalidValue;
+  if (n_tokens == 0) return 0;
+  if (((uintptr_t)acc & 15) || ((uintptr_t)proj & 7)) return lg::kInvalidValue;
+  const int64_t rows = (int64_t)n_tokens * heads;
+  const int wpb = 8;
+  gdn_finish_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+      (float*)acc, (int64_t)ld_acc, (const float*)A_log, (const float*)dt_bias, (__nv_bfloat16*)proj, (int64_t)ld_proj, (float*)g,
+      (float*)beta, rows, heads);
+  return lg::launch_status();
+}
 
 extern "C" uint32_t logismos_launch_gdn_decode_step(void* state, const void* q, const void* k, const void* v,
                                                     const void* g, const void* beta, void* o, int32_t n_seqs,

@@ -125,17 +125,34 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       m->launches += 1;
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, QW, s)) return rc;
     } else {
-      // columns: q [GW] | k [GW] | v [GW] | z [GW]; a | b as fp32 [T, 2 GH] through the accumulate epilogue
-      if (uint32_t rc = qlinear(m, m->h.p, L.w_in, m->proj.p, T, H, GN, LG_EPI_BF16, s)) return rc;
-      LG_TRY(cudaMemsetAsync(m->ab.p, 0, (size_t)T * 2 * GH * 4, s), "memset a|b");
-      if (uint32_t rc = qlinear(m, m->h.p, L.w_ab, m->ab.p, T, H, 2 * GH, LG_EPI_RESID_F32, s)) return rc;
-      LG_TRY(logismos_launch_gdn_prepare(p16, p16 + GW, m->ab.p, (const float*)m->ab.p + GH, L.A_log.p, L.dt_bias.p, m->g.p,
-                                         m->beta.p, T, GH, GN, 2 * GH, s), "gdn_prepare");
+      // columns: q [GW] | k [GW] | v [GW] | z [GW] | a [GH] | b [GH] of one weight matrix
+      if (T <= kFusedDequantMaxRows) {
+        // one fused-dequant accumulation of all six blocks, finished by the kernel that also normalises
+        // q, k and computes the gates from the fp32 sums
+        const int ld = GN + 2 * GH;
+        LG_TRY(logismos_launch_qlinear_int4_g32_acc_f32(m->h.p, L.w_in.codes.p, L.w_in.scales.p, m->accws.p, T, ld, H, H, ld, st, s),
+               "int4 linear");
+        LG_TRY(logismos_launch_gdn_finish(m->accws.p, ld, L.A_log.p, L.dt_bias.p, m->proj.p, GN, m->g.p, m->beta.p, T, GH, s), "gdn_finish");
+        m->launches += 2;
+      } else {
+        // dense path: q | k | v | z to bf16, a | b as fp32 through the accumulate epilogue
+        QMat main_rows = L.w_in, ab_rows = L.w_in;  // views of the row blocks (no ownership)
+        main_rows.n = GN;
+        ab_rows.n = 2 * GH;
+        ab_rows.codes.p = (uint8_t*)L.w_in.codes.p + (size_t)GN * (H / 2);
+        ab_rows.scales.p = (uint8_t*)L.w_in.scales.p + (size_t)GN * (H / 32) * 2;
+        if (uint32_t rc = qlinear(m, m->h.p, main_rows, m->proj.p, T, H, GN, LG_EPI_BF16, s)) return rc;
+        LG_TRY(cudaMemsetAsync(m->ab.p, 0, (size_t)T * 2 * GH * 4, s), "memset a|b");
+        if (uint32_t rc = qlinear(m, m->h.p, ab_rows, m->ab.p, T, H, 2 * GH, LG_EPI_RESID_F32, s)) return rc;
+        LG_TRY(logismos_launch_gdn_prepare(p16, p16 + GW, m->ab.p, (const float*)m->ab.p + GH, L.A_log.p, L.dt_bias.p, m->g.p,
+                                           m->beta.p, T, GH, GN, 2 * GH, s), "gdn_prepare");
+        m->launches += 1;
+      }
       LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, m->cu_all.p,
                                          m->state_slots.p, m->fresh.p, m->n_seqs, GH, GN, 1.0f / std::sqrt((float)kGdnDim), s),
              "gdn recurrence");
       LG_TRY(logismos_launch_gated_mul_bf16(m->mix.p, GW, p16 + 3 * GW, GN, T, GW, 1, s), "linear-attention gate");
-      m->launches += 4;
+      m->launches += 2;
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
     }
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
@@ -220,8 +237,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
       ok = ok && cudaMemset(L.kpool.p, 0, pool_bytes) == cudaSuccess && cudaMemset(L.vpool.p, 0, pool_bytes) == cudaSuccess;
     } else {
       if (!lw.A_log || !lw.dt_bias) { ok = false; break; }
-      ok = ok && upload_q(L.w_in, {&lw.wq, &lw.wk, &lw.wv, &lw.wgate}, {GW, GW, GW, GW}, H);
-      ok = ok && upload_q(L.w_ab, {&lw.wa, &lw.wb}, {GH, GH}, H);
+      ok = ok && upload_q(L.w_in, {&lw.wq, &lw.wk, &lw.wv, &lw.wgate, &lw.wa, &lw.wb}, {GW, GW, GW, GW, GH, GH}, H);
       ok = ok && upload_q(L.w_out, {&lw.wo}, {H}, GW);
       ok = ok && L.A_log.upload(lw.A_log, (size_t)GH * 4) && L.dt_bias.upload(lw.dt_bias, (size_t)GH * 4);
       ok = ok && L.state.alloc(state_bytes) && cudaMemset(L.state.p, 0, state_bytes) == cudaSuccess;
@@ -246,7 +262,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
   if ((size_t)2 * I * H > wmax) wmax = (size_t)2 * I * H;
   if ((size_t)m->mix_w * H > wmax) wmax = (size_t)m->mix_w * H;
   m->max_chunks = S * ((MB * kBlock + kChunkTokens - 1) / kChunkTokens);
-  const size_t acc_n = pn > (size_t)2 * I ? pn : (size_t)2 * I;
+  const size_t acc_n = pn + 2 * GH > (size_t)2 * I ? pn + 2 * GH : (size_t)2 * I;
   ok = ok && m->x.alloc(T * H * 4) && m->delta.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->proj.alloc(T * pn * 2) && m->mix.alloc(T * m->mix_w * 2) &&
        m->qdec.alloc(S * QW * 2) && m->ab.alloc(T * 2 * GH * 4) && m->g.alloc(T * GH * 4) && m->beta.alloc(T * GH * 4) &&
        m->act.alloc(T * I * 2) && m->wscratch.alloc(wmax * 2) && m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) &&

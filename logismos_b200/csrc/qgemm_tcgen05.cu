@@ -9,7 +9,7 @@
 // tensor work scales with the real token count and the kernel stays bound by the int4 stream up to
 // about 64 tokens. The work is cut into units (128 weight rows x 256 values of k); one persistent
 // CTA per SM takes a contiguous, equal span of units, and consecutive units of one weight tile form
-// one accumulation with one epilogue. 24 warps:
+// one accumulation with one epilogue. 28 warps:
 //   warp 0      TMA producer of the raw int4 tiles: codes [128 rows x 128 B] (128-byte swizzle) and
 //               fp16 scales [128 rows x 8] per 256 values of k, ring of 3
 //   warp 1      TMA producer of the activation tiles [NT x 64] bf16 (128-byte swizzle), its own ring
@@ -24,7 +24,7 @@
 //               the group scale in bf16x2, stored with one tcgen05.st into the tensor-memory tile the
 //               MMA reads as its row operand (lane = weight row, column = two values of k), so the
 //               expanded weights never pass through shared memory
-//   warps 20-23 epilogue: read the accumulator from TMEM (lane = weight row, column = token) and add
+//   warps 20-27 epilogue (two per lane quarter, half of the token columns each): read the accumulator from TMEM (lane = weight row, column = token) and add
 //               it to acc with fire-and-forget fp32 reductions, one coalesced 128-byte row segment
 //               per instruction, while the other accumulator buffer is being filled
 // Spans that split a weight tile meet in the fp32 reductions; the order of those additions, and
@@ -52,8 +52,8 @@ constexpr int kRawStage = kRawCodes + kRawScales; // 18 KB (codes first: 1024-al
 constexpr int kWdCols = kKB / 2;                  // TMEM columns of one dequantised k block: 128 lanes x 32 columns x 2 bf16
 constexpr int kDqWarps = 4 * kGroups;             // 16
 constexpr int kIssuers = 2;                       // MMA-issuing threads (warps 2 and 3), two k blocks of every unit each
-constexpr int kEpiWarps = 4;
-constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps);  // 768
+constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, half of the token columns each
+constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps);  // 896
 
 template <int NT>
 struct QCfg {
@@ -84,11 +84,12 @@ LG_DEVINL bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* ab
   return false;
 }
 
-// two nibbles of one byte (k even in the low nibble) -> bf16x2 {136 + q_even, 136 + q_odd}
-LG_DEVINL uint32_t nib_pair_136(uint32_t lo, uint32_t hi, uint32_t sel) {
+// two nibbles of byte p of a code word (k even in the low nibble) -> bf16x2 {136 + q_even, 136 + q_odd}:
+// the permute puts byte p of w under bits 0-7 and byte p of w >> 4 under bits 16-23; one logic op
+// keeps the two low nibbles, flips their sign bit and ors in the exponent 0x4300
+LG_DEVINL uint32_t nib_pair_136(uint32_t w, uint32_t w_shr4, uint32_t sel) {
   uint32_t t;
-  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(t) : "r"(lo), "r"(hi), "r"(sel));
-  // bytes 1 and 3 hold data of other pairs: keep the nibbles, flip their sign bit, or in 0x4300
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(t) : "r"(w), "r"(w_shr4), "r"(sel));
   return (t & 0x000f000fu) ^ 0x43084308u;
 }
 
@@ -128,7 +129,7 @@ LG_DEVINL void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::
 // 8 codes of one 32-bit word -> 8 bf16 (one 16-byte chunk of the operand tile), scaled
 LG_DEVINL uint4 dequant_word(uint32_t w, uint32_t s2) {
   const uint32_t c136 = 0x43084308u;
-  const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+  const uint32_t lo = w, hi = w >> 4;
   uint4 o;
   o.x = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0400u), c136, s2);  // bytes {lo.b0, x, hi.b0, x}
   o.y = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0501u), c136, s2);
@@ -316,7 +317,8 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   } else if (warp >= 4 + kDqWarps) {
     // ---------------- epilogue: TMEM (lane = weight row, column = token) -> fp32 reductions ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int chalf = (warp - 4 - kDqWarps) >> 2;  // which half of the token columns
     int seg = 0;
     bool ok = true;
     for (int u = u0; u < u1 && ok; ++u) {
@@ -328,16 +330,16 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       tc_fence_after();
       const int f = (u / n_raw) * kWRows + q * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < NT; c += 32) {
+      for (int c = chalf * (NT / 2); c < (chalf + 1) * (NT / 2); c += 16) {
         if (c >= M) break;
-        uint32_t r[32], r1[32];
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + buf * NT + c), r);
-        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + (C::kAccBufs + buf) * NT + c), r1);
+        uint32_t r[16], r1[16];
+        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + buf * NT + c), r);
+        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + (C::kAccBufs + buf) * NT + c), r1);
         tc_wait_ld();
         if (f < N) {
           float* dst = acc + (size_t)c * ldc + f;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < 16; ++j)
             if (c + j < M) atomicAdd(dst + (size_t)j * ldc, __uint_as_float(r[j]) + __uint_as_float(r1[j]));
         }
       }
