@@ -73,7 +73,10 @@ constexpr int kFusedDequantMaxRows = 256;
 inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc, int epi,
                             void* wscratch, void* accws, void* status, int* launches, cudaStream_t s) {
   uint32_t rc;
-  if (T <= kFusedDequantMaxRows && w.k % 256 == 0) {
+  // measured crossover: the fused kernel wins up to 128 rows everywhere, and up to 256 rows where it
+  // accumulates straight into the residual stream (narrow outputs, long reductions); the wide
+  // projections with a bf16 / SwiGLU epilogue are faster through the dense GEMM above 128 rows
+  if (T <= kFusedDequantMaxRows && w.k % 256 == 0 && (T <= 128 || epi == LG_EPI_RESID_F32)) {
     if (epi == LG_EPI_RESID_F32 && !bias) {
       *launches += 1;
       return logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);

@@ -5,6 +5,7 @@ stream, operands rotated over several copies so that every launch reads from HBM
   python -m logismos_b200.microbench gemv  [--n N --k K --batch B --iters I]
   python -m logismos_b200.microbench gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
   python -m logismos_b200.microbench qlinear [--m M --n N --k K --iters I]   (m <= 256, fused int4 dequant)
+  python -m logismos_b200.microbench qdense  [--m M --n N --k K --iters I]   (bf16 expansion + dense GEMM)
   python -m logismos_b200.microbench paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
   python -m logismos_b200.microbench attn  [--seqs S --len L --iters I]
   python -m logismos_b200.microbench sweep          (every benchmark shape, one JSON line each)
@@ -111,6 +112,28 @@ def bench_qlinear(m, n, k, iters, copies=None, pk=None):
             "device_status": int(status.item()), "peak_src": pk["src"], "weight_copies": copies}
 
 
+def bench_qdense(m, n, k, iters, copies=None, pk=None):
+    """The dense route for more rows: expand the int4 matrix to bf16, then the tcgen05 GEMM (fp32 accumulate epilogue)."""
+    pk = pk or peaks()
+    wbytes = n * k // 2 + n * (k // 32) * 2
+    copies = copies or max(2, min(16, int(300e6 // wbytes) + 1))
+    codes = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+    scales = [(torch.rand((n, k // 32), device="cuda") * 0.02).to(torch.float16) for _ in range(copies)]
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    acc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    w = torch.empty((n, k), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run(i):
+        s = torch.cuda.current_stream().cuda_stream
+        ops.check(lib.logismos_launch_dequant_int4_g32_bf16(codes[i % copies].data_ptr(), scales[i % copies].data_ptr(), w.data_ptr(), n, k, s), "dequant")
+        ops.check(lib.logismos_launch_linear_t_bf16(x.data_ptr(), w.data_ptr(), None, acc.data_ptr(), m, n, k, k, n, 1, status.data_ptr(), s), "linear_t")
+    t = timeit(run, iters)
+    fl = 2.0 * m * n * k
+    return {"kernel": "dequant_int4 + linear_t_tcgen05", "m": m, "n": n, "k": k, "us": t * 1e6, "TFLOPs": fl / t / 1e12,
+            "GBps": (wbytes + m * k * 2 + m * n * 4) / t / 1e9, "frac_hbm": 0.0, "device_status": int(status.item())}
+
+
 def bench_gemm(m, n, k, epi, iters, pk=None):
     pk = pk or peaks()
     a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
@@ -176,7 +199,7 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="logismos_b200.microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "paged", "attn", "sweep"])
+    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "paged", "attn", "sweep"])
     ap.add_argument("--m", type=int, default=2176)
     ap.add_argument("--n", type=int, default=151936)
     ap.add_argument("--k", type=int, default=1536)
@@ -196,6 +219,8 @@ def main(argv=None):
         print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
     elif a.what == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.epi, a.iters)))
+    elif a.what == "qdense":
+        print(json.dumps(bench_qdense(a.m, a.n, a.k, a.iters)))
     elif a.what == "qlinear":
         print(json.dumps(bench_qlinear(a.m, a.n, a.k, a.iters)))
     elif a.what == "paged":
