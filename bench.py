@@ -145,17 +145,11 @@ def workload_config(cfg, cu):
 # ------------------------------------------------------------------------------------ GPU arm
 
 def time_kernel(fn, iters, stream):
-    import torch
-    for _ in range(3):
-        fn(0)
-    stream.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(iters):
-        fn(i)
-    e1.record(stream)
-    e1.synchronize()
-    return e0.elapsed_time(e1) / iters * 1e-3
+    """Seconds per launch: the launches are captured into one CUDA graph and the replay is timed with
+    CUDA events on the launch stream, so that host launch cost (ctypes, descriptor encoding, ~10 us per
+    call) is not charged to kernels of a few tens of microseconds."""
+    from logismos_b200.microbench import timeit
+    return timeit(fn, iters)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under

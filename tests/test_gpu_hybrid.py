@@ -64,6 +64,26 @@ def test_mixed_steps_equal_per_sequence_execution_head_dim_128():
     drive(TINY_HYBRID_128, 22, 4)
 
 
+def test_every_linear_route_gives_the_same_model():
+    """Steps of 1..128 rows run every projection through the fused-dequant kernel, 129..256 rows split
+    between it and the dense GEMM, more rows use the dense GEMM only: all three against the oracle."""
+    cfg = TINY_HYBRID
+    qw, deq = make_hybrid(cfg, 41)
+    oracle = O.OracleHybrid(cfg, deq)
+    rng = np.random.default_rng(9)
+    model = HybridModel(cfg, qw, n_pool_blocks=64, max_blocks_per_seq=24, max_step_tokens=512, max_step_seqs=4, n_state_slots=4)
+    blocks = BlockAllocator(64, 24, seed=5)
+    for sid, n in enumerate((200, 330, 60)):
+        ids = rng.integers(0, cfg["vocab"], n)
+        toks = model.step(ids, [0], [n], blocks.ensure(sid, n)[None, :], [sid])
+        assert model.device_status() == 0
+        h_ref, l_ref = oracle.forward(ids.astype(np.uint32))
+        assert max_rel(model.last_hidden()[0], h_ref[-1]) <= TOL, n
+        assert max_rel(model.last_logits()[0], l_ref) <= TOL
+        assert toks[0] == O.greedy(model.last_logits()[0])
+    model.close()
+
+
 def test_step_rejects_what_it_cannot_run():
     qw, _ = make_hybrid(TINY_HYBRID_128, 3)
     model = HybridModel(TINY_HYBRID_128, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2, n_state_slots=2)
