@@ -90,8 +90,8 @@ constexpr int kPfQuarterPitch = 36;    // floats between the quarters of k / q i
 __global__ void __launch_bounds__(128)
 gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
-                   __nv_bfloat16* __restrict__ o, const int* __restrict__ cu, const int* __restrict__ slots,
-                   const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
+                   __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
+                   const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
   __shared__ __align__(16) float ks[2][4 * kPfQuarterPitch], qs[2][4 * kPfQuarterPitch];
   const int part = blockIdx.x & 3, sh = blockIdx.x >> 2;
   const int seq = sh / heads, head = sh % heads;
@@ -113,17 +113,19 @@ gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ 
     qs[0][stage_at] = __bfloat162float(q[tq + tid]);
   }
   float v_cur = __bfloat162float(v[(int64_t)t0 * qkv_stride + head * KD + col]);
+  float z_cur = z ? __bfloat162float(z[(int64_t)t0 * qkv_stride + head * KD + col]) : 0.f;
   float g_cur = g[(int64_t)t0 * heads + head], b_cur = beta[(int64_t)t0 * heads + head];
   __syncthreads();
   for (int t = t0; t < t1; ++t) {
     const int b = (t - t0) & 1;
     // fetch the next token while this one is computed
-    float k_nx = 0.f, q_nx = 0.f, v_nx = 0.f, g_nx = 0.f, b_nx = 0.f;
+    float k_nx = 0.f, q_nx = 0.f, v_nx = 0.f, g_nx = 0.f, b_nx = 0.f, z_nx = 0.f;
     if (t + 1 < t1) {
       const int64_t tq = (int64_t)(t + 1) * qkv_stride + head * KD;
       k_nx = __bfloat162float(k[tq + tid]);
       q_nx = __bfloat162float(q[tq + tid]);
       v_nx = __bfloat162float(v[tq + col]);
+      if (z) z_nx = __bfloat162float(z[tq + col]);
       g_nx = g[(int64_t)(t + 1) * heads + head];
       b_nx = beta[(int64_t)(t + 1) * heads + head];
     }
@@ -151,10 +153,12 @@ gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ 
     float ov = (a0 + a1) + (a2 + a3);
     ov += __shfl_xor_sync(0xffffffffu, ov, 1);
     ov += __shfl_xor_sync(0xffffffffu, ov, 2);
-    if (kq == 0) o[((int64_t)t * heads + head) * VD + col] = __float2bfloat16(ov * scale);
+    ov *= scale;
+    if (z) ov *= z_cur / (1.0f + __expf(-z_cur));  // output gate silu(z), fused
+    if (kq == 0) o[((int64_t)t * heads + head) * VD + col] = __float2bfloat16(ov);
     ks[b ^ 1][stage_at] = k_nx;
     qs[b ^ 1][stage_at] = q_nx;
-    v_cur = v_nx; g_cur = g_nx; b_cur = b_nx;
+    v_cur = v_nx; g_cur = g_nx; b_cur = b_nx; z_cur = z_nx;
     __syncthreads();
   }
 #pragma unroll
@@ -270,7 +274,7 @@ extern "C" uint32_t logismos_launch_gdn_decode_step(void* state, const void* q, 
 }
 
 extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, const void* k, const void* v, const void* g,
-                                                const void* beta, void* o, const void* cu_seqlens,
+                                                const void* beta, void* o, const void* gate_z, const void* cu_seqlens,
                                                 const void* state_slots, const void* fresh, int32_t n_seqs,
                                                 int32_t heads, int32_t qkv_stride, float scale, void* stream) {
   lg::LaunchScope launch_scope_;
@@ -281,7 +285,7 @@ extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, cons
   if (ctas > 2147483647ll) return lg::kInvalidValue;
   gdn_prefill_kernel<<<(unsigned)ctas, 128, 0, (cudaStream_t)stream>>>(
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g,
-      (const float*)beta, (__nv_bfloat16*)o, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
+      (const float*)beta, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate_z, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
       (int64_t)qkv_stride, scale);
   return lg::launch_status();
 }

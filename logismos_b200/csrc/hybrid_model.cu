@@ -148,11 +148,10 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
                                            m->beta.p, T, GH, GN, 2 * GH, s), "gdn_prepare");
         m->launches += 1;
       }
-      LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, m->cu_all.p,
+      LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW, m->cu_all.p,
                                          m->state_slots.p, m->fresh.p, m->n_seqs, GH, GN, 1.0f / std::sqrt((float)kGdnDim), s),
              "gdn recurrence");
-      LG_TRY(logismos_launch_gated_mul_bf16(m->mix.p, GW, p16 + 3 * GW, GN, T, GW, 1, s), "linear-attention gate");
-      m->launches += 2;
+      m->launches += 1;
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
     }
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");

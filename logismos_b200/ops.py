@@ -344,8 +344,9 @@ def gdn_decode_step_(state, q, k, v, g, beta, scale, sync=True):
     return o
 
 
-def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, sync=True):
-    """Gated delta rule over a ragged batch; q, k, v bf16 [T, heads, 128]; state updated in place."""
+def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, sync=True):
+    """Gated delta rule over a ragged batch; q, k, v bf16 [T, heads, 128]; state updated in place.
+    gate_z bf16 [T, heads, 128] (optional) multiplies the output by silu(z) in the same pass."""
     _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
     _req(v, "v", torch.bfloat16, 3); _req(g, "g", torch.float32, 2); _req(beta, "beta", torch.float32, 2)
     _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
@@ -353,7 +354,7 @@ def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, sync=True):
         raise InvalidOp("gdn_prefill: state must be [n_seqs, heads, 128, 128]")
     o = torch.empty_like(v)
     with torch.cuda.device(state.device):
-        check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(cu_seqlens), _p(None), _p(None),
+        check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(gate_z) if gate_z is not None else None, _p(cu_seqlens), _p(None), _p(None),
                                               state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale), _stream()), "gdn_prefill")
         _done(sync)
     return o

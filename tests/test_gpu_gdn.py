@@ -71,3 +71,48 @@ def test_ragged_prefill_matches_chunk_reference_and_continues_into_decode():
             o_ref, states = O.gdn_chunk_fwd(q[sl, h], k[sl, h], v[sl, h], beta_np[sl, h], g_np[sl, h], D ** -0.5, state0[s, h], D, D, 64)
             assert max_rel(o[sl, h], o_ref.reshape(-1, D)) <= 2e-2
             assert max_rel(final[s, h], states[-1].reshape(D, D)) <= 1e-4
+
+
+def test_output_gate_fused_into_the_recurrence_equals_the_separate_gate():
+    rng = np.random.default_rng(8)
+    heads, D, lens = 2, 128, [19, 3]
+    T = sum(lens)
+    cu = torch.tensor([0, 19, 22], dtype=torch.int32, device=DEV)
+    mk = lambda: bf16_cuda(rng.standard_normal((T, heads, D)))[0]
+    q_t, k_t, v_t, z_t = mk(), mk(), mk(), mk()
+    g_t = torch.from_numpy(-np.abs(rng.standard_normal((T, heads))).astype(np.float32)).to(DEV)
+    beta_t = torch.from_numpy(rng.uniform(0, 1, (T, heads)).astype(np.float32)).to(DEV)
+    st_a = torch.zeros((2, heads, D, D), dtype=torch.float32, device=DEV); st_b = st_a.clone()
+    plain = to_np(ops.gdn_prefill_(st_a, q_t, k_t, v_t, g_t, beta_t, cu, D ** -0.5)).astype(np.float64)
+    gated = to_np(ops.gdn_prefill_(st_b, q_t, k_t, v_t, g_t, beta_t, cu, D ** -0.5, gate_z=z_t))
+    z = to_np(z_t).astype(np.float64)
+    want = plain * z / (1 + np.exp(-z))
+    assert torch.equal(st_a, st_b)                       # the gate does not touch the state
+    assert np.abs(gated - want).max() <= 2 ** -6 * np.abs(want).max()  # two bf16 roundings apart at most
+
+
+def test_finish_of_the_input_projection_workspace():
+    """gdn_finish on an fp32 workspace [T, q|k|v|z|a|b] equals: L2-normalise q, k in fp32, round once to
+    bf16, gates from a, b (the oracle's formulas), workspace handed back zeroed."""
+    from logismos_b200._lib import check, lib
+    rng = np.random.default_rng(12)
+    T, heads, D = 21, 8, 128
+    W = heads * D
+    ld = 4 * W + 2 * heads
+    acc_np = rng.standard_normal((T, ld)).astype(np.float32)
+    acc = torch.from_numpy(acc_np.copy()).to(DEV)
+    A_log = rng.uniform(-1, 0.5, heads).astype(np.float32); dt_bias = rng.standard_normal(heads).astype(np.float32)
+    proj = torch.empty((T, 4 * W), dtype=torch.bfloat16, device=DEV)
+    g = torch.empty((T, heads), dtype=torch.float32, device=DEV); beta = torch.empty_like(g)
+    A_t, dt_t = torch.from_numpy(A_log).to(DEV), torch.from_numpy(dt_bias).to(DEV)
+    check(lib.logismos_launch_gdn_finish(acc.data_ptr(), ld, A_t.data_ptr(), dt_t.data_ptr(), proj.data_ptr(), 4 * W, g.data_ptr(),
+                                         beta.data_ptr(), T, heads, torch.cuda.current_stream().cuda_stream), "gdn_finish")
+    torch.cuda.synchronize()
+    assert float(acc.abs().max()) == 0.0
+    got = to_np(proj)
+    qk = acc_np[:, :2 * W].reshape(T, 2 * heads, D).astype(np.float64)
+    qk = qk / np.maximum(np.linalg.norm(qk, axis=-1, keepdims=True), 1e-12)
+    want = np.concatenate([qk.reshape(T, 2 * W), acc_np[:, 2 * W:4 * W]], axis=1)
+    assert np.abs(got - want).max() <= 2 ** -8 * np.abs(want).max()
+    g_ref, beta_ref = O.gdn_gates(np.ascontiguousarray(acc_np[:, 4 * W:4 * W + heads]), np.ascontiguousarray(acc_np[:, 4 * W + heads:]), A_log, dt_bias)
+    assert np.abs(to_np(g) - g_ref).max() <= 1e-5 * max(1, np.abs(g_ref).max()) and np.abs(to_np(beta) - beta_ref).max() <= 1e-6
