@@ -112,6 +112,8 @@ typedef struct lg_decoder_config {
   int32_t max_blocks_per_seq;  /* width of a block-table row */
   int32_t max_step_tokens;     /* capacity of one packed step */
   int32_t max_step_seqs;
+  int32_t keep_bf16_copy;      /* != 0: also keep a bf16 expansion of every layer matrix (2 B per weight) for
+                                  steps of more than 128 rows, instead of expanding per layer per step */
 } lg_decoder_config_t;
 
 /* int4 group-32 matrix on the HOST: codes u8 [n, k/2], scales fp16 bits [n, k/32]
@@ -177,6 +179,7 @@ typedef struct lg_hybrid_config {
   int32_t max_step_tokens;
   int32_t max_step_seqs;
   int32_t n_state_slots;       /* recurrent-state slots per linear-attention layer */
+  int32_t keep_bf16_copy;      /* as in lg_decoder_config_t */
 } lg_hybrid_config_t;
 
 typedef struct lg_hybrid_layer_weights {

@@ -163,6 +163,7 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
     ok = ok && upload_q(L.wo, {&lw.wo}, {(int)H}, (int)H);
     ok = ok && upload_q_gate_up(L.wgu, lw.w_gate, lw.w_up, (int)I, (int)H);
     ok = ok && upload_q(L.wdown, {&lw.w_down}, {(int)H}, (int)I);
+    if (c.keep_bf16_copy) ok = ok && make_dense_copy(L.wqkv) && make_dense_copy(L.wo) && make_dense_copy(L.wgu) && make_dense_copy(L.wdown);
     ok = ok && L.kpool.alloc(pool_bytes) && L.vpool.alloc(pool_bytes);
     ok = ok && cudaMemset(L.kpool.p, 0, pool_bytes) == cudaSuccess && cudaMemset(L.vpool.p, 0, pool_bytes) == cudaSuccess;
   }
@@ -214,7 +215,7 @@ void lg_decoder_destroy(void* model) {
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.bqkv, &L.kpool, &L.vpool, &L.wqkv.codes, &L.wqkv.scales, &L.wo.codes, &L.wo.scales,
-                 &L.wgu.codes, &L.wgu.scales, &L.wdown.codes, &L.wdown.scales};
+                 &L.wgu.codes, &L.wgu.scales, &L.wdown.codes, &L.wdown.scales, &L.wqkv.dense, &L.wo.dense, &L.wgu.dense, &L.wdown.dense};
     for (Buf* b : lb) b->release();
   }
   if (m->pinned) cudaFreeHost(m->pinned);

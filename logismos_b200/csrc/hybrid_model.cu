@@ -141,6 +141,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
         ab_rows.n = 2 * GH;
         ab_rows.codes.p = (uint8_t*)L.w_in.codes.p + (size_t)GN * (H / 2);
         ab_rows.scales.p = (uint8_t*)L.w_in.scales.p + (size_t)GN * (H / 32) * 2;
+        if (L.w_in.dense.p) ab_rows.dense.p = (uint8_t*)L.w_in.dense.p + (size_t)GN * H * 2;
         if (uint32_t rc = qlinear(m, m->h.p, main_rows, m->proj.p, T, H, GN, LG_EPI_BF16, s)) return rc;
         LG_TRY(cudaMemsetAsync(m->ab.p, 0, (size_t)T * 2 * GH * 4, s), "memset a|b");
         if (uint32_t rc = qlinear(m, m->h.p, ab_rows, m->ab.p, T, H, 2 * GH, LG_EPI_RESID_F32, s)) return rc;
@@ -243,6 +244,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
     }
     ok = ok && upload_q_gate_up(L.wgu, lw.w_gate, lw.w_up, I, H);
     ok = ok && upload_q(L.wdown, {&lw.w_down}, {H}, I);
+    if (c.keep_bf16_copy) ok = ok && make_dense_copy(L.w_in) && make_dense_copy(L.w_out) && make_dense_copy(L.wgu) && make_dense_copy(L.wdown);
   }
   if (ok) {  // RoPE table in f64 then f32 (cpu_f32/mod.rs:599-619)
     const size_t half = c.attn_head_dim / 2;
@@ -296,7 +298,7 @@ void lg_hybrid_destroy(void* model) {
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.kpool, &L.vpool, &L.state, &L.A_log, &L.dt_bias, &L.w_in.codes, &L.w_in.scales,
                  &L.w_ab.codes, &L.w_ab.scales, &L.w_out.codes, &L.w_out.scales, &L.wgu.codes, &L.wgu.scales, &L.wdown.codes,
-                 &L.wdown.scales};
+                 &L.wdown.scales, &L.w_in.dense, &L.w_out.dense, &L.wgu.dense, &L.wdown.dense};
     for (Buf* b : lb) b->release();
   }
   if (m->pinned) cudaFreeHost(m->pinned);

@@ -30,7 +30,16 @@ struct Buf {
   void release() { if (p) cudaFree(p); p = nullptr; }
 };
 
-struct QMat { Buf codes, scales; int n = 0, k = 0; };
+// an int4 matrix on the device; `dense` is its optional bf16 expansion [n, k], made once at load for
+// the steps that are bound by tensor throughput rather than by the weight stream
+struct QMat { Buf codes, scales, dense; int n = 0, k = 0; };
+
+// expands q into q.dense (blocking); false on allocation or launch failure
+inline bool make_dense_copy(QMat& q) {
+  if (!q.dense.alloc((size_t)q.n * q.k * 2)) return false;
+  if (logismos_launch_dequant_int4_g32_bf16(q.codes.p, q.scales.p, q.dense.p, q.n, q.k, nullptr) != 0) return false;
+  return cudaDeviceSynchronize() == cudaSuccess;
+}
 
 // gate and up rows interleaved in blocks of 32 (32 gate rows, then the 32 matching up rows), the
 // row order the fused SwiGLU epilogue of the GEMM expects
@@ -65,18 +74,19 @@ inline bool upload_q(QMat& q, const std::vector<const lg_int4_matrix_t*>& parts,
   return q.codes.upload(codes.data(), codes.size()) && q.scales.upload(scales.data(), scales.size() * 2);
 }
 
-// C = A W^T with int4 weights, epilogue as for logismos_launch_linear_t_bf16. Up to 256 rows the
+// C = A W^T with int4 weights, epilogue as for logismos_launch_linear_t_bf16. Up to 128 rows the
 // dequantisation is fused into the tensor-core kernel (fp32 accumulation into the residual stream
 // itself, or into the zeroed workspace `accws` finished to bf16); above that the weights are
-// expanded to bf16 once into `wscratch` and the dense GEMM runs with its fused epilogues.
-constexpr int kFusedDequantMaxRows = 256;
+// expanded to bf16 (the matrix's persistent copy when it has one, else into `wscratch` on every
+// call) and the dense GEMM runs with its fused epilogues. The
+// crossover is measured: the fused kernel's fp32 reductions grow with rows x columns, and the kernel
+// that reads the accumulation target next waits for them to drain (a finishing kernel of 4 us alone
+// took 21 us behind a 256-row accumulation).
+constexpr int kFusedDequantMaxRows = 128;
 inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc, int epi,
                             void* wscratch, void* accws, void* status, int* launches, cudaStream_t s) {
   uint32_t rc;
-  // measured crossover: the fused kernel wins up to 128 rows everywhere, and up to 256 rows where it
-  // accumulates straight into the residual stream (narrow outputs, long reductions); the wide
-  // projections with a bf16 / SwiGLU epilogue are faster through the dense GEMM above 128 rows
-  if (T <= kFusedDequantMaxRows && w.k % 256 == 0 && (T <= 128 || epi == LG_EPI_RESID_F32)) {
+  if (T <= kFusedDequantMaxRows && w.k % 256 == 0) {
     if (epi == LG_EPI_RESID_F32 && !bias) {
       *launches += 1;
       return logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);
@@ -87,6 +97,10 @@ inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void
       *launches += 2;
       return logismos_launch_qlinear_finish_bf16(accws, bias, out, T, w.n, w.n, ldc, epi == LG_EPI_SWIGLU ? 1 : 0, s);
     }
+  }
+  if (w.dense.p) {
+    *launches += 1;
+    return logismos_launch_linear_t_bf16(a, w.dense.p, bias, out, T, w.n, w.k, lda, ldc, epi, status, s);
   }
   rc = logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, wscratch, w.n, w.k, s);
   if (rc) return rc;

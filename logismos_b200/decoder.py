@@ -22,7 +22,7 @@ _u16 = C.POINTER(C.c_uint16)
 class _Cfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "hidden", "n_layers", "n_heads", "n_kv_heads", "intermediate", "max_pos")] + [
         ("rms_eps", C.c_float), ("rope_theta", C.c_double)] + [
-        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs")]
+        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs", "keep_bf16_copy")]
 
 
 class _Q(C.Structure):
@@ -81,9 +81,10 @@ class DecoderModel:
     (codes u8 [n, k/2], scales f16 [n, k/32]) pairs."""
 
     def __init__(self, cfg: dict, weights: dict, n_pool_blocks: int, max_blocks_per_seq: int, max_step_tokens: int,
-                 max_step_seqs: int, device: int = 0):
+                 max_step_seqs: int, device: int = 0, keep_bf16_copy: bool = True):
         c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"],
-                 cfg["max_pos"], cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs)
+                 cfg["max_pos"], cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs,
+                 int(keep_bf16_copy))
         L = (_LayerW * max(1, cfg["n_layers"]))()
         for i, lw in enumerate(weights["layers"]):
             for n in ("norm1", "norm2", "bq", "bk", "bv"):

@@ -22,7 +22,7 @@ class _Cfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "hidden", "n_layers", "n_heads", "n_kv_heads", "attn_head_dim", "gdn_heads",
                                          "intermediate", "max_pos", "full_attn_interval")] + [
         ("rms_eps", C.c_float), ("rope_theta", C.c_double)] + [
-        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs", "n_state_slots")]
+        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs", "n_state_slots", "keep_bf16_copy")]
 
 
 _QNAMES = ("wq", "wk", "wv", "wgate", "wo", "wa", "wb")
@@ -68,10 +68,10 @@ class HybridModel:
     for linear-attention layers wa, wb pairs plus A_log, dt_bias (fp32 [gdn_heads])."""
 
     def __init__(self, cfg: dict, weights: dict, n_pool_blocks: int, max_blocks_per_seq: int, max_step_tokens: int,
-                 max_step_seqs: int, n_state_slots: int, device: int = 0):
+                 max_step_seqs: int, n_state_slots: int, device: int = 0, keep_bf16_copy: bool = True):
         c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["attn_head_dim"],
                  cfg["gdn_heads"], cfg["intermediate"], cfg["max_pos"], cfg["full_attn_interval"], cfg["rms_eps"],
-                 cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs, n_state_slots)
+                 cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs, n_state_slots, int(keep_bf16_copy))
         L = (_LayerW * max(1, cfg["n_layers"]))()
         for i, lw in enumerate(weights["layers"]):
             L[i].norm1, L[i].norm2 = _f(lw["norm1"]), _f(lw["norm2"])

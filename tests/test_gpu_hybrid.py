@@ -64,14 +64,17 @@ def test_mixed_steps_equal_per_sequence_execution_head_dim_128():
     drive(TINY_HYBRID_128, 22, 4)
 
 
-def test_every_linear_route_gives_the_same_model():
-    """Steps of 1..128 rows run every projection through the fused-dequant kernel, 129..256 rows split
-    between it and the dense GEMM, more rows use the dense GEMM only: all three against the oracle."""
+@pytest.mark.parametrize("keep_bf16_copy", [True, False])
+def test_every_linear_route_gives_the_same_model(keep_bf16_copy):
+    """Steps of up to 128 rows run every projection through the fused-dequant kernel, larger steps
+    through the dense GEMM over the persistent bf16 copy of the weights or, without one, over a
+    per-layer expansion: all against the oracle."""
     cfg = TINY_HYBRID
     qw, deq = make_hybrid(cfg, 41)
     oracle = O.OracleHybrid(cfg, deq)
     rng = np.random.default_rng(9)
-    model = HybridModel(cfg, qw, n_pool_blocks=64, max_blocks_per_seq=24, max_step_tokens=512, max_step_seqs=4, n_state_slots=4)
+    model = HybridModel(cfg, qw, n_pool_blocks=64, max_blocks_per_seq=24, max_step_tokens=512, max_step_seqs=4, n_state_slots=4,
+                        keep_bf16_copy=keep_bf16_copy)
     blocks = BlockAllocator(64, 24, seed=5)
     for sid, n in enumerate((200, 330, 60)):
         ids = rng.integers(0, cfg["vocab"], n)
