@@ -482,6 +482,10 @@ def run_serving_sweep(args, rank, world, local_rank):
                 "gpu_launches": int(launches_all), "clocks": clocks, "device_status": status,
                 "prefill_tokens_per_s": pre_all / dt, "total_tokens_per_s": (pre_all + gen_all) / dt,
                 "decode_only_step_ms_median": float(np.median(dec_only)) if dec_only else None,
+                "decode_only_steps": len(dec_only), "decode_only_ms_total": float(np.sum(dec_only)) if dec_only else 0.0,
+                "prefill_steps": len(step_ms[warm:]) - len(dec_only),
+                "prefill_steps_ms_total": float(sum(m for m, nd, npre in step_ms[warm:] if npre > 0)),
+                "longest_step_ms": float(max(m for m, nd, npre in step_ms[warm:])) if step_ms[warm:] else None,
                 "requests_finished_rank0": len(sched.done), "sweep_complete": sched.idle()}
         print(json.dumps(line))
     if world > 1:

@@ -243,16 +243,19 @@ uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, co
  * [n_tokens, heads]; state f32 [n_seqs, heads, 128, 128] is the initial state on entry and the
  * final state on return; o bf16 [n_tokens, heads, 128]. Tokens are processed in order.
  * q, k, v may be column blocks of a wider projection output: token t, head h starts at
- * t * qkv_stride + h * 128 (elements). state_slots i32 [n_seqs] (may be NULL = identity) selects
+ * t * qkv_stride + h * 128 (elements; qkv_stride % 8 == 0, 16-byte aligned bases). state_slots i32 [n_seqs] (may be NULL = identity) selects
  * each sequence's slot in a state pool [n_slots, heads, 128, 128]; fresh u8 [n_seqs] (may be NULL)
  * marks sequences that start here and therefore begin from the zero state. gate_z bf16 (may be
  * NULL), addressed like q, k, v, applies the layer's output gate in the same pass:
- * o *= silu(z) in fp32 before the bf16 rounding. */
+ * o *= silu(z) in fp32 before the bf16 rounding. mode selects the kernel shape: 1 = throughput (64
+ * value columns per CTA; decode and many sequences), 2 = latency (32 columns per CTA: more
+ * CTAs per head for a few long sequences), 0 = by the number of (sequence, head) pairs. */
 uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const void* k_bf16,
                                      const void* v_bf16, const void* g_f32, const void* beta_f32,
                                      void* o_bf16, const void* gate_z_bf16, const void* cu_seqlens_i32,
                                      const void* state_slots_i32, const void* fresh_u8, int32_t n_seqs,
-                                     int32_t heads, int32_t qkv_stride, float scale, void* stream);
+                                     int32_t heads, int32_t qkv_stride, float scale, int32_t mode,
+                                     void* stream);
 /* Inputs of the recurrence from the layer's projections (no reference code; the formulas are
  * those of research/14-gdn-aiter-preflight.md:190-198, :209-219): q, k bf16 [n_tokens, heads, 128]
  * are L2-normalised per head row in place (l2_norm_in_place, cpu.rs:19-34);

@@ -78,91 +78,189 @@ gdn_decode_step_kernel(float* __restrict__ state, const __nv_bfloat16* __restric
 // sequences of one token): tokens are taken in order, which is what gated_delta_rule_chunk_fwd
 // specifies (the recurrence applied chunk by chunk with the state carried, cpu.rs:201-249).
 //
-// The latency of one token is what bounds a long prompt, so the 128 x 128 state of a (sequence,
-// head) is spread over 512 threads: CTA = (sequence, head, 32 value columns), 128 threads; a
-// thread owns one value column and one quarter of the key rows (32 floats in registers), the four
-// quarter-owners of a column are neighbouring lanes, and both column sums are two shuffles. There
-// is no cross-warp reduction; the only barrier per token is the one that publishes the next token's
-// k and q, which were fetched from global memory while the current token was being computed.
-constexpr int kPfCols = 32;            // value columns per CTA
-constexpr int kPfQuarterPitch = 36;    // floats between the quarters of k / q in shared memory (bank offset 4)
+// CTA = (sequence, head, a block of value columns), 128 threads. A thread owns CPT value columns and
+// 1/KS of the key rows (CPT x 128/KS floats of state in registers); the KS owners of a column are
+// neighbouring lanes and the column sums are log2(KS) shuffles. There is no cross-warp reduction.
+// Two shapes are built:
+//   <CPT=2, KS=4>  64 columns per CTA: the throughput shape (decode and many sequences). Every read of
+//                  k and q from shared memory serves two columns; at decode the kernel moves the
+//                  state at 87 % of the measured HBM rate.
+//   <CPT=1, KS=4>  32 columns per CTA: the shape for a few long sequences, where the token-serial
+//                  dependency chain bounds the prompt (about 0.5 us per token whatever the split: 16
+//                  columns with key rows in eighths measured the same) and more CTAs per head fill
+//                  the SMs.
+// k is read once per token and kept in registers for both passes over the state; the decay is folded
+// into the second pass (hk = decay * h^T k). Inputs arrive eight tokens at a time: the k, q, v, z rows
+// and gates of the next eight tokens are fetched with cp.async while the current eight are computed,
+// so the memory latency is paid once per eight tokens and there are two barriers per eight tokens.
+constexpr int kPfChunk = 8;            // tokens per staged chunk
 
+template <int COLS>
+struct PfRaw {  // one staged chunk as it arrives from global memory
+  __nv_bfloat16 k[kPfChunk][KD], q[kPfChunk][KD];
+  __nv_bfloat16 v[kPfChunk][COLS], z[kPfChunk][COLS];
+  float g[kPfChunk], beta[kPfChunk];
+};
+
+template <int CPT, int KS>
+struct PfCfg {
+  static constexpr int kRows = KD / KS;                 // key rows per thread: 32 or 16
+  static constexpr int kCols = 4 * (32 / KS) * CPT;     // value columns per CTA: 64 or 16
+  static constexpr int kPitch = kRows + 4;              // floats between the row blocks of k / q in shared memory
+  static constexpr int kParts = VD / kCols;
+};
+
+template <int CPT, int KS>
 __global__ void __launch_bounds__(128)
 gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                    __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
                    const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
-  __shared__ __align__(16) float ks[2][4 * kPfQuarterPitch], qs[2][4 * kPfQuarterPitch];
-  const int part = blockIdx.x & 3, sh = blockIdx.x >> 2;
+  using C = PfCfg<CPT, KS>;
+  constexpr int R = C::kRows, R4 = R / 4;
+  __shared__ __align__(16) PfRaw<C::kCols> raw[2];
+  __shared__ __align__(16) float kf[kPfChunk][KS * C::kPitch], qf[kPfChunk][KS * C::kPitch];
+  const int part = blockIdx.x % C::kParts, sh = blockIdx.x / C::kParts;
   const int seq = sh / heads, head = sh % heads;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kq = lane & 3;                                   // quarter of the key rows: 32 kq .. 32 kq + 31
-  const int col = part * kPfCols + warp * 8 + (lane >> 2);   // value column
+  const int kq = lane % KS;                                        // block of key rows: R kq .. R kq + R - 1
+  const int lcol = CPT * (warp * (32 / KS) + lane / KS);           // first of this thread's columns inside the CTA's block
+  const int col = part * C::kCols + lcol;
   const int t0 = cu[seq], t1 = cu[seq + 1];
   if (t1 <= t0) return;
   const int64_t slot = slots ? slots[seq] : seq;
-  float* hp = state + (slot * heads + head) * (int64_t)(KD * VD) + (int64_t)(kq * 32) * VD + col;
+  float* hp = state + (slot * heads + head) * (int64_t)(KD * VD) + (int64_t)(kq * R) * VD + col;
   const bool zero_start = fresh && fresh[seq];  // a sequence that starts here begins from the zero state
-  float h[32];
+  float h[R][CPT];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) h[i] = zero_start ? 0.f : hp[i * VD];
-  const int stage_at = (tid >> 5) * kPfQuarterPitch + (tid & 31);  // where this thread's k / q element lands
-  {
-    const int64_t tq = (int64_t)t0 * qkv_stride + head * KD;
-    ks[0][stage_at] = __bfloat162float(k[tq + tid]);
-    qs[0][stage_at] = __bfloat162float(q[tq + tid]);
+  for (int i = 0; i < R; ++i) {
+    if (CPT == 2) {  // the two columns are adjacent and even-aligned: one 8-byte access
+      const float2 x = zero_start ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(hp + i * VD);
+      h[i][0] = x.x;
+      h[i][CPT - 1] = x.y;
+    } else {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) h[i][c] = zero_start ? 0.f : hp[i * VD + c];
+    }
   }
-  float v_cur = __bfloat162float(v[(int64_t)t0 * qkv_stride + head * KD + col]);
-  float z_cur = z ? __bfloat162float(z[(int64_t)t0 * qkv_stride + head * KD + col]) : 0.f;
-  float g_cur = g[(int64_t)t0 * heads + head], b_cur = beta[(int64_t)t0 * heads + head];
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int b = (t - t0) & 1;
-    // fetch the next token while this one is computed
-    float k_nx = 0.f, q_nx = 0.f, v_nx = 0.f, g_nx = 0.f, b_nx = 0.f, z_nx = 0.f;
-    if (t + 1 < t1) {
-      const int64_t tq = (int64_t)(t + 1) * qkv_stride + head * KD;
-      k_nx = __bfloat162float(k[tq + tid]);
-      q_nx = __bfloat162float(q[tq + tid]);
-      v_nx = __bfloat162float(v[tq + col]);
-      if (z) z_nx = __bfloat162float(z[tq + col]);
-      g_nx = g[(int64_t)(t + 1) * heads + head];
-      b_nx = beta[(int64_t)(t + 1) * heads + head];
+
+  // thread tid fetches 16-byte piece (tid % 16) of token (tid / 16) of k and of q; the first threads the
+  // 16-byte pieces of the v (and z) slices; threads 0..7 the two gates of token tid
+  constexpr int kVPieces = C::kCols / 8;  // 16-byte pieces of one token's v slice: 8 or 2
+  auto fetch = [&](int chunk, int buf) {
+    const int tb = t0 + chunk * kPfChunk;
+    const int tt = tb + (tid >> 4);
+    if (tt < t1) {
+      const int64_t row = (int64_t)tt * qkv_stride + head * KD + (tid & 15) * 8;
+      cp_async16(smem_u32(&raw[buf].k[tid >> 4][(tid & 15) * 8]), k + row);
+      cp_async16(smem_u32(&raw[buf].q[tid >> 4][(tid & 15) * 8]), q + row);
     }
-    const float decay = expf(g_cur);
-    const float4* k4 = reinterpret_cast<const float4*>(&ks[b][kq * kPfQuarterPitch]);
-    const float4* q4 = reinterpret_cast<const float4*>(&qs[b][kq * kPfQuarterPitch]);
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 kk = k4[i];
-      h[4 * i] *= decay; h[4 * i + 1] *= decay; h[4 * i + 2] *= decay; h[4 * i + 3] *= decay;
-      a0 += h[4 * i] * kk.x; a1 += h[4 * i + 1] * kk.y; a2 += h[4 * i + 2] * kk.z; a3 += h[4 * i + 3] * kk.w;
+    if (tid < kPfChunk * kVPieces) {
+      const int tv = tb + tid / kVPieces;
+      if (tv < t1) {
+        const int64_t row = (int64_t)tv * qkv_stride + head * KD + part * C::kCols + (tid % kVPieces) * 8;
+        cp_async16(smem_u32(&raw[buf].v[tid / kVPieces][(tid % kVPieces) * 8]), v + row);
+        if (z) cp_async16(smem_u32(&raw[buf].z[tid / kVPieces][(tid % kVPieces) * 8]), z + row);
+      }
     }
-    float hk = (a0 + a1) + (a2 + a3);
-    hk += __shfl_xor_sync(0xffffffffu, hk, 1);
-    hk += __shfl_xor_sync(0xffffffffu, hk, 2);
-    const float vd = b_cur * (v_cur - hk);
-    a0 = a1 = a2 = a3 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 kk = k4[i], qq = q4[i];
-      h[4 * i] += kk.x * vd; h[4 * i + 1] += kk.y * vd; h[4 * i + 2] += kk.z * vd; h[4 * i + 3] += kk.w * vd;
-      a0 += h[4 * i] * qq.x; a1 += h[4 * i + 1] * qq.y; a2 += h[4 * i + 2] * qq.z; a3 += h[4 * i + 3] * qq.w;
+    if (tid < kPfChunk && tb + tid < t1) {
+      raw[buf].g[tid] = g[(int64_t)(tb + tid) * heads + head];
+      raw[buf].beta[tid] = beta[(int64_t)(tb + tid) * heads + head];
     }
-    float ov = (a0 + a1) + (a2 + a3);
-    ov += __shfl_xor_sync(0xffffffffu, ov, 1);
-    ov += __shfl_xor_sync(0xffffffffu, ov, 2);
-    ov *= scale;
-    if (z) ov *= z_cur / (1.0f + __expf(-z_cur));  // output gate silu(z), fused
-    if (kq == 0) o[((int64_t)t * heads + head) * VD + col] = __float2bfloat16(ov);
-    ks[b ^ 1][stage_at] = k_nx;
-    qs[b ^ 1][stage_at] = q_nx;
-    v_cur = v_nx; g_cur = g_nx; b_cur = b_nx; z_cur = z_nx;
+    cp_async_commit();
+  };
+
+  const int n_chunks = (t1 - t0 + kPfChunk - 1) / kPfChunk;
+  fetch(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    const int buf = c & 1;
+    cp_async_wait<0>();
+    __syncthreads();  // chunk c has landed; everyone is done with chunk c - 1 (kf / qf and its raw buffer)
+    if (c + 1 < n_chunks) fetch(c + 1, buf ^ 1);  // lands while chunk c is computed
+    // bf16 -> fp32 once per chunk, into the pitched layout the float4 reads want
+    const int n_tok = min(kPfChunk, t1 - t0 - c * kPfChunk);
+    for (int i = 0; i < n_tok; ++i) {
+      kf[i][(tid / R) * C::kPitch + (tid % R)] = __bfloat162float(raw[buf].k[i][tid]);
+      qf[i][(tid / R) * C::kPitch + (tid % R)] = __bfloat162float(raw[buf].q[i][tid]);
+    }
     __syncthreads();
+    for (int i = 0; i < n_tok; ++i) {
+      const int t = t0 + c * kPfChunk + i;
+      const float decay = expf(raw[buf].g[i]);
+      const float b_cur = raw[buf].beta[i];
+      float v_cur[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) v_cur[cc] = __bfloat162float(raw[buf].v[i][lcol + cc]);
+      const float4* k4 = reinterpret_cast<const float4*>(&kf[i][kq * C::kPitch]);
+      const float4* q4 = reinterpret_cast<const float4*>(&qf[i][kq * C::kPitch]);
+      float4 kk[R4];
+#pragma unroll
+      for (int j = 0; j < R4; ++j) kk[j] = k4[j];
+      // hk = (decay h)^T k = decay (h^T k): the decay joins the state in the second pass
+      float acc[4][CPT];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) acc[a][cc] = 0.f;
+#pragma unroll
+      for (int j = 0; j < R4; ++j)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          acc[0][cc] += h[4 * j][cc] * kk[j].x;
+          acc[1][cc] += h[4 * j + 1][cc] * kk[j].y;
+          acc[2][cc] += h[4 * j + 2][cc] * kk[j].z;
+          acc[3][cc] += h[4 * j + 3][cc] * kk[j].w;
+        }
+      float vd[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        float hk = (acc[0][cc] + acc[1][cc]) + (acc[2][cc] + acc[3][cc]);
+#pragma unroll
+        for (int m = 1; m < KS; m <<= 1) hk += __shfl_xor_sync(0xffffffffu, hk, m);
+        vd[cc] = b_cur * (v_cur[cc] - decay * hk);
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) acc[a][cc] = 0.f;
+#pragma unroll
+      for (int j = 0; j < R4; ++j) {
+        const float4 qq = q4[j];
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          h[4 * j][cc] = fmaf(h[4 * j][cc], decay, kk[j].x * vd[cc]);
+          h[4 * j + 1][cc] = fmaf(h[4 * j + 1][cc], decay, kk[j].y * vd[cc]);
+          h[4 * j + 2][cc] = fmaf(h[4 * j + 2][cc], decay, kk[j].z * vd[cc]);
+          h[4 * j + 3][cc] = fmaf(h[4 * j + 3][cc], decay, kk[j].w * vd[cc]);
+          acc[0][cc] += h[4 * j][cc] * qq.x;
+          acc[1][cc] += h[4 * j + 1][cc] * qq.y;
+          acc[2][cc] += h[4 * j + 2][cc] * qq.z;
+          acc[3][cc] += h[4 * j + 3][cc] * qq.w;
+        }
+      }
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        float ov = (acc[0][cc] + acc[1][cc]) + (acc[2][cc] + acc[3][cc]);
+#pragma unroll
+        for (int m = 1; m < KS; m <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, m);
+        ov *= scale;
+        if (z) {  // output gate silu(z), fused
+          const float zc = __bfloat162float(raw[buf].z[i][lcol + cc]);
+          ov *= zc / (1.0f + __expf(-zc));
+        }
+        if (kq == 0) o[((int64_t)t * heads + head) * VD + col + cc] = __float2bfloat16(ov);
+      }
+    }
   }
 #pragma unroll
-  for (int i = 0; i < 32; ++i) hp[i * VD] = h[i];
+  for (int i = 0; i < R; ++i) {
+    if (CPT == 2) {
+      *reinterpret_cast<float2*>(hp + i * VD) = make_float2(h[i][0], h[i][CPT - 1]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) hp[i * VD + c] = h[i][c];
+    }
+  }
 }
 
 // Per (token, head): g = -exp(A_log[h]) * softplus(a + dt_bias[h]) with softplus(x) = x for
@@ -276,14 +374,23 @@ extern "C" uint32_t logismos_launch_gdn_decode_step(void* state, const void* q, 
 extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, const void* k, const void* v, const void* g,
                                                 const void* beta, void* o, const void* gate_z, const void* cu_seqlens,
                                                 const void* state_slots, const void* fresh, int32_t n_seqs,
-                                                int32_t heads, int32_t qkv_stride, float scale, void* stream) {
+                                                int32_t heads, int32_t qkv_stride, float scale, int32_t mode, void* stream) {
   lg::LaunchScope launch_scope_;
-  if (n_seqs < 0 || heads <= 0 || qkv_stride < heads * KD || (qkv_stride % 4)) return lg::kInvalidValue;
+  if (n_seqs < 0 || heads <= 0 || qkv_stride < heads * KD || (qkv_stride % 8) || mode < 0 || mode > 2) return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
-  if (((uintptr_t)state & 15) || ((uintptr_t)v & 7) || ((uintptr_t)o & 7)) return lg::kInvalidValue;
-  const int64_t ctas = (int64_t)n_seqs * heads * (VD / kPfCols);
+  // rows are fetched in 16-byte pieces
+  if (((uintptr_t)state & 15) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)gate_z & 15) || ((uintptr_t)o & 1))
+    return lg::kInvalidValue;
+  // few (sequence, head) pairs: the latency shape (more, shorter dependency chains per head); otherwise
+  // the throughput shape
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool latency = mode == 2 || (mode == 0 && (int64_t)n_seqs * heads < 2ll * sms);
+  const int64_t ctas = (int64_t)n_seqs * heads * (latency ? PfCfg<1, 4>::kParts : PfCfg<2, 4>::kParts);
   if (ctas > 2147483647ll) return lg::kInvalidValue;
-  gdn_prefill_kernel<<<(unsigned)ctas, 128, 0, (cudaStream_t)stream>>>(
+  auto kern = latency ? gdn_prefill_kernel<1, 4> : gdn_prefill_kernel<2, 4>;
+  kern<<<(unsigned)ctas, 128, 0, (cudaStream_t)stream>>>(
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g,
       (const float*)beta, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate_z, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
       (int64_t)qkv_stride, scale);

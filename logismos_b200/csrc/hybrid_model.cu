@@ -149,10 +149,22 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
                                            m->beta.p, T, GH, GN, 2 * GH, s), "gdn_prepare");
         m->launches += 1;
       }
-      LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW, m->cu_all.p,
-                                         m->state_slots.p, m->fresh.p, m->n_seqs, GH, GN, 1.0f / std::sqrt((float)kGdnDim), s),
-             "gdn recurrence");
-      m->launches += 1;
+      // decode sequences (one token each, bound by the state traffic) and prefill sequences (bound by the
+      // token-serial chain) take different kernel shapes; they are disjoint runs of the packed batch
+      const float gscale = 1.0f / std::sqrt((float)kGdnDim);
+      if (m->n_dec > 0) {
+        LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
+                                           m->cu_all.p, m->state_slots.p, m->fresh.p, m->n_dec, GH, GN, gscale, 1, s),
+               "gdn recurrence (decode rows)");
+        m->launches += 1;
+      }
+      if (m->n_pre > 0) {
+        LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
+                                           (const int32_t*)m->cu_all.p + m->n_dec, (const int32_t*)m->state_slots.p + m->n_dec,
+                                           (const uint8_t*)m->fresh.p + m->n_dec, m->n_pre, GH, GN, gscale, 0, s),
+               "gdn recurrence (prefill rows)");
+        m->launches += 1;
+      }
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
     }
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");

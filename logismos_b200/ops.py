@@ -344,7 +344,7 @@ def gdn_decode_step_(state, q, k, v, g, beta, scale, sync=True):
     return o
 
 
-def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, sync=True):
+def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, mode=0, sync=True):
     """Gated delta rule over a ragged batch; q, k, v bf16 [T, heads, 128]; state updated in place.
     gate_z bf16 [T, heads, 128] (optional) multiplies the output by silu(z) in the same pass."""
     _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
@@ -355,7 +355,7 @@ def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, sync=T
     o = torch.empty_like(v)
     with torch.cuda.device(state.device):
         check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(gate_z) if gate_z is not None else None, _p(cu_seqlens), _p(None), _p(None),
-                                              state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale), _stream()), "gdn_prefill")
+                                              state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale), int(mode), _stream()), "gdn_prefill")
         _done(sync)
     return o
 

@@ -116,3 +116,31 @@ def test_finish_of_the_input_projection_workspace():
     assert np.abs(got - want).max() <= 2 ** -8 * np.abs(want).max()
     g_ref, beta_ref = O.gdn_gates(np.ascontiguousarray(acc_np[:, 4 * W:4 * W + heads]), np.ascontiguousarray(acc_np[:, 4 * W + heads:]), A_log, dt_bias)
     assert np.abs(to_np(g) - g_ref).max() <= 1e-5 * max(1, np.abs(g_ref).max()) and np.abs(to_np(beta) - beta_ref).max() <= 1e-6
+
+
+def test_both_kernel_shapes_agree_with_the_reference():
+    """The throughput shape (64 columns per CTA, key rows in quarters) and the latency shape (32 columns, one per thread) against the oracle's recurrence, from a non-zero state, ragged lengths that
+    end inside and on the eight-token staging chunks."""
+    rng = np.random.default_rng(17)
+    heads, D = 2, 128
+    lens = [8, 13, 1, 24]
+    T = sum(lens)
+    cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
+    nrm = lambda x: x / np.linalg.norm(x, axis=-1, keepdims=True)
+    q_t, q = bf16_cuda(nrm(rng.standard_normal((T, heads, D)))); k_t, k = bf16_cuda(nrm(rng.standard_normal((T, heads, D))))
+    v_t, v = bf16_cuda(rng.standard_normal((T, heads, D)))
+    g = (-np.abs(rng.standard_normal((T, heads))) * 0.3).astype(np.float32); beta = rng.uniform(0, 1, (T, heads)).astype(np.float32)
+    state0 = (rng.standard_normal((len(lens), heads, D, D)) * 0.05).astype(np.float32)
+    outs = []
+    for mode in (1, 2):
+        st = torch.from_numpy(state0.copy()).to(DEV)
+        o = to_np(ops.gdn_prefill_(st, q_t, k_t, v_t, torch.from_numpy(g).to(DEV), torch.from_numpy(beta).to(DEV),
+                                   torch.from_numpy(cu).to(DEV), D ** -0.5, mode=mode))
+        outs.append((o, to_np(st)))
+        for s in range(len(lens)):
+            sl = slice(cu[s], cu[s + 1])
+            for h in range(heads):
+                o_ref, states = O.gdn_chunk_fwd(q[sl, h], k[sl, h], v[sl, h], beta[sl, h], g[sl, h], D ** -0.5, state0[s, h], D, D, 64)
+                assert max_rel(o[sl, h], o_ref.reshape(-1, D)) <= 2e-2, (mode, s, h)
+                assert max_rel(outs[-1][1][s, h], states[-1].reshape(D, D)) <= 1e-4, (mode, s, h)
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-5 * np.abs(outs[0][1]).max()
