@@ -507,7 +507,7 @@ def main():
     ap.add_argument("--max-seqs", type=int, default=256, help="serving_sweep: concurrent sequences per GPU")
     ap.add_argument("--arrival-rate", type=float, default=64.0, help="serving_sweep: Poisson arrivals per second per GPU")
     ap.add_argument("--tp", type=int, default=1, help="serving_sweep: tensor-parallel degree (ranks form one replica)")
-    ap.add_argument("--prefill-budget", type=int, default=8192, help="serving_sweep: prompt tokens admitted per step")
+    ap.add_argument("--prefill-budget", type=int, default=16384, help="serving_sweep: prompt tokens admitted per step (larger = better prefill throughput, longer steps)")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 0 if args.workload == "serving_sweep" else 20
