@@ -9,11 +9,14 @@ batch. Weak scaling over GPUs: every rank holds a full replica and its own batch
 sharding, no collective on the data path).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+  python bench.py --workload ragged_step                    (continuous-batching step of the int4 decoder)
+  python bench.py --workload serving_sweep [--requests R --max-seqs S --arrival-rate L --tp T]
+                                                            (hybrid decoder under the host scheduler)
 
 `value`  embeddings/s with ids already resident on the device (CUDA events on the launch stream)
 `e2e`    the same through lg_stella_encode_ids_batch with host buffers (H2D + D2H inside)
 `roofline`      the dominant kernel (gate/up tcgen05 GEMM) against the measured bf16 peak
-`extra_rooflines` the two HBM-bound decode kernels (int4 GEMV, paged attention) against HBM peak
+`extra_rooflines` the HBM-bound decode kernels (int4 GEMV, paged attention, fused-dequant linear) against HBM peak
 `cpu_baseline`  the CPU oracle (a port of the reference's fp32 path) on the host cores
 """
 from __future__ import annotations
