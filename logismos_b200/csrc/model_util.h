@@ -86,7 +86,11 @@ constexpr int kFusedDequantMaxRows = 128;
 inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc, int epi,
                             void* wscratch, void* accws, void* status, int* launches, cudaStream_t s) {
   uint32_t rc;
-  if (T <= kFusedDequantMaxRows && w.k % 256 == 0) {
+  // with a persistent bf16 copy at hand, the wide projections that need a finishing pass (bf16 / SwiGLU
+  // outputs through the fp32 workspace) are already faster through the dense GEMM above 32 rows
+  // (measured: 14-18 us against 19-24 us); the narrow, deep output projections stay fused
+  const bool fused_ok = T <= kFusedDequantMaxRows && w.k % 256 == 0 && (epi == LG_EPI_RESID_F32 || !w.dense.p || T <= 32);
+  if (fused_ok) {
     if (epi == LG_EPI_RESID_F32 && !bias) {
       *launches += 1;
       return logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);
