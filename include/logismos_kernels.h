@@ -256,6 +256,16 @@ uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const 
                                      const void* state_slots_i32, const void* fresh_u8, int32_t n_seqs,
                                      int32_t heads, int32_t qkv_stride, float scale, int32_t mode,
                                      void* stream);
+/* The same function in chunk-parallel form (gated_delta_rule_chunk_fwd, cpu.rs:201-249): the 64 tokens
+ * of a chunk are resolved together by matrix products (a triangular solve for the in-chunk
+ * dependencies, tensor-core products against the carried state), so a long prompt is not bound by a
+ * token-serial chain. Arguments as logismos_launch_gdn_prefill. The state stays fp32 and enters the
+ * products rounded to bf16: outputs within 2e-2 of the recurrence, final state within 1e-2. */
+uint32_t logismos_launch_gdn_chunked(void* state_f32, const void* q_bf16, const void* k_bf16,
+                                     const void* v_bf16, const void* g_f32, const void* beta_f32,
+                                     void* o_bf16, const void* gate_z_bf16, const void* cu_seqlens_i32,
+                                     const void* state_slots_i32, const void* fresh_u8, int32_t n_seqs,
+                                     int32_t heads, int32_t qkv_stride, float scale, void* stream);
 /* Inputs of the recurrence from the layer's projections (no reference code; the formulas are
  * those of research/14-gdn-aiter-preflight.md:190-198, :209-219): q, k bf16 [n_tokens, heads, 128]
  * are L2-normalised per head row in place (l2_norm_in_place, cpu.rs:19-34);

@@ -149,8 +149,8 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
                                            m->beta.p, T, GH, GN, 2 * GH, s), "gdn_prepare");
         m->launches += 1;
       }
-      // decode sequences (one token each, bound by the state traffic) and prefill sequences (bound by the
-      // token-serial chain) take different kernel shapes; they are disjoint runs of the packed batch
+      // decode sequences (one token each, bound by the state traffic) run the token-serial kernel,
+      // prefill sequences the chunk-parallel one; they are disjoint runs of the packed batch
       const float gscale = 1.0f / std::sqrt((float)kGdnDim);
       if (m->n_dec > 0) {
         LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
@@ -159,10 +159,10 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
         m->launches += 1;
       }
       if (m->n_pre > 0) {
-        LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
+        LG_TRY(logismos_launch_gdn_chunked(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
                                            (const int32_t*)m->cu_all.p + m->n_dec, (const int32_t*)m->state_slots.p + m->n_dec,
-                                           (const uint8_t*)m->fresh.p + m->n_dec, m->n_pre, GH, GN, gscale, 0, s),
-               "gdn recurrence (prefill rows)");
+                                           (const uint8_t*)m->fresh.p + m->n_dec, m->n_pre, GH, GN, gscale, s),
+               "gdn chunk-parallel (prefill rows)");
         m->launches += 1;
       }
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
