@@ -6,13 +6,13 @@
 //
 // For a chunk with incoming state S [K, V], cumulative log-decays c_i = g_1 + .. + g_i, gamma_i = exp(c_i):
 //   A = strict_tril( diag(beta) (K K^T) * exp(c_i - c_j) )            [64 x 64]
-//   [W | U] = (I + A)^-1 diag(beta) [K * gamma | V]                    forward substitution
+//   T = (I + A)^-1 (forward substitution, fp32, then bf16);  [W | U] = T diag(beta) [K * gamma | V]
 //   dV = U - W S                                                       the values the chunk really adds
 //   O  = scale * ( gamma_i (Q S) + tril( (Q K^T) * exp(c_i - c_j) ) dV )
 //   S' = gamma_64 S + K^T ( dV * exp(c_64 - c_i) )
 // which equals the recurrence exactly in exact arithmetic. The products run on mma.sync m16n8k16
 // (bf16 operands, fp32 accumulation); the state is kept in fp32 and enters the products rounded to
-// bf16, the triangular solve and all decay factors are fp32.
+// bf16, the triangular inverse is computed in fp32 (and applied in bf16), all decay factors are fp32.
 //
 // CTA = (sequence, head, half of the value columns), 256 threads, chunks of the sequence in order.
 #include "common.cuh"
@@ -105,6 +105,9 @@ struct Smem {
   __align__(128) __nv_bfloat16 Pb[CH * CH];      // tril((Q K^T) * decay), [token i][token j] rows of 128 B
   __align__(128) __nv_bfloat16 dVb[CH * VW];     // dV, [token][v]
   __align__(128) __nv_bfloat16 dVs[CH * VW];     // dV * exp(c_64 - c_i)
+  __align__(128) __nv_bfloat16 Ks[CH * KD];      // beta gamma K, [token][k]
+  __align__(128) __nv_bfloat16 Vs[CH * VW];      // beta V, [token][v]
+  __align__(128) __nv_bfloat16 Tb[CH * CH];      // (I + A)^-1 rounded to bf16, [i][j] rows of 128 B
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -124,7 +127,8 @@ gdn_chunk_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q,
   float* gstate = state + (slot * heads + head) * (int64_t)(KD * VDIM) + part * VW;
   const bool zero_start = fresh && fresh[seq];
   const uint32_t Sb_a = smem_u32(sm.Sb), Kt_a = smem_u32(sm.Kt), Qt_a = smem_u32(sm.Qt), Wb_a = smem_u32(sm.Wb), Vt_a = smem_u32(sm.Vt),
-                 Zt_a = smem_u32(sm.Zt), Pb_a = smem_u32(sm.Pb), dVb_a = smem_u32(sm.dVb), dVs_a = smem_u32(sm.dVs);
+                 Zt_a = smem_u32(sm.Zt), Pb_a = smem_u32(sm.Pb), dVb_a = smem_u32(sm.dVb), dVs_a = smem_u32(sm.dVs), Ks_a = smem_u32(sm.Ks),
+                 Vs_a = smem_u32(sm.Vs), Tb_a = smem_u32(sm.Tb);
   auto bf16_at = [&](__nv_bfloat16* tile, uint32_t tile_a, int rb, int row, int col) -> __nv_bfloat16* {
     // generic pointer to element (row, col) of a swizzled tile with rb bytes per row
     const uint32_t off = (uint32_t)row * rb + (uint32_t)((((col >> 3) ^ (row & 7)) << 4) + (col & 7) * 2);
@@ -209,44 +213,95 @@ gdn_chunk_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q,
         for (int t = 0; t < CH / 8; ++t) {
           const int j0 = 8 * t + 2 * fc, j1 = j0 + 1;
           const float cj0 = sm.cg[j0], cj1 = sm.cg[j1];
-          sm.A32[i0][j0] = i0 > j0 ? b0 * s[t][0] * expf(ci0 - cj0) : 0.f;
-          sm.A32[i0][j1] = i0 > j1 ? b0 * s[t][1] * expf(ci0 - cj1) : 0.f;
-          sm.A32[i1][j0] = i1 > j0 ? b1 * s[t][2] * expf(ci1 - cj0) : 0.f;
-          sm.A32[i1][j1] = i1 > j1 ? b1 * s[t][3] * expf(ci1 - cj1) : 0.f;
+          sm.A32[i0][j0] = i0 > j0 ? b0 * s[t][0] * __expf(ci0 - cj0) : 0.f;
+          sm.A32[i0][j1] = i0 > j1 ? b0 * s[t][1] * __expf(ci0 - cj1) : 0.f;
+          sm.A32[i1][j0] = i1 > j0 ? b1 * s[t][2] * __expf(ci1 - cj0) : 0.f;
+          sm.A32[i1][j1] = i1 > j1 ? b1 * s[t][3] * __expf(ci1 - cj1) : 0.f;
         }
       } else {
 #pragma unroll
         for (int t = 0; t < CH / 8; ++t) {
           const int j0 = 8 * t + 2 * fc, j1 = j0 + 1;
           const float cj0 = sm.cg[j0], cj1 = sm.cg[j1];
-          const float p00 = i0 >= j0 ? s[t][0] * expf(ci0 - cj0) : 0.f, p01 = i0 >= j1 ? s[t][1] * expf(ci0 - cj1) : 0.f;
-          const float p10 = i1 >= j0 ? s[t][2] * expf(ci1 - cj0) : 0.f, p11 = i1 >= j1 ? s[t][3] * expf(ci1 - cj1) : 0.f;
+          const float p00 = i0 >= j0 ? s[t][0] * __expf(ci0 - cj0) : 0.f, p01 = i0 >= j1 ? s[t][1] * __expf(ci0 - cj1) : 0.f;
+          const float p10 = i1 >= j0 ? s[t][2] * __expf(ci1 - cj0) : 0.f, p11 = i1 >= j1 ? s[t][3] * __expf(ci1 - cj1) : 0.f;
           *reinterpret_cast<uint32_t*>(bf16_at(sm.Pb, Pb_a, 128, i0, j0)) = pack_bf16x2(p00, p01);
           *reinterpret_cast<uint32_t*>(bf16_at(sm.Pb, Pb_a, 128, i1, j0)) = pack_bf16x2(p10, p11);
         }
       }
     }
     __syncthreads();
-    // ---- stage 4: [W | U] = (I + A)^-1 diag(beta) [K gamma | V], one column per thread, forward substitution
-    if (tid < KD + VW) {
-      const bool is_w = tid < KD;
-      const int col = is_w ? tid : tid - KD;
+    // ---- stage 4a: T = (I + A)^-1 by forward substitution, one column per thread (threads 0-63), while
+    // the other threads scale the right-hand sides: Ks = beta gamma K, Vs = beta V
+    if (tid < CH) {
+      const int col = tid;
       float x[CH];
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
-        const float rhs = is_w ? sm.gam[i] * __bfloat162float(*bf16_at(sm.Kt, Kt_a, 256, i, col))
-                               : __bfloat162float(*bf16_at(sm.Vt, Vt_a, 128, i, col));
-        float acc = sm.bet[i] * rhs;
+        // four partial sums: the dependency chain of a row is a quarter of its length
+        float a0 = i == col ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < i; ++j) acc -= sm.A32[i][j] * x[j];
-        x[i] = acc;
+        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+          const float4 a = *reinterpret_cast<const float4*>(&sm.A32[i][4 * j4]);  // entries at j >= i are zero
+          a0 -= a.x * x[4 * j4];
+          if (4 * j4 + 1 < i) a1 -= a.y * x[4 * j4 + 1];
+          if (4 * j4 + 2 < i) a2 -= a.z * x[4 * j4 + 2];
+          if (4 * j4 + 3 < i) a3 -= a.w * x[4 * j4 + 3];
+        }
+        x[i] = (a0 + a1) + (a2 + a3);
       }
-      if (is_w) {
 #pragma unroll
-        for (int i = 0; i < CH; ++i) *bf16_at(sm.Wb, Wb_a, 256, i, col) = __float2bfloat16(x[i]);
-      } else {
+      for (int i = 0; i < CH; ++i) *bf16_at(sm.Tb, Tb_a, 128, i, col) = __float2bfloat16(x[i]);
+    } else {
+      for (int e = tid - CH; e < CH * (KD / 8); e += kThreads - CH) {  // 16-byte pieces of K
+        const int row = e / (KD / 8), piece = e % (KD / 8);
+        const float f = sm.bet[row] * sm.gam[row];
+        const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Kt) + (taddr<256>(Kt_a, row, piece) - Kt_a));
+        uint4 out;
+        float2 t;
+        t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Ks) + (taddr<256>(Ks_a, row, piece) - Ks_a)) = out;
+      }
+      for (int e = tid - CH; e < CH * (VW / 8); e += kThreads - CH) {  // 16-byte pieces of V
+        const int row = e / (VW / 8), piece = e % (VW / 8);
+        const float f = sm.bet[row];
+        const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Vt) + (taddr<128>(Vt_a, row, piece) - Vt_a));
+        uint4 out;
+        float2 t;
+        t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
+        t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Vs) + (taddr<128>(Vs_a, row, piece) - Vs_a)) = out;
+      }
+    }
+    __syncthreads();
+    // ---- stage 4b: W = T Ks (bf16, the row operand of stage 5), U = T Vs (fp32)  (warp: 16 rows x half of the columns)
+    {
+      const int rr = (warp & 3) * 16, hh = warp >> 2;
+      uint32_t tf[CH / 16][4];
+      load_a<128, CH / 16>(Tb_a, rr, lane, tf);
+      float wacc[8][4];
+      zero_acc(wacc);
+      mma_ab<256, CH / 16, 8>(tf, Ks_a, hh * 8, lane, wacc);
+      float uacc[4][4];
+      zero_acc(uacc);
+      mma_ab<128, CH / 16, 4>(tf, Vs_a, hh * 4, lane, uacc);
+      const int i0 = rr + fg, i1 = i0 + 8;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) sm.U32[i][col] = x[i];
+      for (int j = 0; j < 8; ++j) {
+        const int col = 8 * (hh * 8 + j) + 2 * fc;
+        *reinterpret_cast<uint32_t*>(bf16_at(sm.Wb, Wb_a, 256, i0, col)) = pack_bf16x2(wacc[j][0], wacc[j][1]);
+        *reinterpret_cast<uint32_t*>(bf16_at(sm.Wb, Wb_a, 256, i1, col)) = pack_bf16x2(wacc[j][2], wacc[j][3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = 8 * (hh * 4 + j) + 2 * fc;
+        *reinterpret_cast<float2*>(&sm.U32[i0][col]) = make_float2(uacc[j][0], uacc[j][1]);
+        *reinterpret_cast<float2*>(&sm.U32[i1][col]) = make_float2(uacc[j][2], uacc[j][3]);
       }
     }
     __syncthreads();

@@ -6,6 +6,7 @@ stream, operands rotated over several copies so that every launch reads from HBM
   python -m logismos_b200.microbench gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
   python -m logismos_b200.microbench qlinear [--m M --n N --k K --iters I]   (m <= 256, fused int4 dequant)
   python -m logismos_b200.microbench qdense  [--m M --n N --k K --iters I]   (bf16 expansion + dense GEMM)
+  python -m logismos_b200.microbench gdn     [--seqs S --len L]                 (token-serial vs chunk-parallel)
   python -m logismos_b200.microbench paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
   python -m logismos_b200.microbench attn  [--seqs S --len L --iters I]
   python -m logismos_b200.microbench sweep          (every benchmark shape, one JSON line each)
@@ -134,6 +135,31 @@ def bench_qdense(m, n, k, iters, copies=None, pk=None):
             "GBps": (wbytes + m * k * 2 + m * n * 4) / t / 1e9, "frac_hbm": 0.0, "device_status": int(status.item())}
 
 
+def bench_gdn(n_seq, length, iters, heads=16, pk=None):
+    """Gated delta rule over n_seq sequences of `length` tokens (16 heads of 128 x 128 fp32 state): the
+    token-serial kernel and the chunk-parallel kernel on the same inputs."""
+    pk = pk or peaks()
+    D, T = 128, n_seq * length
+    mk = lambda: torch.randn((T, heads, D), device="cuda").to(torch.bfloat16)
+    q, k, v, z = mk(), mk(), mk(), mk()
+    q = torch.nn.functional.normalize(q.float(), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(k.float(), dim=-1).to(torch.bfloat16)
+    g = -torch.rand((T, heads), device="cuda") * 0.1
+    beta = torch.rand((T, heads), device="cuda")
+    cu = torch.arange(0, T + 1, length, dtype=torch.int32, device="cuda")
+    st = torch.zeros((n_seq, heads, D, D), device="cuda")
+    t_serial = timeit(lambda i: ops.gdn_prefill_(st, q, k, v, g, beta, cu, D ** -0.5, gate_z=z, sync=False), iters)
+    out = {"kernel": "gated_delta_rule", "seqs": n_seq, "len": length, "heads": heads, "us_token_serial": t_serial * 1e6,
+           "state_GBps_token_serial": 2.0 * n_seq * heads * D * D * 4 / t_serial / 1e9, "peak": pk["hbm"], "peak_src": pk["src"]}
+    if length > 1:
+        t_chunk = timeit(lambda i: ops.gdn_chunked_(st, q, k, v, g, beta, cu, D ** -0.5, gate_z=z, sync=False), iters)
+        out.update({"us_chunk_parallel": t_chunk * 1e6, "us_per_token_chunk_parallel": t_chunk * 1e6 / length,
+                    "us_per_token_serial": t_serial * 1e6 / length, "speedup": t_serial / t_chunk})
+    else:
+        out["frac_hbm_token_serial"] = out["state_GBps_token_serial"] / pk["hbm"]
+    return out
+
+
 def bench_gemm(m, n, k, epi, iters, pk=None):
     pk = pk or peaks()
     a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
@@ -199,7 +225,7 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="logismos_b200.microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "paged", "attn", "sweep"])
+    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "gdn", "paged", "attn", "sweep"])
     ap.add_argument("--m", type=int, default=2176)
     ap.add_argument("--n", type=int, default=151936)
     ap.add_argument("--k", type=int, default=1536)
@@ -219,6 +245,8 @@ def main(argv=None):
         print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
     elif a.what == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.epi, a.iters)))
+    elif a.what == "gdn":
+        print(json.dumps(bench_gdn(a.seqs, a.len, min(a.iters, 5))))
     elif a.what == "qdense":
         print(json.dumps(bench_qdense(a.m, a.n, a.k, a.iters)))
     elif a.what == "qlinear":
