@@ -93,7 +93,7 @@ LG_DEVINL void zero_acc(float (&c)[NT][4]) {
 
 struct Smem {
   float S32[KD][VW];                       // state slice, fp32
-  float A32[CH][kAPitch];                  // strictly lower triangular coefficients
+  float A32[CH][kAPitch];                  // strictly lower triangular coefficients, stored transposed: [j][i] = A[i][j]
   float U32[CH][VW];                       // U of the solve
   float cg[CH], gam[CH], bet[CH];
   __align__(128) __nv_bfloat16 Sb[KD * VW];      // state slice rounded to bf16, [k][v] rows of 128 B
@@ -213,10 +213,11 @@ gdn_chunk_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q,
         for (int t = 0; t < CH / 8; ++t) {
           const int j0 = 8 * t + 2 * fc, j1 = j0 + 1;
           const float cj0 = sm.cg[j0], cj1 = sm.cg[j1];
-          sm.A32[i0][j0] = i0 > j0 ? b0 * s[t][0] * __expf(ci0 - cj0) : 0.f;
-          sm.A32[i0][j1] = i0 > j1 ? b0 * s[t][1] * __expf(ci0 - cj1) : 0.f;
-          sm.A32[i1][j0] = i1 > j0 ? b1 * s[t][2] * __expf(ci1 - cj0) : 0.f;
-          sm.A32[i1][j1] = i1 > j1 ? b1 * s[t][3] * __expf(ci1 - cj1) : 0.f;
+          // stored transposed (At[j][i] = A[i][j]): the inverse below walks A by columns
+          sm.A32[j0][i0] = i0 > j0 ? b0 * s[t][0] * __expf(ci0 - cj0) : 0.f;
+          sm.A32[j1][i0] = i0 > j1 ? b0 * s[t][1] * __expf(ci0 - cj1) : 0.f;
+          sm.A32[j0][i1] = i1 > j0 ? b1 * s[t][2] * __expf(ci1 - cj0) : 0.f;
+          sm.A32[j1][i1] = i1 > j1 ? b1 * s[t][3] * __expf(ci1 - cj1) : 0.f;
         }
       } else {
 #pragma unroll
@@ -231,51 +232,56 @@ gdn_chunk_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q,
       }
     }
     __syncthreads();
-    // ---- stage 4a: T = (I + A)^-1 by forward substitution, one column per thread (threads 0-63), while
-    // the other threads scale the right-hand sides: Ks = beta gamma K, Vs = beta V
-    if (tid < CH) {
-      const int col = tid;
-      float x[CH];
+    // ---- stage 4a: scale the right-hand sides (Ks = beta gamma K, Vs = beta V), then T = (I + A)^-1 by
+    // forward substitution: four neighbouring lanes per column, rows dealt round-robin (row i to lane
+    // i % 4), right-looking: the owner of row j broadcasts x_j with one shuffle and every lane takes that
+    // term out of its later rows at once, so the updates of a step are independent of each other; the
+    // coefficients of step j + 1 are fetched before the shuffle of step j. (Measured: this stage takes
+    // about 7500 cycles per chunk however the 64 x 64 substitution is spread over threads - one, two or
+    // four lanes per column, unrolled or looped - and is a third of the kernel.)
+    for (int e = tid; e < CH * (KD / 8); e += kThreads) {  // 16-byte pieces of K
+      const int row = e / (KD / 8), piece = e % (KD / 8);
+      const float f = sm.bet[row] * sm.gam[row];
+      const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Kt) + (taddr<256>(Kt_a, row, piece) - Kt_a));
+      uint4 out;
+      float2 t;
+      t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Ks) + (taddr<256>(Ks_a, row, piece) - Ks_a)) = out;
+    }
+    for (int e = tid; e < CH * (VW / 8); e += kThreads) {  // 16-byte pieces of V
+      const int row = e / (VW / 8), piece = e % (VW / 8);
+      const float f = sm.bet[row];
+      const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Vt) + (taddr<128>(Vt_a, row, piece) - Vt_a));
+      uint4 out;
+      float2 t;
+      t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
+      t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Vs) + (taddr<128>(Vs_a, row, piece) - Vs_a)) = out;
+    }
+    {
+      const int col = tid >> 2, part = tid & 3;
+      float acc[CH / 4];  // acc[m] is row 4 m + part of column `col`
 #pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        // four partial sums: the dependency chain of a row is a quarter of its length
-        float a0 = i == col ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int m = 0; m < CH / 4; ++m) acc[m] = (4 * m + part) == col ? 1.f : 0.f;
+      float a_cur[CH / 4];
 #pragma unroll
-        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-          const float4 a = *reinterpret_cast<const float4*>(&sm.A32[i][4 * j4]);  // entries at j >= i are zero
-          a0 -= a.x * x[4 * j4];
-          if (4 * j4 + 1 < i) a1 -= a.y * x[4 * j4 + 1];
-          if (4 * j4 + 2 < i) a2 -= a.z * x[4 * j4 + 2];
-          if (4 * j4 + 3 < i) a3 -= a.w * x[4 * j4 + 3];
-        }
-        x[i] = (a0 + a1) + (a2 + a3);
-      }
+      for (int m = 0; m < CH / 4; ++m) a_cur[m] = sm.A32[0][4 * m + part];
 #pragma unroll
-      for (int i = 0; i < CH; ++i) *bf16_at(sm.Tb, Tb_a, 128, i, col) = __float2bfloat16(x[i]);
-    } else {
-      for (int e = tid - CH; e < CH * (KD / 8); e += kThreads - CH) {  // 16-byte pieces of K
-        const int row = e / (KD / 8), piece = e % (KD / 8);
-        const float f = sm.bet[row] * sm.gam[row];
-        const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Kt) + (taddr<256>(Kt_a, row, piece) - Kt_a));
-        uint4 out;
-        float2 t;
-        t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Ks) + (taddr<256>(Ks_a, row, piece) - Ks_a)) = out;
-      }
-      for (int e = tid - CH; e < CH * (VW / 8); e += kThreads - CH) {  // 16-byte pieces of V
-        const int row = e / (VW / 8), piece = e % (VW / 8);
-        const float f = sm.bet[row];
-        const uint4 in = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sm.Vt) + (taddr<128>(Vt_a, row, piece) - Vt_a));
-        uint4 out;
-        float2 t;
-        t = unpack_bf16x2(in.x); out.x = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.y); out.y = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.z); out.z = pack_bf16x2(t.x * f, t.y * f);
-        t = unpack_bf16x2(in.w); out.w = pack_bf16x2(t.x * f, t.y * f);
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm.Vs) + (taddr<128>(Vs_a, row, piece) - Vs_a)) = out;
+      for (int j = 0; j < CH; ++j) {
+        float a_nxt[CH / 4];
+#pragma unroll
+        for (int m = 0; m < CH / 4; ++m) a_nxt[m] = (j + 1 < CH && m >= ((j + 1) >> 2)) ? sm.A32[(j + 1) % CH][4 * m + part] : 0.f;
+        const float xj = __shfl_sync(0xffffffffu, acc[j >> 2], (lane & ~3) | (j & 3));
+        if (part == (j & 3)) *bf16_at(sm.Tb, Tb_a, 128, j, col) = __float2bfloat16(xj);
+#pragma unroll
+        for (int m = j >> 2; m < CH / 4; ++m) acc[m] -= a_cur[m] * xj;  // A[i][j], zero where i <= j
+#pragma unroll
+        for (int m = 0; m < CH / 4; ++m) a_cur[m] = a_nxt[m];
       }
     }
     __syncthreads();
