@@ -72,7 +72,8 @@ uint32_t logismos_launch_rms_norm_f32(const void* x_f32, const void* w_f32, void
  *                    interleaved in blocks of 32 rows (32 gate rows, then the 32 matching up
  *                    rows); n % 64 == 0; fuses cpu_f32::silu + hadamard (mod.rs:349-374)
  * bias_f32 may be NULL. ldc is the row stride of out in elements. status_i32 (may be NULL)
- * receives 2 if a bounded wait inside the kernel expired (the output is then invalid). */
+ * receives 2 if a bounded wait inside the kernel expired (the output is then invalid).  * With few output tiles and a long reduction the accumulating epilogue splits k over CTAs; the
+ * slices meet in the fp32 reduce-add, so the last bits of the sum can differ between runs. */
 enum { LG_EPI_BF16 = 0, LG_EPI_RESID_F32 = 1, LG_EPI_SWIGLU = 2 };
 uint32_t logismos_launch_linear_t_bf16(const void* a_bf16, const void* w_bf16,
                                        const void* bias_f32, void* out, int32_t m, int32_t n,

@@ -49,7 +49,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
-                        void* __restrict__ out, int M, int N, int K, int ldc, int* __restrict__ status) {
+                        void* __restrict__ out, int M, int N, int K, int ldc, int splits, int* __restrict__ status) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume
@@ -67,8 +67,12 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int num_kb = K / BK;
+  // a work item is (k slice, output tile); slices of k exist only for the accumulating epilogue, whose
+  // reduce-add makes them meet in the output
+  const int out_tiles = m_tiles * n_tiles;
+  const int total_tiles = out_tiles * splits;
+  const int all_kb = K / BK;
+  const int kb_per = (all_kb + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -93,8 +97,10 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int ot = tile % out_tiles, sp = tile / out_tiles;
+        const int m_blk = ot % m_tiles, n_blk = ot / m_tiles;
+        const int kb0 = sp * kb_per, kb1 = min(all_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), (uint32_t)C::kStage);
           const uint32_t sa = smem_base + stage * C::kStage;
@@ -118,7 +124,9 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int sp = tile / out_tiles;
+        const int kb0 = sp * kb_per, kb1 = min(all_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + stage * C::kStage;
@@ -126,7 +134,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 bf16 along K inside the swizzle row = +32 B = +2 in the encoded address
-            tc_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) ? 1u : 0u);
+            tc_mma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, ((kb - kb0) | k) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -161,7 +169,9 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       ++n_store;
     };
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+      const int ot = tile % out_tiles;
+      const int m_blk = ot % m_tiles, n_blk = ot / m_tiles;
+      const bool first_slice = tile < out_tiles;  // the bias joins once
       const int buf = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
@@ -180,7 +190,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           for (int j = 0; j < 8; ++j) {
             float a0 = __uint_as_float(r[4 * j]), a1 = __uint_as_float(r[4 * j + 1]);
             float a2 = __uint_as_float(r[4 * j + 2]), a3 = __uint_as_float(r[4 * j + 3]);
-            if (bias && ncol + 4 * j < N) { a0 += bias[ncol + 4 * j]; a1 += bias[ncol + 4 * j + 1]; a2 += bias[ncol + 4 * j + 2]; a3 += bias[ncol + 4 * j + 3]; }
+            if (bias && first_slice && ncol + 4 * j < N) { a0 += bias[ncol + 4 * j]; a1 += bias[ncol + 4 * j + 1]; a2 += bias[ncol + 4 * j + 2]; a3 += bias[ncol + 4 * j + 3]; }
             slab_write(slabs + b * 4096, lane, j, make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3)));
           }
           slab_release(b, ncol, row0, ncol < N && row0 < M);
@@ -294,8 +304,21 @@ uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmem);
   if (e != cudaSuccess) return (uint32_t)e;
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, mo, bias, out, m, n, k, ldc, status);
+  // few output tiles and a long reduction (the output projections of a small step): the accumulating
+  // epilogue lets slices of k run on otherwise idle SMs; every slice gets at least four k blocks
+  int splits = 1;
+  if (EPI == LG_EPI_RESID_F32) {
+    const int all_kb = k / BK;
+    if (tiles * 2 <= sm_count() && all_kb >= 8) {
+      const int want = sm_count() / tiles;
+      int kb_per = (all_kb + want - 1) / want;
+      if (kb_per < 4) kb_per = 4;
+      splits = (all_kb + kb_per - 1) / kb_per;
+    }
+  }
+  const int items = tiles * splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, mo, bias, out, m, n, k, ldc, splits, status);
   return lg::launch_status();
 }
 

@@ -67,7 +67,10 @@ def test_embedding_model_contract(tiny):  # crates/core/src/lib.rs:139-163, crat
     ids2, cu2 = make_batch(TINY, 5, n_seq=9, lo=20, hi=120)
     big = m.encode_ids_batch(ids2, cu2)
     for i in (0, 4, 8):
-        assert np.abs(big[i] - m.encode_ids(ids2[cu2[i]:cu2[i + 1]])).max() < 1e-5
+        # not bit-identical: the split of the long reductions over CTAs depends on the number of rows in
+        # the batch, so the last bits of the fp32 residual stream differ and a few bf16 roundings flip
+        alone = m.encode_ids(ids2[cu2[i]:cu2[i + 1]])
+        assert float(big[i] @ alone) >= 0.9999 and np.abs(big[i] - alone).max() < 2e-3
     # empty batch and out-of-range ids (zero embedding rows, cpu_f32/mod.rs:96-104)
     assert m.encode_ids_batch(np.zeros(0, np.uint32), np.zeros(1, np.int32)).shape == (0, 128)
     weird = np.array([1, TINY["vocab"] + 5, 7], np.uint32)
