@@ -201,7 +201,8 @@ def micro_rooflines(peaks, T, cfg):
     acc = torch.zeros((64, n), dtype=torch.float32, device=dev)
     stw = torch.zeros(1, dtype=torch.int32, device=dev)
     t = time_kernel(lambda i: ops.check(ops.lib.logismos_launch_qlinear_int4_g32_acc_f32(
-        x2.data_ptr(), codes2[i % 2].data_ptr(), scales2[i % 2].data_ptr(), acc.data_ptr(), 64, n, k2, k2, n, stw.data_ptr(), st.cuda_stream), "qlinear"), 20, st)
+        x2.data_ptr(), codes2[i % 2].data_ptr(), scales2[i % 2].data_ptr(), acc.data_ptr(), 64, n, k2, k2, n, stw.data_ptr(),
+        torch.cuda.current_stream().cuda_stream), "qlinear"), 20, st)  # the stream is looked up per call: graph capture switches it
     by2 = n * k2 / 2 + n * (k2 // 32) * 2 + 64 * k2 * 2 + 64 * n * 4
     out["qlinear"] = {"kernel": "qlinear_int4_tcgen05 (151936 x 2048, 64 tokens, fp32 accumulate)", "bound": "hbm", "achieved": by2 / t / 1e9,
                       "peak": peaks["hbm"], "unit": "GB/s", "frac": by2 / t / 1e9 / peaks["hbm"], "traffic": None, "bytes_per_launch": by2,
