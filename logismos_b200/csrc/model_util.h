@@ -86,10 +86,11 @@ constexpr int kFusedDequantMaxRows = 128;
 inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc, int epi,
                             void* wscratch, void* accws, void* status, int* launches, cudaStream_t s) {
   uint32_t rc;
-  // with a persistent bf16 copy at hand, the wide projections that need a finishing pass (bf16 / SwiGLU
-  // outputs through the fp32 workspace) are already faster through the dense GEMM above 32 rows
-  // (measured: 14-18 us against 19-24 us); the narrow, deep output projections stay fused
-  const bool fused_ok = T <= kFusedDequantMaxRows && w.k % 256 == 0 && (epi == LG_EPI_RESID_F32 || !w.dense.p || T <= 32);
+  // with a persistent bf16 copy at hand the dense GEMM (split over k for the narrow output projections)
+  // is as fast or faster above 32 rows (measured at 64 / 128 rows: 6.5 / 6.7 us against 6.7 / 8.2 us for
+  // 2048 x 2048, 9.5 / 9.8 against 10.7 / 14.6 us for 2048 x 6144, 14-18 against 19-24 us for the wide
+  // projections with their finishing pass); below that the int4 stream wins
+  const bool fused_ok = T <= kFusedDequantMaxRows && w.k % 256 == 0 && (!w.dense.p || T <= 32);
   if (fused_ok) {
     if (epi == LG_EPI_RESID_F32 && !bias) {
       *launches += 1;
