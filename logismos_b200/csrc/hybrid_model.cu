@@ -126,10 +126,11 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, QW, s)) return rc;
     } else {
       // columns: q [GW] | k [GW] | v [GW] | z [GW] | a [GH] | b [GH] of one weight matrix
-      // fused up to 32 rows when the dense route has a bf16 copy to work on (inside a step the finishing
-      // kernel waits for the accumulation's fp32 reductions to drain: 16 + 18 us at 64 rows against 26 us
-      // for the three dense launches), else up to the fused kernel's limit
-      if (T <= (L.w_in.dense.p ? 32 : kFusedDequantMaxRows)) {
+      // fused up to 96 rows even when the dense route has a bf16 copy to work on: measured per step,
+      // the one accumulation + finishing kernel (16 + 18 us at 64 rows, the finishing kernel waiting for
+      // the fp32 reductions to drain) still beats GEMM + memset + a|b GEMM + prepare (5.72 against 5.97 ms
+      // per 64-sequence step); at 128 rows the two routes are level
+      if (T <= (L.w_in.dense.p ? 96 : kFusedDequantMaxRows)) {
         // one fused-dequant accumulation of all six blocks, finished by the kernel that also normalises
         // q, k and computes the gates from the fp32 sums
         const int ld = GN + 2 * GH;
