@@ -160,7 +160,7 @@ def time_kernel(fn, iters, stream):
 # processed, as the summaries state). bytes per unit: gate/up GEMM at M=2176 (read 61.97 + write 7.44 MB,
 # the bf16 output lands in L2 first); GEMV lm_head (131.30 + 5.89 MB); paged decode 1027 B per context
 # token + 7.09 MB of partials per 328868 tokens.
-NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 137.19e6, "paged_per_context_token": (337.73e6 + 7.09e6) / 328868}
+NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 7.09e6) / 328868}
 
 
 def micro_rooflines(peaks, T, cfg):

@@ -226,22 +226,31 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
 // scales (16 rows x 8 B) travel global -> shared with cp.async through a per-warp ring of STAGES
 // slots that runs ahead across row-tile boundaries; ldmatrix.x4 hands lane (g, c) exactly "word c of
 // groups 0..3 of row g"; no block-wide barrier and no cross-warp reduction in the loop.
-constexpr int kWPitch = 80;                       // row pitch of a staged weight step: conflict-free ldmatrix
-constexpr int kSlotBytes = 16 * kWPitch + 16 * 8 + 16 * 16;  // codes, 16 x 4 fp16 scales, the same as fp32
+constexpr int kWPitch = 80;  // row pitch of a staged weight step: conflict-free ldmatrix
+// One ring slot holds one warp step: RT row tiles of 16 rows x (64 B of codes at kWPitch, 4 fp16
+// scales, the same 4 scales widened to fp32).
+__host__ __device__ constexpr int slot_bytes(int rt) { return rt * (16 * kWPitch + 16 * 8 + 16 * 16); }
 
-template <int NT, int STAGES>
-__global__ void __launch_bounds__(512)
+// RT = 16-row tiles a warp carries side by side (1 or 2). With two, the activation fragments and the
+// group corrections fetched from shared memory, the ring bookkeeping and the copy addressing are paid
+// once for twice the weights, which is what bounds this kernel at batch <= 16: issue slots, not HBM.
+template <int NT, int STAGES, int RT>
+__global__ void __launch_bounds__(STAGES == 8 ? 256 : (RT == 2 ? 384 : (NT <= 2 ? 768 : 512)))
 gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
                             const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
                             int N, int K) {
   extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int kSlot = slot_bytes(RT);
+  constexpr int kRows = 16 * RT;
+  constexpr uint32_t kScaleH = kRows * kWPitch;      // fp16 scales of the slot
+  constexpr uint32_t kScaleF = kScaleH + kRows * 8;  // fp32 scales of the slot, [row][4]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int groups = K / kGroup, iters = K / kIterK;
   const int xrow_stride = groups * 64 + 64;
   uint8_t* xs = smem;
   float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
-  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kSlotBytes;
+  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kSlot;
   const uint32_t ring = smem_u32(ring_gen);
 
   // stage x (bf16, fragment order) and the per-group corrections, once
@@ -263,34 +272,37 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
   }
   __syncthreads();
 
-  const int row_tiles = (N + 15) / 16;
+  const int row_tiles = (N + kRows - 1) / kRows;
   const int tile_stride = gridDim.x * nwarps;
   const int first_tile = blockIdx.x * nwarps + warp;
   const int my_tiles = first_tile < row_tiles ? (row_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
   const int total_steps = my_tiles * iters;
-  const uint32_t ring_end = ring + STAGES * kSlotBytes;
+  const uint32_t ring_end = ring + STAGES * kSlot;
 
   // ---- producer: runs STAGES-1 steps ahead of the consumer, across row-tile boundaries. All
   // addresses advance by constants inside a tile; they are rebuilt only when the tile changes.
   int p_left = total_steps, p_it = 0, p_tile = first_tile;
   uint32_t p_slot = ring;
-  const uint8_t *pw0, *pw1;
+  const uint8_t* pw[2 * RT];
   const __half* ps;
   auto producer_tile = [&](int tile) {
-    const int rb = tile * 16;
-    pw0 = codes + (size_t)min(rb + g, N - 1) * (K / 2) + c * 16;
-    pw1 = codes + (size_t)min(rb + g + 8, N - 1) * (K / 2) + c * 16;
-    ps = scales + (size_t)min(rb + (lane & 15), N - 1) * groups;
+    const int rb = tile * kRows;
+#pragma unroll
+    for (int h = 0; h < 2 * RT; ++h) pw[h] = codes + (size_t)min(rb + g + 8 * h, N - 1) * (K / 2) + c * 16;
+    ps = scales + (size_t)min(rb + (lane & (kRows - 1)), N - 1) * groups;
   };
   producer_tile(p_tile);
-  const uint32_t dst_w = (uint32_t)(g * kWPitch + c * 16), dst_s = (uint32_t)(16 * kWPitch + (lane & 15) * 8);
+  const uint32_t dst_w = (uint32_t)(g * kWPitch + c * 16), dst_s = kScaleH + (uint32_t)((lane & (kRows - 1)) * 8);
   auto issue = [&]() {
     if (p_left > 0) {
-      cp_async16(p_slot + dst_w, pw0);
-      cp_async16(p_slot + dst_w + 8 * kWPitch, pw1);
-      if (lane < 16) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(p_slot + dst_s), "l"(ps));
-      pw0 += 64; pw1 += 64; ps += 4;
-      p_slot += kSlotBytes;
+#pragma unroll
+      for (int h = 0; h < 2 * RT; ++h) {
+        cp_async16(p_slot + dst_w + h * 8 * kWPitch, pw[h]);
+        pw[h] += 64;
+      }
+      if (lane < kRows) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(p_slot + dst_s), "l"(ps));
+      ps += 4;
+      p_slot += kSlot;
       if (p_slot == ring_end) p_slot = ring;
       --p_left;
       if (++p_it == iters) { p_it = 0; p_tile += tile_stride; producer_tile(p_tile); }
@@ -302,76 +314,100 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
 
   // ---- consumer
   const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: lanes 8j..8j+7 address the rows of matrix j (= group j)
-  const uint32_t ld_off0 = (uint32_t)(mr * kWPitch + mat * 16), ld_off1 = ld_off0 + 8 * kWPitch;
-  const uint32_t sc_off0 = (uint32_t)(16 * kWPitch + 128 + g * 16), sc_off1 = sc_off0 + 128;
+  const uint32_t ld_off = (uint32_t)(mr * kWPitch + mat * 16);
+  const uint32_t sc_off = kScaleF + (uint32_t)(g * 16);
   const uint32_t xs_a = smem_u32(xs) + (uint32_t)(g * xrow_stride + c * 16);
   const uint32_t nc_a = smem_u32(negcorr) + (uint32_t)(2 * c * 4);
   uint32_t c_slot = ring;
   int c_tile = first_tile;
   for (int t = 0; t < my_tiles; ++t, c_tile += tile_stride) {
-    float acc[NT][4];
+    float acc[RT][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int r = 0; r < RT; ++r)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][nt][i] = 0.0f;
     uint32_t xa = xs_a, na = nc_a;
     for (int it = 0; it < iters; ++it) {
       issue();
       cp_async_wait<STAGES - 1>();
       __syncwarp();
-      uint32_t w0[4], w1[4];
-      ldmatrix_x4(w0, c_slot + ld_off0);
-      ldmatrix_x4(w1, c_slot + ld_off1);
-      {  // each lane widens two of the step's 64 scales to fp32 (instead of every lane widening eight)
+      uint32_t w[2 * RT][4];  // [2r] rows g, [2r+1] rows g+8 of row tile r: word c of groups 0..3
+#pragma unroll
+      for (int h = 0; h < 2 * RT; ++h) ldmatrix_x4(w[h], c_slot + ld_off + h * 8 * kWPitch);
+      // each lane widens 2*RT of the step's 64*RT scales to fp32 (instead of every lane widening 8*RT)
+      if constexpr (RT == 1) {
         uint32_t sh;
-        asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(sh) : "r"(c_slot + (uint32_t)(16 * kWPitch + lane * 4)));
+        asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(sh) : "r"(c_slot + kScaleH + (uint32_t)(lane * 4)));
         const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sh));
-        asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(c_slot + (uint32_t)(16 * kWPitch + 128 + lane * 8)), "f"(sf.x), "f"(sf.y));
+        asm volatile("st.shared.v2.f32 [%0], {%1, %2};\n" ::"r"(c_slot + kScaleF + (uint32_t)(lane * 8)), "f"(sf.x), "f"(sf.y));
+      } else {
+        uint32_t sh0, sh1;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(sh0), "=r"(sh1) : "r"(c_slot + kScaleH + (uint32_t)(lane * 8)));
+        const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(&sh0));
+        const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(&sh1));
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(c_slot + kScaleF + (uint32_t)(lane * 16)), "f"(sa.x), "f"(sa.y), "f"(sb.x), "f"(sb.y));
       }
       __syncwarp();
-      float sc0[4], sc1[4];
-      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(sc0[0]), "=f"(sc0[1]), "=f"(sc0[2]), "=f"(sc0[3]) : "r"(c_slot + sc_off0));
-      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(sc1[0]), "=f"(sc1[1]), "=f"(sc1[2]), "=f"(sc1[3]) : "r"(c_slot + sc_off1));
+      float sc[2 * RT][4];
+#pragma unroll
+      for (int h = 0; h < 2 * RT; ++h)
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                     : "=f"(sc[h][0]), "=f"(sc[h][1]), "=f"(sc[h][2]), "=f"(sc[h][3])
+                     : "r"(c_slot + sc_off + h * 128));
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t w0s = w0[j] >> 8, w1s = w1[j] >> 8;
-        const uint32_t a_lo[4] = {nib_pair_bf16(w0[j]), nib_pair_bf16(w1[j]), nib_pair_bf16(w0s), nib_pair_bf16(w1s)};
-        const uint32_t a_hi[4] = {nib_pair_f16_hi(w0[j]), nib_pair_f16_hi(w1[j]), nib_pair_f16_hi(w0s), nib_pair_f16_hi(w1s)};
+        uint32_t a_lo[RT][4], a_hi[RT][4];
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+          const uint32_t w0 = w[2 * r][j], w1 = w[2 * r + 1][j];
+          const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+          a_lo[r][0] = nib_pair_bf16(w0); a_lo[r][1] = nib_pair_bf16(w1);
+          a_lo[r][2] = nib_pair_bf16(w0s); a_lo[r][3] = nib_pair_bf16(w1s);
+          a_hi[r][0] = nib_pair_f16_hi(w0); a_hi[r][1] = nib_pair_f16_hi(w1);
+          a_hi[r][2] = nib_pair_f16_hi(w0s); a_hi[r][3] = nib_pair_f16_hi(w1s);
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           uint32_t b_lo[2], b_hi[2];
-          float d[4];
+          float nc[2];
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
                        : "=r"(b_lo[0]), "=r"(b_lo[1]), "=r"(b_hi[0]), "=r"(b_hi[1])
                        : "r"(xa + (uint32_t)(nt * 8 * xrow_stride + j * 64)));
-          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];\n" : "=f"(d[0]), "=f"(d[1]) : "r"(na + (uint32_t)((j * NT * 8 + nt * 8) * 4)));
-          d[2] = d[0];
-          d[3] = d[1];
-          mma_bf16_16816(d, a_lo, b_lo, d);
-          mma_f16_16816(d, a_hi, b_hi, d);
-          acc[nt][0] = fmaf(sc0[j], d[0], acc[nt][0]);
-          acc[nt][1] = fmaf(sc0[j], d[1], acc[nt][1]);
-          acc[nt][2] = fmaf(sc1[j], d[2], acc[nt][2]);
-          acc[nt][3] = fmaf(sc1[j], d[3], acc[nt][3]);
+          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];\n" : "=f"(nc[0]), "=f"(nc[1]) : "r"(na + (uint32_t)((j * NT * 8 + nt * 8) * 4)));
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+            float d[4] = {nc[0], nc[1], nc[0], nc[1]};
+            mma_bf16_16816(d, a_lo[r], b_lo, d);
+            mma_f16_16816(d, a_hi[r], b_hi, d);
+            acc[r][nt][0] = fmaf(sc[2 * r][j], d[0], acc[r][nt][0]);
+            acc[r][nt][1] = fmaf(sc[2 * r][j], d[1], acc[r][nt][1]);
+            acc[r][nt][2] = fmaf(sc[2 * r + 1][j], d[2], acc[r][nt][2]);
+            acc[r][nt][3] = fmaf(sc[2 * r + 1][j], d[3], acc[r][nt][3]);
+          }
         }
       }
       __syncwarp();  // every lane is done with the slot before a later issue() refills it
-      c_slot += kSlotBytes;
+      c_slot += kSlot;
       if (c_slot == ring_end) c_slot = ring;
       xa += 4 * 64;
       na += 4 * NT * 8 * 4;
     }
-    const int ra = c_tile * 16 + g, rb = ra + 8;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int b0 = nt * 8 + 2 * c;
-      if (ra < N) {
-        if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[nt][0]);
-        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[nt][1]);
-      }
-      if (rb < N) {
-        if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[nt][2]);
-        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[nt][3]);
+    for (int r = 0; r < RT; ++r) {
+      const int ra = c_tile * kRows + r * 16 + g, rb = ra + 8;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b0 = nt * 8 + 2 * c;
+        if (ra < N) {
+          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[r][nt][0]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[r][nt][1]);
+        }
+        if (rb < N) {
+          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[r][nt][2]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[r][nt][3]);
+        }
       }
     }
   }
@@ -388,6 +424,31 @@ int gemv_sm_count() {
   return n;
 }
 
+template <int NT, int STAGES, int RT>
+uint32_t launch_stream(const void* codes, const void* scales, const void* x, void* y, int batch, int N, int K,
+                       int grid, int warps, size_t smem, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, STAGES, RT>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (uint32_t)e;
+  gemv_int4_g32_stream_kernel<NT, STAGES, RT><<<grid, warps * 32, smem, stream>>>(
+      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
+  return lg::launch_status();
+}
+
+// Among warp counts lo..hi, the one that leaves the least idle tail: every warp gets floor or ceil of
+// tiles / (sms * warps) row tiles, and the kernel ends with the slowest warp.
+int best_warp_count(int row_tiles, int sms, int lo, int hi) {
+  double best_eff = -1.0;
+  int best_w = hi;
+  for (int wv = hi; wv >= lo; --wv) {
+    const long slots = (long)sms * wv;
+    const long per = (row_tiles + slots - 1) / slots;
+    const double eff = (double)row_tiles / (double)(per * slots);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best_w = wv; }
+  }
+  return best_w;
+}
+
 // Returns true (and the status in *rc) when the streaming variant applies and was launched.
 template <int NT>
 bool try_launch_stream(const void* codes, const void* scales, const void* x, void* y, int batch, int N, int K,
@@ -397,40 +458,34 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
   if (row_tiles < 2 * sms) return false;  // too few row tiles per SM: the k-split kernel spreads better
   const int groups = K / kGroup;
   const size_t xbytes = (size_t)NT * 8 * (groups * 64 + 64) + (size_t)groups * NT * 8 * 4;
-  // warps per CTA: enough to keep ~48 KB of weights in flight per SM, and among those counts the one
-  // that leaves the least idle tail (every warp gets floor or ceil of tiles / (grid * warps))
+  const size_t budget = 200 * 1024;
+  if (xbytes + 2 * 8 * slot_bytes(1) > budget) return false;  // x does not fit: chunked kernel
   int warps = (row_tiles + sms - 1) / sms;
-  warps = warps < 2 ? 2 : (warps > 16 ? 16 : warps);
-  if (warps > 8) {
-    double best_eff = -1.0;
-    int best_w = warps;
-    for (int wv = 16; wv >= 10; --wv) {
-      const long slots = (long)sms * wv;
-      const long per = (row_tiles + slots - 1) / slots;
-      const double eff = (double)row_tiles / (double)(per * slots);
-      if (eff > best_eff + 1e-9) { best_eff = eff; best_w = wv; }
+  if (warps <= 8) {  // short matrix: few warps, each with a deep ring
+    warps = warps < 2 ? 2 : warps;
+    while (xbytes + (size_t)warps * 8 * slot_bytes(1) > budget) --warps;
+    const int grid = (row_tiles + warps - 1) / warps < sms ? (row_tiles + warps - 1) / warps : sms;
+    *rc = launch_stream<NT, 8, 1>(codes, scales, x, y, batch, N, K, grid, warps, xbytes + (size_t)warps * 8 * slot_bytes(1), stream);
+    return true;
+  }
+  // Up to 16 batch rows a warp carries two row tiles side by side (fewer instructions per weight);
+  // the warp counts are the measured optimum on 148 SMs for a 151936-row matrix: 11 with one batch
+  // tile, 7 with two (more warps there lose to shared-memory pressure from the fragment loads).
+  const int rt = (NT <= 2 && row_tiles >= 32 * sms) ? 2 : 1;  // two tiles only when every warp gets several
+  const int max_warps = (int)((budget - xbytes) / (4 * slot_bytes(rt)));
+  const int tiles = (N + 16 * rt - 1) / (16 * rt);
+  int hi = rt == 1 ? 16 : (NT == 1 ? 12 : 8), lo = rt == 1 ? 10 : (NT == 1 ? 8 : 6);
+  if (hi > max_warps) hi = max_warps;
+  if (lo > hi) lo = hi;
+  warps = best_warp_count(tiles, sms, lo, hi);
+  const size_t smem = xbytes + (size_t)warps * 4 * slot_bytes(rt);
+  if constexpr (NT <= 2) {
+    if (rt == 2) {
+      *rc = launch_stream<NT, 4, 2>(codes, scales, x, y, batch, N, K, sms, warps, smem, stream);
+      return true;
     }
-    warps = best_w;
   }
-  const bool deep = warps <= 8;
-  const int stages = deep ? 8 : 4;
-  size_t smem = xbytes + (size_t)warps * stages * kSlotBytes;
-  while (smem > 200 * 1024 && warps > 2) { --warps; smem = xbytes + (size_t)warps * stages * kSlotBytes; }
-  if (smem > 200 * 1024) return false;  // x does not fit: chunked kernel
-  const int grid = (row_tiles + warps - 1) / warps < sms ? (row_tiles + warps - 1) / warps : sms;
-  cudaError_t e;
-  if (deep) {
-    e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
-    gemv_int4_g32_stream_kernel<NT, 8><<<grid, warps * 32, smem, stream>>>(
-        (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
-  } else {
-    e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
-    gemv_int4_g32_stream_kernel<NT, 4><<<grid, warps * 32, smem, stream>>>(
-        (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
-  }
-  *rc = lg::launch_status();
+  *rc = launch_stream<NT, 4, 1>(codes, scales, x, y, batch, N, K, sms, warps, smem, stream);
   return true;
 }
 
