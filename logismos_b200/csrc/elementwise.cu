@@ -63,6 +63,58 @@ __global__ void rms_norm_f32_kernel(const float* __restrict__ x, const float* __
   }
 }
 
+// The same normalisation with one WARP per row (no block barrier, shuffle reduction only) for tall
+// inputs: NV float4 per lane hold the row between the two passes (n <= 128 * NV).
+template <bool OUT_F32, int NV>
+__global__ void __launch_bounds__(256)
+rms_norm_f32_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ y,
+                         int rows, int n, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* src = x + (size_t)row * n;
+  float4 v[NV];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    v[i] = j < n ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    if (j < n) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(w + j));
+      const float o0 = v[i].x * inv * g.x, o1 = v[i].y * inv * g.y;
+      const float o2 = v[i].z * inv * g.z, o3 = v[i].w * inv * g.w;
+      if (OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + (size_t)row * n + j) = make_float4(o0, o1, o2, o3);
+      } else {
+        uint2 p;
+        p.x = pack_bf16x2(o0, o1);
+        p.y = pack_bf16x2(o2, o3);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)row * n + j) = p;
+      }
+    }
+  }
+}
+
+template <bool OUT_F32, int NV>
+void launch_rms_warp(const void* x, const void* w, void* y, int rows, int n, float eps, cudaStream_t s) {
+  rms_norm_f32_warp_kernel<OUT_F32, NV><<<(rows + 7) / 8, 256, 0, s>>>((const float*)x, (const float*)w, y, rows, n, eps);
+}
+
+template <bool OUT_F32>
+void launch_rms_warp_nv(const void* x, const void* w, void* y, int rows, int n, float eps, cudaStream_t s) {
+  if (n <= 512) launch_rms_warp<OUT_F32, 4>(x, w, y, rows, n, eps, s);
+  else if (n <= 1024) launch_rms_warp<OUT_F32, 8>(x, w, y, rows, n, eps, s);
+  else if (n <= 1536) launch_rms_warp<OUT_F32, 12>(x, w, y, rows, n, eps, s);
+  else launch_rms_warp<OUT_F32, 16>(x, w, y, rows, n, eps, s);
+}
+
 // cpu_f32::rope_halves_in_place (mod.rs:502-547): y[i] = x[i] c - x[i+d/2] s,
 // y[i+d/2] = x[i] s + x[i+d/2] c, in fp32, on bf16 storage. One thread per (token, head, pair of
 // adjacent i), i.e. bf16x2 accesses in both halves.
@@ -90,6 +142,44 @@ __global__ void rope_halves_kernel(__nv_bfloat16* __restrict__ qk, const float* 
   const float2 x0 = unpack_bf16x2(*lo), x1 = unpack_bf16x2(*hi);
   *lo = pack_bf16x2(x0.x * c.x - x1.x * s.x, x0.y * c.y - x1.y * s.y);
   *hi = pack_bf16x2(x0.x * s.x + x1.x * c.x, x0.y * s.y + x1.y * c.y);
+}
+
+// The same rotation with 128-bit accesses: one thread per (token, head, 8 adjacent i); head_dim % 16 == 0.
+__global__ void rope_halves_vec8_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cosT,
+                                        const float* __restrict__ sinT, const int* __restrict__ positions,
+                                        int n_tokens, int n_heads, int head_dim, int row_stride,
+                                        int max_pos, int* __restrict__ status) {
+  const int half = head_dim >> 1, octs = half >> 3;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)n_tokens * n_heads * octs;
+  if (idx >= total) return;
+  const int p = (int)(idx % octs);
+  const int h = (int)((idx / octs) % n_heads);
+  const int t = (int)(idx / ((int64_t)octs * n_heads));
+  const int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) {  // RopeTable::gather rejects it (rope.rs:57-66)
+    if (status) atomicExch(status, 1);
+    return;
+  }
+  __nv_bfloat16* base = qk + (size_t)t * row_stride + h * head_dim + 8 * p;
+  const float4* cp = reinterpret_cast<const float4*>(cosT + (size_t)pos * half + 8 * p);
+  const float4* sp = reinterpret_cast<const float4*>(sinT + (size_t)pos * half + 8 * p);
+  const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  uint4* lo = reinterpret_cast<uint4*>(base);
+  uint4* hi = reinterpret_cast<uint4*>(base + half);
+  const uint4 a = *lo, b = *hi;
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t ow[4], pw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x0 = unpack_bf16x2(aw[i]), x1 = unpack_bf16x2(bw[i]);
+    ow[i] = pack_bf16x2(x0.x * c[2 * i] - x1.x * s[2 * i], x0.y * c[2 * i + 1] - x1.y * s[2 * i + 1]);
+    pw[i] = pack_bf16x2(x0.x * s[2 * i] + x1.x * c[2 * i], x0.y * s[2 * i + 1] + x1.y * c[2 * i + 1]);
+  }
+  *lo = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  *hi = make_uint4(pw[0], pw[1], pw[2], pw[3]);
 }
 
 // cpu_f32::silu (x / (1 + e^-x), mod.rs:349-351) times up (hadamard, :365-374).
@@ -247,6 +337,11 @@ uint32_t logismos_launch_rms_norm_f32(const void* x, const void* w, void* y, int
   lg::LaunchScope launch_scope_;
   if (rows < 0 || n <= 0 || (n % 4) || n > 8 * 4 * 256) return lg::kInvalidValue;
   if (rows == 0) return 0;
+  if (rows >= 1024 && n <= 2048) {  // tall input: a warp per row
+    if (out_f32) launch_rms_warp_nv<true>(x, w, y, rows, n, eps, (cudaStream_t)stream);
+    else launch_rms_warp_nv<false>(x, w, y, rows, n, eps, (cudaStream_t)stream);
+    return lg::launch_status();
+  }
   int bs = 32;
   while (bs * 4 * 2 < n && bs < 256) bs <<= 1;  // aim for ~2 float4 per thread
   if (out_f32)
@@ -266,8 +361,15 @@ uint32_t logismos_launch_rope_halves_bf16(void* qk, const void* cos_f32, const v
       row_stride < n_rot_heads * head_dim || (row_stride % 2))
     return lg::kInvalidValue;
   if (n_tokens == 0) return 0;
-  const int64_t total = (int64_t)n_tokens * n_rot_heads * (head_dim / 4);
   const int bs = 256;
+  if (head_dim % 16 == 0 && row_stride % 8 == 0 && (((uintptr_t)qk | (uintptr_t)cos_f32 | (uintptr_t)sin_f32) % 16) == 0) {
+    const int64_t total8 = (int64_t)n_tokens * n_rot_heads * (head_dim / 16);
+    rope_halves_vec8_kernel<<<(unsigned)((total8 + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)qk, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions,
+        n_tokens, n_rot_heads, head_dim, row_stride, max_pos, (int*)status);
+    return lg::launch_status();
+  }
+  const int64_t total = (int64_t)n_tokens * n_rot_heads * (head_dim / 4);
   rope_halves_kernel<<<(unsigned)((total + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)qk, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions,
       n_tokens, n_rot_heads, head_dim, row_stride, max_pos, (int*)status);

@@ -21,7 +21,8 @@ def test_embed_lookup_is_a_bit_exact_gather_with_zero_rows_for_bad_ids():
     assert (to_np(out).view(np.uint32) == ref.view(np.uint32)).all()
 
 
-@pytest.mark.parametrize("rows,n", [(1, 4), (5, 1536), (33, 2048), (3, 8192), (7, 100)])
+@pytest.mark.parametrize("rows,n", [(1, 4), (5, 1536), (33, 2048), (3, 8192), (7, 100),
+                                    (1500, 1536), (1030, 2048), (1024, 512), (1100, 100), (1025, 1028)])  # tall: a warp per row
 def test_rms_norm_f32(rows, n):
     rng = np.random.default_rng(rows + n)
     x = rng.standard_normal((rows, n)).astype(np.float32) * 3; w = rng.standard_normal(n).astype(np.float32)
@@ -32,9 +33,10 @@ def test_rms_norm_f32(rows, n):
     assert max_rel(to_np(yb), ref) < 8e-3  # one bf16 rounding
 
 
-def test_rope_halves_on_packed_qkv_rows():
+@pytest.mark.parametrize("d", [128, 256, 40])  # 40: not a multiple of 16, the narrow-access kernel
+def test_rope_halves_on_packed_qkv_rows(d):
     rng = np.random.default_rng(2)
-    T, nh, nkv, d = 37, 6, 2, 128
+    T, nh, nkv = 37, 6, 2
     stride = (nh + 2 * nkv) * d
     qkv_t, qkv = bf16_cuda(rng.standard_normal((T, stride)))
     pos = rng.integers(0, 300, T).astype(np.int32)
