@@ -414,6 +414,206 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
   cp_async_wait<0>();
 }
 
+// ---- wide-slot streaming variant ------------------------------------------------------------------
+// For the tallest matrices at batch <= 16 whose rows lie a multiple of 1 KB apart: a warp carries two 16-row tiles side by side, and a ring slot
+// holds TWO k steps of them: 32 rows x 128 B of codes (whole 128-byte lines, four per copy instruction)
+// and 32 rows x 8 fp16 scales (16 B per row, one copy per lane). Against the narrow slot this halves
+// the copy rounds, waits and ring bookkeeping, requests whole lines from L2, and stops fetching every
+// 32-byte sector of scales four times. Lanes read their scales as fp16 straight from the slot.
+template <int KS> struct Wide {
+  static constexpr int kPitch = KS * 64 + 16;            // codes of KS k steps + 16: conflict-free ldmatrix
+  static constexpr int kSPitch = KS == 2 ? 16 : 48;      // KS * 4 fp16 scales per row (+16 at KS = 4: conflict-free)
+  static constexpr int kSlot = 32 * kPitch + 32 * kSPitch;
+};
+
+template <int NT, int STAGES, int KS>
+__global__ void __launch_bounds__(384)
+gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
+                          const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                          int N, int K) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int kWidePitch = Wide<KS>::kPitch, kSPitch = Wide<KS>::kSPitch, kWideSlot = Wide<KS>::kSlot;
+  constexpr uint32_t kScaleOff = 32 * kWidePitch;
+  constexpr int kCh = 4 * KS;          // 16-byte chunks per row per slot
+  constexpr int kRowsPer = 32 / kCh;  // rows one copy instruction covers
+  constexpr int kCopies = 32 / kRowsPer;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int groups = K / kGroup, iters2 = K / (KS * kIterK);  // slots per row tile
+  const int xrow_stride = groups * 64 + 64;
+  uint8_t* xs = smem;
+  float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
+  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kWideSlot;
+  const uint32_t ring = smem_u32(ring_gen);
+
+  // stage x (bf16, fragment order) and the per-group corrections, once
+  {
+    const int units_row = K / 8;
+    const int total = NT * 8 * units_row;
+    for (int u = tid; u < total; u += blockDim.x) {
+      const int n = u / units_row, kk = u % units_row;
+      const int G = kk >> 2, cc = kk & 3;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + kk * 8));
+      uint4 perm;
+      float s = stage_unit(raw, perm);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
+      if (cc == 0) negcorr[G * (NT * 8) + n] = -s;
+    }
+  }
+  __syncthreads();
+
+  const int row_tiles = (N + 31) / 32;
+  const int tile_stride = gridDim.x * nwarps;
+  const int first_tile = blockIdx.x * nwarps + warp;
+  const int my_tiles = first_tile < row_tiles ? (row_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+  const int total_slots = my_tiles * iters2;
+  const uint32_t ring_end = ring + STAGES * kWideSlot;
+
+  // ---- producer: lane (r4 = lane / 8, ch = lane % 8) copies chunk ch of rows r4, r4 + 4, ... of the
+  // tile, so one instruction moves four whole 128-byte lines; lane L also copies row L's scales.
+  const int r4 = lane / kCh, ch = lane % kCh;
+  const size_t row_bytes = (size_t)(K / 2);
+  int p_left = total_slots, p_it = 0, p_tile = first_tile;
+  uint32_t p_slot = ring;
+  const uint8_t* pw;   // codes of row (tile * 32 + r4), chunk ch, current slot
+  const __half* ps;    // scales of row (tile * 32 + lane), current slot
+  bool p_full;         // all 32 rows of the producer's tile exist
+  auto producer_tile = [&](int tile) {
+    const int rb = tile * 32;
+    p_full = rb + 32 <= N;
+    pw = codes + (size_t)min(rb + r4, N - 1) * row_bytes + ch * 16;
+    ps = scales + (size_t)min(rb + lane, N - 1) * groups;
+  };
+  producer_tile(p_tile);
+  const uint32_t dst_w = (uint32_t)(r4 * kWidePitch + ch * 16), dst_s = kScaleOff + (uint32_t)(lane * kSPitch);
+  auto issue = [&]() {
+    if (p_left > 0) {
+      if (p_full) {
+#pragma unroll
+        for (int i = 0; i < kCopies; ++i) cp_async16(p_slot + dst_w + i * kRowsPer * kWidePitch, pw + (size_t)(kRowsPer * i) * row_bytes);
+      } else {  // last tile of a ragged matrix: rows past the end re-read the last row (never stored)
+        const int rb = p_tile * 32;
+        const size_t koff = (size_t)p_it * (KS * 64) + ch * 16;
+#pragma unroll
+        for (int i = 0; i < kCopies; ++i)
+          cp_async16(p_slot + dst_w + i * kRowsPer * kWidePitch, codes + (size_t)min(rb + r4 + kRowsPer * i, N - 1) * row_bytes + koff);
+      }
+#pragma unroll
+      for (int i = 0; i < KS / 2; ++i) cp_async16(p_slot + dst_s + i * 16, ps + i * 8);
+      pw += KS * 64; ps += KS * 4;
+      p_slot += kWideSlot;
+      if (p_slot == ring_end) p_slot = ring;
+      --p_left;
+      if (++p_it == iters2) { p_it = 0; p_tile += tile_stride; producer_tile(p_tile); }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) issue();
+
+  // ---- consumer
+  const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: lanes 8j..8j+7 address the rows of matrix j (= group j)
+  const uint32_t ld_off = (uint32_t)(mr * kWidePitch + mat * 16);
+  const uint32_t sc_off = kScaleOff + (uint32_t)(g * kSPitch);
+  const uint32_t xs_a = smem_u32(xs) + (uint32_t)(g * xrow_stride + c * 16);
+  const uint32_t nc_a = smem_u32(negcorr) + (uint32_t)(2 * c * 4);
+  uint32_t c_slot = ring;
+  int c_tile = first_tile;
+  for (int t = 0; t < my_tiles; ++t, c_tile += tile_stride) {
+    float acc[2][NT][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][nt][i] = 0.0f;
+    uint32_t xa = xs_a, na = nc_a;
+    for (int it = 0; it < iters2; ++it) {
+      issue();
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+      uint32_t sraw[4][2 * KS];  // [h]: the 4 * KS fp16 scales (KS k steps x four groups) of row g + 8h
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+#pragma unroll
+        for (int i = 0; i < KS / 2; ++i)
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                       : "=r"(sraw[h][4 * i]), "=r"(sraw[h][4 * i + 1]), "=r"(sraw[h][4 * i + 2]), "=r"(sraw[h][4 * i + 3])
+                       : "r"(c_slot + sc_off + h * 8 * kSPitch + i * 16));
+#pragma unroll
+      for (int half = 0; half < KS; ++half) {
+        uint32_t w[4][4];  // [2r] rows g, [2r+1] rows g+8 of row tile r: word c of groups 0..3 of this k step
+#pragma unroll
+        for (int h = 0; h < 4; ++h) ldmatrix_x4(w[h], c_slot + ld_off + h * 8 * kWidePitch + half * 64);
+        float sc[4][4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[h][2 * half]));
+          const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[h][2 * half + 1]));
+          sc[h][0] = s01.x; sc[h][1] = s01.y; sc[h][2] = s23.x; sc[h][3] = s23.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t a_lo[2][4], a_hi[2][4];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint32_t w0 = w[2 * r][j], w1 = w[2 * r + 1][j];
+            const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+            a_lo[r][0] = nib_pair_bf16(w0); a_lo[r][1] = nib_pair_bf16(w1);
+            a_lo[r][2] = nib_pair_bf16(w0s); a_lo[r][3] = nib_pair_bf16(w1s);
+            a_hi[r][0] = nib_pair_f16_hi(w0); a_hi[r][1] = nib_pair_f16_hi(w1);
+            a_hi[r][2] = nib_pair_f16_hi(w0s); a_hi[r][3] = nib_pair_f16_hi(w1s);
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            uint32_t b_lo[2], b_hi[2];
+            float nc[2];
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                         : "=r"(b_lo[0]), "=r"(b_lo[1]), "=r"(b_hi[0]), "=r"(b_hi[1])
+                         : "r"(xa + (uint32_t)(nt * 8 * xrow_stride + j * 64)));
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];\n" : "=f"(nc[0]), "=f"(nc[1]) : "r"(na + (uint32_t)((j * NT * 8 + nt * 8) * 4)));
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              float d[4] = {nc[0], nc[1], nc[0], nc[1]};
+              mma_bf16_16816(d, a_lo[r], b_lo, d);
+              mma_f16_16816(d, a_hi[r], b_hi, d);
+              acc[r][nt][0] = fmaf(sc[2 * r][j], d[0], acc[r][nt][0]);
+              acc[r][nt][1] = fmaf(sc[2 * r][j], d[1], acc[r][nt][1]);
+              acc[r][nt][2] = fmaf(sc[2 * r + 1][j], d[2], acc[r][nt][2]);
+              acc[r][nt][3] = fmaf(sc[2 * r + 1][j], d[3], acc[r][nt][3]);
+            }
+          }
+        }
+        xa += 4 * 64;
+        na += 4 * NT * 8 * 4;
+      }
+      __syncwarp();  // every lane is done with the slot before a later issue() refills it
+      c_slot += kWideSlot;
+      if (c_slot == ring_end) c_slot = ring;
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int ra = c_tile * 32 + r * 16 + g, rb = ra + 8;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b0 = nt * 8 + 2 * c;
+        if (ra < N) {
+          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[r][nt][0]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[r][nt][1]);
+        }
+        if (rb < N) {
+          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[r][nt][2]);
+          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[r][nt][3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
 int gemv_sm_count() {
   static int n = 0;
   if (n) return n;
@@ -478,10 +678,25 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
   if (hi > max_warps) hi = max_warps;
   if (lo > hi) lo = hi;
   warps = best_warp_count(tiles, sms, lo, hi);
+  if constexpr (NT <= 2) {
+    // Wide slots where the narrow ones measured slower: rows a multiple of 1 KB apart (K = 2048:
+    // 38.3 against 41.2 us for 151936 rows; at K = 1536 the narrow slots win, 28.6 against 29.1 us).
+    const size_t wsmem = xbytes + (size_t)warps * 2 * Wide<2>::kSlot;
+    if (rt == 2 && K % 2048 == 0 && wsmem <= budget) {
+      auto kern = gemv_int4_g32_wide_kernel<NT, 2, 2>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
+      if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
+      kern<<<sms, warps * 32, wsmem, stream>>>((const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x,
+                                               (__nv_bfloat16*)y, batch, N, K);
+      *rc = lg::launch_status();
+      return true;
+    }
+  }
   const size_t smem = xbytes + (size_t)warps * 4 * slot_bytes(rt);
   if constexpr (NT <= 2) {
     if (rt == 2) {
-      *rc = launch_stream<NT, 4, 2>(codes, scales, x, y, batch, N, K, sms, warps, smem, stream);
+      // three ring slots measured best with two tiles per warp (28.6 us against 28.9 with four, 29.9 with two)
+      *rc = launch_stream<NT, 3, 2>(codes, scales, x, y, batch, N, K, sms, warps, xbytes + (size_t)warps * 3 * slot_bytes(2), stream);
       return true;
     }
   }

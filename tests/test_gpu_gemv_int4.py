@@ -94,11 +94,13 @@ def test_lm_head_shape_linearity_and_sampled_rows():
     assert max_rel(y12[:, rows], ref) <= TOL
 
 
-@pytest.mark.parametrize("n,k,b", [(75795, 256, 3), (75795, 384, 16), (75776, 128, 9), (80001, 256, 24)])
+@pytest.mark.parametrize("n,k,b", [(75795, 256, 3), (75795, 384, 16), (75776, 128, 9), (80001, 256, 24), (75795, 512, 16), (75809, 768, 1),
+                                   (75795, 2048, 2), (75809, 2048, 16)])  # rows 1 KB apart: the wide-slot kernel
 def test_tall_ragged_matrix_every_row(n, k, b):
-    """Matrices tall enough for the route where a warp carries two 16-row tiles side by side (at
-    least 32 row tiles per SM), with a row count that is not a multiple of 32 or 16, at batch sizes on
-    both sides of the 16-row limit of that route: every row against the oracle."""
+    """Matrices tall enough for the routes where a warp carries two 16-row tiles side by side (at
+    least 32 row tiles per SM; one or two k steps per ring slot), with a row count that is not a
+    multiple of 32 or 16, at batch sizes on both sides of the 16-row limit of those routes: every row
+    against the oracle."""
     _, packed, scales, x_t, x = make_case(n, k, b, seed=n + b)
     y = run(packed, scales, x_t)
     ref = O.int4_gemv(packed, scales.view(np.uint16), x)
