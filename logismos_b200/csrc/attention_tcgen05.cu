@@ -1,0 +1,393 @@
+// Ragged-batch attention at head_dim 128 on the 5th-generation tensor cores: the score / softmax / PV
+// stage of QwenAttention::forward (crates/transformers/src/attention.rs:226-296, GQA mapping
+// :366-382) without materialising scores, the same contract as the mma.sync kernel in attention.cu.
+//
+// CTA = (128 queries, one query head, one sequence), 6 warps:
+//   warp 0      TMA producer: the query tile once, then per block of 128 keys the K tile and the V^T
+//               tile (each two [128 x 64] bf16 tiles, 128-byte swizzle), one slot each: K(j+1) lands
+//               while the softmax of block j runs, V(j+1) while S(j+1) is computed
+//   warp 1      one thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 128, K = 16):
+//               S = Q K^T with both operands in shared memory into TMEM, and O += P V with P read from
+//               TMEM (lane = query, one 32-bit column = two keys) and V^T from shared memory
+//   warps 2-5   online softmax, thread = query row: tcgen05.ld of S, running maximum and sum in fp32,
+//               P rounded to bf16 and written over S with tcgen05.st, O rescaled in TMEM only when a
+//               row's maximum grew by more than 2^8; at the end O / l to global memory
+// One CTA uses 97 KB of shared memory and 256 TMEM columns, so two CTAs share an SM: while one runs its
+// softmax on the CUDA cores the other has the tensor cores.
+// V is consumed as V^T [kv_head * 128 + d, key] so that the PV product sees a K-major operand like
+// every other operand in this library; a small kernel transposes the V columns of qkv into a scratch
+// buffer first, every sequence starting at a multiple of 8 keys (the 16-byte rule of TMA) with its
+// padding zeroed.
+// Every mbarrier wait is bounded; on expiry the kernel raises the status word, lets copies in flight
+// land, frees its TMEM and returns. No cluster launch and no multicast.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "logismos_kernels.h"
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace lg;
+using namespace lg::tc;
+
+constexpr int kTileBytes = 128 * 128;        // one [128 rows x 64 bf16] tile
+constexpr int kQBytes = 2 * kTileBytes;      // d 0..63 and 64..127
+constexpr int kKBytes = 2 * kTileBytes;      // one K tile pair, or one V^T tile pair
+constexpr int kBars = 8;                     // q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done
+constexpr size_t kAttnSmem = 1024 + kQBytes + 2 * kKBytes + 8 * kBars + 16;  // ~97 KB: two CTAs per SM
+constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 256;                  // P replaces S in place
+
+LG_DEVINL float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+LG_DEVINL void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+LG_DEVINL void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+LG_DEVINL void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+LG_DEVINL int round8(int v) { return (v + 7) & ~7; }
+
+// V columns of qkv -> vt [n_kv * 128, tp] (row = kv head * 128 + d, column = padded key index), and the
+// padded start of every sequence -> pstart[n_seqs]. Grid (key blocks of 64, kv heads, sequences).
+__global__ void __launch_bounds__(256)
+transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu, __nv_bfloat16* __restrict__ vt,
+                   int* __restrict__ pstart, int n_seqs, int row_stride, int v_off, int tp) {
+  __shared__ __align__(16) __nv_bfloat16 tile[64][136];
+  __shared__ int p0_s;
+  const int s = blockIdx.z, kvh = blockIdx.y, tb = blockIdx.x;
+  const int tid = threadIdx.x;
+  if (tid < 32) {
+    int part = 0;
+    for (int i = tid; i < s; i += 32) part += round8(cu[i + 1] - cu[i]);
+    part += __shfl_xor_sync(0xffffffffu, part, 16);
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    if (tid == 0) p0_s = part;
+  }
+  __syncthreads();
+  const int p0 = p0_s;
+  const int t0 = cu[s], len = cu[s + 1] - t0, plen = round8(len);
+  if (tb == 0 && kvh == 0 && tid == 0) pstart[s] = p0;
+  if (tb == 0 && s == n_seqs - 1) {  // columns after the last sequence are read as padding by the last key block
+    const int d = tid >> 1;
+    for (int col = p0 + plen + (tid & 1) * 8; col + 8 <= tp; col += 16)
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * 128 + d) * tp + col) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (tb * 64 >= plen) return;
+  for (int u = tid; u < 64 * 16; u += 256) {
+    const int r = u >> 4, ch = u & 15, t = tb * 64 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t < len) v = __ldg(reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + t) * row_stride + v_off + kvh * 128 + ch * 8));
+    *reinterpret_cast<uint4*>(&tile[r][ch * 8]) = v;
+  }
+  __syncthreads();
+  const int d = tid >> 1, half = tid & 1;
+#pragma unroll
+  for (int g8 = 0; g8 < 4; ++g8) {
+    const int tl = half * 32 + g8 * 8;
+    if (tb * 64 + tl < plen) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t lo = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i][d]);
+        const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i + 1][d]);
+        w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * 128 + d) * tp + p0 + tb * 64 + tl) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+template <bool CAUSAL>
+__global__ void __launch_bounds__(192, 2)
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_vt,
+                    const int* __restrict__ cu, const int* __restrict__ pstart, __nv_bfloat16* __restrict__ out,
+                    int n_heads, int n_kv, int k_off, float sl2, int* __restrict__ status) {
+  const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * 128;
+  const int t0 = cu[s], len = cu[s + 1] - t0;
+  if (q0 >= len) return;  // before any barrier or TMEM allocation
+  const int kvh = h / (n_heads / n_kv);
+  const int kv_len = CAUSAL ? min(len, q0 + 128) : len;
+  const int nb = (kv_len + 127) >> 7;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_smem = smem_base, k_smem = smem_base + kQBytes, v_smem = k_smem + kKBytes;
+  const uint32_t bars = v_smem + kKBytes;
+  uint8_t* bars_gen = smem_gen + kQBytes + 2 * kKBytes;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  const uint32_t q_full = bar(0), k_full = bar(1), k_empty = bar(2), v_full = bar(3), v_empty = bar(4);
+  const uint32_t s_full = bar(5), p_full = bar(6), o_done = bar(7);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * kBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * kBars + 8);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kBars; ++i) mbar_init(bar(i), i == 6 ? 4u : 1u);  // p_full: one arrival per softmax warp
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: K(j) as soon as S(j-1) has read its slot, V(j) once PV(j-1) has ----------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, (uint32_t)kQBytes);
+      tma_load_2d(q_smem, &map_qk, q_full, h * 128, t0 + q0);
+      tma_load_2d(q_smem + kTileBytes, &map_qk, q_full, h * 128 + 64, t0 + q0);
+      const int pv = pstart[s];
+      for (int j = 0; j < nb; ++j) {
+        const uint32_t phase = (uint32_t)j & 1u;
+        if (!mbar_wait(k_empty, phase ^ 1u, abort_flag)) break;
+        mbar_expect_tx(k_full, (uint32_t)kKBytes);
+        tma_load_2d(k_smem, &map_qk, k_full, k_off + kvh * 128, t0 + j * 128);
+        tma_load_2d(k_smem + kTileBytes, &map_qk, k_full, k_off + kvh * 128 + 64, t0 + j * 128);
+        if (!mbar_wait(v_empty, phase ^ 1u, abort_flag)) break;
+        mbar_expect_tx(v_full, (uint32_t)kKBytes);
+        tma_load_2d(v_smem, &map_vt, v_full, pv + j * 128, kvh * 128);
+        tma_load_2d(v_smem + kTileBytes, &map_vt, v_full, pv + j * 128 + 64, kvh * 128);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    // The tensor pipe runs the MMAs of one CTA in issue order, so S(j) (issued after PV(j-1)) never
+    // overwrites the P columns PV(j-1) still reads, and "S(j) complete" implies "PV(j-1) complete".
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<128>();
+      bool ok = mbar_wait(q_full, 0u, abort_flag);
+      for (int j = 0; j < nb && ok; ++j) {
+        const uint32_t phase = (uint32_t)j & 1u;
+        if (!mbar_wait(k_full, phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t da = make_smem_desc(q_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
+          const uint64_t db = make_smem_desc(k_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
+          tc_mma_bf16(tmem_base + kColS, da, db, idesc, kk ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        tc_commit(k_empty);
+        if (!mbar_wait(p_full, phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(v_full, phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t db = make_smem_desc(v_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
+          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + 8u * kk, db, idesc, (j | kk) ? 1u : 0u);
+        }
+        tc_commit(v_empty);
+        if (j == nb - 1) tc_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------- softmax and epilogue: thread = query row ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int row = q * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_off + kColS, t_o = tmem_base + lane_off + kColO;
+    float m = -1e30f, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      if (!mbar_wait(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      // keys this row may see in this block: [0, lim)
+      int lim = kv_len - j * 128;
+      if (CAUSAL) lim = min(lim, q0 + row + 1 - j * 128);
+      const bool full = lim >= 128;
+      float mx = -1e30f;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t ra[32], rb[32];
+        tc_ld32(t_s + c2 * 64, ra);
+        tc_ld32(t_s + c2 * 64 + 32, rb);
+        tc_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(ra[i]), __uint_as_float(rb[i])));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c2 * 64 + i < lim) mx = fmaxf(mx, __uint_as_float(ra[i]));
+            if (c2 * 64 + 32 + i < lim) mx = fmaxf(mx, __uint_as_float(rb[i]));
+          }
+        }
+      }
+      // The maximum only moves when it would grow by more than 2^8: P then stays below 256 (exact
+      // enough in bf16, summed in fp32) and O is rescaled far less often.
+      const float cand = mx * sl2;
+      float alpha = 1.0f;
+      if (cand > m + 8.0f) { alpha = fast_exp2(m - cand); m = cand; }
+      float sum = 0.0f;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t ra[32], rb[32], v[32];
+        tc_ld32(t_s + c2 * 64, ra);
+        tc_ld32(t_s + c2 * 64 + 32, rb);
+        tc_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float a0 = fast_exp2(fmaf(__uint_as_float(ra[i]), sl2, -m)), a1 = fast_exp2(fmaf(__uint_as_float(ra[i + 1]), sl2, -m));
+            const float b0 = fast_exp2(fmaf(__uint_as_float(rb[i]), sl2, -m)), b1 = fast_exp2(fmaf(__uint_as_float(rb[i + 1]), sl2, -m));
+            sum += (a0 + a1) + (b0 + b1);
+            v[i >> 1] = pack_bf16x2(a0, a1);
+            v[16 + (i >> 1)] = pack_bf16x2(b0, b1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int ka = c2 * 64 + i, kb = ka + 32;
+            const float a0 = ka < lim ? fast_exp2(fmaf(__uint_as_float(ra[i]), sl2, -m)) : 0.0f;
+            const float a1 = ka + 1 < lim ? fast_exp2(fmaf(__uint_as_float(ra[i + 1]), sl2, -m)) : 0.0f;
+            const float b0 = kb < lim ? fast_exp2(fmaf(__uint_as_float(rb[i]), sl2, -m)) : 0.0f;
+            const float b1 = kb + 1 < lim ? fast_exp2(fmaf(__uint_as_float(rb[i + 1]), sl2, -m)) : 0.0f;
+            sum += (a0 + a1) + (b0 + b1);
+            v[i >> 1] = pack_bf16x2(a0, a1);
+            v[16 + (i >> 1)] = pack_bf16x2(b0, b1);
+          }
+        }
+        // P takes the place of S: columns [32 c2, 32 c2 + 32) hold keys [64 c2, 64 c2 + 64); the S values
+        // they replace (keys [32 c2, 32 c2 + 32)) were read in this or the previous half
+        tc_st32(t_s + c2 * 32, v);
+      }
+      l = l * alpha + sum;
+      // S(j) complete means PV(j-1) is complete: O may be rescaled in place
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tc_ld32(t_o + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tc_st32(t_o + c * 32, r);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(o_done, 0u, abort_flag)) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool store = q0 + row < len;
+      __nv_bfloat16* dst = out + (size_t)(t0 + q0 + row) * (size_t)(n_heads * 128) + h * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tc_ld32(t_o + c * 32, r);
+        tc_wait_ld();
+        if (store) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  __syncwarp();
+  if (*abort_flag) {
+    // a wait expired somewhere: give copies that may still be in flight time to land before the
+    // shared memory and TMEM are released, and report
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+namespace {
+inline size_t pstart_bytes(int n_seqs) { return ((size_t)n_seqs * 4 + 255) & ~(size_t)255; }
+inline int padded_tokens(int n_tokens, int n_seqs) { return (n_tokens + 8 * n_seqs + 7) & ~7; }
+}  // namespace
+
+extern "C" {
+
+size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads) {
+  if (n_tokens < 0 || n_seqs < 0 || n_kv_heads <= 0) return 0;
+  return pstart_bytes(n_seqs) + (size_t)n_kv_heads * 128 * (size_t)padded_tokens(n_tokens, n_seqs) * 2;
+}
+
+uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* cu_seqlens, void* out, void* scratch,
+                                                  int32_t n_tokens, int32_t n_seqs, int32_t max_seqlen, int32_t n_heads,
+                                                  int32_t n_kv_heads, int32_t row_stride, int32_t k_off, int32_t v_off,
+                                                  int32_t causal, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (n_tokens < 0 || n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || (n_heads % n_kv_heads) ||
+      (row_stride % 8) || (k_off % 8) || (v_off % 8) || k_off + n_kv_heads * 128 > row_stride || v_off + n_kv_heads * 128 > row_stride ||
+      n_heads * 128 > row_stride || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || !scratch || ((uintptr_t)scratch & 255))
+    return lg::kInvalidValue;
+  if (n_seqs == 0 || max_seqlen == 0 || n_tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  int* pstart = (int*)scratch;
+  __nv_bfloat16* vt = (__nv_bfloat16*)((uint8_t*)scratch + pstart_bytes(n_seqs));
+  const int tp = padded_tokens(n_tokens, n_seqs);
+  CUtensorMap map_qk, map_vt;
+  if (!make_map(&map_qk, qkv, (uint64_t)n_tokens, (uint64_t)row_stride, (uint64_t)row_stride, 128) ||
+      !make_map(&map_vt, vt, (uint64_t)n_kv_heads * 128, (uint64_t)tp, (uint64_t)tp, 128))
+    return lg::kInvalidValue;
+  const int max8 = (max_seqlen + 7) & ~7;
+  transpose_v_kernel<<<dim3((max8 + 63) / 64, n_kv_heads, n_seqs), 256, 0, s>>>(
+      (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
+  uint32_t rc = lg::launch_status();
+  if (rc) return rc;
+  const float sl2 = 1.4426950408889634f / sqrtf(128.0f);
+  dim3 grid((max_seqlen + 127) / 128, n_heads, n_seqs);
+  auto launch = [&](auto kern) -> uint32_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+    if (e != cudaSuccess) return (uint32_t)e;
+    kern<<<grid, 192, kAttnSmem, s>>>(map_qk, map_vt, (const int*)cu_seqlens, pstart, (__nv_bfloat16*)out, n_heads,
+                                      n_kv_heads, k_off, sl2, (int*)status);
+    return lg::launch_status();
+  };
+  return causal ? launch(attn_tcgen05_kernel<true>) : launch(attn_tcgen05_kernel<false>);
+}
+
+}  // extern "C"

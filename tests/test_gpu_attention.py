@@ -49,3 +49,70 @@ def test_rejects_unsupported_head_dim():
     qkv = torch.zeros((4, 3 * 64), dtype=torch.bfloat16, device=DEV)
     with pytest.raises(Exception):
         ops.varlen_attention(qkv, torch.tensor([0, 4], dtype=torch.int32, device=DEV), 1, 1, 64)
+
+
+# ---- the tcgen05 kernel (head_dim 128): same oracle, same cases ----
+
+def run_case_tc(lens, nh, nkv, causal, seed):
+    rng = np.random.default_rng(seed)
+    d = 128
+    T = int(sum(lens))
+    stride = (nh + 2 * nkv) * d
+    qkv_t, qkv = bf16_cuda(rng.standard_normal((T, stride)))
+    cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = to_np(ops.varlen_attention_tc(qkv_t, torch.from_numpy(cu).to(DEV), nh, nkv, causal=causal, status=status))
+    assert int(status.item()) == 0
+    for i, L in enumerate(lens):
+        if L == 0:
+            continue
+        seg = qkv[cu[i]:cu[i + 1]]
+        q = np.ascontiguousarray(seg[:, : nh * d]); k = np.ascontiguousarray(seg[:, nh * d:(nh + nkv) * d])
+        v = np.ascontiguousarray(seg[:, (nh + nkv) * d:])
+        ref = O.sdpa(q, k, v, nh, nkv, d, causal=causal)
+        assert max_rel(out[cu[i]:cu[i + 1]], ref) <= TOL, (i, L)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_stella_head_layout_ragged_lengths(causal):  # lengths around the 128-key block and 8-key padding edges
+    run_case_tc([32, 512, 1, 63, 64, 65, 200, 0, 129, 127, 128, 7, 8, 9, 385], 12, 2, causal, 1)
+
+
+@pytest.mark.parametrize("nh,nkv", [(16, 2), (4, 4), (8, 1)])
+def test_tc_other_gqa_layouts(nh, nkv):
+    run_case_tc([100, 17, 300], nh, nkv, False, nh)
+    run_case_tc([70, 260], nh, nkv, True, nh + 1)
+
+
+def test_tc_long_sequence_and_large_scores():
+    """1100 keys (nine key blocks: both S buffers and both ring stages wrap several times) and inputs
+    scaled so that the running maximum moves between blocks (the O rescale path)."""
+    run_case_tc([1100, 5], 4, 2, False, 31)
+    run_case_tc([700], 2, 1, True, 32)
+    rng = np.random.default_rng(33)
+    T, nh, nkv, d = 400, 2, 1, 128
+    x = rng.standard_normal((T, (nh + 2 * nkv) * d)) * np.linspace(0.2, 3.0, T)[:, None]  # later keys score higher
+    qkv_t, qkv = bf16_cuda(x)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    out = to_np(ops.varlen_attention_tc(qkv_t, cu, nh, nkv))
+    ref = O.sdpa(np.ascontiguousarray(qkv[:, : nh * d]), np.ascontiguousarray(qkv[:, nh * d:(nh + nkv) * d]),
+                 np.ascontiguousarray(qkv[:, (nh + nkv) * d:]), nh, nkv, d, causal=False)
+    assert max_rel(out, ref) <= TOL
+
+
+def test_tc_agrees_with_the_mma_sync_kernel_on_a_full_batch():
+    rng = np.random.default_rng(5)
+    lens = rng.integers(32, 513, 8)
+    T = int(lens.sum())
+    qkv_t, _ = bf16_cuda(rng.standard_normal((T, 16 * 128)))
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(DEV)
+    a = to_np(ops.varlen_attention_tc(qkv_t, cu, 12, 2)).astype(np.float32)
+    b = to_np(ops.varlen_attention(qkv_t, cu, 12, 2, 128)).astype(np.float32)
+    assert max_rel(a, b) <= TOL
+
+
+def test_tc_rejects_bad_arguments():
+    qkv = torch.zeros((4, 3 * 128), dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
+    with pytest.raises(Exception):
+        ops.varlen_attention_tc(qkv, cu, 3, 2)  # heads % kv heads
