@@ -47,7 +47,7 @@ struct Decoder {
   std::vector<DLayer> layers;
   // workspace
   Buf x, h, qkv, attn, qdec, gu, act, wscratch, accws, last, last_bf16, logits, tokens, status;
-  Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch;
+  Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws;
   // pinned staging (one block)
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
@@ -93,10 +93,18 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
       m->launches += 2;
     }
     if (m->n_pre > 0) {
-      LG_TRY(logismos_launch_varlen_attention_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
-                                                   (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->n_pre, m->max_pre_len,
-                                                   c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, s), "varlen_attention");
-      m->launches += 1;
+      if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
+        LG_TRY(logismos_launch_varlen_attention_tc_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
+                                                        (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->attn_ws.p, T - m->n_dec,
+                                                        m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, QKV, H, H + KV, 1, st, s),
+               "varlen_attention");
+        m->launches += 2;
+      } else {
+        LG_TRY(logismos_launch_varlen_attention_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
+                                                     (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->n_pre, m->max_pre_len,
+                                                     c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, s), "varlen_attention");
+        m->launches += 1;
+      }
     }
     if (uint32_t rc = qlinear(m, m->attn.p, L.wo, nullptr, m->x.p, T, H, H, LG_EPI_RESID_F32, s)) return rc;
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
@@ -190,7 +198,8 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
        m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->slots.alloc(T * 8) &&
        m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&
        m->dec_chunks.alloc((S + 1) * 4) &&
-       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim));
+       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim)) &&
+       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads));
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
   ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4;
@@ -211,7 +220,7 @@ void lg_decoder_destroy(void* model) {
   cudaSetDevice(m->device);
   Buf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->qkv,
                  &m->attn, &m->qdec, &m->gu, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens, &m->status,
-                 &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch};
+                 &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch, &m->attn_ws};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.bqkv, &L.kpool, &L.vpool, &L.wqkv.codes, &L.wqkv.scales, &L.wo.codes, &L.wo.scales,

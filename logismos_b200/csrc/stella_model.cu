@@ -66,7 +66,7 @@ struct Stella {
   std::vector<Layer> layers;
   DevBuf head_w[8], head_b[8];
   // workspace
-  DevBuf x, h, qkv, attn, gu, act, hidden_out, pooled, ids, pos, cu, out, status;
+  DevBuf x, h, qkv, attn, attn_ws, gu, act, hidden_out, pooled, ids, pos, cu, out, status;
   // pinned staging
   uint32_t* h_ids = nullptr;
   int32_t* h_pos = nullptr;
@@ -118,8 +118,13 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
     LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wqkv.p, L.bqkv.p, m->qkv.p, T, QKV, H, H, QKV, LG_EPI_BF16, st, s), "qkv_proj");
     LG_TRY(logismos_launch_rope_halves_bf16(m->qkv.p, m->cos.p, m->sin.p, pos, T, c.n_heads + c.n_kv_heads, D, QKV,
                                             c.max_pos, st, s), "rope");
-    LG_TRY(logismos_launch_varlen_attention_bf16(m->qkv.p, cu, m->attn.p, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads,
-                                                 D, QKV, H, H + c.n_kv_heads * D, causal, s), "attention");
+    if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
+      LG_TRY(logismos_launch_varlen_attention_tc_bf16(m->qkv.p, cu, m->attn.p, m->attn_ws.p, T, n_seqs, max_seqlen, c.n_heads,
+                                                      c.n_kv_heads, QKV, H, H + c.n_kv_heads * D, causal, st, s), "attention");
+    } else {
+      LG_TRY(logismos_launch_varlen_attention_bf16(m->qkv.p, cu, m->attn.p, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads,
+                                                   D, QKV, H, H + c.n_kv_heads * D, causal, s), "attention");
+    }
     LG_TRY(logismos_launch_linear_t_bf16(m->attn.p, L.wo.p, nullptr, m->x.p, T, H, H, H, H, LG_EPI_RESID_F32, st, s), "o_proj");
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
     if (c.fuse_swiglu) {
@@ -217,6 +222,7 @@ uint32_t lg_stella_create(int32_t device, const lg_stella_config_t* cfg, const l
   int max_dim = 0;
   for (int i = 0; i < c.n_dims; ++i) max_dim = c.dims[i] > max_dim ? c.dims[i] : max_dim;
   ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
+       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int)T, (int)S, c.n_kv_heads)) &&
        m->gu.alloc(c.fuse_swiglu ? 16 : T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->hidden_out.alloc(T * H * 4) && m->pooled.alloc(S * H * 4) &&
        m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->cu.alloc((S + 1) * 4) && m->out.alloc(S * max_dim * 4) &&
        m->status.alloc(4);
@@ -238,7 +244,7 @@ void lg_stella_destroy(void* model) {
   if (!model) return;
   Stella* m = static_cast<Stella*>(model);
   cudaSetDevice(m->device);
-  DevBuf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->x, &m->h, &m->qkv, &m->attn, &m->gu,
+  DevBuf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->x, &m->h, &m->qkv, &m->attn, &m->attn_ws, &m->gu,
                     &m->act, &m->hidden_out, &m->pooled, &m->ids, &m->pos, &m->cu, &m->out, &m->status};
   for (DevBuf* b : bufs) b->release();
   for (auto& L : m->layers) {
@@ -262,7 +268,7 @@ int32_t lg_stella_supported_dims(const void* model, int32_t* out, int32_t cap) {
 int32_t lg_stella_max_tokens(const void* model) { return static_cast<const Stella*>(model)->cfg.max_tokens; }
 int32_t lg_stella_launches_per_forward(const void* model) {
   const Stella* m = static_cast<const Stella*>(model);
-  return 1 + m->cfg.n_layers * (m->cfg.fuse_swiglu ? 8 : 9) + 4;
+  return 1 + m->cfg.n_layers * ((m->cfg.fuse_swiglu ? 8 : 9) + (m->head_dim == 128 ? 1 : 0)) + 4;
 }
 
 uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* dev_cu, const void* dev_pos,
