@@ -115,20 +115,21 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv_bf16, const void*
                                                int32_t head_dim, int32_t row_stride, int32_t k_off,
                                                int32_t v_off, int32_t causal, void* stream);
 
-/* The same stage (attention.rs:226-296, head_dim 128 only) on the tcgen05 tensor cores: S = Q K^T and
+/* The same stage (attention.rs:226-296, head_dim 128 or 256) on the tcgen05 tensor cores: S = Q K^T and
  * O += P V as tcgen05.mma with the accumulators and P in tensor memory, operands moved by TMA. Same
  * layout contract as logismos_launch_varlen_attention_bf16; n_tokens = cu_seqlens[n_seqs]. scratch:
- * logismos_varlen_attention_tc_scratch_bytes(n_tokens, n_seqs, n_kv_heads) bytes, 256-byte aligned
+ * logismos_varlen_attention_tc_scratch_bytes(n_tokens, n_seqs, n_kv_heads, head_dim) bytes, 256-byte aligned
  * (receives V transposed per kv head with every sequence padded to a multiple of 8 keys). qkv and out
  * 16-byte aligned. Two launches. status (int32, may be NULL) is set to 2 if a bounded wait inside
  * the kernel expired. */
-size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads);
+size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads,
+                                                  int32_t head_dim);
 uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv_bf16, const void* cu_seqlens_i32,
                                                   void* out_bf16, void* scratch, int32_t n_tokens,
                                                   int32_t n_seqs, int32_t max_seqlen, int32_t n_heads,
-                                                  int32_t n_kv_heads, int32_t row_stride, int32_t k_off,
-                                                  int32_t v_off, int32_t causal, void* status,
-                                                  void* stream);
+                                                  int32_t n_kv_heads, int32_t head_dim, int32_t row_stride,
+                                                  int32_t k_off, int32_t v_off, int32_t causal,
+                                                  void* status, void* stream);
 
 /* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
  * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), mask all ones.

@@ -68,7 +68,7 @@ def _declare(l):
         "logismos_launch_rope_halves_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_swiglu_bf16": [vp, vp, i32, i32, vp],
         "logismos_launch_varlen_attention_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
-        "logismos_launch_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
@@ -119,7 +119,7 @@ def _declare(l):
     l.lg_last_error.restype = C.c_char_p
     l.logismos_paged_decode_scratch_bytes.argtypes = [i32, i32, i32]
     l.logismos_paged_decode_scratch_bytes.restype = sz
-    l.logismos_varlen_attention_tc_scratch_bytes.argtypes = [i32, i32, i32]
+    l.logismos_varlen_attention_tc_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.logismos_varlen_attention_tc_scratch_bytes.restype = sz
     l.logismos_build_packing.argtypes = [vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp]
     l.logismos_build_packing.restype = i64

@@ -32,11 +32,18 @@ using namespace lg;
 using namespace lg::tc;
 
 constexpr int kTileBytes = 128 * 128;        // one [128 rows x 64 bf16] tile
-constexpr int kQBytes = 2 * kTileBytes;      // d 0..63 and 64..127
-constexpr int kKBytes = 2 * kTileBytes;      // one K tile pair, or one V^T tile pair
 constexpr int kBars = 8;                     // q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_done
-constexpr size_t kAttnSmem = 1024 + kQBytes + 2 * kKBytes + 8 * kBars + 16;  // ~97 KB: two CTAs per SM
-constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 256;                  // P replaces S in place
+constexpr uint32_t kColS = 0, kColO = 128;   // P replaces S in place; O takes HD columns after it
+
+// HD = head_dim, 128 or 256. Q and K: HD / 64 tiles of [128 rows x 64]; V^T: two tiles of [HD rows x 64 keys].
+template <int HD> struct Attn {
+  static constexpr int kQBytes = (HD / 64) * kTileBytes;
+  static constexpr int kKBytes = (HD / 64) * kTileBytes;
+  static constexpr int kVTile = HD * 128;
+  static constexpr int kVBytes = 2 * kVTile;
+  static constexpr size_t kSmem = 1024 + kQBytes + kKBytes + kVBytes + 8 * kBars + 16;  // 97 KB (two CTAs per SM) or 193 KB
+  static constexpr uint32_t kTmemCols = HD == 128 ? 256 : 512;
+};
 
 LG_DEVINL float fast_exp2(float x) {
   float y;
@@ -70,10 +77,12 @@ LG_DEVINL int round8(int v) { return (v + 7) & ~7; }
 
 // V columns of qkv -> vt [n_kv * 128, tp] (row = kv head * 128 + d, column = padded key index), and the
 // padded start of every sequence -> pstart[n_seqs]. Grid (key blocks of 64, kv heads, sequences).
+template <int HD>
 __global__ void __launch_bounds__(256)
 transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu, __nv_bfloat16* __restrict__ vt,
                    int* __restrict__ pstart, int n_seqs, int row_stride, int v_off, int tp) {
-  __shared__ __align__(16) __nv_bfloat16 tile[64][136];
+  __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
+  constexpr int kParts = 256 / HD, kChunks = HD / 8;  // threads per d row; 16-byte chunks per token row
   __shared__ int p0_s;
   const int s = blockIdx.z, kvh = blockIdx.y, tb = blockIdx.x;
   const int tid = threadIdx.x;
@@ -92,22 +101,22 @@ transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict_
   const int t0 = cu[s], len = cu[s + 1] - t0, plen = round8(len);
   if (tb == 0 && kvh == 0 && tid == 0) pstart[s] = p0;
   if (tb == 0 && s == n_seqs - 1) {  // columns after the last sequence are read as padding by the last key block
-    const int d = tid >> 1;
-    for (int col = p0 + plen + (tid & 1) * 8; col + 8 <= tp; col += 16)
-      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * 128 + d) * tp + col) = make_uint4(0u, 0u, 0u, 0u);
+    const int d = tid / kParts;
+    for (int col = p0 + plen + (tid % kParts) * 8; col + 8 <= tp; col += 8 * kParts)
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + col) = make_uint4(0u, 0u, 0u, 0u);
   }
   if (tb * 64 >= plen) return;
-  for (int u = tid; u < 64 * 16; u += 256) {
-    const int r = u >> 4, ch = u & 15, t = tb * 64 + r;
+  for (int u = tid; u < 64 * kChunks; u += 256) {
+    const int r = u / kChunks, ch = u % kChunks, t = tb * 64 + r;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (t < len) v = __ldg(reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + t) * row_stride + v_off + kvh * 128 + ch * 8));
+    if (t < len) v = __ldg(reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + t) * row_stride + v_off + kvh * HD + ch * 8));
     *reinterpret_cast<uint4*>(&tile[r][ch * 8]) = v;
   }
   __syncthreads();
-  const int d = tid >> 1, half = tid & 1;
+  const int d = tid / kParts, half = tid % kParts;
 #pragma unroll
-  for (int g8 = 0; g8 < 4; ++g8) {
-    const int tl = half * 32 + g8 * 8;
+  for (int g8 = 0; g8 < 8 / kParts; ++g8) {
+    const int tl = half * (64 / kParts) + g8 * 8;
     if (tb * 64 + tl < plen) {
       uint32_t w[4];
 #pragma unroll
@@ -116,17 +125,21 @@ transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict_
         const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i + 1][d]);
         w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
       }
-      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * 128 + d) * tp + p0 + tb * 64 + tl) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + p0 + tb * 64 + tl) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
 
-template <bool CAUSAL>
-__global__ void __launch_bounds__(192, 2)
+template <bool CAUSAL, int HD>
+__global__ void __launch_bounds__(192, HD == 128 ? 2 : 1)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_vt,
                     const int* __restrict__ cu, const int* __restrict__ pstart, __nv_bfloat16* __restrict__ out,
                     int n_heads, int n_kv, int k_off, float sl2, int* __restrict__ status) {
-  const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * 128;
+  using C = Attn<HD>;
+  constexpr int kQBytes = C::kQBytes, kKBytes = C::kKBytes, kVBytes = C::kVBytes, kVTile = C::kVTile;
+  constexpr uint32_t kTmemCols = C::kTmemCols;
+  // causal: the query tiles with the most keys start first
+  const int s = blockIdx.z, h = blockIdx.y, q0 = (CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * 128;
   const int t0 = cu[s], len = cu[s + 1] - t0;
   if (q0 >= len) return;  // before any barrier or TMEM allocation
   const int kvh = h / (n_heads / n_kv);
@@ -138,8 +151,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_smem = smem_base, k_smem = smem_base + kQBytes, v_smem = k_smem + kKBytes;
-  const uint32_t bars = v_smem + kKBytes;
-  uint8_t* bars_gen = smem_gen + kQBytes + 2 * kKBytes;
+  const uint32_t bars = v_smem + kVBytes;
+  uint8_t* bars_gen = smem_gen + kQBytes + kKBytes + kVBytes;
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   const uint32_t q_full = bar(0), k_full = bar(1), k_empty = bar(2), v_full = bar(3), v_empty = bar(4);
   const uint32_t s_full = bar(5), p_full = bar(6), o_done = bar(7);
@@ -165,19 +178,19 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
     // ---------------- TMA producer: K(j) as soon as S(j-1) has read its slot, V(j) once PV(j-1) has ----------------
     if (lane == 0) {
       mbar_expect_tx(q_full, (uint32_t)kQBytes);
-      tma_load_2d(q_smem, &map_qk, q_full, h * 128, t0 + q0);
-      tma_load_2d(q_smem + kTileBytes, &map_qk, q_full, h * 128 + 64, t0 + q0);
+#pragma unroll
+      for (int i = 0; i < HD / 64; ++i) tma_load_2d(q_smem + i * kTileBytes, &map_qk, q_full, h * HD + i * 64, t0 + q0);
       const int pv = pstart[s];
       for (int j = 0; j < nb; ++j) {
         const uint32_t phase = (uint32_t)j & 1u;
         if (!mbar_wait(k_empty, phase ^ 1u, abort_flag)) break;
         mbar_expect_tx(k_full, (uint32_t)kKBytes);
-        tma_load_2d(k_smem, &map_qk, k_full, k_off + kvh * 128, t0 + j * 128);
-        tma_load_2d(k_smem + kTileBytes, &map_qk, k_full, k_off + kvh * 128 + 64, t0 + j * 128);
+#pragma unroll
+        for (int i = 0; i < HD / 64; ++i) tma_load_2d(k_smem + i * kTileBytes, &map_qk, k_full, k_off + kvh * HD + i * 64, t0 + j * 128);
         if (!mbar_wait(v_empty, phase ^ 1u, abort_flag)) break;
-        mbar_expect_tx(v_full, (uint32_t)kKBytes);
-        tma_load_2d(v_smem, &map_vt, v_full, pv + j * 128, kvh * 128);
-        tma_load_2d(v_smem + kTileBytes, &map_vt, v_full, pv + j * 128 + 64, kvh * 128);
+        mbar_expect_tx(v_full, (uint32_t)kVBytes);
+        tma_load_2d(v_smem, &map_vt, v_full, pv + j * 128, kvh * HD);
+        tma_load_2d(v_smem + kVTile, &map_vt, v_full, pv + j * 128 + 64, kvh * HD);
       }
     }
   } else if (warp == 1) {
@@ -185,17 +198,17 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
     // The tensor pipe runs the MMAs of one CTA in issue order, so S(j) (issued after PV(j-1)) never
     // overwrites the P columns PV(j-1) still reads, and "S(j) complete" implies "PV(j-1) complete".
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<128>();
+      constexpr uint32_t idesc_s = make_idesc<128>(), idesc_o = make_idesc<HD>();
       bool ok = mbar_wait(q_full, 0u, abort_flag);
       for (int j = 0; j < nb && ok; ++j) {
         const uint32_t phase = (uint32_t)j & 1u;
         if (!mbar_wait(k_full, phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t da = make_smem_desc(q_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
           const uint64_t db = make_smem_desc(k_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
-          tc_mma_bf16(tmem_base + kColS, da, db, idesc, kk ? 1u : 0u);
+          tc_mma_bf16(tmem_base + kColS, da, db, idesc_s, kk ? 1u : 0u);
         }
         tc_commit(s_full);
         tc_commit(k_empty);
@@ -204,8 +217,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t db = make_smem_desc(v_smem + (kk >> 2) * kTileBytes) + (uint64_t)(2 * (kk & 3));
-          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + 8u * kk, db, idesc, (j | kk) ? 1u : 0u);
+          const uint64_t db = make_smem_desc(v_smem + (kk >> 2) * kVTile) + (uint64_t)(2 * (kk & 3));
+          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + 8u * kk, db, idesc_o, (j | kk) ? 1u : 0u);
         }
         tc_commit(v_empty);
         if (j == nb - 1) tc_commit(o_done);
@@ -286,7 +299,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
       // S(j) complete means PV(j-1) is complete: O may be rescaled in place
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t r[32];
           tc_ld32(t_o + c * 32, r);
           tc_wait_ld();
@@ -304,9 +317,9 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool store = q0 + row < len;
-      __nv_bfloat16* dst = out + (size_t)(t0 + q0 + row) * (size_t)(n_heads * 128) + h * 128;
+      __nv_bfloat16* dst = out + (size_t)(t0 + q0 + row) * (size_t)(n_heads * HD) + h * HD;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         tc_ld32(t_o + c * 32, r);
         tc_wait_ld();
@@ -350,19 +363,21 @@ inline int padded_tokens(int n_tokens, int n_seqs) { return (n_tokens + 8 * n_se
 
 extern "C" {
 
-size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads) {
-  if (n_tokens < 0 || n_seqs < 0 || n_kv_heads <= 0) return 0;
-  return pstart_bytes(n_seqs) + (size_t)n_kv_heads * 128 * (size_t)padded_tokens(n_tokens, n_seqs) * 2;
+size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads, int32_t head_dim) {
+  if (n_tokens < 0 || n_seqs < 0 || n_kv_heads <= 0 || (head_dim != 128 && head_dim != 256)) return 0;
+  return pstart_bytes(n_seqs) + (size_t)n_kv_heads * head_dim * (size_t)padded_tokens(n_tokens, n_seqs) * 2;
 }
 
 uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* cu_seqlens, void* out, void* scratch,
                                                   int32_t n_tokens, int32_t n_seqs, int32_t max_seqlen, int32_t n_heads,
-                                                  int32_t n_kv_heads, int32_t row_stride, int32_t k_off, int32_t v_off,
-                                                  int32_t causal, void* status, void* stream) {
+                                                  int32_t n_kv_heads, int32_t head_dim, int32_t row_stride, int32_t k_off,
+                                                  int32_t v_off, int32_t causal, void* status, void* stream) {
   lg::LaunchScope launch_scope_;
-  if (n_tokens < 0 || n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || (n_heads % n_kv_heads) ||
-      (row_stride % 8) || (k_off % 8) || (v_off % 8) || k_off + n_kv_heads * 128 > row_stride || v_off + n_kv_heads * 128 > row_stride ||
-      n_heads * 128 > row_stride || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || !scratch || ((uintptr_t)scratch & 255))
+  const int D = head_dim;
+  if (n_tokens < 0 || n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || (D != 128 && D != 256) ||
+      (n_heads % n_kv_heads) || (row_stride % 8) || (k_off % 8) || (v_off % 8) || k_off + n_kv_heads * D > row_stride ||
+      v_off + n_kv_heads * D > row_stride || n_heads * D > row_stride || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) ||
+      !scratch || ((uintptr_t)scratch & 255))
     return lg::kInvalidValue;
   if (n_seqs == 0 || max_seqlen == 0 || n_tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
@@ -371,23 +386,27 @@ uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* c
   const int tp = padded_tokens(n_tokens, n_seqs);
   CUtensorMap map_qk, map_vt;
   if (!make_map(&map_qk, qkv, (uint64_t)n_tokens, (uint64_t)row_stride, (uint64_t)row_stride, 128) ||
-      !make_map(&map_vt, vt, (uint64_t)n_kv_heads * 128, (uint64_t)tp, (uint64_t)tp, 128))
+      !make_map(&map_vt, vt, (uint64_t)n_kv_heads * D, (uint64_t)tp, (uint64_t)tp, (uint32_t)D))
     return lg::kInvalidValue;
   const int max8 = (max_seqlen + 7) & ~7;
-  transpose_v_kernel<<<dim3((max8 + 63) / 64, n_kv_heads, n_seqs), 256, 0, s>>>(
-      (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
+  const dim3 tgrid((max8 + 63) / 64, n_kv_heads, n_seqs);
+  if (D == 128)
+    transpose_v_kernel<128><<<tgrid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
+  else
+    transpose_v_kernel<256><<<tgrid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
   uint32_t rc = lg::launch_status();
   if (rc) return rc;
-  const float sl2 = 1.4426950408889634f / sqrtf(128.0f);
+  const float sl2 = 1.4426950408889634f / sqrtf((float)D);
   dim3 grid((max_seqlen + 127) / 128, n_heads, n_seqs);
-  auto launch = [&](auto kern) -> uint32_t {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  auto launch = [&](auto kern, size_t smem) -> uint32_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, 192, kAttnSmem, s>>>(map_qk, map_vt, (const int*)cu_seqlens, pstart, (__nv_bfloat16*)out, n_heads,
-                                      n_kv_heads, k_off, sl2, (int*)status);
+    kern<<<grid, 192, smem, s>>>(map_qk, map_vt, (const int*)cu_seqlens, pstart, (__nv_bfloat16*)out, n_heads,
+                                 n_kv_heads, k_off, sl2, (int*)status);
     return lg::launch_status();
   };
-  return causal ? launch(attn_tcgen05_kernel<true>) : launch(attn_tcgen05_kernel<false>);
+  if (D == 128) return causal ? launch(attn_tcgen05_kernel<true, 128>, Attn<128>::kSmem) : launch(attn_tcgen05_kernel<false, 128>, Attn<128>::kSmem);
+  return causal ? launch(attn_tcgen05_kernel<true, 256>, Attn<256>::kSmem) : launch(attn_tcgen05_kernel<false, 256>, Attn<256>::kSmem);
 }
 
 }  // extern "C"

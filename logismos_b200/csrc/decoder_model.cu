@@ -96,7 +96,7 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
       if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
         LG_TRY(logismos_launch_varlen_attention_tc_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
                                                         (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->attn_ws.p, T - m->n_dec,
-                                                        m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, QKV, H, H + KV, 1, st, s),
+                                                        m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, st, s),
                "varlen_attention");
         m->launches += 2;
       } else {
@@ -199,7 +199,7 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
        m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&
        m->dec_chunks.alloc((S + 1) * 4) &&
        m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim)) &&
-       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads));
+       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads, 128));
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
   ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4;

@@ -54,7 +54,7 @@ struct Hybrid {
   lg_allreduce_f32_fn allreduce = nullptr;
   void* allreduce_user = nullptr;
   Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
-  Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, state_slots, fresh;
+  Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh;
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
   cudaStream_t stream = nullptr;
@@ -116,10 +116,12 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
         m->launches += 2;
       }
       if (m->n_pre > 0) {
-        LG_TRY(logismos_launch_varlen_attention_bf16(p16 + (size_t)m->n_dec * AN, m->cu_prefill.p,
-                                                     (uint16_t*)m->mix.p + (size_t)m->n_dec * QW, m->n_pre, m->max_pre_len,
-                                                     c.n_heads, c.n_kv_heads, D, AN, QW, QW + KW, 1, s), "varlen_attention");
-        m->launches += 1;
+        // tcgen05 kernel; V transposed into attn_ws first
+        LG_TRY(logismos_launch_varlen_attention_tc_bf16(p16 + (size_t)m->n_dec * AN, m->cu_prefill.p,
+                                                        (uint16_t*)m->mix.p + (size_t)m->n_dec * QW, m->attn_ws.p, T - m->n_dec,
+                                                        m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, D, AN, QW, QW + KW, 1,
+                                                        st, s), "varlen_attention");
+        m->launches += 2;
       }
       LG_TRY(logismos_launch_gated_mul_bf16(m->mix.p, QW, p16 + QW + 2 * KW, AN, T, QW, 0, s), "attention gate");
       m->launches += 1;
@@ -287,7 +289,8 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
        m->pos.alloc(T * 4) && m->slots.alloc(T * 8) && m->cu_all.alloc((S + 1) * 4) && m->cu_prefill.alloc((S + 1) * 4) &&
        m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) && m->dec_chunks.alloc((S + 1) * 4) &&
        m->state_slots.alloc(S * 4) && m->fresh.alloc(S) &&
-       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim));
+       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim)) &&
+       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes(c.max_step_tokens, c.max_step_seqs, c.n_kv_heads, c.attn_head_dim));
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
   ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4 + S + 64;
@@ -309,7 +312,7 @@ void lg_hybrid_destroy(void* model) {
   Buf* bufs[] = {&m->delta, &m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
                  &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens,
                  &m->status, &m->ids, &m->pos, &m->slots, &m->cu_all, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables,
-                 &m->dec_chunks, &m->dec_scratch, &m->state_slots, &m->fresh};
+                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.kpool, &L.vpool, &L.state, &L.A_log, &L.dt_bias, &L.w_in.codes, &L.w_in.scales,

@@ -120,7 +120,7 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
                                             c.max_pos, st, s), "rope");
     if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
       LG_TRY(logismos_launch_varlen_attention_tc_bf16(m->qkv.p, cu, m->attn.p, m->attn_ws.p, T, n_seqs, max_seqlen, c.n_heads,
-                                                      c.n_kv_heads, QKV, H, H + c.n_kv_heads * D, causal, st, s), "attention");
+                                                      c.n_kv_heads, D, QKV, H, H + c.n_kv_heads * D, causal, st, s), "attention");
     } else {
       LG_TRY(logismos_launch_varlen_attention_bf16(m->qkv.p, cu, m->attn.p, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads,
                                                    D, QKV, H, H + c.n_kv_heads * D, causal, s), "attention");
@@ -222,7 +222,7 @@ uint32_t lg_stella_create(int32_t device, const lg_stella_config_t* cfg, const l
   int max_dim = 0;
   for (int i = 0; i < c.n_dims; ++i) max_dim = c.dims[i] > max_dim ? c.dims[i] : max_dim;
   ok = ok && m->x.alloc(T * H * 4) && m->h.alloc(T * H * 2) && m->qkv.alloc(T * QKV * 2) && m->attn.alloc(T * H * 2) &&
-       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int)T, (int)S, c.n_kv_heads)) &&
+       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int)T, (int)S, c.n_kv_heads, 128)) &&
        m->gu.alloc(c.fuse_swiglu ? 16 : T * 2 * I * 2) && m->act.alloc(T * I * 2) && m->hidden_out.alloc(T * H * 4) && m->pooled.alloc(S * H * 4) &&
        m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->cu.alloc((S + 1) * 4) && m->out.alloc(S * max_dim * 4) &&
        m->status.alloc(4);

@@ -219,7 +219,7 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
     qkv = torch.randn((T, (n_heads + 2 * n_kv) * d), device="cuda").to(torch.bfloat16)
     cu = torch.arange(0, T + 1, length, dtype=torch.int32, device="cuda")
     t = timeit(lambda i: ops.varlen_attention(qkv, cu, n_heads, n_kv, d, max_seqlen=length, sync=False), iters)
-    scratch = torch.empty(int(lib.logismos_varlen_attention_tc_scratch_bytes(T, seqs, n_kv)), dtype=torch.uint8, device="cuda")
+    scratch = torch.empty(int(lib.logismos_varlen_attention_tc_scratch_bytes(T, seqs, n_kv, d)), dtype=torch.uint8, device="cuda")
     t_tc = timeit(lambda i: ops.varlen_attention_tc(qkv, cu, n_heads, n_kv, max_seqlen=length, sync=False, scratch=scratch), iters)
     fl = 4.0 * n_heads * d * length * length * seqs
     return {"kernel": "varlen_attention", "seqs": seqs, "len": length, "flops": fl, "us_mma_sync": t * 1e6, "TFLOPs_mma_sync": fl / t / 1e12,

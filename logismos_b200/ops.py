@@ -185,19 +185,20 @@ def swiglu(gu, sync=True):
     return out
 
 
-def varlen_attention_tc(qkv, cu_seqlens, n_heads, n_kv_heads, causal=False, max_seqlen=None, sync=True, scratch=None, status=None):
-    """Ragged-batch attention at head_dim 128 on the tcgen05 tensor cores (same layout contract as
-    varlen_attention). Returns out bf16 [n_tokens, n_heads * 128]."""
+def varlen_attention_tc(qkv, cu_seqlens, n_heads, n_kv_heads, causal=False, max_seqlen=None, sync=True, scratch=None, status=None,
+                        head_dim=128):
+    """Ragged-batch attention at head_dim 128 or 256 on the tcgen05 tensor cores (same layout contract as
+    varlen_attention). Returns out bf16 [n_tokens, n_heads * head_dim]."""
     _req(qkv, "qkv", torch.bfloat16, 2); _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
-    n_seqs, T = cu_seqlens.shape[0] - 1, qkv.shape[0]
+    n_seqs, T, D = cu_seqlens.shape[0] - 1, qkv.shape[0], head_dim
     if max_seqlen is None:
         max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item()) if n_seqs > 0 else 0
-    out = torch.empty((T, n_heads * 128), dtype=torch.bfloat16, device=qkv.device)
+    out = torch.empty((T, n_heads * D), dtype=torch.bfloat16, device=qkv.device)
     if scratch is None:
-        scratch = torch.empty(max(256, int(lib.logismos_varlen_attention_tc_scratch_bytes(T, n_seqs, n_kv_heads))), dtype=torch.uint8, device=qkv.device)
+        scratch = torch.empty(max(256, int(lib.logismos_varlen_attention_tc_scratch_bytes(T, n_seqs, n_kv_heads, D))), dtype=torch.uint8, device=qkv.device)
     with torch.cuda.device(qkv.device):
         check(lib.logismos_launch_varlen_attention_tc_bf16(_p(qkv), _p(cu_seqlens), _p(out), _p(scratch), T, n_seqs, max_seqlen, n_heads,
-                                                           n_kv_heads, qkv.shape[1], n_heads * 128, (n_heads + n_kv_heads) * 128,
+                                                           n_kv_heads, D, qkv.shape[1], n_heads * D, (n_heads + n_kv_heads) * D,
                                                            int(causal), _p(status) if status is not None else None, _stream()), "varlen_attention_tc")
         _done(sync)
     return out

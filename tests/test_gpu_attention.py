@@ -53,15 +53,14 @@ def test_rejects_unsupported_head_dim():
 
 # ---- the tcgen05 kernel (head_dim 128): same oracle, same cases ----
 
-def run_case_tc(lens, nh, nkv, causal, seed):
+def run_case_tc(lens, nh, nkv, causal, seed, d=128):
     rng = np.random.default_rng(seed)
-    d = 128
     T = int(sum(lens))
     stride = (nh + 2 * nkv) * d
     qkv_t, qkv = bf16_cuda(rng.standard_normal((T, stride)))
     cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    out = to_np(ops.varlen_attention_tc(qkv_t, torch.from_numpy(cu).to(DEV), nh, nkv, causal=causal, status=status))
+    out = to_np(ops.varlen_attention_tc(qkv_t, torch.from_numpy(cu).to(DEV), nh, nkv, causal=causal, status=status, head_dim=d))
     assert int(status.item()) == 0
     for i, L in enumerate(lens):
         if L == 0:
@@ -82,6 +81,13 @@ def test_tc_stella_head_layout_ragged_lengths(causal):  # lengths around the 128
 def test_tc_other_gqa_layouts(nh, nkv):
     run_case_tc([100, 17, 300], nh, nkv, False, nh)
     run_case_tc([70, 260], nh, nkv, True, nh + 1)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_tc_head_dim_256(causal):  # the hybrid decoder's full-attention layers: 16 q / 2 kv heads of 256
+    run_case_tc([70, 1, 33, 200, 64, 0, 385, 128], 16, 2, causal, 21, d=256)
+    run_case_tc([129], 4, 4, causal, 22, d=256)
+    run_case_tc([900], 2, 1, causal, 23, d=256)
 
 
 def test_tc_long_sequence_and_large_scores():
