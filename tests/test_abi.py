@@ -54,6 +54,10 @@ def test_launcher_shape_guards_reject_without_launching():  # matmul/mod.rs:213-
     assert lib.logismos_launch_linear_t_bf16(z, z, z, z, 8, 16, 100, 100, 16, 0, z, z) == 1  # k % 64
     assert lib.logismos_launch_varlen_attention_bf16(z, z, z, 1, 8, 4, 3, 128, 1024, 512, 768, 0, z) == 1  # heads % kv
     assert lib.logismos_launch_varlen_attention_bf16(z, z, z, 1, 8, 4, 2, 64, 512, 256, 384, 0, z) == 1    # head_dim
+    assert lib.logismos_launch_varlen_attention_tc_bf16(z, z, z, z, 8, 1, 8, 4, 2, 64, 512, 256, 384, 0, z, z) == 1   # head_dim
+    assert lib.logismos_launch_varlen_attention_tc_bf16(z, z, z, z, 8, 1, 8, 4, 3, 128, 1024, 512, 768, 0, z, z) == 1  # heads % kv, no scratch
+    assert lib.logismos_varlen_attention_tc_scratch_bytes(100, 3, 2, 128) == 256 + 2 * 128 * 128 * 2  # 100 + 24 -> 128 padded keys
+    assert lib.logismos_varlen_attention_tc_scratch_bytes(100, 3, 2, 64) == 0
     assert lib.logismos_launch_paged_attention_decode_bf16(z, z, z, z, z, z, z, z, z, z, z, 1, 1, 100, 4, 4, 16, 2, 128, z) == 1
 
 
