@@ -131,6 +131,20 @@ uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv_bf16, const vo
                                                   int32_t k_off, int32_t v_off, int32_t causal,
                                                   void* status, void* stream);
 
+/* The same with the halves-RoPE of the q and k heads (logismos_launch_rope_halves_bf16's contract:
+ * the first n_rot_heads heads of every row are rotated in place by cos/sin f32 [max_pos, head_dim/2]
+ * at positions[token]; a position outside [0, max_pos) sets status to 1) done by extra blocks of the
+ * V-transposing launch, so the pair is still two launches. qkv is modified in place. */
+uint32_t logismos_launch_rope_varlen_attention_tc_bf16(void* qkv_bf16, const void* cos_f32,
+                                                       const void* sin_f32, const void* positions_i32,
+                                                       int32_t n_rot_heads, int32_t max_pos,
+                                                       const void* cu_seqlens_i32, void* out_bf16,
+                                                       void* scratch, int32_t n_tokens, int32_t n_seqs,
+                                                       int32_t max_seqlen, int32_t n_heads,
+                                                       int32_t n_kv_heads, int32_t head_dim,
+                                                       int32_t row_stride, int32_t k_off, int32_t v_off,
+                                                       int32_t causal, void* status, void* stream);
+
 /* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
  * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), mask all ones.
  * hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden]; head_b f32 [dim]; out f32

@@ -69,6 +69,7 @@ def _declare(l):
         "logismos_launch_swiglu_bf16": [vp, vp, i32, i32, vp],
         "logismos_launch_varlen_attention_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
         "logismos_launch_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_rope_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],

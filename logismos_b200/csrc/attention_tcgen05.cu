@@ -77,15 +77,67 @@ LG_DEVINL int round8(int v) { return (v + 7) & ~7; }
 
 // V columns of qkv -> vt [n_kv * 128, tp] (row = kv head * 128 + d, column = padded key index), and the
 // padded start of every sequence -> pstart[n_seqs]. Grid (key blocks of 64, kv heads, sequences).
+// Optional halves-RoPE on the q and k heads in the same launch (cpu_f32::rope_halves_in_place,
+// crates/kernels/src/cpu_f32/mod.rs:502-547): the blocks after the transposing ones take one
+// (token, head, 8 adjacent i) per thread with 128-bit accesses.
+struct RopeArgs {
+  __nv_bfloat16* qk;      // nullptr: no RoPE blocks
+  const float* cosT;      // [max_pos, HD / 2]
+  const float* sinT;
+  const int* positions;   // [n_tokens]
+  int n_tokens, n_rot_heads, max_pos;
+  int* status;
+};
+
+template <int HD>
+LG_DEVINL void rope_block(const RopeArgs& r, int row_stride, int64_t idx) {
+  constexpr int half = HD / 2, octs = half / 8;
+  const int64_t total = (int64_t)r.n_tokens * r.n_rot_heads * octs;
+  if (idx >= total) return;
+  const int p = (int)(idx % octs);
+  const int h = (int)((idx / octs) % r.n_rot_heads);
+  const int t = (int)(idx / ((int64_t)octs * r.n_rot_heads));
+  const int pos = r.positions[t];
+  if (pos < 0 || pos >= r.max_pos) {  // RopeTable::gather rejects it (rope.rs:57-66)
+    if (r.status) atomicExch(r.status, 1);
+    return;
+  }
+  __nv_bfloat16* base = r.qk + (size_t)t * row_stride + h * HD + 8 * p;
+  const float4* cp = reinterpret_cast<const float4*>(r.cosT + (size_t)pos * half + 8 * p);
+  const float4* sp = reinterpret_cast<const float4*>(r.sinT + (size_t)pos * half + 8 * p);
+  const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  uint4* lo = reinterpret_cast<uint4*>(base);
+  uint4* hi = reinterpret_cast<uint4*>(base + half);
+  const uint4 a = *lo, b = *hi;
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t ow[4], pw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x0 = unpack_bf16x2(aw[i]), x1 = unpack_bf16x2(bw[i]);
+    ow[i] = pack_bf16x2(x0.x * c[2 * i] - x1.x * sn[2 * i], x0.y * c[2 * i + 1] - x1.y * sn[2 * i + 1]);
+    pw[i] = pack_bf16x2(x0.x * sn[2 * i] + x1.x * c[2 * i], x0.y * sn[2 * i + 1] + x1.y * c[2 * i + 1]);
+  }
+  *lo = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  *hi = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+}
+
+// Grid: tx * n_kv * n_seqs transposing blocks (key block of 64, kv head, sequence), then the RoPE blocks.
 template <int HD>
 __global__ void __launch_bounds__(256)
 transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu, __nv_bfloat16* __restrict__ vt,
-                   int* __restrict__ pstart, int n_seqs, int row_stride, int v_off, int tp) {
+                   int* __restrict__ pstart, int n_seqs, int row_stride, int v_off, int tp, int tx, int n_kv, RopeArgs rope) {
   __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
   constexpr int kParts = 256 / HD, kChunks = HD / 8;  // threads per d row; 16-byte chunks per token row
   __shared__ int p0_s;
-  const int s = blockIdx.z, kvh = blockIdx.y, tb = blockIdx.x;
   const int tid = threadIdx.x;
+  const int t_blocks = tx * n_kv * n_seqs;
+  if ((int)blockIdx.x >= t_blocks) {
+    rope_block<HD>(rope, row_stride, (int64_t)((int)blockIdx.x - t_blocks) * 256 + tid);
+    return;
+  }
+  const int tb = (int)blockIdx.x % tx, kvh = ((int)blockIdx.x / tx) % n_kv, s = (int)blockIdx.x / (tx * n_kv);
   if (tid < 32) {
     int part = 0;
     for (int i = tid; i < s; i += 32) part += round8(cu[i + 1] - cu[i]);
@@ -368,16 +420,18 @@ size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_se
   return pstart_bytes(n_seqs) + (size_t)n_kv_heads * head_dim * (size_t)padded_tokens(n_tokens, n_seqs) * 2;
 }
 
-uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* cu_seqlens, void* out, void* scratch,
-                                                  int32_t n_tokens, int32_t n_seqs, int32_t max_seqlen, int32_t n_heads,
-                                                  int32_t n_kv_heads, int32_t head_dim, int32_t row_stride, int32_t k_off,
-                                                  int32_t v_off, int32_t causal, void* status, void* stream) {
-  lg::LaunchScope launch_scope_;
+static uint32_t launch_attn_tc(const void* qkv, const void* cu_seqlens, void* out, void* scratch, int32_t n_tokens,
+                               int32_t n_seqs, int32_t max_seqlen, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                               int32_t row_stride, int32_t k_off, int32_t v_off, int32_t causal, RopeArgs rope, void* status,
+                               void* stream) {
   const int D = head_dim;
   if (n_tokens < 0 || n_seqs < 0 || max_seqlen < 0 || n_heads <= 0 || n_kv_heads <= 0 || (D != 128 && D != 256) ||
       (n_heads % n_kv_heads) || (row_stride % 8) || (k_off % 8) || (v_off % 8) || k_off + n_kv_heads * D > row_stride ||
       v_off + n_kv_heads * D > row_stride || n_heads * D > row_stride || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) ||
       !scratch || ((uintptr_t)scratch & 255))
+    return lg::kInvalidValue;
+  if (rope.qk && (rope.n_rot_heads <= 0 || rope.n_rot_heads * D > row_stride || rope.max_pos <= 0 || !rope.cosT || !rope.sinT ||
+                  !rope.positions || (((uintptr_t)rope.cosT | (uintptr_t)rope.sinT) & 15)))
     return lg::kInvalidValue;
   if (n_seqs == 0 || max_seqlen == 0 || n_tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
@@ -389,11 +443,16 @@ uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* c
       !make_map(&map_vt, vt, (uint64_t)n_kv_heads * D, (uint64_t)tp, (uint64_t)tp, (uint32_t)D))
     return lg::kInvalidValue;
   const int max8 = (max_seqlen + 7) & ~7;
-  const dim3 tgrid((max8 + 63) / 64, n_kv_heads, n_seqs);
+  const int tx = (max8 + 63) / 64;
+  const int64_t rope_threads = rope.qk ? (int64_t)rope.n_tokens * rope.n_rot_heads * (D / 16) : 0;
+  const int64_t blocks = (int64_t)tx * n_kv_heads * n_seqs + (rope_threads + 255) / 256;
+  if (blocks > 0x7fffffff) return lg::kInvalidValue;
   if (D == 128)
-    transpose_v_kernel<128><<<tgrid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
+    transpose_v_kernel<128><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
+                                                             row_stride, v_off, tp, tx, n_kv_heads, rope);
   else
-    transpose_v_kernel<256><<<tgrid, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs, row_stride, v_off, tp);
+    transpose_v_kernel<256><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
+                                                             row_stride, v_off, tp, tx, n_kv_heads, rope);
   uint32_t rc = lg::launch_status();
   if (rc) return rc;
   const float sl2 = 1.4426950408889634f / sqrtf((float)D);
@@ -407,6 +466,29 @@ uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* c
   };
   if (D == 128) return causal ? launch(attn_tcgen05_kernel<true, 128>, Attn<128>::kSmem) : launch(attn_tcgen05_kernel<false, 128>, Attn<128>::kSmem);
   return causal ? launch(attn_tcgen05_kernel<true, 256>, Attn<256>::kSmem) : launch(attn_tcgen05_kernel<false, 256>, Attn<256>::kSmem);
+}
+
+uint32_t logismos_launch_varlen_attention_tc_bf16(const void* qkv, const void* cu_seqlens, void* out, void* scratch,
+                                                  int32_t n_tokens, int32_t n_seqs, int32_t max_seqlen, int32_t n_heads,
+                                                  int32_t n_kv_heads, int32_t head_dim, int32_t row_stride, int32_t k_off,
+                                                  int32_t v_off, int32_t causal, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  RopeArgs none{};
+  return launch_attn_tc(qkv, cu_seqlens, out, scratch, n_tokens, n_seqs, max_seqlen, n_heads, n_kv_heads, head_dim, row_stride,
+                        k_off, v_off, causal, none, status, stream);
+}
+
+uint32_t logismos_launch_rope_varlen_attention_tc_bf16(void* qkv, const void* cos_f32, const void* sin_f32, const void* positions,
+                                                       int32_t n_rot_heads, int32_t max_pos, const void* cu_seqlens, void* out,
+                                                       void* scratch, int32_t n_tokens, int32_t n_seqs, int32_t max_seqlen,
+                                                       int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t row_stride,
+                                                       int32_t k_off, int32_t v_off, int32_t causal, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (!qkv) return lg::kInvalidValue;
+  RopeArgs r{(__nv_bfloat16*)qkv, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions, n_tokens, n_rot_heads, max_pos,
+             (int*)status};
+  return launch_attn_tc(qkv, cu_seqlens, out, scratch, n_tokens, n_seqs, max_seqlen, n_heads, n_kv_heads, head_dim, row_stride,
+                        k_off, v_off, causal, r, status, stream);
 }
 
 }  // extern "C"

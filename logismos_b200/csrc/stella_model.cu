@@ -116,12 +116,13 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
     Layer& L = m->layers[l];
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm1.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
     LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wqkv.p, L.bqkv.p, m->qkv.p, T, QKV, H, H, QKV, LG_EPI_BF16, st, s), "qkv_proj");
-    LG_TRY(logismos_launch_rope_halves_bf16(m->qkv.p, m->cos.p, m->sin.p, pos, T, c.n_heads + c.n_kv_heads, D, QKV,
-                                            c.max_pos, st, s), "rope");
-    if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
-      LG_TRY(logismos_launch_varlen_attention_tc_bf16(m->qkv.p, cu, m->attn.p, m->attn_ws.p, T, n_seqs, max_seqlen, c.n_heads,
-                                                      c.n_kv_heads, D, QKV, H, H + c.n_kv_heads * D, causal, st, s), "attention");
+    if (D == 128) {  // tcgen05 kernel; its first launch rotates q and k and transposes V into attn_ws
+      LG_TRY(logismos_launch_rope_varlen_attention_tc_bf16(m->qkv.p, m->cos.p, m->sin.p, pos, c.n_heads + c.n_kv_heads, c.max_pos, cu,
+                                                           m->attn.p, m->attn_ws.p, T, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads, D,
+                                                           QKV, H, H + c.n_kv_heads * D, causal, st, s), "rope + attention");
     } else {
+      LG_TRY(logismos_launch_rope_halves_bf16(m->qkv.p, m->cos.p, m->sin.p, pos, T, c.n_heads + c.n_kv_heads, D, QKV,
+                                              c.max_pos, st, s), "rope");
       LG_TRY(logismos_launch_varlen_attention_bf16(m->qkv.p, cu, m->attn.p, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads,
                                                    D, QKV, H, H + c.n_kv_heads * D, causal, s), "attention");
     }
@@ -268,7 +269,7 @@ int32_t lg_stella_supported_dims(const void* model, int32_t* out, int32_t cap) {
 int32_t lg_stella_max_tokens(const void* model) { return static_cast<const Stella*>(model)->cfg.max_tokens; }
 int32_t lg_stella_launches_per_forward(const void* model) {
   const Stella* m = static_cast<const Stella*>(model);
-  return 1 + m->cfg.n_layers * ((m->cfg.fuse_swiglu ? 8 : 9) + (m->head_dim == 128 ? 1 : 0)) + 4;
+  return 1 + m->cfg.n_layers * (m->cfg.fuse_swiglu ? 8 : 9) + 4;
 }
 
 uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* dev_cu, const void* dev_pos,

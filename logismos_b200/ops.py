@@ -204,6 +204,26 @@ def varlen_attention_tc(qkv, cu_seqlens, n_heads, n_kv_heads, causal=False, max_
     return out
 
 
+def rope_varlen_attention_tc_(qkv, cos, sin, positions, cu_seqlens, n_heads, n_kv_heads, causal=False, max_seqlen=None, sync=True,
+                             scratch=None, status=None, head_dim=128):
+    """halves-RoPE of the q and k heads of qkv (in place) fused into the first launch of varlen_attention_tc."""
+    _req(qkv, "qkv", torch.bfloat16, 2); _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _req(cos, "cos", torch.float32, 2); _req(sin, "sin", torch.float32, 2); _req(positions, "positions", torch.int32, 1)
+    n_seqs, T, D = cu_seqlens.shape[0] - 1, qkv.shape[0], head_dim
+    if max_seqlen is None:
+        max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item()) if n_seqs > 0 else 0
+    out = torch.empty((T, n_heads * D), dtype=torch.bfloat16, device=qkv.device)
+    if scratch is None:
+        scratch = torch.empty(max(256, int(lib.logismos_varlen_attention_tc_scratch_bytes(T, n_seqs, n_kv_heads, D))), dtype=torch.uint8, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        check(lib.logismos_launch_rope_varlen_attention_tc_bf16(_p(qkv), _p(cos), _p(sin), _p(positions), n_heads + n_kv_heads, cos.shape[0],
+                                                                _p(cu_seqlens), _p(out), _p(scratch), T, n_seqs, max_seqlen, n_heads, n_kv_heads, D,
+                                                                qkv.shape[1], n_heads * D, (n_heads + n_kv_heads) * D, int(causal),
+                                                                _p(status) if status is not None else None, _stream()), "rope_varlen_attention_tc")
+        _done(sync)
+    return out
+
+
 def varlen_attention(qkv, cu_seqlens, n_heads, n_kv_heads, head_dim, causal=False, max_seqlen=None, sync=True):
     _req(qkv, "qkv", torch.bfloat16, 2); _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
     n_seqs = cu_seqlens.shape[0] - 1

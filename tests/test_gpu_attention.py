@@ -122,3 +122,27 @@ def test_tc_rejects_bad_arguments():
     cu = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
     with pytest.raises(Exception):
         ops.varlen_attention_tc(qkv, cu, 3, 2)  # heads % kv heads
+
+
+@pytest.mark.parametrize("d,causal", [(128, False), (256, True)])
+def test_tc_with_fused_rope_equals_rope_then_attention(d, causal):
+    """The entry point that rotates q and k inside the V-transposing launch: bit-identical qkv and output
+    to the RoPE launch followed by the plain entry point; a position beyond the table is reported."""
+    rng = np.random.default_rng(41)
+    lens = [70, 1, 200, 33]
+    T, nh, nkv = sum(lens), 4, 2
+    qkv_t, _ = bf16_cuda(rng.standard_normal((T, (nh + 2 * nkv) * d)))
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(DEV)
+    pos = torch.from_numpy(np.concatenate([np.arange(L) for L in lens]).astype(np.int32)).to(DEV)
+    cos, sin = O.build_rope_table_f32(256, d, 1e6)
+    cos_t = torch.from_numpy(cos.reshape(256, d // 2)).to(DEV); sin_t = torch.from_numpy(sin.reshape(256, d // 2)).to(DEV)
+    a_qkv = ops.rope_halves_(qkv_t.clone(), cos_t, sin_t, pos, nh + nkv, d)
+    a_out = ops.varlen_attention_tc(a_qkv, cu, nh, nkv, causal=causal, head_dim=d)
+    b_qkv = qkv_t.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    b_out = ops.rope_varlen_attention_tc_(b_qkv, cos_t, sin_t, pos, cu, nh, nkv, causal=causal, head_dim=d, status=status)
+    assert int(status.item()) == 0
+    assert torch.equal(a_qkv, b_qkv) and torch.equal(a_out, b_out)
+    bad = pos.clone(); bad[5] = 256
+    ops.rope_varlen_attention_tc_(qkv_t.clone(), cos_t, sin_t, bad, cu, nh, nkv, causal=causal, head_dim=d, status=status)
+    assert int(status.item()) == 1
