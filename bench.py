@@ -220,16 +220,17 @@ def micro_rooflines(peaks, T, cfg):
     kp = torch.randn((n_pool, 16, 256), device=dev).to(torch.bfloat16); vp = torch.randn((n_pool, 16, 256), device=dev).to(torch.bfloat16)
     q = torch.randn((256, 2048), device=dev).to(torch.bfloat16)
     nk = torch.randn((256, 256), device=dev).to(torch.bfloat16); nv = torch.randn((256, 256), device=dev).to(torch.bfloat16)
-    off, total = ops.build_decode_chunks(ctx.astype(np.int32), 512)
+    chunk = ops.pick_decode_chunk(ctx.astype(np.int32), 2, 128)  # the choice the executors make for a step
+    off, total = ops.build_decode_chunks(ctx.astype(np.int32), chunk)
     d_tab, d_ctx, d_off = torch.from_numpy(tables).to(dev), torch.from_numpy(ctx.astype(np.int32)).to(dev), off.to(dev)
     scratch = torch.empty(int(ops.lib.logismos_paged_decode_scratch_bytes(total, 16, 128)), dtype=torch.uint8, device=dev)
-    t = time_kernel(lambda i: ops.paged_attention_decode(q, kp, vp, nk, nv, d_tab, d_ctx, d_off, total, 512, 16, 2, 128, scratch=scratch,
+    t = time_kernel(lambda i: ops.paged_attention_decode(q, kp, vp, nk, nv, d_tab, d_ctx, d_off, total, chunk, 16, 2, 128, scratch=scratch,
                                                          sync=False), 10, st)
     by = float(ctx.sum()) * 1024 + 256 * (2048 * 2 * 2 + 512 * 2) + tables.size * 4
     out["paged"] = {"kernel": "paged_attention_decode (256 seqs, ctx log-U[128,32768], GQA 16/2, fused append) incl. merge kernel",
                     "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"],
                     "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences scaled by context tokens",
-                    "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()),
+                    "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()), "chunk_tokens": chunk,
                     "peak_source": peaks["src"]}
     return out
 

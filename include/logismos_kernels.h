@@ -348,6 +348,10 @@ int64_t logismos_build_packing(const int32_t* host_cached_lens, const int32_t* h
 /* chunk_offsets [n+1] for the paged decode kernel; returns total_chunks. */
 int32_t logismos_build_decode_chunks(const int32_t* host_context_lens, int32_t n_seqs,
                                      int32_t chunk_tokens, int32_t* host_chunk_offsets);
+/* chunk_tokens for one step's contexts: the largest of 512, 1024, 2048 that leaves the decode launch at
+ * least 32768 / head_dim CTAs (chunks x kv heads); 512 otherwise. Host-side, no device work. */
+int32_t logismos_pick_decode_chunk(const int32_t* host_context_lens, int32_t n_seqs,
+                                   int32_t n_kv_heads, int32_t head_dim);
 
 #ifdef __cplusplus
 }

@@ -126,6 +126,8 @@ def _declare(l):
     l.logismos_build_packing.restype = i64
     l.logismos_build_decode_chunks.argtypes = [vp, i32, i32, vp]
     l.logismos_build_decode_chunks.restype = i32
+    l.logismos_pick_decode_chunk.argtypes = [vp, i32, i32, i32]
+    l.logismos_pick_decode_chunk.restype = i32
     l.lg_stella_destroy.argtypes = [vp]
     l.lg_stella_destroy.restype = None
     l.lg_decoder_destroy.argtypes = [vp]

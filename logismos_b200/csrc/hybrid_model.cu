@@ -59,7 +59,7 @@ struct Hybrid {
   size_t pinned_bytes = 0;
   cudaStream_t stream = nullptr;
   std::mutex mu;
-  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, max_pre_len = 0, total_chunks = 0, launches = 0, logits_f32 = 0;
+  int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, max_pre_len = 0, total_chunks = 0, chunk_tokens = kChunkTokens, launches = 0, logits_f32 = 0;
   std::vector<int> order;
   size_t max_chunks = 0;
 };
@@ -111,7 +111,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
                                  cudaMemcpyDeviceToDevice, s), "q gather");
         LG_TRY(logismos_launch_paged_attention_decode_bf16(m->qdec.p, L.kpool.p, L.vpool.p, nullptr, nullptr, m->dec_tables.p,
                                                            m->dec_ctx.p, m->dec_chunks.p, m->mix.p, m->dec_scratch.p, st, m->n_dec,
-                                                           m->total_chunks, kChunkTokens, c.max_blocks_per_seq, c.n_pool_blocks,
+                                                           m->total_chunks, m->chunk_tokens, c.max_blocks_per_seq, c.n_pool_blocks,
                                                            c.n_heads, c.n_kv_heads, D, s), "paged_attention_decode");
         m->launches += 2;
       }
@@ -399,7 +399,8 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
       if (o_new[s] > max_pre) max_pre = o_new[s];
     }
   }
-  const int total_chunks = n_dec > 0 ? logismos_build_decode_chunks(h_ctx, n_dec, kChunkTokens, h_chunks) : 0;
+  m->chunk_tokens = n_dec > 0 ? logismos_pick_decode_chunk(h_ctx, n_dec, m->cfg.n_kv_heads, m->cfg.attn_head_dim) : kChunkTokens;
+  const int total_chunks = n_dec > 0 ? logismos_build_decode_chunks(h_ctx, n_dec, m->chunk_tokens, h_chunks) : 0;
   if (total_chunks < 0 || (size_t)total_chunks > m->max_chunks) { set_error("lg_hybrid_step: decode chunk count exceeds the scratch"); return LG_EMB_COMPUTE; }
   m->T = (int)total; m->n_dec = n_dec; m->n_pre = n_pre; m->n_seqs = n_seqs; m->max_pre_len = max_pre; m->total_chunks = total_chunks;
   m->order = order;

@@ -192,9 +192,8 @@ def paged_case(seqs, min_ctx, max_ctx, seed=3):
     return ctx, tables, n_pool
 
 
-def bench_paged(seqs, min_ctx, max_ctx, chunk, iters, n_heads=16, n_kv=2, pk=None):
+def bench_paged(seqs, min_ctx, max_ctx, chunk, iters, n_heads=16, n_kv=2, pk=None, d=128):
     pk = pk or peaks()
-    d = 128
     ctx, tables, n_pool = paged_case(seqs, min_ctx, max_ctx)
     row = n_kv * d
     kp = torch.randn((n_pool, 16, row), device="cuda").to(torch.bfloat16)
@@ -202,6 +201,8 @@ def bench_paged(seqs, min_ctx, max_ctx, chunk, iters, n_heads=16, n_kv=2, pk=Non
     q = torch.randn((seqs, n_heads * d), device="cuda").to(torch.bfloat16)
     nk = torch.randn((seqs, row), device="cuda").to(torch.bfloat16)
     nv = torch.randn((seqs, row), device="cuda").to(torch.bfloat16)
+    if chunk <= 0:
+        chunk = ops.pick_decode_chunk(ctx.astype(np.int32), n_kv, d)
     off, total = ops.build_decode_chunks(ctx.astype(np.int32), chunk)
     d_tab, d_ctx, d_off = torch.from_numpy(tables).cuda(), torch.from_numpy(ctx.astype(np.int32)).cuda(), off.cuda()
     scratch = torch.empty(int(lib.logismos_paged_decode_scratch_bytes(total, n_heads, d)), dtype=torch.uint8, device="cuda")
@@ -209,7 +210,7 @@ def bench_paged(seqs, min_ctx, max_ctx, chunk, iters, n_heads=16, n_kv=2, pk=Non
                                                     scratch=scratch, sync=False), iters)
     by = float(ctx.sum()) * row * 2 * 2 + seqs * (n_heads * d * 2 * 2 + row * 2 * 2) + tables.size * 4
     return {"kernel": "paged_attention_decode+merge", "seqs": seqs, "context_tokens": int(ctx.sum()), "pool_blocks": n_pool,
-            "chunk_tokens": chunk, "total_chunks": total, "bytes": by, "us": t * 1e6, "GBps": by / t / 1e9,
+            "head_dim": d, "chunk_tokens": chunk, "total_chunks": total, "bytes": by, "us": t * 1e6, "GBps": by / t / 1e9,
             "frac_hbm": by / t / 1e9 / pk["hbm"], "scratch_bytes": scratch.numel(), "peak": pk["hbm"], "peak_src": pk["src"]}
 
 
@@ -238,7 +239,8 @@ def main(argv=None):
     ap.add_argument("--len", type=int, default=512)
     ap.add_argument("--min-ctx", type=int, default=128)
     ap.add_argument("--max-ctx", type=int, default=32768)
-    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=0, help="paged: tokens per chunk; 0 = the library's choice for the contexts")
+    ap.add_argument("--head-dim", type=int, default=128, help="paged: 128 or 256")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-graph", action="store_true", help="time back-to-back launches from Python instead of a CUDA graph")
     a = ap.parse_args(argv)
@@ -255,7 +257,7 @@ def main(argv=None):
     elif a.what == "qlinear":
         print(json.dumps(bench_qlinear(a.m, a.n, a.k, a.iters)))
     elif a.what == "paged":
-        print(json.dumps(bench_paged(a.seqs, a.min_ctx, a.max_ctx, a.chunk, a.iters)))
+        print(json.dumps(bench_paged(a.seqs, a.min_ctx, a.max_ctx, a.chunk, a.iters, d=a.head_dim)))
     elif a.what == "attn":
         print(json.dumps(bench_attn(a.seqs, a.len, a.iters)))
     else:

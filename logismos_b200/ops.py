@@ -308,6 +308,12 @@ def qlinear_finish(acc, bias=None, swiglu=False, sync=True):
     return out
 
 
+def pick_decode_chunk(context_lens_host, n_kv_heads, head_dim) -> int:
+    """Host helper: tokens per decode chunk for one step's contexts (512, 1024 or 2048)."""
+    cl = torch.as_tensor(context_lens_host, dtype=torch.int32).contiguous()
+    return int(lib.logismos_pick_decode_chunk(C.c_void_p(cl.data_ptr()), cl.numel(), n_kv_heads, head_dim))
+
+
 def build_decode_chunks(context_lens_host, chunk_tokens):
     """Host helper: (chunk_offsets int32 CPU tensor [n+1], total_chunks)."""
     cl = torch.as_tensor(context_lens_host, dtype=torch.int32).contiguous()

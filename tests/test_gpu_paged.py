@@ -85,7 +85,7 @@ def decode_case(ctx_lens, nh, nkv, chunk, seed, append=True, d=128):
         assert (to_np(gk) == hist_k[i]).all() and (to_np(gv) == hist_v[i]).all()
 
 
-@pytest.mark.parametrize("chunk", [64, 512])
+@pytest.mark.parametrize("chunk", [64, 512, 1024, 2048])  # 1024 and 2048: the executors' choice for large steps
 def test_decode_with_fused_append_gqa8(chunk):  # the benchmark head layout: 16 q heads, 2 kv heads
     decode_case([1, 15, 16, 17, 128, 129, 700, 1000, 2049, 64, 513], 16, 2, chunk, 3)
 
@@ -99,6 +99,8 @@ def test_decode_without_append_and_other_layouts():
 
 def test_decode_head_dim_256():  # 16 q / 2 kv heads of 256, the hybrid decoder's full-attention layout
     decode_case([1, 16, 17, 300, 1100, 64], 16, 2, 256, 31, d=256)
+    decode_case([2049, 5000, 1024, 1025, 7], 16, 2, 2048, 33, d=256)
+    decode_case([2049, 1500], 16, 2, 1024, 34, d=256)
     decode_case([45, 513], 8, 2, 512, 32, append=False, d=256)
 
 
@@ -114,3 +116,4 @@ def test_block_id_outside_the_pool_is_reported_not_dereferenced():
 
 def test_long_context_split_over_many_chunks():
     decode_case([32768, 128, 9000], 16, 2, 512, 8)
+    decode_case([32768, 128, 9000], 16, 2, 2048, 9)

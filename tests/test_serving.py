@@ -96,3 +96,21 @@ def test_stalled_pool_is_reported():
     sched = Scheduler(n_pool_blocks=2, max_blocks_per_seq=4, n_state_slots=2, max_step_tokens=64, max_step_seqs=2)
     with pytest.raises(RuntimeError):
         serve(lambda p: np.zeros(len(p.rids), np.uint32), sched, [Request(0, np.ones(40, np.uint32), 8)], Clock())
+
+
+def test_decode_chunk_choice_follows_the_cta_count():
+    """logismos_pick_decode_chunk: the largest of 512 / 1024 / 2048 tokens that leaves chunks x kv heads
+    >= 32768 / head_dim CTAs; 512 when neither does (host-side arithmetic only)."""
+    import ctypes as C
+    from logismos_b200._lib import lib
+
+    def pick(ctx, n_kv, d):
+        a = np.ascontiguousarray(ctx, dtype=np.int32)
+        return lib.logismos_pick_decode_chunk(a.ctypes.data_as(C.c_void_p), a.size, n_kv, d)
+
+    assert pick([1500] * 256, 2, 256) == 2048   # 256 chunks x 2 heads
+    assert pick([1500] * 32, 2, 256) == 1024    # 2048 would leave 64 CTAs, 1024 leaves 128
+    assert pick([100] * 4, 2, 256) == 512
+    assert pick([4000] * 64, 2, 128) == 2048    # 128 chunks x 2 = 256 = 32768 / 128
+    assert pick([4000] * 63, 2, 128) == 1024
+    assert pick([], 2, 128) == 512 and pick([5, -3, 0], 2, 128) == 512
