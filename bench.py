@@ -229,7 +229,7 @@ def micro_rooflines(peaks, T, cfg):
     by = float(ctx.sum()) * 1024 + 256 * (2048 * 2 * 2 + 512 * 2) + tables.size * 4
     out["paged"] = {"kernel": "paged_attention_decode (256 seqs, ctx log-U[128,32768], GQA 16/2, fused append) incl. merge kernel",
                     "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"],
-                    "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences scaled by context tokens",
+                    "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences at 512-token chunks scaled by context tokens (slightly over-states the partial results written at larger chunks)",
                     "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()), "chunk_tokens": chunk,
                     "peak_source": peaks["src"]}
     return out
