@@ -247,14 +247,23 @@ varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __rest
 
 // ================================ paged decode =================================================
 
+inline int lg_sm_count_cached() {
+  static int n = 0;
+  if (n) return n;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (n <= 0) n = 148;
+  return n;
+}
+
 constexpr int kBlock = 16;          // tokens per KV block
-constexpr int kDecWarps = 4;
-constexpr int kDecStages = 3;
-template <int HD>
+// W warps per CTA, each with its own ring of S stages
+template <int HD, int W, int S>
 struct DecCfg {
   static constexpr int kRowBytes = HD * 2;
   static constexpr int kStageBytes = 2 * kBlock * kRowBytes;  // K block + V block of one kv head: 8 KB at head_dim 128
-  static constexpr int kSmem = kDecWarps * kDecStages * kStageBytes + 16 * kRowBytes;  // + Q tile
+  static constexpr int kSmem = W * S * kStageBytes + 16 * kRowBytes;  // + Q tile
 };
 
 // issue the cp.async copies of one 16-token block (K then V) of kv head `kvh` into a warp's stage
@@ -273,7 +282,7 @@ LG_DEVINL void stage_block(uint32_t sbase, const __nv_bfloat16* kpool, const __n
   }
 }
 
-template <int HD>
+template <int HD, int kDecWarps, int kDecStages>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ kpool,
                     __nv_bfloat16* __restrict__ vpool, const __nv_bfloat16* __restrict__ new_k,
@@ -288,7 +297,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
   const int g = lane >> 2, c = lane & 3;
   const int n_rep = n_heads / n_kv;
   constexpr int D = HD, kRowBytes = HD * 2, DT = HD / 8, CH = HD / 8;
-  constexpr int kDecStageBytes = DecCfg<HD>::kStageBytes;
+  constexpr int kDecStageBytes = DecCfg<HD, kDecWarps, kDecStages>::kStageBytes;
   const int row_elems = n_kv * D;
 
   // which sequence owns this chunk: largest s with chunk_offsets[s] <= chunk_id
@@ -562,17 +571,24 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
   float* part_ml = part_o + (size_t)total_chunks * n_heads * head_dim;
   const float sl2 = kLog2e / sqrtf((float)head_dim);
   dim3 grid(total_chunks, n_kv_heads);
-  auto launch = [&](auto kern, int smem) -> uint32_t {
+  auto launch = [&](auto kern, int warps, int smem) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, kDecWarps * 32, smem, (cudaStream_t)stream>>>(
+    kern<<<grid, warps * 32, smem, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)new_k,
         (const __nv_bfloat16*)new_v, (const int*)block_tables, (const int*)context_lens, (const int*)chunk_offsets,
         (__nv_bfloat16*)out, part_o, part_ml, (int*)status, n_seqs, chunk_tokens, max_blocks, n_pool_blocks, n_heads,
         n_kv_heads, sl2);
     return lg::launch_status();
   };
-  uint32_t rc = head_dim == 128 ? launch(paged_decode_kernel<128>, DecCfg<128>::kSmem) : launch(paged_decode_kernel<256>, DecCfg<256>::kSmem);
+  uint32_t rc;
+  if (head_dim == 128) rc = launch(paged_decode_kernel<128, 4, 3>, 4, DecCfg<128, 4, 3>::kSmem);
+  else if ((int64_t)total_chunks * n_kv_heads >= 2 * lg_sm_count_cached())
+    // head_dim 256, many CTAs: 3 warps x 2 stages = 104 KB so that two CTAs share an SM (256 sequences of
+    // 1-2 K tokens: 152 us against 182 us with one CTA of 4 warps x 3 stages)
+    rc = launch(paged_decode_kernel<256, 3, 2>, 3, DecCfg<256, 3, 2>::kSmem);
+  else  // few CTAs: one CTA of 6 warps x 2 stages per SM (64 such sequences: 49 against 56 us)
+    rc = launch(paged_decode_kernel<256, 6, 2>, 6, DecCfg<256, 6, 2>::kSmem);
   if (rc) return rc;
   if (total_chunks > n_seqs) {  // at least one sequence spans several chunks
     dim3 mgrid(n_seqs, n_heads);
