@@ -582,7 +582,10 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
     return lg::launch_status();
   };
   uint32_t rc;
-  if (head_dim == 128) rc = launch(paged_decode_kernel<128, 4, 3>, 4, DecCfg<128, 4, 3>::kSmem);
+  if (head_dim == 128)
+    // 4 warps x 2 stages = 68 KB: three CTAs per SM (256 sequences log-uniform in [128, 32768]: 234 us against
+    // 242 us with 3 stages and two CTAs; 64 sequences in [256, 8192]: 36 against 43 us)
+    rc = launch(paged_decode_kernel<128, 4, 2>, 4, DecCfg<128, 4, 2>::kSmem);
   else if ((int64_t)total_chunks * n_kv_heads >= 2 * lg_sm_count_cached())
     // head_dim 256, many CTAs: 3 warps x 2 stages = 104 KB so that two CTAs share an SM (256 sequences of
     // 1-2 K tokens: 152 us against 182 us with one CTA of 4 warps x 3 stages)
