@@ -160,7 +160,7 @@ def time_kernel(fn, iters, stream):
 # processed, as the summaries state). bytes per unit: gate/up GEMM at M=2176 (read 61.97 + write 7.44 MB,
 # the bf16 output lands in L2 first); GEMV lm_head (131.30 + 5.89 MB); paged decode 1027 B per context
 # token + 7.09 MB of partials per 328868 tokens.
-NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 7.09e6) / 328868}
+NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 4.56e6) / 328868}
 
 
 def micro_rooflines(peaks, T, cfg):
@@ -229,7 +229,7 @@ def micro_rooflines(peaks, T, cfg):
     by = float(ctx.sum()) * 1024 + 256 * (2048 * 2 * 2 + 512 * 2) + tables.size * 4
     out["paged"] = {"kernel": "paged_attention_decode (256 seqs, ctx log-U[128,32768], GQA 16/2, fused append) incl. merge kernel",
                     "bound": "hbm", "achieved": by / t / 1e9, "peak": peaks["hbm"], "unit": "GB/s", "frac": by / t / 1e9 / peaks["hbm"],
-                    "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences at 512-token chunks scaled by context tokens (slightly over-states the partial results written at larger chunks)",
+                    "traffic": NCU_TRAFFIC["paged_per_context_token"] * float(ctx.sum()), "traffic_note": "ncu capture of 64 sequences (2048-token chunks) scaled by context tokens",
                     "bytes_per_launch": by, "us_per_launch": t * 1e6, "context_tokens": int(ctx.sum()), "chunk_tokens": chunk,
                     "peak_source": peaks["src"]}
     return out
