@@ -72,7 +72,8 @@ uint32_t logismos_launch_rms_norm_f32(const void* x_f32, const void* w_f32, void
  *                    interleaved in blocks of 32 rows (32 gate rows, then the 32 matching up
  *                    rows); n % 64 == 0; fuses cpu_f32::silu + hadamard (mod.rs:349-374)
  * bias_f32 may be NULL. ldc is the row stride of out in elements. status_i32 (may be NULL)
- * receives 2 if a bounded wait inside the kernel expired (the output is then invalid).  * With few output tiles and a long reduction the accumulating epilogue splits k over CTAs; the
+ * receives 2 if a bounded wait inside the kernel expired (the output is then invalid).
+ * With few output tiles and a long reduction the accumulating epilogue splits k over CTAs; the
  * slices meet in the fp32 reduce-add, so the last bits of the sum can differ between runs. */
 enum { LG_EPI_BF16 = 0, LG_EPI_RESID_F32 = 1, LG_EPI_SWIGLU = 2 };
 uint32_t logismos_launch_linear_t_bf16(const void* a_bf16, const void* w_bf16,
@@ -145,6 +146,30 @@ uint32_t logismos_launch_rope_varlen_attention_tc_bf16(void* qkv_bf16, const voi
                                                        int32_t row_stride, int32_t k_off, int32_t v_off,
                                                        int32_t causal, void* status, void* stream);
 
+/* A prefill chunk that continues a cached sequence (the reference has no scheduler, crates/sched/src/
+ * lib.rs:1-30, and no paged cache; the anchors are QwenAttention::forward's score stage, crates/
+ * transformers/src/attention.rs:226-296, made causal, and KvCache::get, crates/cache/src/flat.rs:254-304):
+ * sequence s brings the query rows cu_seqlens_q[s] .. cu_seqlens_q[s+1] of q bf16 [n_q_tokens,
+ * q_row_stride] (q heads at column 0, RoPE applied) and attends to its kv_lens[s] tokens in the paged
+ * cache (k_pool / v_pool bf16 [n_pool_blocks, 16, n_kv_heads * head_dim], block_tables i32 [n_seqs,
+ * max_blocks]); the K/V rows of the chunk's own tokens must already be stored there, so kv_lens[s] =
+ * cached + new >= new, and query i sees keys 0 .. kv_lens[s] - new + i. out bf16 [n_q_tokens,
+ * n_heads * head_dim]. total_kv_tokens >= sum(kv_lens), max_q_len / max_kv_len bound the grids (host
+ * values). scratch: logismos_paged_prefix_attention_scratch_bytes(total_kv_tokens, n_seqs, n_kv_heads,
+ * head_dim) bytes, 256-byte aligned: the first launch gathers each sequence's K rows and transposed V
+ * through its block table into it, the second is the tcgen05 kernel of
+ * logismos_launch_varlen_attention_tc_bf16. status (int32, may be NULL): 1 if a block id fell outside
+ * the pool (zero rows are used) or kv_lens[s] is below the number of queries, 2 if a bounded wait
+ * expired. head_dim 128 or 256. */
+size_t logismos_paged_prefix_attention_scratch_bytes(int32_t total_kv_tokens, int32_t n_seqs,
+                                                     int32_t n_kv_heads, int32_t head_dim);
+uint32_t logismos_launch_paged_prefix_attention_tc_bf16(
+    const void* q_bf16, int32_t q_row_stride, const void* cu_seqlens_q_i32, const void* kv_lens_i32,
+    const void* k_pool_bf16, const void* v_pool_bf16, const void* block_tables_i32, int32_t max_blocks,
+    int32_t n_pool_blocks, void* out_bf16, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
+    int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads, int32_t n_kv_heads,
+    int32_t head_dim, void* status, void* stream);
+
 /* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
  * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), mask all ones.
  * hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden]; head_b f32 [dim]; out f32
@@ -167,6 +192,12 @@ uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu_se
 uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
                                             const void* x_bf16, void* y_bf16, int32_t batch,
                                             int32_t n, int32_t k, void* stream);
+/* The same product with the fp32 accumulators stored unrounded, y f32 [batch, n]: the lm_head of a
+ * decode step, whose logits go to decode::greedy (crates/decode/src/lib.rs:73-83), which takes the
+ * first strict maximum of fp32 logits (a bf16 rounding would turn near-ties into ties). */
+uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes_u8, const void* scales_f16,
+                                           const void* x_bf16, void* y_f32, int32_t batch, int32_t n,
+                                           int32_t k, void* stream);
 
 /* Expands int4 group-32 weights (same storage as above) to bf16 [n, k]: w = bf16(scale * code).
  * The prefill side of a mixed step runs its contractions on the tcgen05 GEMM over this expansion.
@@ -199,7 +230,9 @@ uint32_t logismos_launch_qlinear_finish_bf16(void* acc_f32, const void* bias_f32
  * For each sequence: the new token's k/v row (new_k / new_v bf16 [n_seqs, n_kv_heads*head_dim])
  * is written at position context_lens[s] - 1 (context_lens counts the new token), then
  * q bf16 [n_seqs, n_heads * head_dim] attends causally to positions 0 .. context_lens[s] - 1.
- * new_k == NULL skips the append. head_dim == 128, n_heads / n_kv_heads <= 16.
+ * new_k == NULL skips the append. head_dim 128 or 256, n_heads / n_kv_heads <= 16. Every
+ * context_lens[s] must be >= 1 (a sequence without a key would get no chunk and its output row
+ * would stay unwritten; logismos_build_decode_chunks rejects such a batch).
  * Work is split along the context in chunks of `chunk_tokens` (a multiple of 64):
  * chunk_offsets i32 [n_seqs + 1] is the exclusive prefix sum of ceil(context_lens / chunk_tokens)
  * and total_chunks its last entry (host copy). scratch must hold
@@ -345,7 +378,8 @@ int64_t logismos_build_packing(const int32_t* host_cached_lens, const int32_t* h
                                int32_t max_blocks, int32_t block_size, int32_t n_pool_blocks,
                                int32_t* host_cu_seqlens, int32_t* host_positions,
                                int64_t* host_slot_mapping, int32_t* host_seq_ids);
-/* chunk_offsets [n+1] for the paged decode kernel; returns total_chunks. */
+/* chunk_offsets [n+1] for the paged decode kernel; returns total_chunks, or -1 if a context length
+ * is below 1 or the chunk count overflows. */
 int32_t logismos_build_decode_chunks(const int32_t* host_context_lens, int32_t n_seqs,
                                      int32_t chunk_tokens, int32_t* host_chunk_offsets);
 /* chunk_tokens for one step's contexts: the largest of 512, 1024, 2048 that leaves the decode launch at

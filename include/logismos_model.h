@@ -83,7 +83,9 @@ uint32_t lg_stella_encode_ids_batch(void* model, const uint32_t* host_ids, const
 /* The same forward with everything already resident: dev_ids u32 [n_tokens], dev_cu_seqlens i32
  * [n_seqs+1], dev_positions i32 [n_tokens] (position of each token inside its sequence),
  * dev_out f32 [n_seqs, dim]. Enqueues on `stream` and returns without synchronising.
- * n_tokens <= max_batch_tokens. causal != 0 runs the decoder-style (causal) variant. */
+ * n_tokens <= max_batch_tokens and n_seqs <= max_batch_seqs (LG_EMB_COMPUTE otherwise); max_seqlen
+ * must be >= the longest sequence of the batch (it sizes the attention grid: queries beyond it are
+ * not computed) and <= max_pos. causal != 0 runs the decoder-style (causal) variant. */
 uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* dev_cu_seqlens,
                                   const void* dev_positions, int32_t n_tokens, int32_t n_seqs,
                                   int32_t max_seqlen, int32_t dim, int32_t causal, void* dev_out, void* stream);
@@ -136,8 +138,10 @@ void lg_decoder_destroy(void* model);
 /* One packed step. Sequence i brings new_lens[i] new tokens (ids packed in sequence order in
  * host_ids) on top of cached_lens[i] tokens already in the paged cache; its block-table row
  * host_block_tables[i, :] must cover cached + new tokens. new_lens[i] == 1 is a decode token,
- * > 1 a prefill chunk, which must start its sequence (cached_lens[i] == 0). All K/V rows of the new
- * tokens are written to the cache; host_next_tokens[i] receives the greedy token after the last
+ * > 1 a prefill chunk, which may start its sequence (cached_lens[i] == 0) or continue it: positions
+ * and cache slots carry on from the cached length and the chunk attends to the cached prefix through
+ * the block table, so a prompt fed in chunks gives the result of the whole prompt fed at once. All
+ * K/V rows of the new tokens are written to the cache; host_next_tokens[i] receives the greedy token after the last
  * new token of sequence i. Synchronises before returning. Status codes as lg_embedding_status. */
 uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* host_cached_lens,
                          const int32_t* host_new_lens, int32_t n_seqs, const int32_t* host_block_tables,
@@ -148,7 +152,7 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* h
 uint32_t lg_decoder_replay_device(void* model, void* stream);
 /* fp32 [n_seqs, hidden]: final-norm output of each sequence's last new token in the last step. */
 uint32_t lg_decoder_last_hidden(void* model, int32_t n_seqs, float* host_out);
-/* bf16 logits of the last step as fp32 [n_seqs, vocab]. */
+/* fp32 logits of the last step [n_seqs, vocab] (the values decode::greedy ran on). */
 uint32_t lg_decoder_last_logits(void* model, int32_t n_seqs, float* host_out);
 int32_t lg_decoder_launches_last_step(const void* model);
 int32_t lg_decoder_device_status(void* model);
@@ -202,7 +206,8 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
 void lg_hybrid_destroy(void* model);
 /* As lg_decoder_step, plus host_state_slots i32 [n_seqs]: the recurrent-state slot of each
  * sequence (distinct within a step, < n_state_slots). A sequence with cached_lens[i] == 0 starts
- * from the zero state; otherwise its slot must hold the state its previous step left. */
+ * from the zero state; otherwise its slot must hold the state its previous step left (decode tokens
+ * and continuing prefill chunks alike). */
 uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* host_cached_lens,
                         const int32_t* host_new_lens, int32_t n_seqs, const int32_t* host_block_tables,
                         const int32_t* host_state_slots, uint32_t* host_next_tokens);

@@ -70,9 +70,12 @@ def _declare(l):
         "logismos_launch_varlen_attention_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp],
         "logismos_launch_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_rope_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_paged_prefix_attention_tc_bf16": [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
+                                                           i32, i32, vp, vp],
         "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_gemv_int4_g32_f32": [vp, vp, vp, vp, i32, i32, i32, vp],
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_qlinear_int4_g32_acc_f32": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_qlinear_finish_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
@@ -122,6 +125,8 @@ def _declare(l):
     l.logismos_paged_decode_scratch_bytes.restype = sz
     l.logismos_varlen_attention_tc_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.logismos_varlen_attention_tc_scratch_bytes.restype = sz
+    l.logismos_paged_prefix_attention_scratch_bytes.argtypes = [i32, i32, i32, i32]
+    l.logismos_paged_prefix_attention_scratch_bytes.restype = sz
     l.logismos_build_packing.argtypes = [vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp]
     l.logismos_build_packing.restype = i64
     l.logismos_build_decode_chunks.argtypes = [vp, i32, i32, vp]

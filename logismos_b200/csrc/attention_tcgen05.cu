@@ -182,11 +182,92 @@ transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// The keys and values of sequences that live in the paged cache, made contiguous for the kernel below:
+// K rows -> kbuf [tp, n_kv * HD] (row = padded key index), V -> vt [n_kv * HD, tp] transposed as above,
+// pstart[s] = padded start of sequence s (every sequence starts at a multiple of 8 keys, padding
+// zeroed). Token t of sequence s is read from block tables[s * max_blocks + t / 16], slot t % 16 of
+// k_pool / v_pool [n_pool_blocks, 16, n_kv * HD] (the row layout of FlatKvCache,
+// crates/cache/src/flat.rs:36-69; the read is KvCache::get, :254-304). A block id outside the pool
+// yields zero rows and raises the status word. Grid (key blocks of 64, kv heads, sequences).
+template <int HD>
+__global__ void __launch_bounds__(256)
+gather_paged_kv_kernel(const __nv_bfloat16* __restrict__ kpool, const __nv_bfloat16* __restrict__ vpool,
+                       const int* __restrict__ tables, int max_blocks, int n_pool_blocks, const int* __restrict__ kv_lens,
+                       __nv_bfloat16* __restrict__ kbuf, __nv_bfloat16* __restrict__ vt, int* __restrict__ pstart, int n_seqs,
+                       int tp, int tx, int n_kv, int* __restrict__ status) {
+  __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
+  constexpr int kParts = 256 / HD, kChunks = HD / 8;
+  __shared__ int p0_s;
+  const int tid = threadIdx.x;
+  const int tb = (int)blockIdx.x % tx, kvh = ((int)blockIdx.x / tx) % n_kv, s = (int)blockIdx.x / (tx * n_kv);
+  if (tid < 32) {
+    int part = 0;
+    for (int i = tid; i < s; i += 32) part += round8(max(kv_lens[i], 0));
+    part += __shfl_xor_sync(0xffffffffu, part, 16);
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    if (tid == 0) p0_s = part;
+  }
+  __syncthreads();
+  const int p0 = p0_s;
+  const int len = max(kv_lens[s], 0), plen = round8(len);
+  const int row_w = n_kv * HD;
+  if (p0 + plen > tp) {  // the caller's total does not cover these lengths: nothing is written
+    if (tid == 0 && status) atomicExch(status, 1);
+    return;
+  }
+  if (tb == 0 && kvh == 0 && tid == 0) pstart[s] = p0;
+  if (tb == 0 && s == n_seqs - 1) {  // rows / columns after the last sequence are read as padding by the last key block
+    const int d = tid / kParts;
+    for (int col = p0 + plen + (tid % kParts) * 8; col + 8 <= tp; col += 8 * kParts)
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + col) = make_uint4(0u, 0u, 0u, 0u);
+    for (int u = tid; u < (tp - p0 - plen) * kChunks; u += 256)
+      *reinterpret_cast<uint4*>(kbuf + (size_t)(p0 + plen + u / kChunks) * row_w + kvh * HD + (u % kChunks) * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (tb * 64 >= plen) return;
+  for (int u = tid; u < 64 * kChunks; u += 256) {
+    const int r = u / kChunks, ch = u % kChunks, t = tb * 64 + r;
+    uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = kq;
+    if (t < len) {
+      const int bi = t >> 4;
+      const int blk = bi < max_blocks ? __ldg(tables + (size_t)s * max_blocks + bi) : -1;
+      if (blk < 0 || blk >= n_pool_blocks) {
+        if (ch == 0 && status) atomicExch(status, 1);
+      } else {
+        const size_t src = ((size_t)blk * 16 + (t & 15)) * row_w + kvh * HD + ch * 8;
+        kq = __ldg(reinterpret_cast<const uint4*>(kpool + src));
+        vq = __ldg(reinterpret_cast<const uint4*>(vpool + src));
+      }
+    }
+    if (t < plen) *reinterpret_cast<uint4*>(kbuf + (size_t)(p0 + t) * row_w + kvh * HD + ch * 8) = kq;
+    *reinterpret_cast<uint4*>(&tile[r][ch * 8]) = vq;
+  }
+  __syncthreads();
+  const int d = tid / kParts, half = tid % kParts;
+#pragma unroll
+  for (int g8 = 0; g8 < 8 / kParts; ++g8) {
+    const int tl = half * (64 / kParts) + g8 * 8;
+    if (tb * 64 + tl < plen) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t lo = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i][d]);
+        const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i + 1][d]);
+        w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + p0 + tb * 64 + tl) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 template <bool CAUSAL, int HD>
 __global__ void __launch_bounds__(192, HD == 128 ? 2 : 1)
-attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_vt,
-                    const int* __restrict__ cu, const int* __restrict__ pstart, __nv_bfloat16* __restrict__ out,
-                    int n_heads, int n_kv, int k_off, float sl2, int* __restrict__ status) {
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ cu, const int* __restrict__ pstart,
+                    const int* __restrict__ kv_lens, __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int k_off,
+                    float sl2, int* __restrict__ status) {
   using C = Attn<HD>;
   constexpr int kQBytes = C::kQBytes, kKBytes = C::kKBytes, kVBytes = C::kVBytes, kVTile = C::kVTile;
   constexpr uint32_t kTmemCols = C::kTmemCols;
@@ -194,8 +275,18 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
   const int s = blockIdx.z, h = blockIdx.y, q0 = (CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * 128;
   const int t0 = cu[s], len = cu[s + 1] - t0;
   if (q0 >= len) return;  // before any barrier or TMEM allocation
+  // kv_lens == nullptr: the keys are the sequence's own token rows (map_k is map_q). Otherwise the
+  // sequence has kv_lens[s] >= len keys in a gathered buffer whose rows start at pstart[s] (the cached
+  // prefix followed by the new tokens), and query i stands at position kv_lens[s] - len + i.
+  const int kv_total = kv_lens ? kv_lens[s] : len;
+  const int q_off = kv_total - len;
+  if (q_off < 0) {  // fewer keys than queries: not a causal continuation
+    if (threadIdx.x == 0 && status) atomicExch(status, 1);
+    return;
+  }
+  const int k_row0 = kv_lens ? pstart[s] : t0;
   const int kvh = h / (n_heads / n_kv);
-  const int kv_len = CAUSAL ? min(len, q0 + 128) : len;
+  const int kv_len = CAUSAL ? min(kv_total, q_off + q0 + 128) : kv_total;
   const int nb = (kv_len + 127) >> 7;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -231,14 +322,14 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
     if (lane == 0) {
       mbar_expect_tx(q_full, (uint32_t)kQBytes);
 #pragma unroll
-      for (int i = 0; i < HD / 64; ++i) tma_load_2d(q_smem + i * kTileBytes, &map_qk, q_full, h * HD + i * 64, t0 + q0);
+      for (int i = 0; i < HD / 64; ++i) tma_load_2d(q_smem + i * kTileBytes, &map_q, q_full, h * HD + i * 64, t0 + q0);
       const int pv = pstart[s];
       for (int j = 0; j < nb; ++j) {
         const uint32_t phase = (uint32_t)j & 1u;
         if (!mbar_wait(k_empty, phase ^ 1u, abort_flag)) break;
         mbar_expect_tx(k_full, (uint32_t)kKBytes);
 #pragma unroll
-        for (int i = 0; i < HD / 64; ++i) tma_load_2d(k_smem + i * kTileBytes, &map_qk, k_full, k_off + kvh * HD + i * 64, t0 + j * 128);
+        for (int i = 0; i < HD / 64; ++i) tma_load_2d(k_smem + i * kTileBytes, &map_k, k_full, k_off + kvh * HD + i * 64, k_row0 + j * 128);
         if (!mbar_wait(v_empty, phase ^ 1u, abort_flag)) break;
         mbar_expect_tx(v_full, (uint32_t)kVBytes);
         tma_load_2d(v_smem, &map_vt, v_full, pv + j * 128, kvh * HD);
@@ -289,7 +380,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
       tc_fence_after();
       // keys this row may see in this block: [0, lim)
       int lim = kv_len - j * 128;
-      if (CAUSAL) lim = min(lim, q0 + row + 1 - j * 128);
+      if (CAUSAL) lim = min(lim, q_off + q0 + row + 1 - j * 128);
       const bool full = lim >= 128;
       float mx = -1e30f;
 #pragma unroll
@@ -460,8 +551,8 @@ static uint32_t launch_attn_tc(const void* qkv, const void* cu_seqlens, void* ou
   auto launch = [&](auto kern, size_t smem) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, 192, smem, s>>>(map_qk, map_vt, (const int*)cu_seqlens, pstart, (__nv_bfloat16*)out, n_heads,
-                                 n_kv_heads, k_off, sl2, (int*)status);
+    kern<<<grid, 192, smem, s>>>(map_qk, map_qk, map_vt, (const int*)cu_seqlens, pstart, (const int*)nullptr, (__nv_bfloat16*)out,
+                                 n_heads, n_kv_heads, k_off, sl2, (int*)status);
     return lg::launch_status();
   };
   if (D == 128) return causal ? launch(attn_tcgen05_kernel<true, 128>, Attn<128>::kSmem) : launch(attn_tcgen05_kernel<false, 128>, Attn<128>::kSmem);
@@ -489,6 +580,67 @@ uint32_t logismos_launch_rope_varlen_attention_tc_bf16(void* qkv, const void* co
              (int*)status};
   return launch_attn_tc(qkv, cu_seqlens, out, scratch, n_tokens, n_seqs, max_seqlen, n_heads, n_kv_heads, head_dim, row_stride,
                         k_off, v_off, causal, r, status, stream);
+}
+
+size_t logismos_paged_prefix_attention_scratch_bytes(int32_t total_kv_tokens, int32_t n_seqs, int32_t n_kv_heads, int32_t head_dim) {
+  if (total_kv_tokens < 0 || n_seqs < 0 || n_kv_heads <= 0 || (head_dim != 128 && head_dim != 256)) return 0;
+  return pstart_bytes(n_seqs) + 2 * (size_t)n_kv_heads * head_dim * (size_t)padded_tokens(total_kv_tokens, n_seqs) * 2;
+}
+
+uint32_t logismos_launch_paged_prefix_attention_tc_bf16(const void* q, int32_t q_row_stride, const void* cu_seqlens_q,
+                                                        const void* kv_lens, const void* k_pool, const void* v_pool,
+                                                        const void* block_tables, int32_t max_blocks, int32_t n_pool_blocks,
+                                                        void* out, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
+                                                        int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads,
+                                                        int32_t n_kv_heads, int32_t head_dim, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  const int D = head_dim;
+  if (n_q_tokens < 0 || total_kv_tokens < 0 || n_seqs < 0 || max_q_len < 0 || max_kv_len < 0 || max_blocks <= 0 ||
+      n_pool_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || (D != 128 && D != 256) || (n_heads % n_kv_heads) ||
+      (q_row_stride % 8) || n_heads * D > q_row_stride || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || !scratch || ((uintptr_t)scratch & 255) || !kv_lens ||
+      !block_tables || max_kv_len > total_kv_tokens)
+    return lg::kInvalidValue;
+  if (n_seqs == 0 || max_q_len == 0 || n_q_tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int tp = padded_tokens(total_kv_tokens, n_seqs);
+  const int row_w = n_kv_heads * D;
+  int* pstart = (int*)scratch;
+  __nv_bfloat16* vt = (__nv_bfloat16*)((uint8_t*)scratch + pstart_bytes(n_seqs));
+  __nv_bfloat16* kbuf = vt + (size_t)row_w * tp;
+  CUtensorMap map_q, map_k, map_vt;
+  if (!make_map(&map_q, q, (uint64_t)n_q_tokens, (uint64_t)q_row_stride, (uint64_t)q_row_stride, 128) ||
+      !make_map(&map_k, kbuf, (uint64_t)tp, (uint64_t)row_w, (uint64_t)row_w, 128) ||
+      !make_map(&map_vt, vt, (uint64_t)row_w, (uint64_t)tp, (uint64_t)tp, (uint32_t)D))
+    return lg::kInvalidValue;
+  const int tx = (((max_kv_len + 7) & ~7) + 63) / 64;
+  const int64_t blocks = (int64_t)tx * n_kv_heads * n_seqs;
+  if (blocks > 0x7fffffff) return lg::kInvalidValue;
+  if (blocks > 0) {
+    if (D == 128)
+      gather_paged_kv_kernel<128><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                                                                   (const int*)block_tables, max_blocks, n_pool_blocks,
+                                                                   (const int*)kv_lens, kbuf, vt, pstart, n_seqs, tp, tx,
+                                                                   n_kv_heads, (int*)status);
+    else
+      gather_paged_kv_kernel<256><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                                                                   (const int*)block_tables, max_blocks, n_pool_blocks,
+                                                                   (const int*)kv_lens, kbuf, vt, pstart, n_seqs, tp, tx,
+                                                                   n_kv_heads, (int*)status);
+    uint32_t rc = lg::launch_status();
+    if (rc) return rc;
+  }
+  const float sl2 = 1.4426950408889634f / sqrtf((float)D);
+  dim3 grid((max_q_len + 127) / 128, n_heads, n_seqs);
+  auto launch = [&](auto kern, size_t smem) -> uint32_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (uint32_t)e;
+    kern<<<grid, 192, smem, s>>>(map_q, map_k, map_vt, (const int*)cu_seqlens_q, pstart, (const int*)kv_lens, (__nv_bfloat16*)out,
+                                 n_heads, n_kv_heads, 0, sl2, (int*)status);
+    return lg::launch_status();
+  };
+  if (D == 128) return launch(attn_tcgen05_kernel<true, 128>, Attn<128>::kSmem);
+  return launch(attn_tcgen05_kernel<true, 256>, Attn<256>::kSmem);
 }
 
 }  // extern "C"

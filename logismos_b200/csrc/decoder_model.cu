@@ -8,7 +8,9 @@
 // A step packs decode tokens (one per sequence) first and prefill chunks after them:
 //   embed -> per layer [ rms_norm -> QKV (int4 weights) + bias -> RoPE at each token's position ->
 //   K/V rows scattered into the paged cache by slot mapping -> attention: paged decode kernel for
-//   the decode rows, ragged causal attention for the prefill rows -> o_proj + residual ->
+//   the decode rows, ragged causal attention for the prefill rows (over the chunk's own rows when every
+//   chunk starts its sequence, else over keys and values gathered from the cache through the block
+//   tables, so a chunk may continue a cached sequence) -> o_proj + residual ->
 //   rms_norm -> gate/up with SwiGLU fused in the GEMM epilogue -> down + residual ] -> last token rows -> final norm ->
 //   lm_head (int4 GEMV) -> greedy argmax.
 // Contractions over the packed rows run on the tcgen05 GEMM over a per-layer bf16 expansion of the
@@ -47,7 +49,7 @@ struct Decoder {
   std::vector<DLayer> layers;
   // workspace
   Buf x, h, qkv, attn, qdec, gu, act, wscratch, accws, last, last_bf16, logits, tokens, status;
-  Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws;
+  Buf ids, pos, slots, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, pre_kv;
   // pinned staging (one block)
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
@@ -57,6 +59,16 @@ struct Decoder {
   int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, pre_tokens = 0, max_pre_len = 0, total_chunks = 0, chunk_tokens = kChunkTokens, launches = 0, logits_f32 = 0;
   std::vector<int> order;  // internal slot -> caller's sequence index
   size_t max_chunks = 0;
+  // the fused int4 linears rely on `accws` being all zero between calls, which their finishing kernels
+  // restore; a step that failed part-way may have left partial sums there, so the next one clears it
+  bool acc_dirty = false;
+  size_t accws_bytes = 0;
+  // prefill chunks that continue cached sequences: runs of prefill sequences whose keys fit the gather
+  // workspace together (one gather + attention launch pair per run)
+  struct PrefixRun { int s0, s1, total_kv, max_q, max_kv; };
+  std::vector<PrefixRun> prefix_runs;
+  bool pre_has_prefix = false;
+  size_t prefix_cap_tokens = 0;
 };
 
 uint32_t qlinear(Decoder* m, const void* a, const QMat& w, const void* bias, void* out, int T, int lda, int ldc,
@@ -70,6 +82,10 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
   const int H = c.hidden, I = c.intermediate, D = m->head_dim, QKV = m->qkv_dim, KV = m->kv_dim, T = m->T;
   void* st = m->status.p;
   m->launches = 0;
+  if (m->acc_dirty) {
+    LG_TRY(cudaMemsetAsync(m->accws.p, 0, m->accws_bytes, s), "clear accumulation workspace");
+    m->acc_dirty = false;
+  }
   LG_TRY(logismos_launch_embed_lookup_bf16(m->tok_embed.p, m->ids.p, m->x.p, T, H, c.vocab, s), "embed_lookup");
   m->launches += 1;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -92,19 +108,25 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
                                                          c.n_heads, c.n_kv_heads, D, s), "paged_attention_decode");
       m->launches += 2;
     }
-    if (m->n_pre > 0) {
-      if (D == 128) {  // tcgen05 kernel; V transposed into attn_ws first
-        LG_TRY(logismos_launch_varlen_attention_tc_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
-                                                        (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->attn_ws.p, T - m->n_dec,
-                                                        m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, st, s),
-               "varlen_attention");
+    if (m->n_pre > 0 && m->pre_has_prefix) {
+      // some chunk continues a cached sequence: keys and values come from the cache (the chunk's own rows
+      // were stored above), gathered per run of sequences into attn_ws
+      const int32_t* tabs = (const int32_t*)m->dec_tables.p + (size_t)m->n_dec * c.max_blocks_per_seq;
+      for (const Decoder::PrefixRun& r : m->prefix_runs) {
+        LG_TRY(logismos_launch_paged_prefix_attention_tc_bf16(
+                   qkv16 + (size_t)m->n_dec * QKV, QKV, (const int32_t*)m->cu_prefill.p + r.s0, (const int32_t*)m->pre_kv.p + r.s0,
+                   L.kpool.p, L.vpool.p, tabs + (size_t)r.s0 * c.max_blocks_per_seq, c.max_blocks_per_seq, c.n_pool_blocks,
+                   (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->attn_ws.p, T - m->n_dec, r.total_kv, r.s1 - r.s0, r.max_q, r.max_kv,
+                   c.n_heads, c.n_kv_heads, D, st, s),
+               "paged_prefix_attention");
         m->launches += 2;
-      } else {
-        LG_TRY(logismos_launch_varlen_attention_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
-                                                     (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->n_pre, m->max_pre_len,
-                                                     c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, s), "varlen_attention");
-        m->launches += 1;
       }
+    } else if (m->n_pre > 0) {  // tcgen05 kernel; V transposed into attn_ws first
+      LG_TRY(logismos_launch_varlen_attention_tc_bf16(qkv16 + (size_t)m->n_dec * QKV, m->cu_prefill.p,
+                                                      (uint16_t*)m->attn.p + (size_t)m->n_dec * H, m->attn_ws.p, T - m->n_dec,
+                                                      m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, st, s),
+             "varlen_attention");
+      m->launches += 2;
     }
     if (uint32_t rc = qlinear(m, m->attn.p, L.wo, nullptr, m->x.p, T, H, H, LG_EPI_RESID_F32, s)) return rc;
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
@@ -197,12 +219,21 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
        m->last.alloc(S * H * 4) && m->last_bf16.alloc(S * H * 2) && m->logits.alloc(S * (size_t)c.vocab * 4) && m->accws.alloc((size_t)kFusedDequantMaxRows * acc_n * 4) &&
        m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) && m->pos.alloc(T * 4) && m->slots.alloc(T * 8) &&
        m->cu_prefill.alloc((S + 1) * 4) && m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) &&
-       m->dec_chunks.alloc((S + 1) * 4) &&
-       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim)) &&
-       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads, 128));
+       m->dec_chunks.alloc((S + 1) * 4) && m->pre_kv.alloc(S * 4) &&
+       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, m->head_dim));
+  {
+    // the attention workspace serves both prefill routes; the gather route holds one run of sequences at
+    // a time, and any single sequence (at most a full block table) must fit
+    m->prefix_cap_tokens = MB * kBlock > T ? MB * kBlock : T;
+    size_t ws = logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads, 128);
+    const size_t ws2 = logismos_paged_prefix_attention_scratch_bytes((int32_t)m->prefix_cap_tokens, (int32_t)S, c.n_kv_heads, 128);
+    if (ws2 > ws) ws = ws2;
+    ok = ok && m->attn_ws.alloc(ws);
+  }
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
-  ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
-  m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4;
+  m->accws_bytes = (size_t)kFusedDequantMaxRows * acc_n * 4;
+  ok = ok && cudaMemset(m->accws.p, 0, m->accws_bytes) == cudaSuccess;
+  m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4;
   ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
   if (!ok) {
@@ -220,7 +251,7 @@ void lg_decoder_destroy(void* model) {
   cudaSetDevice(m->device);
   Buf* bufs[] = {&m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->qkv,
                  &m->attn, &m->qdec, &m->gu, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens, &m->status,
-                 &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch, &m->attn_ws};
+                 &m->ids, &m->pos, &m->slots, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables, &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->pre_kv};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.bqkv, &L.kpool, &L.vpool, &L.wqkv.codes, &L.wqkv.scales, &L.wo.codes, &L.wo.scales,
@@ -249,7 +280,6 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   int64_t off = 0, total = 0;
   for (int i = 0; i < n_seqs; ++i) {
     if (newl[i] <= 0 || cached[i] < 0) { set_error("lg_decoder_step: every sequence needs >= 1 new token"); return LG_EMB_COMPUTE; }
-    if (newl[i] > 1 && cached[i] != 0) { set_error("lg_decoder_step: a prefill chunk must start its sequence (cached_len == 0)"); return LG_EMB_COMPUTE; }
     if ((int64_t)cached[i] + newl[i] > c.max_pos || (int64_t)cached[i] + newl[i] > (int64_t)MB * kBlock) {
       set_error("lg_decoder_step: sequence exceeds max_pos or its block table");
       return LG_EMB_INPUT_TOO_LONG;
@@ -273,7 +303,8 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   int32_t* h_last = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
   int32_t* h_chunks = (int32_t*)pp; pp += (size_t)(n_seqs + 1) * 4;
   int32_t* h_tables = (int32_t*)pp; pp += (size_t)n_seqs * MB * 4;
-  int32_t* h_ctx = (int32_t*)pp;
+  int32_t* h_ctx = (int32_t*)pp; pp += (size_t)n_seqs * 4;
+  int32_t* h_prekv = (int32_t*)pp;
   std::vector<int32_t> o_cached(n_seqs), o_new(n_seqs), o_seqids((size_t)total);
   int64_t t = 0;
   for (int s = 0; s < n_seqs; ++s) {
@@ -288,20 +319,37 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
                                                h_pos, h_slots, o_seqids.data());
   if (built != total) { set_error("lg_decoder_step: a block table entry is missing or outside the pool"); return LG_EMB_COMPUTE; }
   int max_pre = 0;
+  bool has_prefix = false;
   h_cu_pre[0] = 0;
   for (int s = 0; s < n_seqs; ++s) {
     h_last[s] = h_cu[s + 1] - 1;
     if (s < n_dec) h_ctx[s] = o_cached[s] + 1;
     else {
       h_cu_pre[s - n_dec + 1] = h_cu[s + 1] - n_dec;
+      h_prekv[s - n_dec] = o_cached[s] + o_new[s];
+      if (o_cached[s] > 0) has_prefix = true;
       if (o_new[s] > max_pre) max_pre = o_new[s];
     }
+  }
+  std::vector<Decoder::PrefixRun> runs;
+  if (has_prefix) {
+    Decoder::PrefixRun r{0, 0, 0, 0, 0};
+    for (int k = 0; k < n_pre; ++k) {
+      const int kv = h_prekv[k], q = o_new[n_dec + k];
+      if (r.s1 > r.s0 && (size_t)r.total_kv + kv > m->prefix_cap_tokens) { runs.push_back(r); r = Decoder::PrefixRun{k, k, 0, 0, 0}; }
+      r.s1 = k + 1; r.total_kv += kv;
+      if (q > r.max_q) r.max_q = q;
+      if (kv > r.max_kv) r.max_kv = kv;
+    }
+    runs.push_back(r);
   }
   m->chunk_tokens = n_dec > 0 ? logismos_pick_decode_chunk(h_ctx, n_dec, m->cfg.n_kv_heads, m->head_dim) : kChunkTokens;
   const int total_chunks = n_dec > 0 ? logismos_build_decode_chunks(h_ctx, n_dec, m->chunk_tokens, h_chunks) : 0;
   if (total_chunks < 0 || (size_t)total_chunks > m->max_chunks) { set_error("lg_decoder_step: decode chunk count exceeds the scratch"); return LG_EMB_COMPUTE; }
   m->T = (int)total; m->n_dec = n_dec; m->n_pre = n_pre; m->n_seqs = n_seqs; m->max_pre_len = max_pre; m->total_chunks = total_chunks;
   m->order = order;
+  m->pre_has_prefix = has_prefix;
+  m->prefix_runs = runs;
   cudaStream_t s = m->stream;
   LG_TRY(cudaMemcpyAsync(m->ids.p, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D ids");
   LG_TRY(cudaMemcpyAsync(m->pos.p, h_pos, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D positions");
@@ -310,15 +358,21 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   LG_TRY(cudaMemcpyAsync(m->last_idx.p, h_last, (size_t)n_seqs * 4, cudaMemcpyHostToDevice, s), "H2D last rows");
   if (n_dec > 0) {
     LG_TRY(cudaMemcpyAsync(m->dec_ctx.p, h_ctx, (size_t)n_dec * 4, cudaMemcpyHostToDevice, s), "H2D context lens");
-    LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)n_dec * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
     LG_TRY(cudaMemcpyAsync(m->dec_chunks.p, h_chunks, (size_t)(n_dec + 1) * 4, cudaMemcpyHostToDevice, s), "H2D chunk offsets");
   }
-  if (uint32_t rc = run_device(m, s)) return rc;
+  if (n_dec > 0 || has_prefix)  // block tables in packed order: decode rows first, prefill rows after them
+    LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)(has_prefix ? n_seqs : n_dec) * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
+  if (has_prefix) LG_TRY(cudaMemcpyAsync(m->pre_kv.p, h_prekv, (size_t)n_pre * 4, cudaMemcpyHostToDevice, s), "H2D prefill key counts");
+  if (uint32_t rc = run_device(m, s)) { m->acc_dirty = true; return rc; }
   std::vector<uint32_t> toks(n_seqs);
   LG_TRY(cudaMemcpyAsync(toks.data(), m->tokens.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, s), "D2H tokens");
   LG_TRY(cudaStreamSynchronize(s), "stream synchronize");
   for (int k = 0; k < n_seqs; ++k) next_tokens[order[k]] = toks[k];
-  if (lg_decoder_device_status(m) != 0) { set_error("a device-side range check or bounded wait failed"); return LG_EMB_COMPUTE; }
+  if (lg_decoder_device_status(m) != 0) {
+    m->acc_dirty = true;
+    set_error("a device-side range check or bounded wait failed");
+    return LG_EMB_COMPUTE;
+  }
   return LG_EMB_OK;
 }
 

@@ -74,6 +74,12 @@ LG_DEVINL float stage_unit(uint4 raw, uint4& out) {
   return 136.0f * lo + 1152.0f * hi;
 }
 
+// y is bf16 [batch, N], or fp32 when the caller keeps full precision up to an argmax
+LG_DEVINL void store_y(void* y, int out_f32, size_t idx, float v) {
+  if (out_f32) reinterpret_cast<float*>(y)[idx] = v;
+  else reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(v);
+}
+
 struct Frag {
   uint32_t w0[4], w1[4];  // word c of groups G0..G0+3 for rows g and g+8
   uint2 s0, s1;           // 4 fp16 scales each
@@ -94,7 +100,7 @@ LG_DEVINL void load_frag(Frag& f, const uint8_t* p0, const uint8_t* p1, const __
 template <int NT>
 __global__ void __launch_bounds__(256)
 gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
-                     const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                     const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                      int N, int K, int kc, int rt, int ks) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -207,12 +213,12 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
       const int b0 = nt * 8 + 2 * c;
       const int ra = row_base + g, rb = row_base + g + 8;
       if (ra < N) {
-        if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(v[0]);
-        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(v[1]);
+        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, v[0]);
+        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, v[1]);
       }
       if (rb < N) {
-        if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(v[2]);
-        if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(v[3]);
+        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, v[2]);
+        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, v[3]);
       }
     }
   }
@@ -237,7 +243,7 @@ __host__ __device__ constexpr int slot_bytes(int rt) { return rt * (16 * kWPitch
 template <int NT, int STAGES, int RT>
 __global__ void __launch_bounds__(STAGES == 8 ? 256 : (RT == 2 ? 384 : (NT <= 2 ? 768 : 512)))
 gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
-                            const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                            const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                             int N, int K) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int kSlot = slot_bytes(RT);
@@ -401,12 +407,12 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
       for (int nt = 0; nt < NT; ++nt) {
         const int b0 = nt * 8 + 2 * c;
         if (ra < N) {
-          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[r][nt][0]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[r][nt][1]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0]);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1]);
         }
         if (rb < N) {
-          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[r][nt][2]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[r][nt][3]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2]);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3]);
         }
       }
     }
@@ -429,7 +435,7 @@ template <int KS> struct Wide {
 template <int NT, int STAGES, int KS>
 __global__ void __launch_bounds__(384)
 gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
-                          const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int batch,
+                          const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                           int N, int K) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int kWidePitch = Wide<KS>::kPitch, kSPitch = Wide<KS>::kSPitch, kWideSlot = Wide<KS>::kSlot;
@@ -601,12 +607,12 @@ gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __res
       for (int nt = 0; nt < NT; ++nt) {
         const int b0 = nt * 8 + 2 * c;
         if (ra < N) {
-          if (b0 < batch) y[(size_t)b0 * N + ra] = __float2bfloat16_rn(acc[r][nt][0]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + ra] = __float2bfloat16_rn(acc[r][nt][1]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0]);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1]);
         }
         if (rb < N) {
-          if (b0 < batch) y[(size_t)b0 * N + rb] = __float2bfloat16_rn(acc[r][nt][2]);
-          if (b0 + 1 < batch) y[(size_t)(b0 + 1) * N + rb] = __float2bfloat16_rn(acc[r][nt][3]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2]);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3]);
         }
       }
     }
@@ -625,13 +631,13 @@ int gemv_sm_count() {
 }
 
 template <int NT, int STAGES, int RT>
-uint32_t launch_stream(const void* codes, const void* scales, const void* x, void* y, int batch, int N, int K,
+uint32_t launch_stream(const void* codes, const void* scales, const void* x, void* y, int out_f32, int batch, int N, int K,
                        int grid, int warps, size_t smem, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, STAGES, RT>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (uint32_t)e;
   gemv_int4_g32_stream_kernel<NT, STAGES, RT><<<grid, warps * 32, smem, stream>>>(
-      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, batch, N, K);
+      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, y, out_f32, batch, N, K);
   return lg::launch_status();
 }
 
@@ -651,7 +657,7 @@ int best_warp_count(int row_tiles, int sms, int lo, int hi) {
 
 // Returns true (and the status in *rc) when the streaming variant applies and was launched.
 template <int NT>
-bool try_launch_stream(const void* codes, const void* scales, const void* x, void* y, int batch, int N, int K,
+bool try_launch_stream(const void* codes, const void* scales, const void* x, void* y, int out_f32, int batch, int N, int K,
                        cudaStream_t stream, uint32_t* rc) {
   const int sms = gemv_sm_count();
   const int row_tiles = (N + 15) / 16;
@@ -665,7 +671,7 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
     warps = warps < 2 ? 2 : warps;
     while (xbytes + (size_t)warps * 8 * slot_bytes(1) > budget) --warps;
     const int grid = (row_tiles + warps - 1) / warps < sms ? (row_tiles + warps - 1) / warps : sms;
-    *rc = launch_stream<NT, 8, 1>(codes, scales, x, y, batch, N, K, grid, warps, xbytes + (size_t)warps * 8 * slot_bytes(1), stream);
+    *rc = launch_stream<NT, 8, 1>(codes, scales, x, y, out_f32, batch, N, K, grid, warps, xbytes + (size_t)warps * 8 * slot_bytes(1), stream);
     return true;
   }
   // Up to 16 batch rows a warp carries two row tiles side by side (fewer instructions per weight);
@@ -687,7 +693,7 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
       if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
       kern<<<sms, warps * 32, wsmem, stream>>>((const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x,
-                                               (__nv_bfloat16*)y, batch, N, K);
+                                               y, out_f32, batch, N, K);
       *rc = lg::launch_status();
       return true;
     }
@@ -696,19 +702,19 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
   if constexpr (NT <= 2) {
     if (rt == 2) {
       // three ring slots measured best with two tiles per warp (28.6 us against 28.9 with four, 29.9 with two)
-      *rc = launch_stream<NT, 3, 2>(codes, scales, x, y, batch, N, K, sms, warps, xbytes + (size_t)warps * 3 * slot_bytes(2), stream);
+      *rc = launch_stream<NT, 3, 2>(codes, scales, x, y, out_f32, batch, N, K, sms, warps, xbytes + (size_t)warps * 3 * slot_bytes(2), stream);
       return true;
     }
   }
-  *rc = launch_stream<NT, 4, 1>(codes, scales, x, y, batch, N, K, sms, warps, smem, stream);
+  *rc = launch_stream<NT, 4, 1>(codes, scales, x, y, out_f32, batch, N, K, sms, warps, smem, stream);
   return true;
 }
 
 template <int NT>
-uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y, int batch, int N,
+uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y, int out_f32, int batch, int N,
                    int K, cudaStream_t stream) {
   uint32_t src = 0;
-  if (try_launch_stream<NT>(codes, scales, x, y, batch, N, K, stream, &src)) return src;
+  if (try_launch_stream<NT>(codes, scales, x, y, out_f32, batch, N, K, stream, &src)) return src;
   const int iters_k = K / kIterK;
   int kc = 4096 / NT;  // x chunk staged per pass: NT * 8 rows * kc * 2 B  (<= 64 KB)
   if (kc > K) kc = K;
@@ -730,25 +736,37 @@ uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y
   }
   const int grid = (row_tiles + rt - 1) / rt;
   gemv_int4_g32_kernel<NT><<<grid, threads, smem, stream>>>(
-      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+      (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, y, out_f32,
       batch, N, K, kc, rt, ks);
   return lg::launch_status();
 }
 
 }  // namespace
 
-extern "C" uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes, const void* scales_f16,
-                                                       const void* x_bf16, void* y_bf16,
-                                                       int32_t batch, int32_t n, int32_t k,
-                                                       void* stream) {
-  lg::LaunchScope launch_scope_;
+static uint32_t launch_gemv(const void* codes, const void* scales_f16, const void* x_bf16, void* y, int out_f32, int32_t batch,
+                            int32_t n, int32_t k, void* stream) {
   if (batch <= 0 || batch > 64 || n <= 0 || k <= 0 || (k % kIterK) != 0) return lg::kInvalidValue;
   if (((uintptr_t)codes & 15) || ((uintptr_t)scales_f16 & 7) || ((uintptr_t)x_bf16 & 15))
     return lg::kInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   const int nt = (batch + 7) / 8;
-  if (nt == 1) return launch_nt<1>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
-  if (nt == 2) return launch_nt<2>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
-  if (nt <= 4) return launch_nt<4>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
-  return launch_nt<8>(codes, scales_f16, x_bf16, y_bf16, batch, n, k, s);
+  if (nt == 1) return launch_nt<1>(codes, scales_f16, x_bf16, y, out_f32, batch, n, k, s);
+  if (nt == 2) return launch_nt<2>(codes, scales_f16, x_bf16, y, out_f32, batch, n, k, s);
+  if (nt <= 4) return launch_nt<4>(codes, scales_f16, x_bf16, y, out_f32, batch, n, k, s);
+  return launch_nt<8>(codes, scales_f16, x_bf16, y, out_f32, batch, n, k, s);
+}
+
+extern "C" uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes, const void* scales_f16,
+                                                       const void* x_bf16, void* y_bf16,
+                                                       int32_t batch, int32_t n, int32_t k,
+                                                       void* stream) {
+  lg::LaunchScope launch_scope_;
+  return launch_gemv(codes, scales_f16, x_bf16, y_bf16, 0, batch, n, k, stream);
+}
+
+extern "C" uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes, const void* scales_f16,
+                                                      const void* x_bf16, void* y_f32, int32_t batch,
+                                                      int32_t n, int32_t k, void* stream) {
+  lg::LaunchScope launch_scope_;
+  return launch_gemv(codes, scales_f16, x_bf16, y_f32, 1, batch, n, k, stream);
 }

@@ -6,12 +6,15 @@
 // formulas are those of research/14-gdn-aiter-preflight.md:190-198, :209-219, and the contract is
 // "a packed step equals running every sequence alone".
 //
-// A step packs decode tokens (one per sequence) first and whole-prompt prefills after them:
+// A step packs decode tokens (one per sequence) first and prefill chunks after them (a chunk may start its
+// sequence or continue it: positions, cache slots and the recurrent state carry on from the cached length):
 //   embed -> per layer [ rms_norm -> mixer -> residual -> rms_norm -> gate/up + SwiGLU -> down +
 //   residual ] -> last token rows -> final norm -> lm_head (int4 GEMV) -> greedy argmax
 //   full-attention mixer: one GEMM to q | k | v | gate columns; RoPE on q and k; K/V rows scattered
 //     into the paged cache; paged decode kernel for the decode rows, ragged causal attention for the
-//     prefill rows; out *= sigmoid(gate); o_proj accumulates into the fp32 residual
+//     prefill rows (over the chunk's own rows when every chunk starts its sequence, else over keys and
+//     values gathered from the cache through the block tables); out *= sigmoid(gate); o_proj
+//     accumulates into the fp32 residual
 //   linear-attention mixer: one GEMM to q | k | v | z columns, one to fp32 a | b columns; L2 norm of
 //     q, k and the fp32 gates; the recurrence over every sequence's new tokens against its state
 //     slot (a decode token is a sequence of one token); out *= silu(z); out_proj accumulates into
@@ -54,7 +57,7 @@ struct Hybrid {
   lg_allreduce_f32_fn allreduce = nullptr;
   void* allreduce_user = nullptr;
   Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
-  Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh;
+  Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh, pre_kv;
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
   cudaStream_t stream = nullptr;
@@ -62,6 +65,16 @@ struct Hybrid {
   int T = 0, n_dec = 0, n_pre = 0, n_seqs = 0, max_pre_len = 0, total_chunks = 0, chunk_tokens = kChunkTokens, launches = 0, logits_f32 = 0;
   std::vector<int> order;
   size_t max_chunks = 0;
+  // the fused int4 linears rely on `accws` being all zero between calls, which their finishing kernels
+  // restore; a step that failed part-way may have left partial sums there, so the next one clears it
+  bool acc_dirty = false;
+  size_t accws_bytes = 0;
+  // prefill chunks that continue cached sequences: runs of prefill sequences whose keys fit the gather
+  // workspace together (one gather + attention launch pair per run)
+  struct PrefixRun { int s0, s1, total_kv, max_q, max_kv; };
+  std::vector<PrefixRun> prefix_runs;
+  bool pre_has_prefix = false;
+  size_t prefix_cap_tokens = 0;
 };
 
 uint32_t qlinear(Hybrid* m, const void* a, const QMat& w, void* out, int T, int lda, int ldc, int epi, cudaStream_t s) {
@@ -91,6 +104,10 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
   const int GW = m->gw, GN = m->gdn_n, GH = c.gdn_heads;
   void* st = m->status.p;
   m->launches = 0;
+  if (m->acc_dirty) {
+    LG_TRY(cudaMemsetAsync(m->accws.p, 0, m->accws_bytes, s), "clear accumulation workspace");
+    m->acc_dirty = false;
+  }
   LG_TRY(logismos_launch_embed_lookup_bf16(m->tok_embed.p, m->ids.p, m->x.p, T, H, c.vocab, s), "embed_lookup");
   m->launches += 1;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -115,7 +132,20 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
                                                            c.n_heads, c.n_kv_heads, D, s), "paged_attention_decode");
         m->launches += 2;
       }
-      if (m->n_pre > 0) {
+      if (m->n_pre > 0 && m->pre_has_prefix) {
+        // some chunk continues a cached sequence: keys and values come from the cache (the chunk's own rows
+        // were stored above), gathered per run of sequences into attn_ws
+        const int32_t* tabs = (const int32_t*)m->dec_tables.p + (size_t)m->n_dec * c.max_blocks_per_seq;
+        for (const Hybrid::PrefixRun& r : m->prefix_runs) {
+          LG_TRY(logismos_launch_paged_prefix_attention_tc_bf16(
+                     p16 + (size_t)m->n_dec * AN, AN, (const int32_t*)m->cu_prefill.p + r.s0, (const int32_t*)m->pre_kv.p + r.s0,
+                     L.kpool.p, L.vpool.p, tabs + (size_t)r.s0 * c.max_blocks_per_seq, c.max_blocks_per_seq, c.n_pool_blocks,
+                     (uint16_t*)m->mix.p + (size_t)m->n_dec * QW, m->attn_ws.p, T - m->n_dec, r.total_kv, r.s1 - r.s0, r.max_q,
+                     r.max_kv, c.n_heads, c.n_kv_heads, D, st, s),
+                 "paged_prefix_attention");
+          m->launches += 2;
+        }
+      } else if (m->n_pre > 0) {
         // tcgen05 kernel; V transposed into attn_ws first
         LG_TRY(logismos_launch_varlen_attention_tc_bf16(p16 + (size_t)m->n_dec * AN, m->cu_prefill.p,
                                                         (uint16_t*)m->mix.p + (size_t)m->n_dec * QW, m->attn_ws.p, T - m->n_dec,
@@ -288,12 +318,21 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
        m->logits.alloc(S * (size_t)c.vocab * 4) && m->accws.alloc((size_t)kFusedDequantMaxRows * acc_n * 4) && m->tokens.alloc(S * 4) && m->status.alloc(4) && m->ids.alloc(T * 4) &&
        m->pos.alloc(T * 4) && m->slots.alloc(T * 8) && m->cu_all.alloc((S + 1) * 4) && m->cu_prefill.alloc((S + 1) * 4) &&
        m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) && m->dec_chunks.alloc((S + 1) * 4) &&
-       m->state_slots.alloc(S * 4) && m->fresh.alloc(S) &&
-       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim)) &&
-       m->attn_ws.alloc(logismos_varlen_attention_tc_scratch_bytes(c.max_step_tokens, c.max_step_seqs, c.n_kv_heads, c.attn_head_dim));
+       m->state_slots.alloc(S * 4) && m->fresh.alloc(S) && m->pre_kv.alloc(S * 4) &&
+       m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim));
+  {
+    // the attention workspace serves both prefill routes; the gather route holds one run of sequences at
+    // a time, and any single sequence (at most a full block table) must fit
+    m->prefix_cap_tokens = MB * kBlock > T ? MB * kBlock : T;
+    size_t ws = logismos_varlen_attention_tc_scratch_bytes(c.max_step_tokens, c.max_step_seqs, c.n_kv_heads, c.attn_head_dim);
+    const size_t ws2 = logismos_paged_prefix_attention_scratch_bytes((int32_t)m->prefix_cap_tokens, c.max_step_seqs, c.n_kv_heads, c.attn_head_dim);
+    if (ws2 > ws) ws = ws2;
+    ok = ok && m->attn_ws.alloc(ws);
+  }
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
-  ok = ok && cudaMemset(m->accws.p, 0, (size_t)kFusedDequantMaxRows * acc_n * 4) == cudaSuccess;
-  m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4 + S + 64;
+  m->accws_bytes = (size_t)kFusedDequantMaxRows * acc_n * 4;
+  ok = ok && cudaMemset(m->accws.p, 0, m->accws_bytes) == cudaSuccess;
+  m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4 + S * 4 + S + 64;
   ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
   if (!ok) {
@@ -312,7 +351,7 @@ void lg_hybrid_destroy(void* model) {
   Buf* bufs[] = {&m->delta, &m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
                  &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens,
                  &m->status, &m->ids, &m->pos, &m->slots, &m->cu_all, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables,
-                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh};
+                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh, &m->pre_kv};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.kpool, &L.vpool, &L.state, &L.A_log, &L.dt_bias, &L.w_in.codes, &L.w_in.scales,
@@ -343,7 +382,6 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
   int64_t off = 0, total = 0;
   for (int i = 0; i < n_seqs; ++i) {
     if (newl[i] <= 0 || cached[i] < 0) { set_error("lg_hybrid_step: every sequence needs >= 1 new token"); return LG_EMB_COMPUTE; }
-    if (newl[i] > 1 && cached[i] != 0) { set_error("lg_hybrid_step: a prefill must start its sequence (cached_len == 0)"); return LG_EMB_COMPUTE; }
     if ((int64_t)cached[i] + newl[i] > c.max_pos || (int64_t)cached[i] + newl[i] > (int64_t)MB * kBlock) {
       set_error("lg_hybrid_step: sequence exceeds max_pos or its block table");
       return LG_EMB_INPUT_TOO_LONG;
@@ -373,6 +411,7 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
   int32_t* h_tables = (int32_t*)pp; pp += (size_t)n_seqs * MB * 4;
   int32_t* h_ctx = (int32_t*)pp; pp += (size_t)n_seqs * 4;
   int32_t* h_state = (int32_t*)pp; pp += (size_t)n_seqs * 4;
+  int32_t* h_prekv = (int32_t*)pp; pp += (size_t)n_seqs * 4;
   uint8_t* h_fresh = pp;
   std::vector<int32_t> o_cached(n_seqs), o_new(n_seqs), o_seqids((size_t)total);
   int64_t t = 0;
@@ -390,20 +429,37 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
                                                h_pos, h_slots, o_seqids.data());
   if (built != total) { set_error("lg_hybrid_step: a block table entry is missing or outside the pool"); return LG_EMB_COMPUTE; }
   int max_pre = 0;
+  bool has_prefix = false;
   h_cu_pre[0] = 0;
   for (int s = 0; s < n_seqs; ++s) {
     h_last[s] = h_cu[s + 1] - 1;
     if (s < n_dec) h_ctx[s] = o_cached[s] + 1;
     else {
       h_cu_pre[s - n_dec + 1] = h_cu[s + 1] - n_dec;
+      h_prekv[s - n_dec] = o_cached[s] + o_new[s];
+      if (o_cached[s] > 0) has_prefix = true;
       if (o_new[s] > max_pre) max_pre = o_new[s];
     }
+  }
+  std::vector<Hybrid::PrefixRun> runs;
+  if (has_prefix) {
+    Hybrid::PrefixRun r{0, 0, 0, 0, 0};
+    for (int k = 0; k < n_pre; ++k) {
+      const int kv = h_prekv[k], q = o_new[n_dec + k];
+      if (r.s1 > r.s0 && (size_t)r.total_kv + kv > m->prefix_cap_tokens) { runs.push_back(r); r = Hybrid::PrefixRun{k, k, 0, 0, 0}; }
+      r.s1 = k + 1; r.total_kv += kv;
+      if (q > r.max_q) r.max_q = q;
+      if (kv > r.max_kv) r.max_kv = kv;
+    }
+    runs.push_back(r);
   }
   m->chunk_tokens = n_dec > 0 ? logismos_pick_decode_chunk(h_ctx, n_dec, m->cfg.n_kv_heads, m->cfg.attn_head_dim) : kChunkTokens;
   const int total_chunks = n_dec > 0 ? logismos_build_decode_chunks(h_ctx, n_dec, m->chunk_tokens, h_chunks) : 0;
   if (total_chunks < 0 || (size_t)total_chunks > m->max_chunks) { set_error("lg_hybrid_step: decode chunk count exceeds the scratch"); return LG_EMB_COMPUTE; }
   m->T = (int)total; m->n_dec = n_dec; m->n_pre = n_pre; m->n_seqs = n_seqs; m->max_pre_len = max_pre; m->total_chunks = total_chunks;
   m->order = order;
+  m->pre_has_prefix = has_prefix;
+  m->prefix_runs = runs;
   cudaStream_t s = m->stream;
   LG_TRY(cudaMemcpyAsync(m->ids.p, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D ids");
   LG_TRY(cudaMemcpyAsync(m->pos.p, h_pos, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D positions");
@@ -415,15 +471,21 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
   LG_TRY(cudaMemcpyAsync(m->fresh.p, h_fresh, (size_t)n_seqs, cudaMemcpyHostToDevice, s), "H2D fresh flags");
   if (n_dec > 0) {
     LG_TRY(cudaMemcpyAsync(m->dec_ctx.p, h_ctx, (size_t)n_dec * 4, cudaMemcpyHostToDevice, s), "H2D context lens");
-    LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)n_dec * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
     LG_TRY(cudaMemcpyAsync(m->dec_chunks.p, h_chunks, (size_t)(n_dec + 1) * 4, cudaMemcpyHostToDevice, s), "H2D chunk offsets");
   }
-  if (uint32_t rc = run_device(m, s)) return rc;
+  if (n_dec > 0 || has_prefix)  // block tables in packed order: decode rows first, prefill rows after them
+    LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)(has_prefix ? n_seqs : n_dec) * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
+  if (has_prefix) LG_TRY(cudaMemcpyAsync(m->pre_kv.p, h_prekv, (size_t)n_pre * 4, cudaMemcpyHostToDevice, s), "H2D prefill key counts");
+  if (uint32_t rc = run_device(m, s)) { m->acc_dirty = true; return rc; }
   std::vector<uint32_t> toks(n_seqs);
   LG_TRY(cudaMemcpyAsync(toks.data(), m->tokens.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, s), "D2H tokens");
   LG_TRY(cudaStreamSynchronize(s), "stream synchronize");
   for (int k = 0; k < n_seqs; ++k) next_tokens[order[k]] = toks[k];
-  if (lg_hybrid_device_status(m) != 0) { set_error("a device-side range check or bounded wait failed"); return LG_EMB_COMPUTE; }
+  if (lg_hybrid_device_status(m) != 0) {
+    m->acc_dirty = true;
+    set_error("a device-side range check or bounded wait failed");
+    return LG_EMB_COMPUTE;
+  }
   return LG_EMB_OK;
 }
 

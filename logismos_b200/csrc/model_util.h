@@ -114,15 +114,17 @@ inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void
 }
 
 // logits = hidden W^T over the vocabulary and decode::greedy (crates/decode/src/lib.rs:73-83) on
-// them. Up to 16 rows the streaming int4 GEMV writes bf16 logits; above that the fused-dequant
-// tensor-core kernel accumulates fp32 logits into the zeroed buffer (which must hold rows * vocab
-// floats). *logits_f32 tells the caller which it was.
+// them. The logits stay fp32 up to the argmax on every route, as in the reference (greedy takes the
+// first strict maximum of fp32 logits), so the emitted token does not depend on how many rows the
+// step had: up to 16 rows the streaming int4 GEMV stores its fp32 accumulators; above that the
+// fused-dequant tensor-core kernel accumulates into the zeroed buffer. `logits` must hold rows * vocab
+// floats. *logits_f32 is always 1 (kept for the readers of the buffer).
 inline uint32_t lm_head_and_greedy(const QMat& lm_head, const void* hidden_bf16, void* logits, void* tokens, int rows, int hidden,
                                    void* status, int* logits_f32, int* launches, cudaStream_t s) {
   uint32_t rc;
   const int vocab = lm_head.n;
+  *logits_f32 = 1;
   if (rows > 16 && hidden % 256 == 0) {
-    *logits_f32 = 1;
     for (int b0 = 0; b0 < rows; b0 += kFusedDequantMaxRows) {
       const int nb = rows - b0 < kFusedDequantMaxRows ? rows - b0 : kFusedDequantMaxRows;
       float* dst = (float*)logits + (size_t)b0 * vocab;
@@ -133,13 +135,16 @@ inline uint32_t lm_head_and_greedy(const QMat& lm_head, const void* hidden_bf16,
       *launches += 1;
     }
   } else {
-    *logits_f32 = 0;
-    rc = logismos_launch_gemv_int4_g32_bf16(lm_head.codes.p, lm_head.scales.p, hidden_bf16, logits, rows, vocab, hidden, s);
-    if (rc) return rc;
-    *launches += 1;
+    for (int b0 = 0; b0 < rows; b0 += 64) {  // the GEMV takes up to 64 rows per launch
+      const int nb = rows - b0 < 64 ? rows - b0 : 64;
+      rc = logismos_launch_gemv_int4_g32_f32(lm_head.codes.p, lm_head.scales.p, (const uint16_t*)hidden_bf16 + (size_t)b0 * hidden,
+                                             (float*)logits + (size_t)b0 * vocab, nb, vocab, hidden, s);
+      if (rc) return rc;
+      *launches += 1;
+    }
   }
   *launches += 1;
-  return logismos_launch_greedy_argmax(logits, *logits_f32, tokens, rows, vocab, s);
+  return logismos_launch_greedy_argmax(logits, 1, tokens, rows, vocab, s);
 }
 
 }  // namespace lgm

@@ -42,7 +42,10 @@ int32_t logismos_build_decode_chunks(const int32_t* context_lens, int32_t n_seqs
   int64_t total = 0;
   chunk_offsets[0] = 0;
   for (int32_t i = 0; i < n_seqs; ++i) {
-    const int64_t len = context_lens[i] > 0 ? context_lens[i] : 0;
+    // a context counts the token being decoded, so it is never empty; the decode launch relies on it
+    // (a sequence without a chunk would leave its output row unwritten)
+    if (context_lens[i] < 1) return -1;
+    const int64_t len = context_lens[i];
     total += (len + chunk_tokens - 1) / chunk_tokens;
     if (total > 2147483647ll) return -1;
     chunk_offsets[i + 1] = (int32_t)total;

@@ -278,10 +278,12 @@ uint32_t lg_stella_forward_device(void* model, const void* dev_ids, const void* 
   Stella* m = static_cast<Stella*>(model);
   const int di = find_dim(m, dim == 0 ? m->cfg.dims[0] : dim);
   if (di < 0) { set_error("unsupported dim"); return LG_EMB_UNSUPPORTED_DIM; }
-  if (n_tokens < 0 || n_tokens > m->cfg.max_batch_tokens || n_seqs < 0) {
-    set_error("forward: batch exceeds workspace capacity");
+  // pooled sums, the padded V^T scratch and the output are sized from max_batch_seqs
+  if (n_tokens < 0 || n_tokens > m->cfg.max_batch_tokens || n_seqs < 0 || n_seqs > m->cfg.max_batch_seqs) {
+    set_error("forward: batch exceeds workspace capacity (max_batch_tokens / max_batch_seqs)");
     return LG_EMB_COMPUTE;
   }
+  if (max_seqlen < 0) { set_error("forward: max_seqlen < 0"); return LG_EMB_COMPUTE; }
   if (max_seqlen > m->cfg.max_pos) { set_error("forward: seq > max_pos"); return LG_EMB_COMPUTE; }
   if (n_tokens == 0 || n_seqs == 0) return LG_EMB_OK;
   if (cudaSetDevice(m->device) != cudaSuccess) { set_error("cudaSetDevice failed"); return LG_EMB_COMPUTE; }

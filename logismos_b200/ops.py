@@ -204,6 +204,31 @@ def varlen_attention_tc(qkv, cu_seqlens, n_heads, n_kv_heads, causal=False, max_
     return out
 
 
+def paged_prefix_attention(q, cu_seqlens_q, kv_lens, k_pool, v_pool, block_tables, n_heads, n_kv_heads, head_dim, sync=True,
+                           status=None):
+    """Causal attention of prefill chunks that continue cached sequences: the queries of sequence s are
+    rows cu_seqlens_q[s]..cu_seqlens_q[s+1] of q (q heads at column 0), its kv_lens[s] keys and values
+    (cached prefix + the chunk itself, already stored) are read from the paged pools through
+    block_tables. Returns out bf16 [n_q_tokens, n_heads * head_dim]."""
+    _req(q, "q", torch.bfloat16, 2); _req(cu_seqlens_q, "cu_seqlens_q", torch.int32, 1); _req(kv_lens, "kv_lens", torch.int32, 1)
+    _req(k_pool, "k_pool", torch.bfloat16, 3); _req(v_pool, "v_pool", torch.bfloat16, 3); _req(block_tables, "block_tables", torch.int32, 2)
+    n_seqs, T, D = kv_lens.shape[0], q.shape[0], head_dim
+    cu = cu_seqlens_q.cpu(); kv = kv_lens.cpu()
+    max_q = int((cu[1:] - cu[:-1]).max().item()) if n_seqs > 0 else 0
+    total_kv, max_kv = (int(kv.sum().item()), int(kv.max().item())) if n_seqs > 0 else (0, 0)
+    out = torch.empty((T, n_heads * D), dtype=torch.bfloat16, device=q.device)
+    scratch = torch.empty(max(256, int(lib.logismos_paged_prefix_attention_scratch_bytes(total_kv, n_seqs, n_kv_heads, D))),
+                          dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        check(lib.logismos_launch_paged_prefix_attention_tc_bf16(_p(q), q.shape[1], _p(cu_seqlens_q), _p(kv_lens), _p(k_pool), _p(v_pool),
+                                                                 _p(block_tables), block_tables.shape[1], k_pool.shape[0], _p(out),
+                                                                 _p(scratch), T, total_kv, n_seqs, max_q, max_kv, n_heads, n_kv_heads, D,
+                                                                 _p(status) if status is not None else None, _stream()),
+              "paged_prefix_attention")
+        _done(sync)
+    return out
+
+
 def rope_varlen_attention_tc_(qkv, cos, sin, positions, cu_seqlens, n_heads, n_kv_heads, causal=False, max_seqlen=None, sync=True,
                              scratch=None, status=None, head_dim=128):
     """halves-RoPE of the q and k heads of qkv (in place) fused into the first launch of varlen_attention_tc."""

@@ -6,7 +6,10 @@ executors give it is "a packed step equals running every sequence alone", so sch
 change throughput only, never results. Policy: first come first served; every running sequence
 decodes one token per step; waiting requests that have arrived are admitted while a state slot, the
 KV blocks of their whole lifetime (prompt + max_new tokens, so nothing is ever preempted), a row of
-the step and room in the step's token budget are available. A prompt is prefilled whole in one step.
+the step and room in the step's token budget are available. With ``chunked_prefill`` a prompt is fed
+in chunks: each step gives the prompts in flight (oldest first) what is left of its prefill budget,
+a sequence starts decoding after the step that took the last token of its prompt, and no step has to
+hold a whole prompt; without it a prompt is prefilled whole in one step.
 """
 from __future__ import annotations
 
@@ -40,6 +43,7 @@ class StepPlan:
     rids: List[int]
     n_decode: int
     n_prefill_tokens: int
+    emits: Optional[np.ndarray] = None   # bool [n]: the entry's next token is a generated token (None: all)
 
 
 def synthetic_load(n_requests: int, seed: int, vocab: int, prompt_median: int = 1024, prompt_sigma: float = 1.0,
@@ -61,9 +65,11 @@ def shard_requests(requests: List[Request], world: int, rank: int) -> List[Reque
 
 class Scheduler:
     def __init__(self, n_pool_blocks: int, max_blocks_per_seq: int, n_state_slots: int, max_step_tokens: int, max_step_seqs: int,
-                 prefill_token_budget: int = 0):
+                 prefill_token_budget: int = 0, chunked_prefill: bool = False):
         self.max_blocks, self.max_step_tokens, self.max_step_seqs = max_blocks_per_seq, max_step_tokens, max_step_seqs
         self.prefill_budget = prefill_token_budget or max_step_tokens
+        self.chunked = chunked_prefill
+        self.prefilling: Dict[int, Request] = {}   # admitted, prompt not yet fully fed (insertion order = age)
         self.free_blocks: List[int] = list(range(n_pool_blocks - 1, -1, -1))
         self.free_slots: List[int] = list(range(n_state_slots - 1, -1, -1))
         self.waiting: Deque[Request] = deque()
@@ -77,7 +83,7 @@ class Scheduler:
 
     def add(self, req: Request):
         need = -(-(len(req.prompt) + req.max_new) // BLOCK)
-        if need > self.max_blocks or len(req.prompt) < 1 or req.max_new < 1 or len(req.prompt) + 0 > self.max_step_tokens:
+        if need > self.max_blocks or len(req.prompt) < 1 or req.max_new < 1 or (not self.chunked and len(req.prompt) > self.max_step_tokens):
             raise ValueError(f"request {req.rid} cannot be served: {len(req.prompt)} + {req.max_new} tokens")
         self.waiting.append(req)
 
@@ -88,41 +94,68 @@ class Scheduler:
         return self.waiting[0].arrival if self.waiting else None
 
     def plan(self, now: float) -> Optional[StepPlan]:
-        """The next step: one decode token for every running sequence (oldest first, up to the step's
-        rows), then admitted prefills. None when nothing can run at `now`."""
-        rids, ids, cached, new = [], [], [], []
+        """The next step: one decode token for every running sequence whose prompt is in the cache (oldest
+        first, up to the step's rows), then prefill: chunks of the prompts in flight, then admitted
+        prompts (whole, or as much as the step's budget leaves when chunking). None when nothing can run
+        at `now`."""
+        rids, ids, cached, new, emits = [], [], [], [], []
         for rid, req in self.running.items():
             if len(rids) >= self.max_step_seqs or len(rids) >= self.max_step_tokens:
                 break
-            rids.append(rid); ids.append(np.asarray([req.output[-1]], np.uint32)); cached.append(self.cached[rid]); new.append(1)
+            if rid in self.prefilling:
+                continue
+            rids.append(rid); ids.append(np.asarray([req.output[-1]], np.uint32)); cached.append(self.cached[rid]); new.append(1); emits.append(True)
         n_decode, tokens, pre_tokens = len(rids), len(rids), 0
+
+        def room():
+            return min(self.max_step_tokens - tokens, self.prefill_budget - pre_tokens)
+
+        for rid, req in self.prefilling.items():  # chunked mode only: continue the prompts in flight
+            if len(rids) >= self.max_step_seqs or room() <= 0:
+                break
+            done = self.cached[rid]
+            n = min(len(req.prompt) - done, room())
+            rids.append(rid); ids.append(req.prompt[done:done + n]); cached.append(done); new.append(n)
+            emits.append(done + n == len(req.prompt))
+            tokens += n; pre_tokens += n
         while self.waiting and self.waiting[0].arrival <= now and len(rids) < self.max_step_seqs:
             req = self.waiting[0]
             p = len(req.prompt)
             need = -(-(p + req.max_new) // BLOCK)
-            if not self.free_slots or need > len(self.free_blocks) or tokens + p > self.max_step_tokens:
+            if not self.free_slots or need > len(self.free_blocks):
                 break
-            if pre_tokens > 0 and pre_tokens + p > self.prefill_budget:
-                break
+            if self.chunked:
+                n = min(p, room())
+                if n <= 0:
+                    break
+            else:
+                n = p
+                if tokens + p > self.max_step_tokens or (pre_tokens > 0 and pre_tokens + p > self.prefill_budget):
+                    break
             self.waiting.popleft()
             row = np.full(self.max_blocks, -1, np.int32)
             row[:need] = [self.free_blocks.pop() for _ in range(need)]
             self.tables[req.rid], self.slot_of[req.rid], self.cached[req.rid] = row, self.free_slots.pop(), 0
             self.running[req.rid] = req
-            rids.append(req.rid); ids.append(req.prompt); cached.append(0); new.append(p)
-            tokens += p; pre_tokens += p
+            if n < p:
+                self.prefilling[req.rid] = req
+            rids.append(req.rid); ids.append(req.prompt[:n]); cached.append(0); new.append(n); emits.append(n == p)
+            tokens += n; pre_tokens += n
         if not rids:
             return None
         return StepPlan(np.concatenate(ids).astype(np.uint32), np.asarray(cached, np.int32), np.asarray(new, np.int32),
                         np.stack([self.tables[r] for r in rids]), np.asarray([self.slot_of[r] for r in rids], np.int32), rids,
-                        n_decode, pre_tokens)
+                        n_decode, pre_tokens, np.asarray(emits, bool))
 
     def commit(self, plan: StepPlan, next_tokens, now: float):
-        """Records the step's results: appends each sequence's new token, retires finished sequences
-        and returns their blocks and slots."""
+        """Records the step's results: appends each sequence's new token (a chunk that does not end its
+        prompt produces none), retires finished sequences and returns their blocks and slots."""
         for i, rid in enumerate(plan.rids):
             req = self.running[rid]
             self.cached[rid] += int(plan.new[i])
+            if plan.emits is not None and not plan.emits[i]:
+                continue
+            self.prefilling.pop(rid, None)
             req.output.append(int(next_tokens[i]))
             self.generated += 1
             if req.first_token_at is None:

@@ -106,10 +106,12 @@ def test_build_packing_matches_oracle_bit_for_bit():
 
 
 def test_build_decode_chunks():
-    cl = np.array([1, 512, 513, 0, 32768], np.int32); off = np.empty(6, np.int32)
+    cl = np.array([1, 512, 513, 17, 32768], np.int32); off = np.empty(6, np.int32)
     P = lambda a: a.ctypes.data_as(C.c_void_p)
-    assert lib.logismos_build_decode_chunks(P(cl), 5, 512, P(off)) == 68
-    assert off.tolist() == [0, 1, 2, 4, 4, 68]
+    assert lib.logismos_build_decode_chunks(P(cl), 5, 512, P(off)) == 69
+    assert off.tolist() == [0, 1, 2, 4, 5, 69]
+    cl[3] = 0  # a context counts the token being decoded: an empty one is rejected
+    assert lib.logismos_build_decode_chunks(P(cl), 5, 512, P(off)) == -1
     assert lib.logismos_paged_decode_scratch_bytes(68, 16, 128) == 68 * 16 * 130 * 4
 
 

@@ -146,3 +146,68 @@ def test_tc_with_fused_rope_equals_rope_then_attention(d, causal):
     bad = pos.clone(); bad[5] = 256
     ops.rope_varlen_attention_tc_(qkv_t.clone(), cos_t, sin_t, bad, cu, nh, nkv, causal=causal, head_dim=d, status=status)
     assert int(status.item()) == 1
+
+
+# ---- prefill chunks that continue a cached sequence: keys and values read through the block tables ----
+
+def run_case_prefix(cached, new, nh, nkv, d, seed, poison=False):
+    """Sequence i holds cached[i] + new[i] tokens in a NaN-prefilled paged pool (seeded random block
+    tables); the queries are its last new[i] positions. Reference: the oracle's causal attention over
+    the whole sequence, rows of the chunk."""
+    rng = np.random.default_rng(seed)
+    n = len(cached)
+    kv = [c + m for c, m in zip(cached, new)]
+    nblk = [-(-L // 16) for L in kv]
+    n_pool = sum(nblk) + 3
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.full((n, max(max(nblk), 1) + 1), -1, np.int32)
+    o = 0
+    for i in range(n):
+        tables[i, :nblk[i]] = perm[o:o + nblk[i]]; o += nblk[i]
+    row = nkv * d
+    kp = torch.full((n_pool, 16, row), float("nan"), dtype=torch.bfloat16, device=DEV); vp = torch.full_like(kp, float("nan"))
+    qs, refs = [], []
+    for i in range(n):
+        L = kv[i]
+        if L == 0:
+            continue
+        q_t, q = bf16_cuda(rng.standard_normal((L, nh * d)))
+        k_t, k = bf16_cuda(rng.standard_normal((L, row))); v_t, v = bf16_cuda(rng.standard_normal((L, row)))
+        p = np.arange(L)
+        ops.paged_kv_store(k_t, v_t, kp, vp, torch.from_numpy(tables[i, p // 16].astype(np.int64) * 16 + p % 16).to(DEV))
+        qs.append(q_t[cached[i]:])
+        refs.append(O.sdpa(q, k, v, nh, nkv, d, causal=True)[cached[i]:] if new[i] else np.zeros((0, nh * d), np.float32))
+    q_all = torch.cat(qs).contiguous() if qs else torch.zeros((0, nh * d), dtype=torch.bfloat16, device=DEV)
+    cu = np.zeros(n + 1, np.int32); cu[1:] = np.cumsum(new)
+    if poison:
+        tables[0, 0] = n_pool + 5
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = to_np(ops.paged_prefix_attention(q_all, torch.from_numpy(cu).to(DEV), torch.tensor(kv, dtype=torch.int32, device=DEV), kp, vp,
+                                           torch.from_numpy(tables).to(DEV), nh, nkv, d, status=status))
+    if poison:
+        assert int(status.item()) == 1
+        return
+    assert int(status.item()) == 0
+    j = 0
+    for i in range(n):
+        if kv[i] == 0:
+            continue
+        if new[i]:
+            assert max_rel(out[cu[i]:cu[i + 1]], refs[j]) <= TOL, (i, cached[i], new[i])
+        j += 1
+
+
+@pytest.mark.parametrize("d", [128, 256])
+def test_paged_prefix_attention_chunks_against_cached_prefixes(d):
+    # prefixes and chunks around the 128-key tile, the 16-token block and the 8-key padding edges; a chunk
+    # that starts its sequence (cached 0) and a single-token chunk ride along
+    run_case_prefix([100, 0, 128, 17, 500, 3, 255], [60, 70, 1, 129, 200, 8, 130], 16 if d == 256 else 12, 2, d, 51)
+    run_case_prefix([1000], [300], 4, 4, d, 52)
+
+
+def test_paged_prefix_attention_equals_the_unpaged_kernel_for_fresh_sequences():
+    run_case_prefix([0, 0, 0], [200, 33, 128], 8, 2, 128, 53)
+
+
+def test_paged_prefix_attention_reports_a_block_outside_the_pool():
+    run_case_prefix([40, 10], [20, 30], 4, 2, 128, 54, poison=True)

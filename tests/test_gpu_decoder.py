@@ -69,6 +69,17 @@ def test_mixed_prefill_and_decode_steps_equal_per_sequence_execution(setup):
     assert len(hist[1]) == 18 and model.launches_last_step() > 0
     # a single-token sequence is a decode against an empty cache
     run([(9, [5])])
+    # a prompt fed in chunks: every chunk after the first continues a cached prefix (positions, cache
+    # slots, keys and values read through the block table), mixed with decode rows and with a chunk that
+    # starts another sequence; every step is compared with the oracle run on the whole history, so
+    # chunked == whole prompt == oracle
+    prompt = rng.integers(0, 1000, 150)
+    run([(11, prompt[:64]), (0, [nxt[0]])])
+    run([(2, [nxt[2]]), (11, prompt[64:129]), (12, rng.integers(0, 1000, 20))])
+    last = run([(11, prompt[129:])])
+    h_chunked = model.last_hidden()[0].copy()
+    whole = run([(13, prompt)])
+    assert max_rel(model.last_hidden()[0], h_chunked) <= TOL and whole[13] == last[11]
     model.close()
 
 
@@ -76,8 +87,6 @@ def test_step_rejects_what_it_cannot_run(setup):
     qw, _, _ = setup
     model = DecoderModel(TINY, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2)
     tab = np.array([[0, 1, 2, 3, 4, 5, 6, 7]], np.int32)
-    with pytest.raises(ComputeError):   # a prefill chunk continuing a cached sequence
-        model.step([1, 2, 3], [4], [3], tab)
     with pytest.raises(ComputeError):   # block table row with a missing entry
         model.step([1] * 20, [0], [20], np.array([[0, -1, -1, -1, -1, -1, -1, -1]], np.int32))
     with pytest.raises(ComputeError):   # more tokens than the step workspace

@@ -53,6 +53,19 @@ def drive(cfg, seed, n_decode_steps):
     # a single-token sequence is a decode against an empty cache and a zero state
     run([(9, [5])])
     assert model.launches_last_step() > 0
+    # a prompt fed in chunks: every chunk after the first continues a cached prefix (positions, cache
+    # slots, keys read through the block table, recurrent state carried in the slot), mixed with decode
+    # rows and with a chunk that starts another sequence; each step is compared with the oracle run on
+    # the whole history, so chunked == whole prompt == oracle
+    slots.release(9); blocks.release(9); slots.release(7); blocks.release(7)
+    prompt = rng.integers(0, V, 150)
+    run([(11, prompt[:64]), (0, [nxt[0]])])
+    nxt.update(run([(2, [nxt[2]]), (11, prompt[64:129]), (12, rng.integers(0, V, 20))]))
+    last = run([(11, prompt[129:])])
+    h_chunked = model.last_hidden()[0].copy()
+    slots.release(12); blocks.release(12)
+    whole = run([(13, prompt)])
+    assert max_rel(model.last_hidden()[0], h_chunked) <= TOL and whole[13] == last[11]
     model.close()
 
 
@@ -91,8 +104,6 @@ def test_step_rejects_what_it_cannot_run():
     qw, _ = make_hybrid(TINY_HYBRID_128, 3)
     model = HybridModel(TINY_HYBRID_128, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2, n_state_slots=2)
     tab = np.array([[0, 1, 2, 3, 4, 5, 6, 7]], np.int32)
-    with pytest.raises(ComputeError):   # a prefill continuing a cached sequence
-        model.step([1, 2, 3], [4], [3], tab, [0])
     with pytest.raises(ComputeError):   # state slot outside the pool
         model.step([1], [0], [1], tab, [2])
     with pytest.raises(ComputeError):   # one slot for two sequences

@@ -76,6 +76,38 @@ def test_outputs_do_not_depend_on_packing(budget, seqs):
         assert r.first_token_at >= r.arrival and r.finished_at >= r.first_token_at
 
 
+@pytest.mark.parametrize("budget,step_tokens,seqs", [(64, 96, 8), (17, 48, 3), (150, 200, 16)])
+def test_chunked_prefill_feeds_prompts_in_pieces_with_the_same_outputs(budget, step_tokens, seqs):
+    """Prompts longer than a step are fed in chunks against their cached prefix; a chunk that does not
+    end its prompt produces no token; outputs equal those of each request run alone."""
+    reqs = synthetic_load(30, 5, 1000, prompt_median=90, prompt_sigma=0.9, prompt_cap=512, out_lo=1, out_hi=12, rate_per_s=80.0)
+    assert max(len(r.prompt) for r in reqs) > step_tokens  # some prompt cannot fit one step
+    sched = Scheduler(n_pool_blocks=400, max_blocks_per_seq=40, n_state_slots=seqs, max_step_tokens=step_tokens, max_step_seqs=seqs,
+                      prefill_token_budget=budget, chunked_prefill=True)
+    ex = FakeExecutor()
+    seen = []
+
+    def step(plan):
+        assert int(plan.new.sum()) <= step_tokens and plan.n_prefill_tokens <= budget
+        seen.append(plan)
+        return ex(plan)
+
+    def on_step(plan):
+        live = {b for r in sched.tables.values() for b in r[r >= 0].tolist()}
+        for b in list(ex.block_owner):
+            if b not in live:
+                del ex.block_owner[b]
+
+    serve(step, sched, reqs, Clock(), on_step=on_step)
+    assert sched.idle() and len(sched.done) == 30 and not sched.prefilling
+    assert len(sched.free_blocks) == 400 and len(sched.free_slots) == seqs
+    assert sched.generated == sum(r.max_new for r in reqs) and sched.prefilled == sum(len(r.prompt) for r in reqs)
+    assert any((p.cached[p.n_decode:] > 0).any() for p in seen), "no chunk ever continued a cached prefix"
+    assert any(not p.emits.all() for p in seen)
+    for r in reqs:
+        assert r.output == alone(r)
+
+
 def test_requests_that_can_never_run_are_refused_and_load_is_seeded():
     sched = Scheduler(n_pool_blocks=8, max_blocks_per_seq=4, n_state_slots=2, max_step_tokens=32, max_step_seqs=2)
     with pytest.raises(ValueError):
