@@ -351,6 +351,7 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   m->pre_has_prefix = has_prefix;
   m->prefix_runs = runs;
   cudaStream_t s = m->stream;
+  LG_TRY(cudaMemsetAsync(m->status.p, 0, 4, s), "clear status");  // the status word describes this step only
   LG_TRY(cudaMemcpyAsync(m->ids.p, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D ids");
   LG_TRY(cudaMemcpyAsync(m->pos.p, h_pos, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D positions");
   LG_TRY(cudaMemcpyAsync(m->slots.p, h_slots, (size_t)total * 8, cudaMemcpyHostToDevice, s), "H2D slots");
