@@ -2,7 +2,7 @@
 tokens each decode one token; the step's device work is replayed and timed with CUDA events, and
 the host-buffer entry point is timed around it. Used for launch lists and per-step rooflines.
 
-  python -m logismos_b200.stepbench [--seqs S --ctx C --layers L --iters I --prefill-chunk P]
+  python bench_decode_step.py [--seqs S --ctx C --layers L --iters I --prefill-chunk P]
 
 Prints one JSON line: device ms per step, host-entry ms per step, launches per step, and the
 algorithmic HBM bytes of the step (int4 weights once, recurrent states read + written, KV rows of
@@ -17,12 +17,17 @@ import time
 import numpy as np
 import torch
 
-from .decoder import BlockAllocator
-from .hybrid import HYBRID_SERVING, HybridModel, random_int4_weights
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from logismos_b200.decoder import BlockAllocator  # noqa: E402
+from logismos_b200.hybrid import HYBRID_SERVING, HybridModel, random_int4_weights  # noqa: E402
 
 
 def main(argv=None):
-    ap = argparse.ArgumentParser(prog="logismos_b200.stepbench")
+    ap = argparse.ArgumentParser(prog="bench_decode_step.py")
     ap.add_argument("--seqs", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=48)

@@ -2,14 +2,14 @@
 configurations, and the model's GEMM shapes), each launch timed with CUDA events on the launch
 stream, operands rotated over several copies so that every launch reads from HBM.
 
-  python -m logismos_b200.microbench gemv  [--n N --k K --batch B --iters I]
-  python -m logismos_b200.microbench gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
-  python -m logismos_b200.microbench qlinear [--m M --n N --k K --iters I]   (m <= 256, fused int4 dequant)
-  python -m logismos_b200.microbench qdense  [--m M --n N --k K --iters I]   (bf16 expansion + dense GEMM)
-  python -m logismos_b200.microbench gdn     [--seqs S --len L]                 (token-serial vs chunk-parallel)
-  python -m logismos_b200.microbench paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
-  python -m logismos_b200.microbench attn  [--seqs S --len L --iters I]
-  python -m logismos_b200.microbench sweep          (every benchmark shape, one JSON line each)
+  python bench_kernels.py gemv  [--n N --k K --batch B --iters I]
+  python bench_kernels.py gemm  [--m M --n N --k K --epi bf16|resid|swiglu --iters I]
+  python bench_kernels.py qlinear [--m M --n N --k K --iters I]   (m <= 256, fused int4 dequant)
+  python bench_kernels.py qdense  [--m M --n N --k K --iters I]   (bf16 expansion + dense GEMM)
+  python bench_kernels.py gdn     [--seqs S --len L]                 (token-serial vs chunk-parallel)
+  python bench_kernels.py paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
+  python bench_kernels.py attn  [--seqs S --len L --iters I]
+  python bench_kernels.py sweep          (every benchmark shape, one JSON line each)
 
 Prints one JSON line per case: achieved GB/s or TFLOP/s, the measured peak it is compared with
 (MEASURED_PEAKS.json next to the package, else the documented fallback) and the fraction.
@@ -24,10 +24,13 @@ import sys
 import numpy as np
 import torch
 
-from . import ops
-from ._lib import lib
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from logismos_b200 import ops  # noqa: E402
+from logismos_b200._lib import lib  # noqa: E402
+from logismos_b200 import timing  # noqa: E402
+from logismos_b200.timing import timeit  # noqa: E402
 
 
 def peaks():
@@ -36,42 +39,6 @@ def peaks():
         d = json.load(open(p))
         return {"hbm": d["hbm_gbs"], "tf": d["bf16_tflops"], "src": "measured"}
     return {"hbm": 6650.0, "tf": 1590.0, "src": "fallback"}
-
-
-USE_GRAPH = True
-
-
-def timeit(fn, iters, warmup=3):
-    """Seconds per launch. The `iters` launches are captured into one CUDA graph and the graph is
-    replayed, so that host-side launch cost (Python, descriptor encoding) is not what is timed; a
-    kernel of a few microseconds is otherwise hidden behind ~15 us of host work per call."""
-    for i in range(warmup):
-        fn(i)
-    torch.cuda.synchronize()
-    if not USE_GRAPH:
-        st = torch.cuda.current_stream()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(st)
-        for i in range(iters):
-            fn(i)
-        e1.record(st)
-        e1.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / iters
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for i in range(iters):
-            fn(i)
-    g.replay()
-    torch.cuda.synchronize()
-    st = torch.cuda.current_stream()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 3
-    e0.record(st)
-    for _ in range(reps):
-        g.replay()
-    e1.record(st)
-    e1.synchronize()
-    return e0.elapsed_time(e1) * 1e-3 / (iters * reps)
 
 
 def bench_gemv(n, k, batch, iters, copies=None, pk=None):
@@ -228,7 +195,7 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
 
 
 def main(argv=None):
-    ap = argparse.ArgumentParser(prog="logismos_b200.microbench")
+    ap = argparse.ArgumentParser(prog="bench_kernels.py")
     ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "gdn", "paged", "attn", "sweep"])
     ap.add_argument("--m", type=int, default=2176)
     ap.add_argument("--n", type=int, default=151936)
@@ -244,8 +211,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-graph", action="store_true", help="time back-to-back launches from Python instead of a CUDA graph")
     a = ap.parse_args(argv)
-    global USE_GRAPH
-    USE_GRAPH = not a.no_graph
+    timing.USE_GRAPH = not a.no_graph
     if a.what == "gemv":
         print(json.dumps(bench_gemv(a.n, a.k, a.batch, a.iters)))
     elif a.what == "gemm":

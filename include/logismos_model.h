@@ -221,11 +221,39 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ho
  * counterpart (the reference has no tensor parallelism). */
 typedef uint32_t (*lg_allreduce_f32_fn)(void* user, void* dev_buf_f32, uint64_t count, void* stream);
 uint32_t lg_hybrid_set_allreduce(void* model, lg_allreduce_f32_fn fn, void* user);
+/* The same slot for a reduction fused with the residual add: each partial sum is computed into a zeroed
+ * fp32 buffer `delta` and fn(user, x, delta, count, status, stream) must leave x += sum over all ranks
+ * of delta, ordered on `stream`, without synchronising; status_i32 is the model's device status word
+ * (a bounded wait that expires raises it). lg_tp_reduce_add_f32 below has this signature. Installing
+ * one kind of reduction removes the other. */
+typedef uint32_t (*lg_reduce_add_f32_fn)(void* user, void* x_f32, void* delta_f32, uint64_t count, void* status_i32, void* stream);
+uint32_t lg_hybrid_set_reduce_add(void* model, lg_reduce_add_f32_fn fn, void* user);
 uint32_t lg_hybrid_replay_device(void* model, void* stream);
 uint32_t lg_hybrid_last_hidden(void* model, int32_t n_seqs, float* host_out);
 uint32_t lg_hybrid_last_logits(void* model, int32_t n_seqs, float* host_out);
 int32_t lg_hybrid_launches_last_step(const void* model);
 int32_t lg_hybrid_device_status(void* model);
+
+/* ====================================================================================
+ * Tensor-parallel exchange over NVLink peer memory (ranks = processes on different GPUs of one node).
+ * No reference counterpart (the reference is single-device, README.md:19-21). One kernel per rank
+ * writes the local partial sum into every peer's receive buffer with plain peer stores, raises a
+ * flag there, waits (bounded: status 3 on expiry, the add is then skipped) for the peers' flags and adds all partial
+ * sums, in rank order, into the residual stream.
+ *   lg_tp_comm_alloc   allocates this rank's region (flags + two receive sets of tp * max_elems floats,
+ *                      zeroed) on `device` and returns its 64-byte cudaIpc handle
+ *   lg_tp_comm_open    given the handles of all ranks [tp][64] (exchanged by the host, e.g. an
+ *                      all-gather over the process group), maps the peers' regions
+ *   lg_tp_reduce_add_f32  x += sum over ranks of delta for count floats (count % 4 == 0, count <=
+ *                      max_elems); every rank makes the same sequence of calls; signature of
+ *                      lg_reduce_add_f32_fn with user = the communicator
+ * ==================================================================================== */
+size_t lg_tp_comm_region_bytes(int32_t tp, uint64_t max_elems);
+uint32_t lg_tp_comm_alloc(int32_t device, int32_t tp, uint64_t max_elems, void** region, uint8_t* handle_out64);
+uint32_t lg_tp_comm_open(int32_t device, void* region, int32_t rank, int32_t tp, uint64_t max_elems,
+                         const uint8_t* all_handles, void** comm);
+void lg_tp_comm_destroy(void* comm, int32_t free_region);
+uint32_t lg_tp_reduce_add_f32(void* comm, void* x_f32, void* delta_f32, uint64_t count, void* status_i32, void* stream);
 
 /* Message of the last failure on the calling thread ("" if none). */
 const char* lg_last_error(void);

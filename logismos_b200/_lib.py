@@ -7,7 +7,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "liblogismos_kernels.so")
 
-vp, i32, i64, u32, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_float, C.c_size_t
+vp, i32, i64, u32, u64, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_uint64, C.c_float, C.c_size_t
 
 
 class LogismosError(RuntimeError):
@@ -105,6 +105,10 @@ def _declare(l):
         "logismos_launch_add_f32": [vp, vp, i64, vp],
         "logismos_launch_gdn_finish": [vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, vp],
         "lg_hybrid_set_allreduce": [vp, vp, vp],
+        "lg_hybrid_set_reduce_add": [vp, vp, vp],
+        "lg_tp_comm_alloc": [i32, i32, u64, C.POINTER(vp), vp],
+        "lg_tp_comm_open": [i32, vp, i32, i32, u64, vp, C.POINTER(vp)],
+        "lg_tp_reduce_add_f32": [vp, vp, vp, u64, vp, vp],
         "lg_hybrid_create": [i32, vp, vp, C.POINTER(vp)],
         "lg_hybrid_step": [vp, vp, vp, vp, i32, vp, vp, vp],
         "lg_hybrid_replay_device": [vp, vp],
@@ -133,6 +137,10 @@ def _declare(l):
     l.logismos_build_decode_chunks.restype = i32
     l.logismos_pick_decode_chunk.argtypes = [vp, i32, i32, i32]
     l.logismos_pick_decode_chunk.restype = i32
+    l.lg_tp_comm_region_bytes.argtypes = [i32, u64]
+    l.lg_tp_comm_region_bytes.restype = sz
+    l.lg_tp_comm_destroy.argtypes = [vp, i32]
+    l.lg_tp_comm_destroy.restype = None
     l.lg_stella_destroy.argtypes = [vp]
     l.lg_stella_destroy.restype = None
     l.lg_decoder_destroy.argtypes = [vp]

@@ -56,6 +56,8 @@ struct Hybrid {
   Buf delta;  // partial sum of an output projection when a cross-rank reduction is installed
   lg_allreduce_f32_fn allreduce = nullptr;
   void* allreduce_user = nullptr;
+  lg_reduce_add_f32_fn reduce_add = nullptr;  // reduction fused with the residual add (takes precedence)
+  void* reduce_add_user = nullptr;
   Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
   Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh, pre_kv;
   uint8_t* pinned = nullptr;
@@ -86,9 +88,17 @@ uint32_t qlinear(Hybrid* m, const void* a, const QMat& w, void* out, int T, int 
 // is reduced over the ranks before it joins the residual stream
 uint32_t out_proj(Hybrid* m, const void* a, const QMat& w, int T, int lda, cudaStream_t s) {
   const int H = m->cfg.hidden;
-  if (!m->allreduce) return qlinear(m, a, w, m->x.p, T, lda, H, LG_EPI_RESID_F32, s);
+  if (!m->allreduce && !m->reduce_add) return qlinear(m, a, w, m->x.p, T, lda, H, LG_EPI_RESID_F32, s);
   LG_TRY(cudaMemsetAsync(m->delta.p, 0, (size_t)T * H * 4, s), "memset partial sum");
   if (uint32_t rc = qlinear(m, a, w, m->delta.p, T, lda, H, LG_EPI_RESID_F32, s)) return rc;
+  if (m->reduce_add) {
+    if (m->reduce_add(m->reduce_add_user, m->x.p, m->delta.p, (uint64_t)T * H, m->status.p, (void*)s) != 0) {
+      set_error("the installed reduce-add reported a failure");
+      return LG_EMB_COMPUTE;
+    }
+    m->launches += 1;
+    return 0;
+  }
   if (m->allreduce(m->allreduce_user, m->delta.p, (uint64_t)T * H, (void*)s) != 0) {
     set_error("the installed all-reduce reported a failure");
     return LG_EMB_COMPUTE;
@@ -496,6 +506,19 @@ uint32_t lg_hybrid_set_allreduce(void* model, lg_allreduce_f32_fn fn, void* user
   std::lock_guard<std::mutex> lock(m->mu);
   m->allreduce = fn;
   m->allreduce_user = user;
+  m->reduce_add = nullptr;
+  m->reduce_add_user = nullptr;
+  return LG_EMB_OK;
+}
+
+uint32_t lg_hybrid_set_reduce_add(void* model, lg_reduce_add_f32_fn fn, void* user) {
+  Hybrid* m = static_cast<Hybrid*>(model);
+  if (!m) { set_error("lg_hybrid_set_reduce_add: null model"); return LG_EMB_COMPUTE; }
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->reduce_add = fn;
+  m->reduce_add_user = user;
+  m->allreduce = nullptr;
+  m->allreduce_user = nullptr;
   return LG_EMB_OK;
 }
 

@@ -65,7 +65,7 @@ def _ptr(a):
 
 
 class StellaModel:
-    """``StellaModel::load`` for in-memory fp32 weights (dict layout of tests/stella_weights.py:
+    """``StellaModel::load`` for in-memory fp32 weights (dict layout of logismos_b200.synthetic.make_weights:
     tok_embed, final_norm, layers[12 tensors], head_w, head_b; ``heads`` maps dim -> (w, b) for
     several dense heads)."""
 

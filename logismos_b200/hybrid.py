@@ -86,6 +86,7 @@ class HybridModel:
         if lib.lg_hybrid_create(device, C.byref(c), C.byref(w), C.byref(h)):
             raise ComputeError(lib.lg_last_error().decode())
         self._h, self.cfg, self.max_blocks = h, cfg, max_blocks_per_seq
+        self.max_step_tokens, self.device = max_step_tokens, device
 
     def close(self):
         if getattr(self, "_h", None):
@@ -116,6 +117,12 @@ class HybridModel:
         sums: a ``tp.ALLREDUCE_FN`` callback (kept alive by this object)."""
         self._allreduce = fn
         if lib.lg_hybrid_set_allreduce(self._h, C.cast(fn, C.c_void_p) if fn is not None else None, None):
+            raise ComputeError(lib.lg_last_error().decode())
+
+    def set_reduce_add(self, fn_ptr, user_ptr):
+        """Installs (or with fn_ptr None removes) a reduction fused with the residual add: a C function of
+        type ``lg_reduce_add_f32_fn`` given by address (``tp.PeerComm`` installs the library's own)."""
+        if lib.lg_hybrid_set_reduce_add(self._h, fn_ptr, user_ptr):
             raise ComputeError(lib.lg_last_error().decode())
 
     def replay_device(self, stream_ptr: int):

@@ -89,6 +89,57 @@ def nccl_allreduce_hook(group=None) -> Callable:
     return ALLREDUCE_FN(fn)
 
 
+class PeerComm:
+    """The reduction for ranks that are processes on different GPUs of one node: the library's own
+    exchange over NVLink peer memory (``lg_tp_reduce_add_f32``: peer stores, flags, one kernel per rank,
+    fused with the residual add). The 64-byte cudaIpc handles of the ranks' regions are exchanged over the
+    torch.distributed process group (``group``), which must hold exactly the tp ranks in rank order."""
+
+    def __init__(self, rank: int, tp: int, max_elems: int, device: int, group=None):
+        import torch
+        import torch.distributed as dist
+        from ._lib import lib
+        self._lib, self._comm = lib, None
+        max_elems = (int(max_elems) + 3) & ~3
+        region, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        rc = lib.lg_tp_comm_alloc(device, tp, max_elems, C.byref(region), handle)
+        if rc:
+            raise RuntimeError(f"lg_tp_comm_alloc failed with CUDA status {rc}")
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=torch.device("cuda", device) if dist.get_backend(group) == "nccl" else "cpu")
+        parts = [torch.zeros_like(mine) for _ in range(tp)]
+        dist.all_gather(parts, mine, group=group)
+        allh = (C.c_uint8 * (64 * tp))(*[int(v) for p_ in parts for v in p_.cpu().tolist()])
+        comm = C.c_void_p()
+        rc = lib.lg_tp_comm_open(device, region, rank, tp, max_elems, allh, C.byref(comm))
+        if rc:
+            raise RuntimeError(f"lg_tp_comm_open failed with CUDA status {rc} (peer access between the GPUs is required)")
+        self._comm = comm
+        dist.barrier(group=group)  # every rank has mapped every region before the first exchange
+
+    def install(self, model):
+        model.set_reduce_add(C.cast(self._lib.lg_tp_reduce_add_f32, C.c_void_p), self._comm)
+
+    def close(self):
+        if self._comm:
+            self._lib.lg_tp_comm_destroy(self._comm, 1)
+            self._comm = None
+
+
+def install_allreduce(model, rank: int, tp: int, kind: str = "peer", group=None):
+    """Joins a rank's HybridModel to its tensor-parallel group. kind "peer": the library's NVLink
+    peer-memory exchange (default); "nccl": torch.distributed's NCCL all-reduce through a Python
+    callback (the slower, library-only route, kept for comparison). Returns the object to keep alive
+    for as long as the model runs."""
+    if kind == "nccl":
+        hook = nccl_allreduce_hook(group)
+        model.set_allreduce(hook)
+        return hook
+    cfg = model.cfg
+    comm = PeerComm(rank, tp, model.max_step_tokens * cfg["hidden"], model.device, group)
+    comm.install(model)
+    return comm
+
+
 class ThreadAllReduce:
     """The reduction for ranks that are threads of one process on ONE GPU (tests): every rank
     synchronises its stream, meets the others at a barrier, rank 0 sums the buffers, and every rank
