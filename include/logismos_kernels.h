@@ -23,6 +23,18 @@
 extern "C" {
 #endif
 
+/* Process-wide switch for bit-reproducible results. By default two GEMM paths split the reduction over
+ * k across CTAs when few output tiles would leave SMs idle (the accumulating epilogue of
+ * logismos_launch_linear_t_bf16 and the spans of logismos_launch_qlinear_int4_g32_acc_f32); the
+ * slices meet in fp32 reductions whose order is not fixed, so the last bits of a result can differ
+ * between runs and between a row computed alone and inside a batch (within the 2e-2 parity bar, but
+ * not bit-identical). With the switch on, those splits are not used: every output element is summed in
+ * one fixed order, at some cost in speed for small steps. The environment variable
+ * LOGISMOS_DETERMINISTIC=1 sets the initial value. No reference counterpart (its CPU path is
+ * deterministic by construction). */
+void logismos_set_deterministic(int32_t on);
+int32_t logismos_get_deterministic(void);
+
 /* ====================================================================================
  * The reference's four fp16 launchers, same symbols and argument lists.
  * ==================================================================================== */
@@ -205,6 +217,14 @@ uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes_u8, const void* sca
 uint32_t logismos_launch_dequant_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
                                                void* out_bf16, int32_t n, int32_t k, void* stream);
 
+/* Quantises fp32 weights [n, k] to the int4 group-32 storage above, on the device: per group of 32
+ * values along k, scale = fp16(max|w| / 7), code = clamp(round-half-even(w / scale), -8, 7) (0 for an
+ * all-zero group), packed in the Turbo4Block nibble order (crates/quant/src/lib.rs:272-301). The
+ * reference has no quantiser (turbo4 encode returns Unsupported, crates/quant/src/lib.rs:361-367);
+ * the output is integer and is checked bit for bit against the CPU definition. k % 32 == 0. */
+uint32_t logismos_launch_quantize_int4_g32(const void* w_f32, void* codes_u8, void* scales_f16,
+                                           int32_t n, int32_t k, void* stream);
+
 /* acc[m, n] += A[m, k] * dequant(W)[n, k]^T for 1 <= m <= 256 tokens, int4 group-32 weights (storage
  * as above), dequantisation fused into the tensor-core operand pipeline. The linear of decode and
  * small mixed steps: linear_t (cpu_f32/mod.rs:271-345) on the dequantised matrix. a bf16 [m, k]
@@ -257,7 +277,11 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
  *     cudaErrorMemoryAllocation (2) without launching and says why on stderr.
  *   - The first call on each device looks up the buffer's device address (that device must be
  *     current, as for any launch) and caches it; make that first call before starting any stream
- *     capture on the device.
+ *     capture on the device. "Allocates nothing" holds from then on: the buffer belongs to the
+ *     library's device code, which the CUDA runtime may load lazily at the first call into the
+ *     library on a device, and loading takes device memory (the 8 MiB included). A host that then
+ *     grabs all free HBM for its KV pool must therefore make one small valid call of this entry
+ *     point on each device BEFORE that grab.
  *   - All calls share the one buffer and it keeps the previous call's contents; nothing in it needs
  *     clearing, since a launch only reads partials it wrote itself. For the same reason two calls
  *     whose kernels can overlap on the GPU (different streams, or threads) race on it: serialise
@@ -363,6 +387,45 @@ uint32_t logismos_launch_add_f32(void* x_f32, const void* d_f32, int64_t n, void
  * never selected. logits bf16 or f32 [rows, n]; out u32 [rows]. */
 uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, void* out_u32,
                                        int32_t rows, int32_t n, void* stream);
+
+/* ====================================================================================
+ * Sampling chain on the device: the logit processors and the multinomial sampler of
+ * crates/decode (chain.rs:33-76 runs processors in insertion order, then the sampler), each as one
+ * launch over fp32 logits [rows, n] IN PLACE, so a caller keeps the reference's free ordering. Rows are
+ * independent. Rows must hold at least one finite logit.
+ * ==================================================================================== */
+
+/* TemperatureScale (processors.rs:18-28): t = max(temperature, 1e-6); |t - 1| < 1e-9 is the identity;
+ * otherwise every logit is divided by t. */
+uint32_t logismos_launch_temperature_f32(void* logits_f32, int32_t rows, int32_t n, float temperature,
+                                         void* stream);
+/* TopK (processors.rs:50-82): k == 0 or k >= n is the identity; otherwise every NaN and every logit
+ * below the k-th largest becomes -inf (ties with the k-th largest survive). Exact. */
+uint32_t logismos_launch_top_k_f32(void* logits_f32, int32_t rows, int32_t n, int32_t k, void* stream);
+/* TopP (processors.rs:89-122): p clamped to [0, 1]; p >= 1 is the identity; otherwise the smallest
+ * prefix of the tokens in order of descending probability (equal probabilities in index order) whose
+ * softmax mass reaches p is kept, the rest becomes -inf. The reference normalises by a sequential
+ * fp32 sum over the vocabulary (about 1e-5 to 1e-4 of relative rounding error at 151936 terms); the
+ * device sums pairwise, so the two nuclei can differ by the tokens whose cumulative mass lies within
+ * that error of p. */
+uint32_t logismos_launch_top_p_f32(void* logits_f32, int32_t rows, int32_t n, float p, void* stream);
+/* MinP (processors.rs:130-146): p clamped; p <= 0 is the identity; tokens whose probability is below
+ * p times the largest probability become -inf. */
+uint32_t logismos_launch_min_p_f32(void* logits_f32, int32_t rows, int32_t n, float p, void* stream);
+/* RepetitionPenalty (processors.rs:160-181): row r lists counts[r] <= max_tokens token ids in
+ * tokens_u32 [rows, max_tokens]; for each in order (a token listed twice is penalised twice; ids >= n
+ * are skipped) a positive logit is divided by penalty, any other multiplied. |penalty - 1| < 1e-9 is
+ * the identity. */
+uint32_t logismos_launch_repetition_penalty_f32(void* logits_f32, int32_t rows, int32_t n,
+                                                const void* tokens_u32, const void* counts_i32,
+                                                int32_t max_tokens, float penalty, void* stream);
+/* MultinomialSampler::sample (sampler.rs:31-58) with the uniform draw of every row supplied by the
+ * caller (uniforms_f32 [rows], each in [0, 1); the reference draws it from its RNG at that point):
+ * probabilities are exp(l - max) of the finite logits over their sum; the token is the first index
+ * whose cumulative probability exceeds the draw; a row without mass falls back to greedy; out u32
+ * [rows]. */
+uint32_t logismos_launch_multinomial_f32(const void* logits_f32, int32_t rows, int32_t n,
+                                         const void* uniforms_f32, void* out_u32, void* stream);
 
 /* ====================================================================================
  * Host-side index builders (no device work). crates/sched is an empty scaffold in the reference

@@ -68,6 +68,15 @@ uint32_t lg_stella_create(int32_t device, const lg_stella_config_t* cfg, const l
                           void** model);
 void lg_stella_destroy(void* model);
 
+/* StellaModel::load (crates/embed/src/stella.rs:138-201) from a checkpoint directory: `root`/
+ * model.safetensors must hold exactly 2 + 12 n_layers fp32 tensors under the names and shapes of
+ * crates/encoders/src/stella.rs:126-127, :326-349 (anything else is LG_EMB_COMPUTE with the reason in
+ * lg_last_error(); a missing or malformed file is LG_EMB_IO), and `root`/2_Dense_<dim>/model.safetensors
+ * one dense head (linear.weight [dim, hidden], linear.bias [dim]) for every cfg->dims entry. The
+ * supported dims are sorted and the default is 1024 when that head is loaded, else the smallest. The
+ * files are mapped, not copied; the mapping is released before returning. */
+uint32_t lg_stella_load(int32_t device, const char* root, const lg_stella_config_t* cfg, void** model);
+
 /* EmbeddingModel::{default_dim, supported_dims, max_tokens} */
 int32_t lg_stella_default_dim(const void* model);
 int32_t lg_stella_supported_dims(const void* model, int32_t* out, int32_t cap);
@@ -133,6 +142,11 @@ typedef struct lg_decoder_weights {
 } lg_decoder_weights_t;
 
 uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const lg_decoder_weights_t* w, void** model);
+/* The decoder from a Qwen2-style fp32 safetensors file (the tensor names of crates/encoders/src/
+ * stella.rs:326-349, plus lm_head.weight [vocab, hidden]; without it the head is tied to the
+ * embedding): exact tensor accounting as lg_stella_load, every matrix quantised to int4 group-32 on
+ * the device (logismos_launch_quantize_int4_g32). */
+uint32_t lg_decoder_load(int32_t device, const char* path, const lg_decoder_config_t* cfg, void** model);
 void lg_decoder_destroy(void* model);
 
 /* One packed step. Sequence i brings new_lens[i] new tokens (ids packed in sequence order in
@@ -254,6 +268,29 @@ uint32_t lg_tp_comm_open(int32_t device, void* region, int32_t rank, int32_t tp,
                          const uint8_t* all_handles, void** comm);
 void lg_tp_comm_destroy(void* comm, int32_t free_region);
 uint32_t lg_tp_reduce_add_f32(void* comm, void* x_f32, void* delta_f32, uint64_t count, void* status_i32, void* stream);
+
+/* ====================================================================================
+ * safetensors reader: crates/loader/src/safetensors.rs:44-197 (Reader::open / get / names / len) with
+ * the dtype map of :199-217 and the truncation guard of crates/loader/src/lib.rs:229-246 (every get
+ * re-stats the file and fails if its length changed since it was mapped). Status codes as
+ * lg_embedding_status: LG_EMB_IO for I/O and format errors, with the reason in lg_last_error().
+ * ==================================================================================== */
+enum lg_dtype { LG_DT_F32 = 0, LG_DT_F16 = 1, LG_DT_BF16 = 2, LG_DT_F8E4M3 = 3, LG_DT_F8E5M2 = 4, LG_DT_I32 = 5, LG_DT_I8 = 6,
+                LG_DT_I4 = 7, LG_DT_U8 = 8 };  /* order of taxis::DType, crates/taxis/src/dtype.rs:16-26 */
+typedef struct lg_tensor_view {
+  int32_t dtype;       /* lg_dtype */
+  int32_t rank;
+  int64_t shape[8];
+  const void* data;    /* into the mapping; valid until lg_safetensors_close */
+  uint64_t nbytes;
+} lg_tensor_view_t;
+uint32_t lg_safetensors_open(const char* path, void** reader);
+void lg_safetensors_close(void* reader);
+int32_t lg_safetensors_len(const void* reader);
+/* name of tensor i in archive order (by on-disk offset); NULL when i is out of range */
+const char* lg_safetensors_name(const void* reader, int32_t i);
+uint64_t lg_safetensors_data_region_start(const void* reader);
+uint32_t lg_safetensors_get(const void* reader, const char* name, lg_tensor_view_t* out);
 
 /* Message of the last failure on the calling thread ("" if none). */
 const char* lg_last_error(void);

@@ -92,7 +92,18 @@ def _declare(l):
         "logismos_launch_gdn_prepare": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
         "logismos_launch_gated_mul_bf16": [vp, i32, vp, i32, i32, i32, i32, vp],
         "logismos_launch_greedy_argmax": [vp, i32, vp, i32, i32, vp],
+        "logismos_launch_temperature_f32": [vp, i32, i32, f32, vp],
+        "logismos_launch_top_k_f32": [vp, i32, i32, i32, vp],
+        "logismos_launch_top_p_f32": [vp, i32, i32, f32, vp],
+        "logismos_launch_min_p_f32": [vp, i32, i32, f32, vp],
+        "logismos_launch_repetition_penalty_f32": [vp, i32, i32, vp, vp, i32, f32, vp],
+        "logismos_launch_multinomial_f32": [vp, i32, i32, vp, vp, vp],
         # model
+        "logismos_launch_quantize_int4_g32": [vp, vp, vp, i32, i32, vp],
+        "lg_safetensors_open": [C.c_char_p, C.POINTER(vp)],
+        "lg_safetensors_get": [vp, C.c_char_p, vp],
+        "lg_stella_load": [i32, C.c_char_p, vp, C.POINTER(vp)],
+        "lg_decoder_load": [i32, C.c_char_p, vp, C.POINTER(vp)],
         "lg_stella_create": [i32, vp, vp, C.POINTER(vp)],
         "lg_stella_encode_ids_batch": [vp, vp, vp, i32, i32, i32, vp],
         "lg_stella_forward_device": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
@@ -141,6 +152,18 @@ def _declare(l):
     l.lg_tp_comm_region_bytes.restype = sz
     l.lg_tp_comm_destroy.argtypes = [vp, i32]
     l.lg_tp_comm_destroy.restype = None
+    l.logismos_set_deterministic.argtypes = [i32]
+    l.logismos_set_deterministic.restype = None
+    l.logismos_get_deterministic.argtypes = []
+    l.logismos_get_deterministic.restype = i32
+    l.lg_safetensors_close.argtypes = [vp]
+    l.lg_safetensors_close.restype = None
+    l.lg_safetensors_len.argtypes = [vp]
+    l.lg_safetensors_len.restype = i32
+    l.lg_safetensors_name.argtypes = [vp, i32]
+    l.lg_safetensors_name.restype = C.c_char_p
+    l.lg_safetensors_data_region_start.argtypes = [vp]
+    l.lg_safetensors_data_region_start.restype = u64
     l.lg_stella_destroy.argtypes = [vp]
     l.lg_stella_destroy.restype = None
     l.lg_decoder_destroy.argtypes = [vp]

@@ -20,6 +20,11 @@ struct LaunchScope {
   LaunchScope() { (void)cudaGetLastError(); }
 };
 
+// Process-wide switch (logismos_set_deterministic): when set, the launchers give up the k splits whose
+// partial sums meet in unordered fp32 reductions, so results are bit-identical from run to run and do
+// not depend on how many rows share a launch.
+bool deterministic();
+
 // Shape-guard failures are reported as cudaErrorInvalidValue (1) without launching.
 constexpr uint32_t kInvalidValue = 1u;
 

@@ -173,6 +173,28 @@ uint32_t lg_error_kind_from_raw(uint32_t code) {
   return LG_ERR_UNKNOWN;
 }
 
+}  // extern "C"
+
+#include <atomic>
+#include <cstdlib>
+namespace lg {
+static std::atomic<int> g_deterministic{-1};
+bool deterministic() {
+  int v = g_deterministic.load(std::memory_order_relaxed);
+  if (v < 0) {  // first use: the environment decides unless the host has set it
+    const char* e = std::getenv("LOGISMOS_DETERMINISTIC");
+    v = (e && e[0] && e[0] != '0') ? 1 : 0;
+    g_deterministic.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
+}  // namespace lg
+
+extern "C" {
+
+void logismos_set_deterministic(int32_t on) { lg::g_deterministic.store(on ? 1 : 0, std::memory_order_relaxed); }
+int32_t logismos_get_deterministic(void) { return lg::deterministic() ? 1 : 0; }
+
 const char* lg_error_kind_name(uint32_t kind) {
   static const char* names[] = {"None", "InvalidValue", "OutOfMemory", "NotInitialized",
                                 "Deinitialized", "InsufficientDriver", "PriorLaunchFailure",

@@ -307,7 +307,7 @@ uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, 
   // few output tiles and a long reduction (the output projections of a small step): the accumulating
   // epilogue lets slices of k run on otherwise idle SMs; every slice gets at least four k blocks
   int splits = 1;
-  if (EPI == LG_EPI_RESID_F32) {
+  if (EPI == LG_EPI_RESID_F32 && !lg::deterministic()) {
     const int all_kb = k / BK;
     if (tiles * 2 <= sm_count() && all_kb >= 8) {
       const int want = sm_count() / tiles;

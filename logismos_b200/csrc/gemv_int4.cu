@@ -20,8 +20,11 @@
 //     high nibbles against x/16, all 16 k-slots of an instruction taken from ONE quantisation
 //     group, so the group scale is applied afterwards in fp32:
 //       acc += s * (sum_lo (136+q) x + sum_hi (1152+16q) x/16 - 136 sum_lo x - 72 sum_hi x).
-//     The correction term is computed once per CTA while x is staged. x/16 is held in fp16: exact
-//     for |x| in [2^-10, 2^20); activations beyond 2^20 in magnitude are outside this kernel's range;
+//     The correction term is computed once per CTA while x is staged. x/16 is held in fp16, whose
+//     range is narrow, so every batch row is first scaled by a power of two that brings its largest
+//     magnitude into [2^13, 2^14) (exact in bf16 and fp16; undone exactly on the fp32 result): rows
+//     of any magnitude, 1e-6 or 1e6, keep full precision, and only elements more than 2^-24 below
+//     their row's maximum fall into fp16's subnormals;
 //   - x is staged in shared memory in the slot order the fragments want (per 8 values:
 //     bf16 [x0,x4,x2,x6] then fp16 [x1,x5,x3,x7]/16), so a lane fetches the B fragments of both
 //     instructions of a group with one 128-bit load.
@@ -59,11 +62,12 @@ LG_DEVINL void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32
 // One 16-byte unit of staged activations from 8 consecutive bf16 values x0..x7 of one batch row:
 // bf16 (x0,x4) (x2,x6) for the low-nibble instruction, fp16 (x1,x5)/16 (x3,x7)/16 for the
 // high-nibble instruction. Returns the unit's share of the group correction.
-LG_DEVINL float stage_unit(uint4 raw, uint4& out) {
-  const float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
-  const float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
-  out.x = __byte_perm(raw.x, raw.z, 0x5410);  // (x0, x4) bf16
-  out.y = __byte_perm(raw.y, raw.w, 0x5410);  // (x2, x6) bf16
+LG_DEVINL float stage_unit(uint4 raw, float f, uint4& out) {
+  float2 v01 = unpack_bf16x2(raw.x), v23 = unpack_bf16x2(raw.y);
+  float2 v45 = unpack_bf16x2(raw.z), v67 = unpack_bf16x2(raw.w);
+  v01.x *= f; v01.y *= f; v23.x *= f; v23.y *= f; v45.x *= f; v45.y *= f; v67.x *= f; v67.y *= f;  // power of two: exact
+  out.x = pack_bf16x2(v01.x, v45.x);  // (x0, x4) bf16
+  out.y = pack_bf16x2(v23.x, v67.x);  // (x2, x6) bf16
   const __half2 h15 = __floats2half2_rn(v01.y * 0.0625f, v45.y * 0.0625f);
   const __half2 h37 = __floats2half2_rn(v23.y * 0.0625f, v67.y * 0.0625f);
   out.z = *reinterpret_cast<const uint32_t*>(&h15);
@@ -72,6 +76,40 @@ LG_DEVINL float stage_unit(uint4 raw, uint4& out) {
   const float lo = (v01.x + v45.x) + (v23.x + v67.x);
   const float hi = (f15.x + f15.y) + (f37.x + f37.y);  // sum of x/16 as the tensor core will see it
   return 136.0f * lo + 1152.0f * hi;
+}
+
+// Per batch row, the power of two f that brings the row's largest magnitude into [2^13, 2^14) and its
+// inverse (both exact); an all-zero or non-finite row keeps f = 1. maxbits, fscale, finv: shared
+// memory arrays of `rows` entries. Ends with a block-wide barrier.
+LG_DEVINL void row_prescale(const __nv_bfloat16* __restrict__ x, int batch, int K, int rows, uint32_t* maxbits, float* fscale,
+                            float* finv) {
+  for (int n = threadIdx.x; n < rows; n += blockDim.x) maxbits[n] = 0u;
+  __syncthreads();
+  const int units_row = K / 8;
+  for (int u = threadIdx.x; u < rows * units_row; u += blockDim.x) {
+    const int n = u / units_row;
+    if (n >= batch) break;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + (size_t)(u % units_row) * 8));
+    uint32_t m = 0;
+    const uint32_t w[4] = {raw.x & 0x7fff7fffu, raw.y & 0x7fff7fffu, raw.z & 0x7fff7fffu, raw.w & 0x7fff7fffu};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m = max(m, max(w[i] & 0xffffu, w[i] >> 16));  // |bf16| orders like its bits
+    if (m > (maxbits[n] >> 16)) atomicMax(&maxbits[n], m << 16);
+  }
+  __syncthreads();
+  for (int n = threadIdx.x; n < rows; n += blockDim.x) {
+    const uint32_t b = maxbits[n];
+    const int e = (int)((b >> 23) & 0xffu);  // biased exponent of the row maximum
+    float f = 1.0f, fi = 1.0f;
+    if (e > 0 && e < 255) {
+      const int fe = min(max(127 + 13 - (e - 127), 2), 252);
+      f = __uint_as_float((uint32_t)fe << 23);
+      fi = __uint_as_float((uint32_t)(254 - fe) << 23);
+    }
+    fscale[n] = f;
+    finv[n] = fi;
+  }
+  __syncthreads();
 }
 
 // y is bf16 [batch, N], or fp32 when the caller keeps full precision up to an argmax
@@ -110,6 +148,9 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
   const int xrow_stride = groups_kc * 64 + 64;  // bytes; +64 keeps 128-bit fragment loads conflict free
   uint8_t* xs = smem;
   float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
+  float* fscale = negcorr + (size_t)groups_kc * NT * 8;
+  float* finv = fscale + NT * 8;
+  row_prescale(x, batch, K, NT * 8, reinterpret_cast<uint32_t*>(finv + NT * 8), fscale, finv);
 
   const int row_base = (blockIdx.x * rt + rt_idx) * 16;
   const int r0 = min(row_base + g, N - 1), r1 = min(row_base + g + 8, N - 1);
@@ -145,7 +186,7 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kk * 8));
         uint4 perm;
-        float s = stage_unit(raw, perm);
+        float s = stage_unit(raw, fscale[n], perm);
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
@@ -193,7 +234,11 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
     }
   }
 
-  // reduce the ks partial sums of each row tile through shared memory, then store bf16
+  // the rows' scales back out of shared memory before the reduction buffer takes its place
+  float iv[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) { iv[nt][0] = finv[nt * 8 + 2 * c]; iv[nt][1] = finv[nt * 8 + 2 * c + 1]; }
+  // reduce the ks partial sums of each row tile through shared memory, then store
   __syncthreads();
   float* red = reinterpret_cast<float*>(smem);  // [warp][NT][4][32]
   if (ks > 1) {
@@ -213,12 +258,12 @@ gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict
       const int b0 = nt * 8 + 2 * c;
       const int ra = row_base + g, rb = row_base + g + 8;
       if (ra < N) {
-        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, v[0]);
-        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, v[1]);
+        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, v[0] * iv[nt][0]);
+        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, v[1] * iv[nt][1]);
       }
       if (rb < N) {
-        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, v[2]);
-        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, v[3]);
+        if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, v[2] * iv[nt][0]);
+        if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, v[3] * iv[nt][1]);
       }
     }
   }
@@ -256,10 +301,13 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
   const int xrow_stride = groups * 64 + 64;
   uint8_t* xs = smem;
   float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
-  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kSlot;
+  float* fscale = negcorr + (size_t)groups * NT * 8;
+  float* finv = fscale + NT * 8;
+  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)NT * 8 * 12 + (size_t)warp * STAGES * kSlot;
   const uint32_t ring = smem_u32(ring_gen);
 
-  // stage x (bf16, fragment order) and the per-group corrections, once
+  // stage x (bf16, fragment order, every row scaled by its power of two) and the per-group corrections, once
+  row_prescale(x, batch, K, NT * 8, reinterpret_cast<uint32_t*>(finv + NT * 8), fscale, finv);
   {
     const int units_row = K / 8;
     const int total = NT * 8 * units_row;
@@ -269,7 +317,7 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + kk * 8));
       uint4 perm;
-      float s = stage_unit(raw, perm);
+      float s = stage_unit(raw, fscale[n], perm);
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
@@ -406,13 +454,14 @@ gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __r
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int b0 = nt * 8 + 2 * c;
+        const float i0 = finv[b0], i1 = finv[b0 + 1];
         if (ra < N) {
-          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0]);
-          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0] * i0);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1] * i1);
         }
         if (rb < N) {
-          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2]);
-          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2] * i0);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3] * i1);
         }
       }
     }
@@ -449,10 +498,13 @@ gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __res
   const int xrow_stride = groups * 64 + 64;
   uint8_t* xs = smem;
   float* negcorr = reinterpret_cast<float*>(smem + (size_t)NT * 8 * xrow_stride);
-  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)warp * STAGES * kWideSlot;
+  float* fscale = negcorr + (size_t)groups * NT * 8;
+  float* finv = fscale + NT * 8;
+  uint8_t* ring_gen = smem + (size_t)NT * 8 * xrow_stride + (size_t)groups * NT * 8 * 4 + (size_t)NT * 8 * 12 + (size_t)warp * STAGES * kWideSlot;
   const uint32_t ring = smem_u32(ring_gen);
 
-  // stage x (bf16, fragment order) and the per-group corrections, once
+  // stage x (bf16, fragment order, every row scaled by its power of two) and the per-group corrections, once
+  row_prescale(x, batch, K, NT * 8, reinterpret_cast<uint32_t*>(finv + NT * 8), fscale, finv);
   {
     const int units_row = K / 8;
     const int total = NT * 8 * units_row;
@@ -462,7 +514,7 @@ gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __res
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (n < batch) raw = __ldg(reinterpret_cast<const uint4*>(x + (size_t)n * K + kk * 8));
       uint4 perm;
-      float s = stage_unit(raw, perm);
+      float s = stage_unit(raw, fscale[n], perm);
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       *reinterpret_cast<uint4*>(xs + (size_t)n * xrow_stride + G * 64 + cc * 16) = perm;
@@ -606,13 +658,14 @@ gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __res
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int b0 = nt * 8 + 2 * c;
+        const float i0 = finv[b0], i1 = finv[b0 + 1];
         if (ra < N) {
-          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0]);
-          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + ra, acc[r][nt][0] * i0);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + ra, acc[r][nt][1] * i1);
         }
         if (rb < N) {
-          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2]);
-          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3]);
+          if (b0 < batch) store_y(y, out_f32, (size_t)b0 * N + rb, acc[r][nt][2] * i0);
+          if (b0 + 1 < batch) store_y(y, out_f32, (size_t)(b0 + 1) * N + rb, acc[r][nt][3] * i1);
         }
       }
     }
@@ -663,7 +716,7 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
   const int row_tiles = (N + 15) / 16;
   if (row_tiles < 2 * sms) return false;  // too few row tiles per SM: the k-split kernel spreads better
   const int groups = K / kGroup;
-  const size_t xbytes = (size_t)NT * 8 * (groups * 64 + 64) + (size_t)groups * NT * 8 * 4;
+  const size_t xbytes = (size_t)NT * 8 * (groups * 64 + 64) + (size_t)groups * NT * 8 * 4 + (size_t)NT * 8 * 12;
   const size_t budget = 200 * 1024;
   if (xbytes + 2 * 8 * slot_bytes(1) > budget) return false;  // x does not fit: chunked kernel
   int warps = (row_tiles + sms - 1) / sms;
@@ -726,7 +779,7 @@ uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y
   while (rt > 1 && row_tiles / rt < 2 * 148) rt >>= 1;
   const int threads = 32 * rt * ks;
   const int groups_kc = kc / kGroup;
-  size_t smem = (size_t)NT * 8 * (groups_kc * 64 + 64) + (size_t)groups_kc * NT * 8 * 4;
+  size_t smem = (size_t)NT * 8 * (groups_kc * 64 + 64) + (size_t)groups_kc * NT * 8 * 4 + (size_t)NT * 8 * 12;
   const size_t red = (size_t)(threads / 32) * NT * 4 * 32 * 4;
   if (red > smem) smem = red;
   if (smem > 48 * 1024) {

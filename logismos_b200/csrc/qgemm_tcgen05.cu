@@ -9,15 +9,15 @@
 // tensor work scales with the real token count and the kernel stays bound by the int4 stream up to
 // about 64 tokens. The work is cut into units (128 weight rows x 256 values of k); one persistent
 // CTA per SM takes a contiguous, equal span of units, and consecutive units of one weight tile form
-// one accumulation with one epilogue. 28 warps:
+// one accumulation with one epilogue. 30 warps:
 //   warp 0      TMA producer of the raw int4 tiles: codes [128 rows x 128 B] (128-byte swizzle) and
 //               fp16 scales [128 rows x 8] per 256 values of k, ring of 3
 //   warp 1      TMA producer of the activation tiles [NT x 64] bf16 (128-byte swizzle), its own ring
 //               of three 32 KB stages so that their L2 latency stays off the critical path
-//   warps 2, 3  one thread each issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=NT, K=16) for two
-//               of the four k blocks of every unit, the weight operand read from TMEM and the
-//               activations from shared memory, into its own fp32 accumulators in TMEM (warp 2 also
-//               allocates the tensor memory)
+//   warps 2, 3, 28, 29  one thread each issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=NT, K=16)
+//               for one of the four k blocks of every unit (two each, from warps 2 and 3 only, above 64
+//               tokens), the weight operand read from TMEM and the activations from shared memory,
+//               into its own fp32 accumulators in TMEM (warp 2 also allocates the tensor memory)
 //   warps 4-19  dequantise: four groups of four warps, group g owns k block g of every unit; thread =
 //               one weight row x 64 values; the raw stage is released as soon as it is in registers;
 //               nibble pairs -> bf16 by byte permute + one logic op (exact 136 + q), minus 136, times
@@ -36,6 +36,17 @@
 #include "logismos_kernels.h"
 #include "tcgen05.cuh"
 
+// Development aid: built with -DLG_QTRACE the first CTA records, per unit, the clock at the points of
+// the hand-offs between its roles into a global buffer (logismos_qtrace_buffer); never defined in the
+// library build.
+#ifdef LG_QTRACE
+__device__ long long g_qtrace[4096 * 12];
+#define QTRACE(unit, slot) do { if (blockIdx.x == 0 && (unit) < 4096) g_qtrace[(unit) * 12 + (slot)] = clock64(); } while (0)
+extern "C" void* logismos_qtrace_buffer() { void* p = nullptr; cudaGetSymbolAddress(&p, g_qtrace); return p; }
+#else
+#define QTRACE(unit, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace lg;
@@ -51,9 +62,9 @@ constexpr int kRawScales = kWRows * 16;           // 2 KB
 constexpr int kRawStage = kRawCodes + kRawScales; // 18 KB (codes first: 1024-aligned)
 constexpr int kWdCols = kKB / 2;                  // TMEM columns of one dequantised k block: 128 lanes x 32 columns x 2 bf16
 constexpr int kDqWarps = 4 * kGroups;             // 16
-constexpr int kIssuers = 2;                       // MMA-issuing threads (warps 2 and 3), two k blocks of every unit each
+constexpr int kMaxIssuers = 4;                    // MMA-issuing threads: warps 2, 3 and (up to 64 tokens) 28, 29, one per scheduler
 constexpr int kEpiWarps = 8;                      // two per TMEM lane quarter, half of the token columns each
-constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps);  // 896
+constexpr int kQThreads = 32 * (4 + kDqWarps + kEpiWarps + 2);  // 960
 
 template <int NT>
 struct QCfg {
@@ -67,7 +78,11 @@ struct QCfg {
   // accumulators. One CTA per SM, so the whole tensor memory is this CTA's.
   static constexpr int kWBufCols = kGroups * kWdCols;  // 128
   static constexpr int kAccCol = 2 * kWBufCols;
-  static constexpr int kAccBufs = NT <= 64 ? 2 : 1;   // accumulator buffers per issuing thread
+  // An issuing thread spends on the order of a hundred cycles per tcgen05.mma whatever the tile width
+  // (traced: 8 MMAs and their waits took 1100-1600 of the 2500 cycles a unit cost with two issuers), so
+  // up to 64 tokens every k block of a unit has its own issuing thread and its own accumulator.
+  static constexpr int kIssuers = NT <= 64 ? 4 : 2;
+  static constexpr int kAccBufs = NT <= 32 ? 2 : 1;   // accumulator buffers per issuing thread
   static constexpr int kTmemCols = 512;
   static_assert(kAccCol + kIssuers * kAccBufs * NT <= 512, "tensor memory budget");
 };
@@ -149,7 +164,7 @@ template <int NT>
 __global__ void __launch_bounds__(kQThreads, 1)
 qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_codes,
                             const __grid_constant__ CUtensorMap map_scales, float* __restrict__ acc, int M, int N, int ldc,
-                            int n_raw, int total_units, int* __restrict__ status) {
+                            int n_raw, int total_units, int whole_tiles, int* __restrict__ status) {
   using C = QCfg<NT>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -164,10 +179,11 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   auto wd_full = [&](int wb, int g) { return bars + 8u * (2 * kRawStages + wb * kGroups + g); };
   auto wd_empty = [&](int wb) { return bars + 8u * (2 * kRawStages + 2 * kGroups + wb); };
   auto tfull = [&](int is, int b) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 2 + is * 2 + b); };
-  auto tempty = [&](int b) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 6 + b); };
-  auto a_full = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 8 + s); };
-  auto a_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 8 + C::kAStages + s); };
-  constexpr int kNumBars = 2 * kRawStages + 2 * kGroups + 8 + 2 * C::kAStages;
+  auto tempty = [&](int b) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 2 + 2 * kMaxIssuers + b); };
+  auto a_full = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 4 + 2 * kMaxIssuers + s); };
+  auto a_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kGroups + 4 + 2 * kMaxIssuers + C::kAStages + s); };
+  constexpr int kNumBars = 2 * kRawStages + 2 * kGroups + 4 + 2 * kMaxIssuers + 2 * C::kAStages;
+  constexpr int kIssuers = C::kIssuers;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_gen + 8 * kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * kNumBars + 8);
 
@@ -175,8 +191,13 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // this CTA's contiguous span of units; unit u = (weight tile u / n_raw, raw block u % n_raw). Units of
   // one tile that fall into one span are one accumulation ("segment") with one epilogue. The weight
   // tiles of a unit go to tensor-memory buffer (unit count & 1).
-  const int u0 = (int)((long long)total_units * blockIdx.x / gridDim.x);
-  const int u1 = (int)((long long)total_units * (blockIdx.x + 1) / gridDim.x);
+  // whole_tiles: spans end at tile boundaries, so every output element is added exactly once (no
+  // reduction between CTAs: bit-identical results from run to run, at the price of uneven spans)
+  const int n_tiles_all = total_units / n_raw;
+  const int u0 = whole_tiles ? (int)((long long)n_tiles_all * blockIdx.x / gridDim.x) * n_raw
+                             : (int)((long long)total_units * blockIdx.x / gridDim.x);
+  const int u1 = whole_tiles ? (int)((long long)n_tiles_all * (blockIdx.x + 1) / gridDim.x) * n_raw
+                             : (int)((long long)total_units * (blockIdx.x + 1) / gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), kDqWarps); }
@@ -186,7 +207,10 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
     // an activation stage of a whole unit is read by both issuing threads, one of half a unit by one
     for (int s = 0; s < C::kAStages; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), C::kABlocksPerStage == kGroups ? kIssuers : 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull(0, b), 1); mbar_init(tfull(1, b), 1); mbar_init(tempty(b), kEpiWarps); }
+    for (int b = 0; b < 2; ++b) {
+      for (int is = 0; is < kMaxIssuers; ++is) mbar_init(tfull(is, b), 1);
+      mbar_init(tempty(b), kEpiWarps);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -205,14 +229,17 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (lane == 0) {
       int rs = 0;
       uint32_t rphase = 0;
+      int tile = u0 / n_raw, rb = u0 % n_raw;  // carried along: no division in the loop
       for (int u = u0; u < u1; ++u) {
-        const int tile = u / n_raw, kk = (u % n_raw) * kRawK;
+        const int kk = rb * kRawK;
         if (!mbar_wait(raw_empty(rs), rphase ^ 1u, abort_flag)) break;
         mbar_expect_tx(raw_full(rs), (uint32_t)kRawStage);
         const uint32_t dst = raw_base + rs * kRawStage;
         tma_load_2d(dst, &map_codes, raw_full(rs), kk / 2, tile * kWRows);
         tma_load_2d(dst + kRawCodes, &map_scales, raw_full(rs), kk / 32, tile * kWRows);
+        QTRACE(u - u0, 0);
         if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+        if (++rb == n_raw) { rb = 0; ++tile; }
       }
     }
   } else if (warp == 1) {
@@ -222,11 +249,14 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       int as = 0;
       uint32_t aphase = 0;
       bool ok = true;
+      int rb = u0 % n_raw;
       for (int u = u0; u < u1 && ok; ++u) {
-        const int kk = (u % n_raw) * kRawK;
+        const int kk = rb * kRawK;
+        if (++rb == n_raw) rb = 0;
 #pragma unroll
         for (int h = 0; h < kGroups / C::kABlocksPerStage; ++h) {
           if (!mbar_wait(a_empty(as), aphase ^ 1u, abort_flag)) { ok = false; break; }
+          if (h == 0) QTRACE(u - u0, 10);
           mbar_expect_tx(a_full(as), (uint32_t)C::kAStage);
 #pragma unroll
           for (int b = 0; b < C::kABlocksPerStage; ++b)
@@ -235,13 +265,13 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
       }
     }
-  } else if (warp == 2 || warp == 3) {
-    // ---------------- MMA issuers: thread `is` takes k blocks 2 is and 2 is + 1 of every unit into its
-    // own accumulators (the epilogue adds the two). Issuing an MMA or a commit costs a thread tens of
-    // cycles whatever the tile size, because it shares its scheduler with busy dequantising warps; two
-    // issuers halve that serial cost, and descriptors are built from constants and one add.
+  } else if (warp == 2 || warp == 3 || ((warp == 28 || warp == 29) && kIssuers == 4)) {
+    // ---------------- MMA issuers: thread `is` takes kGroups / kIssuers k blocks of every unit into its
+    // own accumulators (the epilogue adds them up). Issuing an MMA or a commit costs a thread on the
+    // order of a hundred cycles whatever the tile size, so the k blocks of a unit are issued in
+    // parallel by threads on different schedulers; descriptors are built from constants and one add.
     if (lane == 0) {
-      const int is = warp - 2;
+      const int is = warp < 4 ? warp - 2 : warp - 26;
       constexpr uint32_t idesc = make_idesc<NT>();
       constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
       constexpr int per = C::kABlocksPerStage;          // k blocks per activation stage: 4 or 2
@@ -251,8 +281,10 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       // activation stages in the order this thread meets them: every stage (per == 4) or every second one
       int ai = per == kGroups ? 0 : is;
       bool ok = true;
+      int rb_next = u0 % n_raw;
       for (int u = u0; u < u1 && ok; ++u, ++n_unit) {
-        const int rb = u % n_raw;
+        const int rb = rb_next;
+        if (++rb_next == n_raw) rb_next = 0;
         const bool seg_start = (u == u0) || rb == 0, seg_end = (u + 1 == u1) || rb == n_raw - 1;
         const int buf = seg % C::kAccBufs, wb = n_unit & 1;
         const uint32_t tphase = (uint32_t)(seg / C::kAccBufs) & 1u;
@@ -261,14 +293,17 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           if (!mbar_wait(tempty(buf), tphase ^ 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
         }
+        if (is == 0) QTRACE(u - u0, 11);
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::kAccCol + (is * C::kAccBufs + buf) * NT);
         const int as = ai % C::kAStages;
         if (!mbar_wait(a_full(as), (uint32_t)(ai / C::kAStages) & 1u, abort_flag)) { ok = false; break; }
+        if (is == 0) QTRACE(u - u0, 6);
 #pragma unroll
         for (int j = 0; j < kMine; ++j) {
           const int g = is * kMine + j;
           if (!mbar_wait(wd_full(wb, g), wphase, abort_flag)) { ok = false; break; }
           tc_fence_after();
+          if (is == 0 && j == 0) QTRACE(u - u0, 7);
           const uint32_t w_tmem = tmem_base + (uint32_t)(wb * C::kWBufCols + g * kWdCols);  // 8 columns per 16 values of k
           const uint32_t a_lo = a_lo0 + (uint32_t)(as * (C::kAStage >> 4) + (g % per) * (C::kABlock >> 4));
 #pragma unroll
@@ -276,8 +311,10 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             tc_mma_bf16_ts(d_tmem, w_tmem + 8u * k, ((uint64_t)desc_hi << 32) | (a_lo + 2u * k), idesc, (!seg_start || j || k) ? 1u : 0u);
         }
         if (!ok) break;
+        if (is == 0) QTRACE(u - u0, 8);
         tc_commit(a_empty(as));
         tc_commit(wd_empty(wb));
+        if (is == 0) QTRACE(u - u0, 9);
         ai += per == kGroups ? 1 : kIssuers;
         if (seg_end) { tc_commit(tfull(is, buf)); ++seg; }
       }
@@ -294,7 +331,9 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     for (int u = u0; u < u1 && ok; ++u, ++n_unit) {
       const int wb = n_unit & 1;
       const uint32_t wphase = ((uint32_t)n_unit >> 1) & 1u;
+      if (wd == 0 && lane == 0) QTRACE(u - u0, 1);
       if (!mbar_wait(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
+      if (wd == 0 && lane == 0) QTRACE(u - u0, 2);
       const uint8_t* raw = smem_gen + rs * kRawStage;
       // this row's 64 codes of k block g (two 16-byte chunks, swizzled by the TMA) and their two scales
       const uint4 c0 = *reinterpret_cast<const uint4*>(raw + row * 128 + (((2 * g) ^ (row & 7)) << 4));
@@ -307,46 +346,58 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       uint4 o[8];
       o[0] = dequant_word(c0.x, s0); o[1] = dequant_word(c0.y, s0); o[2] = dequant_word(c0.z, s0); o[3] = dequant_word(c0.w, s0);
       o[4] = dequant_word(c1.x, s1); o[5] = dequant_word(c1.y, s1); o[6] = dequant_word(c1.z, s1); o[7] = dequant_word(c1.w, s1);
+      if (wd == 0 && lane == 0) QTRACE(u - u0, 3);
       if (!mbar_wait(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      if (wd == 0 && lane == 0) QTRACE(u - u0, 4);
       tc_st32(wt0 + (uint32_t)(wb * C::kWBufCols), o);  // lane = weight row, 32 columns = its 64 bf16 in k order
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(wd_full(wb, g));
+      if (wd == 0 && lane == 0) QTRACE(u - u0, 5);
     }
-  } else if (warp >= 4 + kDqWarps) {
+  } else if (warp >= 4 + kDqWarps && warp < 4 + kDqWarps + kEpiWarps) {
     // ---------------- epilogue: TMEM (lane = weight row, column = token) -> fp32 reductions ----------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
     const int chalf = (warp - 4 - kDqWarps) >> 2;  // which half of the token columns
     int seg = 0;
     bool ok = true;
-    for (int u = u0; u < u1 && ok; ++u) {
-      const int rb = u % n_raw;
-      if (!((u + 1 == u1) || rb == n_raw - 1)) continue;  // not the end of a segment
+    // segment ends: the last unit of every weight tile in the span, and the span's last unit
+    for (int u = u0 + (n_raw - 1 - u0 % n_raw); ok && u0 < u1; u += n_raw) {
+      if (u >= u1 - 1) u = u1 - 1;
       const int buf = seg % C::kAccBufs;
       const uint32_t tphase = (uint32_t)(seg / C::kAccBufs) & 1u;
-      if (!mbar_wait_relaxed(tfull(0, buf), tphase, abort_flag) || !mbar_wait_relaxed(tfull(1, buf), tphase, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int is = 0; is < kIssuers; ++is)
+        if (ok && !mbar_wait_relaxed(tfull(is, buf), tphase, abort_flag)) ok = false;
+      if (!ok) break;
       tc_fence_after();
       const int f = (u / n_raw) * kWRows + q * 32 + lane;
 #pragma unroll 1
       for (int c = chalf * (NT / 2); c < (chalf + 1) * (NT / 2); c += 16) {
         if (c >= M) break;
-        uint32_t r[16], r1[16];
-        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + buf * NT + c), r);
-        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + (C::kAccBufs + buf) * NT + c), r1);
-        tc_wait_ld();
+        float sum[16];
+#pragma unroll
+        for (int is = 0; is < kIssuers; ++is) {
+          uint32_t r[16];
+          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(C::kAccCol + (is * C::kAccBufs + buf) * NT + c), r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[j] = is ? sum[j] + __uint_as_float(r[j]) : __uint_as_float(r[j]);
+        }
         if (f < N) {
           float* dst = acc + (size_t)c * ldc + f;
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (c + j < M) atomicAdd(dst + (size_t)j * ldc, __uint_as_float(r[j]) + __uint_as_float(r1[j]));
+            if (c + j < M) atomicAdd(dst + (size_t)j * ldc, sum[j]);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty(buf));
       ++seg;
+      if (u == u1 - 1) break;
     }
   }
 
@@ -435,8 +486,10 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
   const long total = (long)n_tiles * n_raw;
   if (total > 2147483647l) return lg::kInvalidValue;
   const int slots = sm_count();
-  const int grid = total < slots ? (int)total : slots;
-  kern<<<grid, kQThreads, QCfg<NT>::kSmem, stream>>>(ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, status);
+  const int whole = lg::deterministic() ? 1 : 0;
+  const long work = whole ? (long)n_tiles : total;
+  const int grid = work < slots ? (int)work : slots;
+  kern<<<grid, kQThreads, QCfg<NT>::kSmem, stream>>>(ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, status);
   return lg::launch_status();
 }
 

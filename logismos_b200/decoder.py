@@ -98,6 +98,21 @@ class DecoderModel:
             raise ComputeError(lib.lg_last_error().decode())
         self._h, self.cfg, self.max_blocks = h, cfg, max_blocks_per_seq
 
+    @classmethod
+    def load(cls, path: str, cfg: dict, n_pool_blocks: int, max_blocks_per_seq: int, max_step_tokens: int, max_step_seqs: int,
+             device: int = 0, keep_bf16_copy: bool = True) -> "DecoderModel":
+        """The decoder from a Qwen2-style fp32 safetensors file: tensor accounting and int4 group-32
+        quantisation on the device by the native loader (``lg_decoder_load``)."""
+        c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"], cfg["max_pos"],
+                 cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs, int(keep_bf16_copy))
+        h = C.c_void_p()
+        rc = lib.lg_decoder_load(device, str(path).encode(), C.byref(c), C.byref(h))
+        if rc:
+            raise (IOError if rc == 5 else ComputeError)(lib.lg_last_error().decode())
+        self = cls.__new__(cls)
+        self._h, self.cfg, self.max_blocks = h, cfg, max_blocks_per_seq
+        return self
+
     def close(self):
         if getattr(self, "_h", None):
             lib.lg_decoder_destroy(self._h)

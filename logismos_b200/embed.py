@@ -31,15 +31,28 @@ class ComputeError(EmbeddingError):
     pass
 
 
-_ERR = {1: InputTooLong, 2: UnsupportedDim, 4: ComputeError}
+class TokenizeError(EmbeddingError):
+    pass
+
+
+class IoError(EmbeddingError):
+    pass
+
+
+class UnsupportedPrompt(EmbeddingError):
+    pass
+
+
+_ERR = {1: InputTooLong, 2: UnsupportedDim, 3: TokenizeError, 4: ComputeError, 5: IoError, 6: UnsupportedPrompt}
 
 
 @dataclass
 class EncodeOpts:
-    """core::EncodeOpts (crates/core/src/lib.rs:59-69); ``prompt`` is applied by the text front end,
-    which stays on the caller's side of the id-level boundary."""
+    """core::EncodeOpts (crates/core/src/lib.rs:59-69). ``prompt`` (a ``text.Prompt``) is applied by the
+    text front end (``text.StellaTextModel``); the id-level entry points ignore it."""
     dim: Optional[int] = None
     max_tokens: Optional[int] = None
+    prompt: Optional[object] = None
 
 
 class _Cfg(C.Structure):
@@ -91,6 +104,28 @@ class StellaModel:
         self._h = h
         self.cfg = cfg
         self.device = device
+
+    @classmethod
+    def load(cls, root: str, dims: Sequence[int] = (1024,), cfg: Optional[dict] = None, device: int = 0, max_batch_tokens: int = 8192,
+             max_batch_seqs: int = 256, fuse_swiglu: bool = True) -> "StellaModel":
+        """``StellaModel::load(root, dims)`` (crates/embed/src/stella.rs:138-201) from a checkpoint directory:
+        ``root/model.safetensors`` and one ``root/2_Dense_<dim>/model.safetensors`` per requested dim,
+        read, validated and uploaded by the native loader (``lg_stella_load``). ``cfg`` defaults to the
+        Stella-1.5B configuration the reference hard-codes."""
+        if cfg is None:
+            from .synthetic import STELLA_1_5B
+            cfg = STELLA_1_5B
+        dims = list(dims)
+        c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"],
+                 cfg["max_pos"], cfg["rms_eps"], cfg["rope_theta"], cfg.get("max_tokens", 512), len(dims),
+                 (C.c_int32 * 8)(*dims), max_batch_tokens, max_batch_seqs, int(fuse_swiglu))
+        h = C.c_void_p()
+        rc = lib.lg_stella_load(device, str(root).encode(), C.byref(c), C.byref(h))
+        if rc:
+            raise _ERR.get(rc, ComputeError)(lib.lg_last_error().decode())
+        self = cls.__new__(cls)
+        self._h, self.cfg, self.device = h, cfg, device
+        return self
 
     def close(self):
         if getattr(self, "_h", None):

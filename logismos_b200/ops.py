@@ -278,15 +278,19 @@ def pool_head(hidden, cu_seqlens, head_w, head_b, sync=True):
 
 # ---- decode path -----------------------------------------------------------------------------
 
-def gemv_int4(codes, scales, x, out=None, sync=True):
-    """y = x @ dequant(codes, scales)^T. codes u8 [n, k/2], scales f16 [n, k/32], x bf16 [b, k]."""
+def gemv_int4(codes, scales, x, out=None, sync=True, out_f32=False):
+    """y = x @ dequant(codes, scales)^T. codes u8 [n, k/2], scales f16 [n, k/32], x bf16 [b, k]; y bf16, or
+    the unrounded fp32 accumulators with ``out_f32`` (what the lm_head hands to the argmax)."""
     _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2); _req(x, "x", torch.bfloat16, 2)
     n, k = codes.shape[0], codes.shape[1] * 2
     if x.shape[1] != k or tuple(scales.shape) != (n, k // 32):
         raise InvalidOp("gemv_int4: shape mismatch")
-    y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.bfloat16, device=x.device)
+    y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    if y.dtype != (torch.float32 if out_f32 else torch.bfloat16):
+        raise InvalidOp("gemv_int4: out has the wrong dtype")
+    fn = lib.logismos_launch_gemv_int4_g32_f32 if out_f32 else lib.logismos_launch_gemv_int4_g32_bf16
     with torch.cuda.device(x.device):
-        check(lib.logismos_launch_gemv_int4_g32_bf16(_p(codes), _p(scales), _p(x), _p(y), x.shape[0], n, k, _stream()), "gemv_int4_g32")
+        check(fn(_p(codes), _p(scales), _p(x), _p(y), x.shape[0], n, k, _stream()), "gemv_int4_g32")
         _done(sync)
     return y
 

@@ -153,6 +153,68 @@ void orc_unpack_turbo3(const uint8_t packed[12], uint8_t idx[32]) {
   }
 }
 
+/* ---- TurboQuant 3-bit head codec (crates/quant/src/lib.rs:73-114, :316-413) ---------------------
+ * One 128-value head chunk -> four 14-byte blocks (2-byte little-endian fp16 norm, repeated in every
+ * block, + 12 bytes of 3-bit codebook indices): L2 norm (sequential fp32 sum of squares), v / norm,
+ * normalised Walsh-Hadamard transform over 128 points, nearest of 8 Lloyd-Max centroids (first minimum
+ * wins), indices packed as above. Decoding looks the centroids up, applies the same transform (it is
+ * its own inverse) and multiplies by the stored norm. */
+static const float kTurbo3Codebook[8] = {-0.1883972972f, -0.1181399059f, -0.0665857641f, -0.0216044751f,
+                                         0.0216041461f,  0.0665854520f,  0.1181396281f,  0.1883970748f};  // lib.rs:73-82
+
+// lib.rs:90-114: butterflies with h = 1, 2, ..., 64 (lo' = lo + hi, hi' = lo - hi), then * 1/sqrt(128)
+void orc_fwht_128(float* d) {
+  for (int h = 1; h < 128; h *= 2)
+    for (int base = 0; base < 128; base += 2 * h)
+      for (int i = 0; i < h; ++i) {
+        const float x = d[base + i], y = d[base + h + i];
+        d[base + i] = x + y;
+        d[base + h + i] = x - y;
+      }
+  const float scale = 0.08838834764831844f;
+  for (int i = 0; i < 128; ++i) d[i] *= scale;
+}
+
+// lib.rs:316-360; out = 4 blocks x 14 bytes
+void orc_turbo3_encode_head(const float* values, uint8_t* out) {
+  float sum_sq = 0.0f;
+  for (int i = 0; i < 128; ++i) sum_sq += values[i] * values[i];
+  const float norm = std::sqrt(sum_sq);
+  const uint16_t nb = f32_to_f16(norm);
+  float t[128];
+  for (int i = 0; i < 128; ++i) t[i] = norm > 1e-12f ? values[i] / norm : 0.0f;
+  orc_fwht_128(t);
+  for (int bi = 0; bi < 4; ++bi) {
+    uint8_t idx[32];
+    for (int i = 0; i < 32; ++i) {
+      const float v = t[bi * 32 + i];
+      int best = 0;
+      float bd = std::fabs(v - kTurbo3Codebook[0]);
+      for (int c = 1; c < 8; ++c) {
+        const float dd = std::fabs(v - kTurbo3Codebook[c]);
+        if (dd < bd) { bd = dd; best = c; }
+      }
+      idx[i] = (uint8_t)best;
+    }
+    uint8_t* blk = out + bi * 14;
+    blk[0] = (uint8_t)(nb & 0xff);
+    blk[1] = (uint8_t)(nb >> 8);
+    orc_pack_turbo3(idx, blk + 2);
+  }
+}
+
+// lib.rs:378-413
+void orc_turbo3_decode_head(const uint8_t* in, float* out) {
+  for (int bi = 0; bi < 4; ++bi) {
+    uint8_t idx[32];
+    orc_unpack_turbo3(in + bi * 14 + 2, idx);
+    for (int i = 0; i < 32; ++i) out[bi * 32 + i] = kTurbo3Codebook[idx[i]];
+  }
+  orc_fwht_128(out);
+  const float norm = f16_to_f32((uint16_t)(in[0] | (in[1] << 8)));
+  for (int i = 0; i < 128; ++i) out[i] *= norm;
+}
+
 /* ===== [NEW] int4 group-32 weights ========================================
  * Layout anchored on Turbo4Block's nibble order (lib.rs:272-301): weight row n, column k
  * lives in byte packed[n*k_dim/2 + k/2], low nibble for even k, high nibble for odd k, as a

@@ -139,6 +139,10 @@ int orc_pack_turbo4(const uint8_t idx[32], uint8_t out[16]);
 void orc_unpack_turbo4(const uint8_t packed[16], uint8_t idx[32]);
 int orc_pack_turbo3(const uint8_t idx[32], uint8_t out[12]);
 void orc_unpack_turbo3(const uint8_t packed[12], uint8_t idx[32]);
+/* TurboQuant 3-bit head codec (crates/quant/src/lib.rs:90-114, :316-413): 128 values <-> 4 x 14 bytes */
+void orc_fwht_128(float* data128);
+void orc_turbo3_encode_head(const float* values128, uint8_t* out56);
+void orc_turbo3_decode_head(const uint8_t* in56, float* out128);
 /* codes: int8 in [-8,7], [n,k] -> packed [n,k/2] two's-complement nibbles */
 int orc_int4_pack(const int8_t* codes, size_t n, size_t k, uint8_t* packed);
 void orc_int4_unpack(const uint8_t* packed, size_t n, size_t k, int8_t* codes);
@@ -198,6 +202,15 @@ void orc_f32_to_bf16(const float* x, size_t n, uint16_t* y);
 void orc_bf16_to_f32(const uint16_t* x, size_t n, float* y);
 void orc_f32_to_f16(const float* x, size_t n, uint16_t* y);
 void orc_f16_to_f32(const uint16_t* x, size_t n, float* y);
+
+/* ---- crates/decode: logit processors and samplers (processors.rs:15-199, sampler.rs:31-58),
+ * one row of logits in place; orc_multinomial takes the uniform draw the reference takes from its RNG */
+void orc_temperature(float* logits, size_t n, float temperature);
+void orc_top_k(float* logits, size_t n, size_t k);
+void orc_top_p(float* logits, size_t n, float p);
+void orc_min_p(float* logits, size_t n, float p);
+void orc_repetition_penalty(float* logits, size_t n, const uint32_t* tokens, size_t n_tokens, float penalty);
+uint32_t orc_multinomial(const float* logits, size_t n, float u);
 
 #ifdef __cplusplus
 }

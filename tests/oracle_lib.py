@@ -599,3 +599,72 @@ class OracleHybrid:
         if rc:
             raise ValueError(f"hybrid forward: error {rc}")
         return hid, lg
+
+
+# ---- crates/decode: logit processors and samplers --------------------------------------------
+
+lib.orc_multinomial.restype = C.c_uint32
+lib.orc_top_k.argtypes = [f32p, c_sz, c_sz]
+lib.orc_temperature.argtypes = [f32p, c_sz, C.c_float]
+lib.orc_top_p.argtypes = [f32p, c_sz, C.c_float]
+lib.orc_min_p.argtypes = [f32p, c_sz, C.c_float]
+lib.orc_repetition_penalty.argtypes = [f32p, c_sz, u32p, c_sz, C.c_float]
+lib.orc_multinomial.argtypes = [f32p, c_sz, C.c_float]
+
+
+def temperature(logits, t):
+    """TemperatureScale::process (crates/decode/src/processors.rs:18-28) on a copy of one row."""
+    x = f32(logits).copy(); lib.orc_temperature(P(x), c_sz(x.size), C.c_float(t)); return x
+
+
+def top_k(logits, k):
+    """TopK::process (processors.rs:50-82)."""
+    x = f32(logits).copy(); lib.orc_top_k(P(x), c_sz(x.size), c_sz(k)); return x
+
+
+def top_p(logits, p):
+    """TopP::process (processors.rs:89-122)."""
+    x = f32(logits).copy(); lib.orc_top_p(P(x), c_sz(x.size), C.c_float(p)); return x
+
+
+def min_p(logits, p):
+    """MinP::process (processors.rs:130-146)."""
+    x = f32(logits).copy(); lib.orc_min_p(P(x), c_sz(x.size), C.c_float(p)); return x
+
+
+def repetition_penalty(logits, tokens, penalty):
+    """RepetitionPenalty::process (processors.rs:160-181)."""
+    x = f32(logits).copy()
+    t = np.ascontiguousarray(tokens, dtype=np.uint32)
+    lib.orc_repetition_penalty(P(x), c_sz(x.size), P(t, u32p), c_sz(t.size), C.c_float(penalty))
+    return x
+
+
+def multinomial(logits, u):
+    """MultinomialSampler::sample (crates/decode/src/sampler.rs:31-58) for the uniform draw u."""
+    x = f32(logits)
+    return int(lib.orc_multinomial(P(x), c_sz(x.size), C.c_float(u)))
+
+
+# ---- TurboQuant 3-bit head codec (crates/quant/src/lib.rs:90-114, :316-413) ----------------------
+
+def fwht_128(x):
+    d = f32(x).copy(); assert d.size == 128
+    lib.orc_fwht_128(P(d)); return d
+
+
+def turbo3_encode(values):
+    """[..., 128] fp32 -> [..., 56] uint8 (four 14-byte blocks per 128-value head chunk)."""
+    v = f32(values).reshape(-1, 128)
+    out = np.empty((v.shape[0], 56), np.uint8)
+    for i in range(v.shape[0]):
+        lib.orc_turbo3_encode_head(P(v[i]), P(out[i], u8p))
+    return out.reshape(np.shape(values)[:-1] + (56,))
+
+
+def turbo3_decode(blocks):
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 56)
+    out = np.empty((b.shape[0], 128), np.float32)
+    for i in range(b.shape[0]):
+        lib.orc_turbo3_decode_head(P(b[i], u8p), P(out[i]))
+    return out.reshape(np.shape(blocks)[:-1] + (128,))

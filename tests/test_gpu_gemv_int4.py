@@ -35,6 +35,28 @@ def test_benchmark_shapes(n, k, b):
     assert np.abs(y - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
 
 
+@pytest.mark.parametrize("n,k", [(1536, 1536), (151936, 1536), (96, 8960)])
+def test_activations_of_any_magnitude_keep_full_precision(n, k):
+    """Rows of tiny and of huge activations in one batch (1e-6 ... 1e5, and one all-zero row): every
+    row is checked against the oracle relative to ITS OWN magnitude (the staged operands are scaled per
+    row by a power of two, so no row falls into the subnormals of fp16)."""
+    rng = np.random.default_rng(n + k)
+    codes = rng.integers(-8, 8, (n, k), dtype=np.int8)
+    scales = np.abs(rng.standard_normal((n, k // 32)) * 0.02).astype(np.float16)
+    mags = np.array([1e-6, 1e-4, 3e-3, 1.0, 50.0, 1e5, 0.0, 2e-5], np.float64)
+    x_t, x = bf16_cuda(rng.standard_normal((8, k)) * mags[:, None])
+    packed = O.int4_pack(codes)
+    y = to_np(ops.gemv_int4(torch.from_numpy(packed).to(DEV), torch.from_numpy(scales).to(DEV), x_t, out_f32=True))
+    rows = np.arange(n) if n <= 2048 else rng.choice(n, 2048, replace=False)
+    ref = O.int4_gemv(np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scales[rows]).view(np.uint16), x)
+    for b in range(8):
+        den = np.abs(ref[b]).max()
+        if den == 0:
+            assert (y[b, rows] == 0).all()
+        else:
+            assert np.abs(y[b, rows] - ref[b]).max() / den <= 1e-4, (b, mags[b])
+
+
 @pytest.mark.parametrize("n,k,b", [(16, 128, 1), (17, 256, 3), (40, 384, 9), (100, 4224, 33), (31, 640, 64)])
 def test_ragged_shapes(n, k, b):
     codes, packed, scales, x_t, x = make_case(n, k, b, 11 * n + b)

@@ -248,3 +248,28 @@ def test_fp16_refs():
     assert qk.tolist() == [1, 2, 3, 4]
     with pytest.raises(ValueError):
         O.rope_apply_fp16_ref(np.ones(7, np.float16), t, 1, 1, 1, 4)
+
+
+def test_turbo3_head_codec_reference_properties():
+    """crates/quant/src/lib.rs:658-697: the transform is an involution and preserves the norm; the
+    reference's round-trip vector stays under its MSE bound; block layout: the fp16 norm, little-endian,
+    repeated in each of the four 14-byte blocks."""
+    i = np.arange(128, dtype=np.float32)
+    d = (np.sin(i) * 0.5).astype(np.float32)
+    assert np.abs(O.fwht_128(O.fwht_128(d)) - d).max() < 1e-5
+    c = (np.cos(i) * 0.3).astype(np.float32)
+    assert abs(np.linalg.norm(O.fwht_128(c)) - np.linalg.norm(c)) < 1e-5
+    src = (np.sin(i * 0.1) * 0.1 + np.cos(i * 0.03) * 0.1).astype(np.float32)
+    blocks = O.turbo3_encode(src)
+    assert blocks.shape == (56,)
+    dec = O.turbo3_decode(blocks)
+    assert np.mean((src - dec) ** 2) < 0.05
+    norm_bits = np.float16(np.sqrt(np.sum(src.astype(np.float32) ** 2, dtype=np.float32))).view(np.uint16)
+    for b in range(4):
+        assert blocks[14 * b] == norm_bits & 0xff and blocks[14 * b + 1] == norm_bits >> 8
+    # indices come back through the pinned 3-bit packing
+    idx = np.concatenate([O.unpack_turbo3(blocks[14 * b + 2:14 * b + 14]) for b in range(4)])
+    assert idx.max() <= 7 and idx.shape == (128,)
+    # an all-zero chunk: norm 0, the transform of zeros picks the centroid nearest to 0, decode gives zeros
+    z = O.turbo3_decode(O.turbo3_encode(np.zeros(128, np.float32)))
+    assert (z == 0).all()

@@ -3,8 +3,9 @@ memory where they decode (an engine whose allocator has already given every free
 the KV pool and the weights; a decode thread that must not hit the device-wide synchronisation an
 allocation implies). Its per-chunk partials live in a buffer built into the library, so the test
 checks what such a caller relies on: through the C ABI, the results equal those of the entry point
-that takes caller scratch, on two calls in a row that share the built-in buffer (the second call
-meets the first call's leftovers), and a request beyond the buffer's size is refused cleanly.
+that takes caller scratch and, directly, the CPU oracle's decode attention over each sequence's
+gathered history, on two calls in a row that share the built-in buffer (the second call meets the
+first call's leftovers), and a request beyond the buffer's size is refused cleanly.
 Collected last on purpose: a failure here cannot hide the other tests from a run that stops at the
 first failure."""
 import ctypes as C
@@ -13,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle_lib as O
 from gpu_util import DEV, TOL, max_rel, to_np
 from logismos_b200 import ops
 from logismos_b200._lib import lib
@@ -79,6 +81,15 @@ def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch():
         assert max_rel(got, ref) <= TOL
         assert (got == ref).all()  # the same kernels on the same inputs: nothing may depend on the buffer's history
         assert torch.equal(kp_r, kp_g) and torch.equal(vp_r, vp_g)  # the fused append wrote the same rows
+        # and against the oracle itself: every sequence's history (the appended token included) gathered
+        # from the pools through its block table, last-row causal attention on the CPU
+        kp, vp, tab, q = to_np(kp_g), to_np(vp_g), case["tables"].cpu().numpy(), to_np(case["q"])
+        for i, L in enumerate(case["ctx"].cpu().tolist()):
+            pos = np.arange(L)
+            rows = tab[i, pos // BS].astype(np.int64) * BS + pos % BS
+            k = np.ascontiguousarray(kp.reshape(-1, kp.shape[-1])[rows]); v = np.ascontiguousarray(vp.reshape(-1, vp.shape[-1])[rows])
+            assert np.array_equal(k[-1], to_np(case["nk"])[i]) and np.array_equal(v[-1], to_np(case["nv"])[i])
+            assert max_rel(got[i], O.decode_attention(q[i], k, v, case["nh"], case["nkv"], D)) <= TOL, (i, L)
 
 
 def test_a_request_beyond_the_built_in_buffer_is_refused_without_launching():
