@@ -227,19 +227,22 @@ def gemv_grid(peaks, shapes):
         copies = max(3, min(320, int(320e6 // wbytes) + 1))
         codes = torch.randint(0, 256, (copies, n, k // 2), dtype=torch.uint8, device=dev)
         scales = (torch.rand((copies, n, k // 32), device=dev) * 0.02).to(torch.float16)
+        ws = torch.zeros(64 * n, dtype=torch.float32, device=dev)  # fp32 workspace of the route above 16 rows (kept zero by it)
+        stw = torch.zeros(1, dtype=torch.int32, device=dev)
         for b in GEMV_BATCHES:
             x = torch.randn((b, k), device=dev).to(torch.bfloat16)
             y = torch.empty((b, n), dtype=torch.bfloat16, device=dev)
             iters = copies if copies > 6 else 2 * copies
-            t_hbm = timeit(lambda i: ops.gemv_int4(codes[i % copies], scales[i % copies], x, out=y, sync=False), iters, reps=2)
-            t_l2 = timeit(lambda i: ops.gemv_int4(codes[0], scales[0], x, out=y, sync=False), 20) if wbytes < 100e6 else None
+            t_hbm = timeit(lambda i: ops.skinny_int4(codes[i % copies], scales[i % copies], x, ws, out=y, status=stw, sync=False), iters, reps=2)
+            t_l2 = timeit(lambda i: ops.skinny_int4(codes[0], scales[0], x, ws, out=y, status=stw, sync=False), 20) if wbytes < 100e6 else None
             by = wbytes + b * k * 2 + b * n * 2
-            out.append({"kernel": "gemv_int4_g32", "shape": name, "n": n, "k": k, "batch": b, "bound": "hbm", "bytes_per_launch": by,
+            out.append({"kernel": "gemv_int4_g32" if b <= 16 or k % 256 else "qlinear_int4_tcgen05 + finish (skinny route above 16 rows)", "shape": name, "n": n, "k": k, "batch": b, "bound": "hbm", "bytes_per_launch": by,
                         "us_per_launch": t_hbm * 1e6, "achieved": by / t_hbm / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                         "frac": by / t_hbm / 1e9 / peaks["hbm"], "weight_copies_rotated": copies,
                         "us_per_launch_l2_resident": t_l2 * 1e6 if t_l2 else None, "achieved_l2_resident": by / t_l2 / 1e9 if t_l2 else None,
                         "traffic": NCU_TRAFFIC["gemv_lm_head"] if (n, k, b) == (151936, 1536, 1) else None, "peak_source": peaks["src"]})
-        del codes, scales
+        assert int(stw.item()) == 0
+        del codes, scales, ws
     return out
 
 

@@ -182,6 +182,17 @@ uint32_t logismos_launch_paged_prefix_attention_tc_bf16(
     int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads, int32_t n_kv_heads,
     int32_t head_dim, void* status, void* stream);
 
+/* The same attention over a cache of TurboQuant 3-bit rows (logismos_launch_paged_kv_store_turbo3
+ * below; pools u8 [n_pool_blocks, 16, n_kv_heads * head_dim / 128 * 56]): the gathering launch decodes
+ * each head chunk (decode_turbo3_0_head, crates/quant/src/lib.rs:378-413) to bf16 on its way into the
+ * scratch; everything else as above, a decode token included (one query per sequence). */
+uint32_t logismos_launch_paged_prefix_attention_turbo3_bf16(
+    const void* q_bf16, int32_t q_row_stride, const void* cu_seqlens_q_i32, const void* kv_lens_i32,
+    const void* k_pool_t3, const void* v_pool_t3, const void* block_tables_i32, int32_t max_blocks,
+    int32_t n_pool_blocks, void* out_bf16, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
+    int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads, int32_t n_kv_heads,
+    int32_t head_dim, void* status, void* stream);
+
 /* mean_pool_masked -> l2_normalize -> linear_t(head) -> l2_normalize (cpu_f32 mod.rs:553-591 as
  * composed by StellaModel::encode_raw, crates/embed/src/stella.rs:231-246), mask all ones.
  * hidden f32 [n_tokens, hidden]; head_w bf16 [dim, hidden]; head_b f32 [dim]; out f32
@@ -210,6 +221,15 @@ uint32_t logismos_launch_gemv_int4_g32_bf16(const void* codes_u8, const void* sc
 uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes_u8, const void* scales_f16,
                                            const void* x_bf16, void* y_f32, int32_t batch, int32_t n,
                                            int32_t k, void* stream);
+
+/* The same product, y bf16 [batch, n], with the kernel chosen by batch: up to 16 rows the streaming
+ * GEMV; from 17 to 64 rows (k % 256 == 0, n % 4 == 0) the fused-dequant tensor-core linear below,
+ * accumulating in workspace_f32 [batch, n] (16-byte aligned, ALL ZERO on entry, left all zero on
+ * return) and rounded once to bf16. workspace_f32 == NULL keeps the GEMV at every batch. status_i32
+ * as for logismos_launch_qlinear_int4_g32_acc_f32. Two launches above 16 rows. */
+uint32_t logismos_launch_skinny_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
+                                              const void* x_bf16, void* y_bf16, int32_t batch, int32_t n,
+                                              int32_t k, void* workspace_f32, void* status_i32, void* stream);
 
 /* Expands int4 group-32 weights (same storage as above) to bf16 [n, k]: w = bf16(scale * code).
  * The prefill side of a mixed step runs its contractions on the tcgen05 GEMM over this expansion.
@@ -309,6 +329,24 @@ uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool_bf16, const voi
                                               int32_t len, int32_t row_elems,
                                               int32_t n_pool_blocks, void* k_out_bf16,
                                               void* v_out_bf16, void* status_i32, void* stream);
+
+/* The same cache with TurboQuant 3-bit rows: KvCache::put / get (crates/cache/src/lib.rs:57-82) through
+ * encode_turbo3_0_head / decode_turbo3_0_head (crates/quant/src/lib.rs:316-413: L2 norm, 128-point
+ * Walsh-Hadamard transform, 8-centroid codebook, four 14-byte blocks per 128-value head chunk). A pool
+ * row holds row_elems / 128 chunks of 56 bytes (logismos_turbo3_row_bytes) instead of row_elems bf16:
+ * pools are u8 [n_pool_blocks, 16, row_bytes]. The store encodes rows of k / v bf16 [n_tokens,
+ * row_elems] (widened to fp32 first) into slot_mapping's slots; the gather decodes the first len rows of
+ * one sequence to bf16 [len, row_elems] (fp32 decode rounded once). Bytes and values are identical to
+ * the CPU definition (the arithmetic follows it operation by operation). row_elems % 128 == 0. */
+size_t logismos_turbo3_row_bytes(int32_t row_elems);
+uint32_t logismos_launch_paged_kv_store_turbo3(const void* k_bf16, const void* v_bf16, int32_t src_row_stride,
+                                               void* k_pool_t3, void* v_pool_t3, const void* slot_mapping_i64,
+                                               int32_t n_tokens, int32_t row_elems, int64_t n_pool_slots,
+                                               void* status_i32, void* stream);
+uint32_t logismos_launch_paged_kv_gather_turbo3(const void* k_pool_t3, const void* v_pool_t3,
+                                                const void* block_table_i32, int32_t table_len, int32_t len,
+                                                int32_t row_elems, int32_t n_pool_blocks, void* k_out_bf16,
+                                                void* v_out_bf16, void* status_i32, void* stream);
 
 /* dst[r, :] = src[idx[r], :] for fp32 rows (bit-exact copy): picks the last token row of every
  * sequence of a packed step before the final norm and the lm_head. An index outside

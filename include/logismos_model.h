@@ -125,6 +125,11 @@ typedef struct lg_decoder_config {
   int32_t max_step_seqs;
   int32_t keep_bf16_copy;      /* != 0: also keep a bf16 expansion of every layer matrix (2 B per weight) for
                                   steps of more than 128 rows, instead of expanding per layer per step */
+  int32_t kv_turbo3;           /* != 0: the paged cache holds TurboQuant 3-bit rows (56 bytes per 128-value head
+                                  chunk instead of 256: crates/quant/src/lib.rs:316-413); every sequence of a step,
+                                  decode tokens included, then attends through the decoding gather of
+                                  logismos_launch_paged_prefix_attention_turbo3_bf16. A capacity mode: 4.57 times
+                                  more context per byte of pool, at the codec's accuracy */
 } lg_decoder_config_t;
 
 /* int4 group-32 matrix on the HOST: codes u8 [n, k/2], scales fp16 bits [n, k/32]

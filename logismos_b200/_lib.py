@@ -72,10 +72,13 @@ def _declare(l):
         "logismos_launch_rope_varlen_attention_tc_bf16": [vp, vp, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_paged_prefix_attention_tc_bf16": [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
                                                            i32, i32, vp, vp],
+        "logismos_launch_paged_prefix_attention_turbo3_bf16": [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32,
+                                                               i32, i32, vp, vp],
         "logismos_launch_pool_head_f32": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
         # decode path
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
         "logismos_launch_gemv_int4_g32_f32": [vp, vp, vp, vp, i32, i32, i32, vp],
+        "logismos_launch_skinny_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp],
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_qlinear_int4_g32_acc_f32": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_qlinear_finish_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
@@ -85,6 +88,8 @@ def _declare(l):
                                                                 i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_kv_store_bf16": [vp, vp, i32, vp, vp, vp, i32, i32, i64, vp, vp],
         "logismos_launch_paged_kv_gather_bf16": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
+        "logismos_launch_paged_kv_store_turbo3": [vp, vp, i32, vp, vp, vp, i32, i32, i64, vp, vp],
+        "logismos_launch_paged_kv_gather_turbo3": [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp],
         "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],
         "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
         "logismos_launch_gdn_prefill": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
@@ -142,6 +147,8 @@ def _declare(l):
     l.logismos_varlen_attention_tc_scratch_bytes.restype = sz
     l.logismos_paged_prefix_attention_scratch_bytes.argtypes = [i32, i32, i32, i32]
     l.logismos_paged_prefix_attention_scratch_bytes.restype = sz
+    l.logismos_turbo3_row_bytes.argtypes = [i32]
+    l.logismos_turbo3_row_bytes.restype = sz
     l.logismos_build_packing.argtypes = [vp, vp, i32, vp, i32, i32, i32, vp, vp, vp, vp]
     l.logismos_build_packing.restype = i64
     l.logismos_build_decode_chunks.argtypes = [vp, i32, i32, vp]

@@ -24,7 +24,7 @@ SO = os.path.join(HERE, "liblogismos_kernels.so")
 AR = os.path.join(HERE, "liblogismos_kernels.a")
 
 CU_SOURCES = ["cudacore.cu", "legacy_fp16.cu", "elementwise.cu", "gemv_int4.cu", "dequant_int4.cu", "gemm_tcgen05.cu", "qgemm_tcgen05.cu",
-              "attention.cu", "attention_tcgen05.cu", "gdn.cu", "gdn_chunk.cu", "sampling.cu", "stella_model.cu", "decoder_model.cu", "hybrid_model.cu", "tp_comm.cu"]
+              "attention.cu", "attention_tcgen05.cu", "gdn.cu", "gdn_chunk.cu", "sampling.cu", "kvquant.cu", "stella_model.cu", "decoder_model.cu", "hybrid_model.cu", "tp_comm.cu"]
 CPP_SOURCES = ["sched.cpp", "loader.cpp"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",

@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "logismos_kernels.h"
 #include "tcgen05.cuh"
+#include "turbo3.cuh"
 
 namespace {
 
@@ -243,6 +244,88 @@ gather_paged_kv_kernel(const __nv_bfloat16* __restrict__ kpool, const __nv_bfloa
     }
     if (t < plen) *reinterpret_cast<uint4*>(kbuf + (size_t)(p0 + t) * row_w + kvh * HD + ch * 8) = kq;
     *reinterpret_cast<uint4*>(&tile[r][ch * 8]) = vq;
+  }
+  __syncthreads();
+  const int d = tid / kParts, half = tid % kParts;
+#pragma unroll
+  for (int g8 = 0; g8 < 8 / kParts; ++g8) {
+    const int tl = half * (64 / kParts) + g8 * 8;
+    if (tb * 64 + tl < plen) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint16_t lo = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i][d]);
+        const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[tl + 2 * i + 1][d]);
+        w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + p0 + tb * 64 + tl) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// The same gather from TurboQuant 3-bit pools (u8 [n_pool_blocks, 16, n_kv * HD / 128 * 56], kvquant.cu):
+// every 128-value head chunk of a key is decoded by one warp (decode_turbo3_0_head, crates/quant/src/
+// lib.rs:378-413), K chunks go straight to kbuf as bf16, V chunks through the shared tile for the
+// transposed write. Same grid, same padding rules.
+template <int HD>
+__global__ void __launch_bounds__(256)
+gather_paged_kv_turbo3_kernel(const uint8_t* __restrict__ kpool, const uint8_t* __restrict__ vpool, const int* __restrict__ tables,
+                              int max_blocks, int n_pool_blocks, const int* __restrict__ kv_lens, __nv_bfloat16* __restrict__ kbuf,
+                              __nv_bfloat16* __restrict__ vt, int* __restrict__ pstart, int n_seqs, int tp, int tx, int n_kv,
+                              int* __restrict__ status) {
+  __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
+  __shared__ uint32_t words[8][16];
+  constexpr int kParts = 256 / HD, kCh = HD / 128;  // threads per d row; head chunks per key
+  __shared__ int p0_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tb = (int)blockIdx.x % tx, kvh = ((int)blockIdx.x / tx) % n_kv, s = (int)blockIdx.x / (tx * n_kv);
+  if (tid < 32) {
+    int part = 0;
+    for (int i = tid; i < s; i += 32) part += round8(max(kv_lens[i], 0));
+    part += __shfl_xor_sync(0xffffffffu, part, 16);
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    if (tid == 0) p0_s = part;
+  }
+  __syncthreads();
+  const int p0 = p0_s;
+  const int len = max(kv_lens[s], 0), plen = round8(len);
+  const int row_w = n_kv * HD, chunks_row = n_kv * kCh;
+  if (p0 + plen > tp) {
+    if (tid == 0 && status) atomicExch(status, 1);
+    return;
+  }
+  if (tb == 0 && kvh == 0 && tid == 0) pstart[s] = p0;
+  if (tb == 0 && s == n_seqs - 1) {
+    const int d = tid / kParts;
+    for (int col = p0 + plen + (tid % kParts) * 8; col + 8 <= tp; col += 8 * kParts)
+      *reinterpret_cast<uint4*>(vt + (size_t)(kvh * HD + d) * tp + col) = make_uint4(0u, 0u, 0u, 0u);
+    for (int u = tid; u < (tp - p0 - plen) * (HD / 8); u += 256)
+      *reinterpret_cast<uint4*>(kbuf + (size_t)(p0 + plen + u / (HD / 8)) * row_w + kvh * HD + (u % (HD / 8)) * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (tb * 64 >= plen) return;
+  // warp tasks: (key r of the tile, head chunk c, K or V)
+  for (int task = warp; task < 64 * kCh * 2; task += 8) {
+    const int kv = task & 1, c = (task >> 1) % kCh, r = (task >> 1) / kCh, t = tb * 64 + r;
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (t < len) {
+      const int bi = t >> 4;
+      const int blk = bi < max_blocks ? __ldg(tables + (size_t)s * max_blocks + bi) : -1;
+      if (blk < 0 || blk >= n_pool_blocks) {
+        if (lane == 0 && status) atomicExch(status, 1);
+      } else {
+        const uint8_t* src = (kv ? vpool : kpool) + (((size_t)blk * 16 + (t & 15)) * chunks_row + kvh * kCh + c) * lg::t3::kChunkBytes;
+        lg::t3::decode_chunk(src, o, words[warp], lane);
+      }
+    }
+    const uint2 pk = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+    if (kv == 0) {
+      if (t < plen) *reinterpret_cast<uint2*>(kbuf + (size_t)(p0 + t) * row_w + kvh * HD + c * 128 + lane * 4) = pk;
+    } else {
+      *reinterpret_cast<uint2*>(&tile[r][c * 128 + lane * 4]) = pk;
+    }
   }
   __syncthreads();
   const int d = tid / kParts, half = tid % kParts;
@@ -587,18 +670,16 @@ size_t logismos_paged_prefix_attention_scratch_bytes(int32_t total_kv_tokens, in
   return pstart_bytes(n_seqs) + 2 * (size_t)n_kv_heads * head_dim * (size_t)padded_tokens(total_kv_tokens, n_seqs) * 2;
 }
 
-uint32_t logismos_launch_paged_prefix_attention_tc_bf16(const void* q, int32_t q_row_stride, const void* cu_seqlens_q,
-                                                        const void* kv_lens, const void* k_pool, const void* v_pool,
-                                                        const void* block_tables, int32_t max_blocks, int32_t n_pool_blocks,
-                                                        void* out, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
-                                                        int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads,
-                                                        int32_t n_kv_heads, int32_t head_dim, void* status, void* stream) {
-  lg::LaunchScope launch_scope_;
+static uint32_t launch_prefix_attn(const void* q, int32_t q_row_stride, const void* cu_seqlens_q, const void* kv_lens, const void* k_pool,
+                                   const void* v_pool, const void* block_tables, int32_t max_blocks, int32_t n_pool_blocks, void* out,
+                                   void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens, int32_t n_seqs, int32_t max_q_len,
+                                   int32_t max_kv_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, bool turbo3, void* status,
+                                   void* stream) {
   const int D = head_dim;
   if (n_q_tokens < 0 || total_kv_tokens < 0 || n_seqs < 0 || max_q_len < 0 || max_kv_len < 0 || max_blocks <= 0 ||
       n_pool_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || (D != 128 && D != 256) || (n_heads % n_kv_heads) ||
       (q_row_stride % 8) || n_heads * D > q_row_stride || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
-      ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || !scratch || ((uintptr_t)scratch & 255) || !kv_lens ||
+      ((uintptr_t)k_pool & (turbo3 ? 7 : 15)) || ((uintptr_t)v_pool & (turbo3 ? 7 : 15)) || !scratch || ((uintptr_t)scratch & 255) || !kv_lens ||
       !block_tables || max_kv_len > total_kv_tokens)
     return lg::kInvalidValue;
   if (n_seqs == 0 || max_q_len == 0 || n_q_tokens == 0) return 0;
@@ -617,16 +698,17 @@ uint32_t logismos_launch_paged_prefix_attention_tc_bf16(const void* q, int32_t q
   const int64_t blocks = (int64_t)tx * n_kv_heads * n_seqs;
   if (blocks > 0x7fffffff) return lg::kInvalidValue;
   if (blocks > 0) {
-    if (D == 128)
-      gather_paged_kv_kernel<128><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-                                                                   (const int*)block_tables, max_blocks, n_pool_blocks,
-                                                                   (const int*)kv_lens, kbuf, vt, pstart, n_seqs, tp, tx,
-                                                                   n_kv_heads, (int*)status);
-    else
-      gather_paged_kv_kernel<256><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-                                                                   (const int*)block_tables, max_blocks, n_pool_blocks,
-                                                                   (const int*)kv_lens, kbuf, vt, pstart, n_seqs, tp, tx,
-                                                                   n_kv_heads, (int*)status);
+    auto go = [&](auto kern, auto* kp, auto* vp) {
+      kern<<<(unsigned)blocks, 256, 0, s>>>(kp, vp, (const int*)block_tables, max_blocks, n_pool_blocks, (const int*)kv_lens, kbuf, vt, pstart,
+                                            n_seqs, tp, tx, n_kv_heads, (int*)status);
+    };
+    if (turbo3) {
+      if (D == 128) go(gather_paged_kv_turbo3_kernel<128>, (const uint8_t*)k_pool, (const uint8_t*)v_pool);
+      else go(gather_paged_kv_turbo3_kernel<256>, (const uint8_t*)k_pool, (const uint8_t*)v_pool);
+    } else {
+      if (D == 128) go(gather_paged_kv_kernel<128>, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool);
+      else go(gather_paged_kv_kernel<256>, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool);
+    }
     uint32_t rc = lg::launch_status();
     if (rc) return rc;
   }
@@ -641,6 +723,29 @@ uint32_t logismos_launch_paged_prefix_attention_tc_bf16(const void* q, int32_t q
   };
   if (D == 128) return launch(attn_tcgen05_kernel<true, 128>, Attn<128>::kSmem);
   return launch(attn_tcgen05_kernel<true, 256>, Attn<256>::kSmem);
+}
+
+uint32_t logismos_launch_paged_prefix_attention_tc_bf16(const void* q, int32_t q_row_stride, const void* cu_seqlens_q,
+                                                        const void* kv_lens, const void* k_pool, const void* v_pool,
+                                                        const void* block_tables, int32_t max_blocks, int32_t n_pool_blocks,
+                                                        void* out, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
+                                                        int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads,
+                                                        int32_t n_kv_heads, int32_t head_dim, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  return launch_prefix_attn(q, q_row_stride, cu_seqlens_q, kv_lens, k_pool, v_pool, block_tables, max_blocks, n_pool_blocks, out, scratch,
+                            n_q_tokens, total_kv_tokens, n_seqs, max_q_len, max_kv_len, n_heads, n_kv_heads, head_dim, false, status, stream);
+}
+
+uint32_t logismos_launch_paged_prefix_attention_turbo3_bf16(const void* q, int32_t q_row_stride, const void* cu_seqlens_q,
+                                                            const void* kv_lens, const void* k_pool_t3, const void* v_pool_t3,
+                                                            const void* block_tables, int32_t max_blocks, int32_t n_pool_blocks,
+                                                            void* out, void* scratch, int32_t n_q_tokens, int32_t total_kv_tokens,
+                                                            int32_t n_seqs, int32_t max_q_len, int32_t max_kv_len, int32_t n_heads,
+                                                            int32_t n_kv_heads, int32_t head_dim, void* status, void* stream) {
+  lg::LaunchScope launch_scope_;
+  return launch_prefix_attn(q, q_row_stride, cu_seqlens_q, kv_lens, k_pool_t3, v_pool_t3, block_tables, max_blocks, n_pool_blocks, out,
+                            scratch, n_q_tokens, total_kv_tokens, n_seqs, max_q_len, max_kv_len, n_heads, n_kv_heads, head_dim, true, status,
+                            stream);
 }
 
 }  // extern "C"

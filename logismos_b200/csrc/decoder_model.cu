@@ -95,6 +95,21 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
     LG_TRY(logismos_launch_rope_halves_bf16(m->qkv.p, m->cos.p, m->sin.p, m->pos.p, T, c.n_heads + c.n_kv_heads, D, QKV,
                                             c.max_pos, st, s), "rope");
     const uint16_t* qkv16 = (const uint16_t*)m->qkv.p;
+    if (c.kv_turbo3) {
+      // TurboQuant 3-bit cache: rows are encoded on the way in and every sequence of the step (decode
+      // tokens are chunks of one query) attends through the decoding gather, run by run
+      LG_TRY(logismos_launch_paged_kv_store_turbo3(qkv16 + H, qkv16 + H + KV, QKV, L.kpool.p, L.vpool.p, m->slots.p, T, KV,
+                                                   (int64_t)c.n_pool_blocks * kBlock, st, s), "paged_kv_store_turbo3");
+      m->launches += 3;
+      for (const Decoder::PrefixRun& r : m->prefix_runs) {
+        LG_TRY(logismos_launch_paged_prefix_attention_turbo3_bf16(
+                   qkv16, QKV, (const int32_t*)m->cu_prefill.p + r.s0, (const int32_t*)m->pre_kv.p + r.s0, L.kpool.p, L.vpool.p,
+                   (const int32_t*)m->dec_tables.p + (size_t)r.s0 * c.max_blocks_per_seq, c.max_blocks_per_seq, c.n_pool_blocks, m->attn.p,
+                   m->attn_ws.p, T, r.total_kv, r.s1 - r.s0, r.max_q, r.max_kv, c.n_heads, c.n_kv_heads, D, st, s),
+               "paged_prefix_attention_turbo3");
+        m->launches += 2;
+      }
+    } else {
     LG_TRY(logismos_launch_paged_kv_store_bf16(qkv16 + H, qkv16 + H + KV, QKV, L.kpool.p, L.vpool.p, m->slots.p, T, KV,
                                                (int64_t)c.n_pool_blocks * kBlock, st, s), "paged_kv_store");
     m->launches += 3;
@@ -127,6 +142,7 @@ uint32_t run_device(Decoder* m, cudaStream_t s) {
                                                       m->n_pre, m->max_pre_len, c.n_heads, c.n_kv_heads, D, QKV, H, H + KV, 1, st, s),
              "varlen_attention");
       m->launches += 2;
+    }
     }
     if (uint32_t rc = qlinear(m, m->attn.p, L.wo, nullptr, m->x.p, T, H, H, LG_EPI_RESID_F32, s)) return rc;
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
@@ -179,7 +195,7 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
   ok = ok && m->final_norm.upload(w->final_norm, H * 4);
   ok = ok && upload_q(m->lm_head, {&w->lm_head}, {c.vocab}, (int)H);
   m->layers.resize(c.n_layers);
-  const size_t pool_bytes = (size_t)c.n_pool_blocks * kBlock * KV * 2;
+  const size_t pool_bytes = (size_t)c.n_pool_blocks * kBlock * (c.kv_turbo3 ? logismos_turbo3_row_bytes((int32_t)KV) : KV * 2);
   for (int l = 0; l < c.n_layers && ok; ++l) {
     const lg_decoder_layer_weights_t& lw = w->layers[l];
     DLayer& L = m->layers[l];
@@ -225,6 +241,11 @@ uint32_t lg_decoder_create(int32_t device, const lg_decoder_config_t* cfg, const
     // the attention workspace serves both prefill routes; the gather route holds one run of sequences at
     // a time, and any single sequence (at most a full block table) must fit
     m->prefix_cap_tokens = MB * kBlock > T ? MB * kBlock : T;
+    if (c.kv_turbo3) {  // every sequence of a step goes through the gather: room for many contexts at once
+      const size_t all = S * MB * kBlock, cap = (size_t)512 * 1024;
+      m->prefix_cap_tokens = all < cap ? all : cap;
+      if (m->prefix_cap_tokens < MB * kBlock) m->prefix_cap_tokens = MB * kBlock;
+    }
     size_t ws = logismos_varlen_attention_tc_scratch_bytes((int32_t)T, (int32_t)S, c.n_kv_heads, 128);
     const size_t ws2 = logismos_paged_prefix_attention_scratch_bytes((int32_t)m->prefix_cap_tokens, (int32_t)S, c.n_kv_heads, 128);
     if (ws2 > ws) ws = ws2;
@@ -332,10 +353,17 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
     }
   }
   std::vector<Decoder::PrefixRun> runs;
+  const bool t3 = c.kv_turbo3 != 0;
+  if (t3) {  // all sequences, packed order: key counts and query offsets of the whole step
+    has_prefix = true;
+    for (int k = 0; k < n_seqs; ++k) h_prekv[k] = o_cached[k] + o_new[k];
+    std::memcpy(h_cu_pre, h_cu, (size_t)(n_seqs + 1) * 4);
+  }
+  const int run_first = t3 ? 0 : n_dec, run_count = t3 ? n_seqs : n_pre;
   if (has_prefix) {
     Decoder::PrefixRun r{0, 0, 0, 0, 0};
-    for (int k = 0; k < n_pre; ++k) {
-      const int kv = h_prekv[k], q = o_new[n_dec + k];
+    for (int k = 0; k < run_count; ++k) {
+      const int kv = h_prekv[k], q = o_new[run_first + k];
       if (r.s1 > r.s0 && (size_t)r.total_kv + kv > m->prefix_cap_tokens) { runs.push_back(r); r = Decoder::PrefixRun{k, k, 0, 0, 0}; }
       r.s1 = k + 1; r.total_kv += kv;
       if (q > r.max_q) r.max_q = q;
@@ -355,7 +383,7 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   LG_TRY(cudaMemcpyAsync(m->ids.p, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D ids");
   LG_TRY(cudaMemcpyAsync(m->pos.p, h_pos, (size_t)total * 4, cudaMemcpyHostToDevice, s), "H2D positions");
   LG_TRY(cudaMemcpyAsync(m->slots.p, h_slots, (size_t)total * 8, cudaMemcpyHostToDevice, s), "H2D slots");
-  LG_TRY(cudaMemcpyAsync(m->cu_prefill.p, h_cu_pre, (size_t)(n_pre + 1) * 4, cudaMemcpyHostToDevice, s), "H2D cu_seqlens");
+  LG_TRY(cudaMemcpyAsync(m->cu_prefill.p, h_cu_pre, (size_t)(run_count + 1) * 4, cudaMemcpyHostToDevice, s), "H2D cu_seqlens");
   LG_TRY(cudaMemcpyAsync(m->last_idx.p, h_last, (size_t)n_seqs * 4, cudaMemcpyHostToDevice, s), "H2D last rows");
   if (n_dec > 0) {
     LG_TRY(cudaMemcpyAsync(m->dec_ctx.p, h_ctx, (size_t)n_dec * 4, cudaMemcpyHostToDevice, s), "H2D context lens");
@@ -363,7 +391,7 @@ uint32_t lg_decoder_step(void* model, const uint32_t* host_ids, const int32_t* c
   }
   if (n_dec > 0 || has_prefix)  // block tables in packed order: decode rows first, prefill rows after them
     LG_TRY(cudaMemcpyAsync(m->dec_tables.p, h_tables, (size_t)(has_prefix ? n_seqs : n_dec) * MB * 4, cudaMemcpyHostToDevice, s), "H2D block tables");
-  if (has_prefix) LG_TRY(cudaMemcpyAsync(m->pre_kv.p, h_prekv, (size_t)n_pre * 4, cudaMemcpyHostToDevice, s), "H2D prefill key counts");
+  if (has_prefix) LG_TRY(cudaMemcpyAsync(m->pre_kv.p, h_prekv, (size_t)run_count * 4, cudaMemcpyHostToDevice, s), "H2D prefill key counts");
   if (uint32_t rc = run_device(m, s)) { m->acc_dirty = true; return rc; }
   std::vector<uint32_t> toks(n_seqs);
   LG_TRY(cudaMemcpyAsync(toks.data(), m->tokens.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, s), "D2H tokens");

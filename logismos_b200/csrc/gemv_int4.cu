@@ -823,3 +823,20 @@ extern "C" uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes, const v
   lg::LaunchScope launch_scope_;
   return launch_gemv(codes, scales_f16, x_bf16, y_f32, 1, batch, n, k, stream);
 }
+
+// The same product for any batch up to 64 with the route chosen by row count: up to 16 rows the
+// streaming GEMV above; from 17 rows the fused-dequant tensor-core kernel (qgemm_tcgen05.cu), whose
+// fp32 sums go through `workspace` and are rounded to bf16 by its finishing kernel. The mma.sync GEMV
+// re-reads the activation fragments from shared memory for every 16 weight rows, which at 64 batch
+// rows costs several times the weight stream; the tensor-core kernel keeps them in one operand tile.
+extern "C" uint32_t logismos_launch_skinny_int4_g32_bf16(const void* codes, const void* scales_f16, const void* x_bf16, void* y_bf16,
+                                                         int32_t batch, int32_t n, int32_t k, void* workspace_f32, void* status_i32,
+                                                         void* stream) {
+  lg::LaunchScope launch_scope_;
+  if (batch <= 16 || (k % 256) != 0 || (n % 4) != 0 || workspace_f32 == nullptr)
+    return launch_gemv(codes, scales_f16, x_bf16, y_bf16, 0, batch, n, k, stream);
+  if (batch > 64 || ((uintptr_t)workspace_f32 & 15)) return lg::kInvalidValue;
+  const uint32_t rc = logismos_launch_qlinear_int4_g32_acc_f32(x_bf16, codes, scales_f16, workspace_f32, batch, n, k, k, n, status_i32, stream);
+  if (rc) return rc;
+  return logismos_launch_qlinear_finish_bf16(workspace_f32, nullptr, y_bf16, batch, n, n, n, 0, stream);
+}

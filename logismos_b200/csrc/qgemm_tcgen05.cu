@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "logismos_kernels.h"
 #include "tcgen05.cuh"
+#include "int4_dequant.cuh"
 
 // Development aid: built with -DLG_QTRACE the first CTA records, per unit, the clock at the points of
 // the hand-offs between its roles into a global buffer (logismos_qtrace_buffer); never defined in the
@@ -99,23 +100,6 @@ LG_DEVINL bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* ab
   return false;
 }
 
-// two nibbles of byte p of a code word (k even in the low nibble) -> bf16x2 {136 + q_even, 136 + q_odd}:
-// the permute puts byte p of w under bits 0-7 and byte p of w >> 4 under bits 16-23; one logic op
-// keeps the two low nibbles, flips their sign bit and ors in the exponent 0x4300
-LG_DEVINL uint32_t nib_pair_136(uint32_t w, uint32_t w_shr4, uint32_t sel) {
-  uint32_t t;
-  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(t) : "r"(w), "r"(w_shr4), "r"(sel));
-  return (t & 0x000f000fu) ^ 0x43084308u;
-}
-
-LG_DEVINL uint32_t bf16x2_sub_mul(uint32_t v, uint32_t c136, uint32_t s2) {
-  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&v);
-  const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&c136);
-  const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(&s2);
-  a = __hmul2(__hsub2(a, c), s);
-  return *reinterpret_cast<uint32_t*>(&a);
-}
-
 // D[tmem] (+)= A[tmem] * B[smem]^T: the weight operand is read from tensor memory, where the
 // dequantising warps put it (lane = row, one 32-bit column = two consecutive values of k)
 LG_DEVINL void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -140,25 +124,6 @@ LG_DEVINL void tc_st32(uint32_t taddr, const uint4 (&v)[8]) {
       : "memory");
 }
 LG_DEVINL void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-// 8 codes of one 32-bit word -> 8 bf16 (one 16-byte chunk of the operand tile), scaled
-LG_DEVINL uint4 dequant_word(uint32_t w, uint32_t s2) {
-  const uint32_t c136 = 0x43084308u;
-  const uint32_t lo = w, hi = w >> 4;
-  uint4 o;
-  o.x = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0400u), c136, s2);  // bytes {lo.b0, x, hi.b0, x}
-  o.y = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0501u), c136, s2);
-  o.z = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0602u), c136, s2);
-  o.w = bf16x2_sub_mul(nib_pair_136(lo, hi, 0x0703u), c136, s2);
-  return o;
-}
-
-LG_DEVINL uint32_t scale_bf16x2(uint32_t packed_f16, int which) {
-  const __half h = __ushort_as_half((unsigned short)(which ? (packed_f16 >> 16) : (packed_f16 & 0xffffu)));
-  const __nv_bfloat16 sb = __float2bfloat16_rn(__half2float(h));
-  const __nv_bfloat162 sb2 = __halves2bfloat162(sb, sb);
-  return *reinterpret_cast<const uint32_t*>(&sb2);
-}
 
 template <int NT>
 __global__ void __launch_bounds__(kQThreads, 1)
@@ -232,7 +197,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       int tile = u0 / n_raw, rb = u0 % n_raw;  // carried along: no division in the loop
       for (int u = u0; u < u1; ++u) {
         const int kk = rb * kRawK;
-        if (!mbar_wait(raw_empty(rs), rphase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_sleep(raw_empty(rs), rphase ^ 1u, abort_flag, 100)) break;
         mbar_expect_tx(raw_full(rs), (uint32_t)kRawStage);
         const uint32_t dst = raw_base + rs * kRawStage;
         tma_load_2d(dst, &map_codes, raw_full(rs), kk / 2, tile * kWRows);
@@ -255,7 +220,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         if (++rb == n_raw) rb = 0;
 #pragma unroll
         for (int h = 0; h < kGroups / C::kABlocksPerStage; ++h) {
-          if (!mbar_wait(a_empty(as), aphase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_sleep(a_empty(as), aphase ^ 1u, abort_flag, 100)) { ok = false; break; }
           if (h == 0) QTRACE(u - u0, 10);
           mbar_expect_tx(a_full(as), (uint32_t)C::kAStage);
 #pragma unroll
@@ -332,7 +297,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int wb = n_unit & 1;
       const uint32_t wphase = ((uint32_t)n_unit >> 1) & 1u;
       if (wd == 0 && lane == 0) QTRACE(u - u0, 1);
-      if (!mbar_wait(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_sleep(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
       if (wd == 0 && lane == 0) QTRACE(u - u0, 2);
       const uint8_t* raw = smem_gen + rs * kRawStage;
       // this row's 64 codes of k block g (two 16-byte chunks, swizzled by the TMA) and their two scales
@@ -347,7 +312,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       o[0] = dequant_word(c0.x, s0); o[1] = dequant_word(c0.y, s0); o[2] = dequant_word(c0.z, s0); o[3] = dequant_word(c0.w, s0);
       o[4] = dequant_word(c1.x, s1); o[5] = dequant_word(c1.y, s1); o[6] = dequant_word(c1.z, s1); o[7] = dequant_word(c1.w, s1);
       if (wd == 0 && lane == 0) QTRACE(u - u0, 3);
-      if (!mbar_wait(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_sleep(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (wd == 0 && lane == 0) QTRACE(u - u0, 4);
       tc_st32(wt0 + (uint32_t)(wb * C::kWBufCols), o);  // lane = weight row, 32 columns = its 64 bf16 in k order

@@ -22,7 +22,7 @@ _u16 = C.POINTER(C.c_uint16)
 class _Cfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("vocab", "hidden", "n_layers", "n_heads", "n_kv_heads", "intermediate", "max_pos")] + [
         ("rms_eps", C.c_float), ("rope_theta", C.c_double)] + [
-        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs", "keep_bf16_copy")]
+        (n, C.c_int32) for n in ("n_pool_blocks", "max_blocks_per_seq", "max_step_tokens", "max_step_seqs", "keep_bf16_copy", "kv_turbo3")]
 
 
 class _Q(C.Structure):
@@ -81,10 +81,10 @@ class DecoderModel:
     (codes u8 [n, k/2], scales f16 [n, k/32]) pairs."""
 
     def __init__(self, cfg: dict, weights: dict, n_pool_blocks: int, max_blocks_per_seq: int, max_step_tokens: int,
-                 max_step_seqs: int, device: int = 0, keep_bf16_copy: bool = True):
+                 max_step_seqs: int, device: int = 0, keep_bf16_copy: bool = True, kv_turbo3: bool = False):
         c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"],
                  cfg["max_pos"], cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs,
-                 int(keep_bf16_copy))
+                 int(keep_bf16_copy), int(kv_turbo3))
         L = (_LayerW * max(1, cfg["n_layers"]))()
         for i, lw in enumerate(weights["layers"]):
             for n in ("norm1", "norm2", "bq", "bk", "bv"):
@@ -100,11 +100,12 @@ class DecoderModel:
 
     @classmethod
     def load(cls, path: str, cfg: dict, n_pool_blocks: int, max_blocks_per_seq: int, max_step_tokens: int, max_step_seqs: int,
-             device: int = 0, keep_bf16_copy: bool = True) -> "DecoderModel":
+             device: int = 0, keep_bf16_copy: bool = True, kv_turbo3: bool = False) -> "DecoderModel":
         """The decoder from a Qwen2-style fp32 safetensors file: tensor accounting and int4 group-32
         quantisation on the device by the native loader (``lg_decoder_load``)."""
         c = _Cfg(cfg["vocab"], cfg["hidden"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"], cfg["intermediate"], cfg["max_pos"],
-                 cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs, int(keep_bf16_copy))
+                 cfg["rms_eps"], cfg["rope_theta"], n_pool_blocks, max_blocks_per_seq, max_step_tokens, max_step_seqs, int(keep_bf16_copy),
+                 int(kv_turbo3))
         h = C.c_void_p()
         rc = lib.lg_decoder_load(device, str(path).encode(), C.byref(c), C.byref(h))
         if rc:

@@ -205,13 +205,14 @@ def varlen_attention_tc(qkv, cu_seqlens, n_heads, n_kv_heads, causal=False, max_
 
 
 def paged_prefix_attention(q, cu_seqlens_q, kv_lens, k_pool, v_pool, block_tables, n_heads, n_kv_heads, head_dim, sync=True,
-                           status=None):
+                           status=None, turbo3=False):
     """Causal attention of prefill chunks that continue cached sequences: the queries of sequence s are
     rows cu_seqlens_q[s]..cu_seqlens_q[s+1] of q (q heads at column 0), its kv_lens[s] keys and values
     (cached prefix + the chunk itself, already stored) are read from the paged pools through
     block_tables. Returns out bf16 [n_q_tokens, n_heads * head_dim]."""
     _req(q, "q", torch.bfloat16, 2); _req(cu_seqlens_q, "cu_seqlens_q", torch.int32, 1); _req(kv_lens, "kv_lens", torch.int32, 1)
-    _req(k_pool, "k_pool", torch.bfloat16, 3); _req(v_pool, "v_pool", torch.bfloat16, 3); _req(block_tables, "block_tables", torch.int32, 2)
+    pool_dt = torch.uint8 if turbo3 else torch.bfloat16   # turbo3: TurboQuant 3-bit rows (paged_kv_store_turbo3)
+    _req(k_pool, "k_pool", pool_dt, 3); _req(v_pool, "v_pool", pool_dt, 3); _req(block_tables, "block_tables", torch.int32, 2)
     n_seqs, T, D = kv_lens.shape[0], q.shape[0], head_dim
     cu = cu_seqlens_q.cpu(); kv = kv_lens.cpu()
     max_q = int((cu[1:] - cu[:-1]).max().item()) if n_seqs > 0 else 0
@@ -220,7 +221,8 @@ def paged_prefix_attention(q, cu_seqlens_q, kv_lens, k_pool, v_pool, block_table
     scratch = torch.empty(max(256, int(lib.logismos_paged_prefix_attention_scratch_bytes(total_kv, n_seqs, n_kv_heads, D))),
                           dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
-        check(lib.logismos_launch_paged_prefix_attention_tc_bf16(_p(q), q.shape[1], _p(cu_seqlens_q), _p(kv_lens), _p(k_pool), _p(v_pool),
+        fn = lib.logismos_launch_paged_prefix_attention_turbo3_bf16 if turbo3 else lib.logismos_launch_paged_prefix_attention_tc_bf16
+        check(fn(_p(q), q.shape[1], _p(cu_seqlens_q), _p(kv_lens), _p(k_pool), _p(v_pool),
                                                                  _p(block_tables), block_tables.shape[1], k_pool.shape[0], _p(out),
                                                                  _p(scratch), T, total_kv, n_seqs, max_q, max_kv, n_heads, n_kv_heads, D,
                                                                  _p(status) if status is not None else None, _stream()),
@@ -291,6 +293,24 @@ def gemv_int4(codes, scales, x, out=None, sync=True, out_f32=False):
     fn = lib.logismos_launch_gemv_int4_g32_f32 if out_f32 else lib.logismos_launch_gemv_int4_g32_bf16
     with torch.cuda.device(x.device):
         check(fn(_p(codes), _p(scales), _p(x), _p(y), x.shape[0], n, k, _stream()), "gemv_int4_g32")
+        _done(sync)
+    return y
+
+
+def skinny_int4(codes, scales, x, workspace, out=None, status=None, sync=True):
+    """y = x @ dequant(codes, scales)^T for 1..64 rows with the kernel chosen by row count (GEMV up to 16
+    rows, fused-dequant tensor-core linear above). ``workspace``: fp32 CUDA tensor of at least
+    batch * n elements, all zero on entry; it is left all zero."""
+    _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2); _req(x, "x", torch.bfloat16, 2)
+    _req(workspace, "workspace", torch.float32, None)
+    n, k = codes.shape[0], codes.shape[1] * 2
+    if x.shape[1] != k or tuple(scales.shape) != (n, k // 32) or workspace.numel() < x.shape[0] * n:
+        raise InvalidOp("skinny_int4: shape mismatch")
+    y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.bfloat16, device=x.device)
+    st = status if status is not None else torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.logismos_launch_skinny_int4_g32_bf16(_p(codes), _p(scales), _p(x), _p(y), x.shape[0], n, k, _p(workspace), _p(st), _stream()),
+              "skinny_int4_g32")
         _done(sync)
     return y
 
@@ -387,6 +407,37 @@ def paged_kv_store(k, v, k_pool, v_pool, slot_mapping, sync=True):
         _done(sync)
         if sync and int(status.item()) != 0:
             raise InvalidOp("paged_kv_store: slot outside the pool")
+
+
+def paged_kv_store_turbo3(k, v, k_pool, v_pool, slot_mapping, sync=True):
+    """KvCache::put into TurboQuant 3-bit pools (uint8 [n_blocks, 16, row_elems / 128 * 56])."""
+    _req(k, "k", torch.bfloat16, 2); _req(v, "v", torch.bfloat16, 2); _req(slot_mapping, "slot_mapping", torch.int64, 1)
+    _req(k_pool, "k_pool", torch.uint8, 3); _req(v_pool, "v_pool", torch.uint8, 3)
+    status = torch.zeros(1, dtype=torch.int32, device=k.device)
+    row = k.shape[1]
+    if k_pool.shape[-1] != lib.logismos_turbo3_row_bytes(row):
+        raise InvalidOp("paged_kv_store_turbo3: pool rows must hold row_elems / 128 chunks of 56 bytes")
+    with torch.cuda.device(k.device):
+        check(lib.logismos_launch_paged_kv_store_turbo3(_p(k), _p(v), k.stride(0), _p(k_pool), _p(v_pool), _p(slot_mapping), k.shape[0], row,
+                                                        k_pool.shape[0] * k_pool.shape[1], _p(status), _stream()), "paged_kv_store_turbo3")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("paged_kv_store_turbo3: slot outside the pool")
+
+
+def paged_kv_gather_turbo3(k_pool, v_pool, block_table, length, row_elems, sync=True):
+    """KvCache::get from TurboQuant 3-bit pools: decoded bf16 [length, row_elems] K and V."""
+    _req(block_table, "block_table", torch.int32, 1); _req(k_pool, "k_pool", torch.uint8, 3)
+    ko = torch.empty((length, row_elems), dtype=torch.bfloat16, device=k_pool.device)
+    vo = torch.empty_like(ko)
+    status = torch.zeros(1, dtype=torch.int32, device=k_pool.device)
+    with torch.cuda.device(k_pool.device):
+        check(lib.logismos_launch_paged_kv_gather_turbo3(_p(k_pool), _p(v_pool), _p(block_table), block_table.shape[0], length, row_elems,
+                                                         k_pool.shape[0], _p(ko), _p(vo), _p(status), _stream()), "paged_kv_gather_turbo3")
+        _done(sync)
+        if sync and int(status.item()) != 0:
+            raise InvalidOp("paged_kv_gather_turbo3: block id outside the pool")
+    return ko, vo
 
 
 def paged_kv_gather(k_pool, v_pool, block_table, length, sync=True):

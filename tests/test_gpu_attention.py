@@ -211,3 +211,43 @@ def test_paged_prefix_attention_equals_the_unpaged_kernel_for_fresh_sequences():
 
 def test_paged_prefix_attention_reports_a_block_outside_the_pool():
     run_case_prefix([40, 10], [20, 30], 4, 2, 128, 54, poison=True)
+
+
+@pytest.mark.parametrize("d", [128, 256])
+def test_attention_over_a_turbo3_cache_equals_attention_over_the_decoded_rows(d):
+    """Keys and values stored as TurboQuant 3-bit rows; prefill chunks and decode tokens (one query) read
+    them through the block tables. Reference: the oracle's causal attention over the rows the oracle's
+    own codec decodes (the quantisation error is the codec's, not the kernel's)."""
+    rng = np.random.default_rng(61)
+    nh, nkv = 8, 2
+    cached, new = [90, 0, 200, 33], [40, 70, 1, 1]
+    n = len(cached)
+    kv = [c + m for c, m in zip(cached, new)]
+    nblk = [-(-L // 16) for L in kv]
+    n_pool = sum(nblk) + 2
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.full((n, max(nblk) + 1), -1, np.int32)
+    o = 0
+    for i in range(n):
+        tables[i, :nblk[i]] = perm[o:o + nblk[i]]; o += nblk[i]
+    row = nkv * d
+    rb = int(ops.lib.logismos_turbo3_row_bytes(row))
+    kp = torch.zeros((n_pool, 16, rb), dtype=torch.uint8, device=DEV); vp = torch.zeros_like(kp)
+    qs, refs = [], []
+    for i in range(n):
+        L = kv[i]
+        q_t, q = bf16_cuda(rng.standard_normal((L, nh * d)))
+        k_t, k = bf16_cuda(rng.standard_normal((L, row))); v_t, v = bf16_cuda(rng.standard_normal((L, row)))
+        p = np.arange(L)
+        ops.paged_kv_store_turbo3(k_t, v_t, kp, vp, torch.from_numpy(tables[i, p // 16].astype(np.int64) * 16 + p % 16).to(DEV))
+        kd = O.bf16_round(O.turbo3_decode(O.turbo3_encode(k.reshape(L, row // 128, 128))).reshape(L, row))
+        vd = O.bf16_round(O.turbo3_decode(O.turbo3_encode(v.reshape(L, row // 128, 128))).reshape(L, row))
+        qs.append(q_t[cached[i]:])
+        refs.append(O.sdpa(q, kd, vd, nh, nkv, d, causal=True)[cached[i]:])
+    cu = np.zeros(n + 1, np.int32); cu[1:] = np.cumsum(new)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = to_np(ops.paged_prefix_attention(torch.cat(qs).contiguous(), torch.from_numpy(cu).to(DEV), torch.tensor(kv, dtype=torch.int32, device=DEV),
+                                           kp, vp, torch.from_numpy(tables).to(DEV), nh, nkv, d, status=status, turbo3=True))
+    assert int(status.item()) == 0
+    for i in range(n):
+        assert max_rel(out[cu[i]:cu[i + 1]], refs[i]) <= TOL, i

@@ -94,3 +94,33 @@ def test_step_rejects_what_it_cannot_run(setup):
     with pytest.raises(Exception):      # beyond the block table
         model.step([1], [128], [1], tab)
     model.close()
+
+
+def test_turbo3_cache_mode_runs_the_same_steps_at_the_codec_accuracy(setup):
+    """kv_turbo3: the cache holds TurboQuant 3-bit rows (4.57 times smaller) and every sequence attends
+    through the decoding gather. The K/V rows carry the codec's error (3 bits per value), so the stack is
+    compared with the fp32 oracle at the codec's accuracy, not at the bf16 bar: the kernel-level tests
+    (test_gpu_paged, test_gpu_attention) hold the cache bytes and the attention over them to the oracle."""
+    from gpu_util import cosine
+    qw, deq, oracle = setup
+    rng = np.random.default_rng(4)
+    alloc = BlockAllocator(64, 16, seed=3)
+    model = DecoderModel(TINY, qw, n_pool_blocks=64, max_blocks_per_seq=16, max_step_tokens=256, max_step_seqs=4, kv_turbo3=True)
+    hist = {0: rng.integers(0, 1000, 60).tolist(), 1: rng.integers(0, 1000, 130).tolist()}
+    # sequence 1 enters in two chunks (the second continues a cached, quantised prefix), sequence 0 whole
+    toks = model.step(hist[0] + hist[1][:64], [0, 0], [60, 64], np.stack([alloc.ensure(0, 60), alloc.ensure(1, 64)]))
+    assert model.device_status() == 0
+    hist[0].append(int(toks[0]))
+    toks = model.step([hist[0][-1]] + hist[1][64:], [60, 64], [1, 66], np.stack([alloc.ensure(0, 61), alloc.ensure(1, 130)]))
+    assert model.device_status() == 0
+    hist[1].append(int(toks[1])); hist[0].append(int(toks[0]))
+    for _ in range(3):
+        toks = model.step([hist[0][-1], hist[1][-1]], [len(hist[0]) - 1, len(hist[1]) - 1], [1, 1],
+                          np.stack([alloc.ensure(0, len(hist[0])), alloc.ensure(1, len(hist[1]))]))
+        assert model.device_status() == 0
+        hs = model.last_hidden()
+        for row, sid in enumerate((0, 1)):
+            h_ref, _ = oracle_last(oracle, deq, hist[sid])
+            assert np.isfinite(hs[row]).all() and cosine(hs[row], h_ref) >= 0.9, (sid, cosine(hs[row], h_ref))
+        hist[0].append(int(toks[0])); hist[1].append(int(toks[1]))
+    model.close()

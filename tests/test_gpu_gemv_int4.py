@@ -127,3 +127,21 @@ def test_tall_ragged_matrix_every_row(n, k, b):
     y = run(packed, scales, x_t)
     ref = O.int4_gemv(packed, scales.view(np.uint16), x)
     assert max_rel(y, ref) <= TOL
+
+
+@pytest.mark.parametrize("n,k,b", [(1536, 1536, 64), (8960, 1536, 17), (1536, 8960, 33), (151936, 1536, 64), (1000, 1536, 40), (256, 640, 64)])
+def test_skinny_route_above_16_rows(n, k, b):
+    """The entry point that picks the kernel by row count: from 17 rows (k a multiple of 256) the
+    fused-dequant tensor-core linear through a zeroed fp32 workspace, which it must leave zeroed; other
+    shapes stay on the GEMV. Same oracle, same bar."""
+    codes, packed, scales, x_t, x = make_case(n, k, b, n + 3 * b)
+    ws = torch.zeros(b * n, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pk, sc = torch.from_numpy(packed).to(DEV), torch.from_numpy(scales).to(DEV)
+    y = to_np(ops.skinny_int4(pk, sc, x_t, ws, status=status))
+    assert int(status.item()) == 0 and float(ws.abs().max()) == 0.0
+    rows = np.arange(n) if n <= 4096 else np.random.default_rng(0).choice(n, 4096, replace=False)
+    ref = O.int4_gemv(np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scales[rows]).view(np.uint16), x)
+    assert max_rel(y[:, rows], ref) <= TOL
+    y2 = to_np(ops.skinny_int4(pk, sc, x_t, ws, status=status))   # the workspace is reusable as left
+    assert max_rel(y2[:, rows], ref) <= TOL
