@@ -208,6 +208,22 @@ def workload_config(cfg, cu):
 # token + 7.09 MB of partials per 328868 tokens.
 NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 4.56e6) / 328868}
 
+PROFILER_RANGE = False
+
+
+def profiler_range(fn):
+    """With --profiler-range: run fn once between cudaProfilerStart and cudaProfilerStop (a profiler started
+    with its collection off captures exactly that step); otherwise nothing."""
+    if not PROFILER_RANGE:
+        return
+    import torch
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    fn()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
 GEMV_SHAPES = [(1536, 1536), (8960, 1536), (1536, 8960), (151936, 1536)]
 # what the decoder executors launch per layer at these dims: q|k|v and gate|up as one matrix each
 GEMV_FUSED_SHAPES = [("q|k|v", 2048, 1536), ("gate|up", 17920, 1536)]
@@ -236,7 +252,7 @@ def gemv_grid(peaks, shapes):
             t_hbm = timeit(lambda i: ops.skinny_int4(codes[i % copies], scales[i % copies], x, ws, out=y, status=stw, sync=False), iters, reps=2)
             t_l2 = timeit(lambda i: ops.skinny_int4(codes[0], scales[0], x, ws, out=y, status=stw, sync=False), 20) if wbytes < 100e6 else None
             by = wbytes + b * k * 2 + b * n * 2
-            out.append({"kernel": "gemv_int4_g32" if b <= 16 or k % 256 else "qlinear_int4_tcgen05 + finish (skinny route above 16 rows)", "shape": name, "n": n, "k": k, "batch": b, "bound": "hbm", "bytes_per_launch": by,
+            out.append({"kernel": "qlinear_int4_tcgen05 + finish (skinny route)" if ops.lib.logismos_skinny_int4_route(b, n, k) else "gemv_int4_g32", "shape": name, "n": n, "k": k, "batch": b, "bound": "hbm", "bytes_per_launch": by,
                         "us_per_launch": t_hbm * 1e6, "achieved": by / t_hbm / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                         "frac": by / t_hbm / 1e9 / peaks["hbm"], "weight_copies_rotated": copies,
                         "us_per_launch_l2_resident": t_l2 * 1e6 if t_l2 else None, "achieved_l2_resident": by / t_l2 / 1e9 if t_l2 else None,
@@ -361,6 +377,7 @@ def ragged_step_measure(R: Ranks, steps, warmup, layers=0):
     stream = torch.cuda.current_stream()
     for _ in range(max(warmup, 3)):
         model.replay_device(stream.cuda_stream)
+    profiler_range(lambda: model.replay_device(stream.cuda_stream))
     R.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -522,6 +539,7 @@ def run_ours(args, cfg, R: Ranks):
         t_wait = time.perf_counter()
         while not sampler.rows and time.perf_counter() - t_wait < 5.0:
             step(); torch.cuda.synchronize()
+    profiler_range(step)
     R.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -607,6 +625,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override depth (development only; the reported configs are 28 / 48)")
+    ap.add_argument("--profiler-range", action="store_true", help="bracket one extra untimed step with cudaProfilerStart/Stop")
     ap.add_argument("--no-micro", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode workloads of the default line")
@@ -620,6 +639,8 @@ def main():
     ap.add_argument("--prefill-budget", type=int, default=4096, help="serving_sweep: prompt tokens fed per step")
     ap.add_argument("--whole-prompts", action="store_true", help="serving_sweep: prefill every prompt whole in one step instead of in chunks")
     args = ap.parse_args()
+    global PROFILER_RANGE
+    PROFILER_RANGE = args.profiler_range
     if args.steps is None:
         args.steps = 0 if args.workload == "serving_sweep" else 20
     cfg = dict(STELLA_1_5B)

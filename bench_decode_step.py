@@ -2,7 +2,7 @@
 tokens each decode one token; the step's device work is replayed and timed with CUDA events, and
 the host-buffer entry point is timed around it. Used for launch lists and per-step rooflines.
 
-  python bench_decode_step.py [--seqs S --ctx C --layers L --iters I --prefill-chunk P]
+  python bench_decode_step.py [--seqs S --ctx C --layers L --iters I --prefill-chunk P --profiler-range]
 
 Prints one JSON line: device ms per step, host-entry ms per step, launches per step, and the
 algorithmic HBM bytes of the step (int4 weights once, recurrent states read + written, KV rows of
@@ -33,6 +33,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--prefill-chunk", type=int, default=8, help="sequences prefilled per step while building the contexts")
+    ap.add_argument("--profiler-range", action="store_true", help="bracket one extra untimed step with cudaProfilerStart/Stop")
     a = ap.parse_args(argv)
     cfg = dict(HYBRID_SERVING, n_layers=a.layers)
     w = random_int4_weights(cfg, 17)
@@ -58,6 +59,11 @@ def main(argv=None):
     for _ in range(3):
         model.replay_device(stream.cuda_stream)
     torch.cuda.synchronize()
+    if a.profiler_range:
+        torch.cuda.profiler.start()
+        model.replay_device(stream.cuda_stream)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(a.iters):

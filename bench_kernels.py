@@ -9,6 +9,8 @@ stream, operands rotated over several copies so that every launch reads from HBM
   python bench_kernels.py gdn     [--seqs S --len L]                 (token-serial vs chunk-parallel)
   python bench_kernels.py paged [--seqs S --min-ctx A --max-ctx B --chunk C --iters I]
   python bench_kernels.py attn  [--seqs S --len L --iters I]
+  python bench_kernels.py prefix [--seqs S --len CHUNK --prefix P --turbo3]   (prefill chunks over a cached, paged prefix)
+  python bench_kernels.py sampling [--seqs ROWS --n VOCAB]           (sampling chain over fp32 logits)
   python bench_kernels.py sweep          (every benchmark shape, one JSON line each)
 
 Prints one JSON line per case: achieved GB/s or TFLOP/s, the measured peak it is compared with
@@ -194,9 +196,69 @@ def bench_attn(seqs, length, iters, n_heads=12, n_kv=2):
             "us_tcgen05": t_tc * 1e6, "TFLOPs_tcgen05": fl / t_tc / 1e12}
 
 
+def bench_prefix(seqs, chunk, prefix, iters, n_heads=12, n_kv=2, d=128, turbo3=False):
+    """Causal attention of `seqs` prefill chunks of `chunk` tokens, each continuing a cached prefix of `prefix`
+    tokens read through block tables (gather launch + attention launch), bf16 or TurboQuant 3-bit pool rows."""
+    kv_len = prefix + chunk
+    nb = (kv_len + 15) // 16
+    T = seqs * chunk
+    row = n_kv * d
+    g = torch.Generator(device="cpu").manual_seed(5)
+    tables = torch.randperm(seqs * nb, generator=g).to(torch.int32).reshape(seqs, nb).cuda()
+    if turbo3:
+        rb = int(lib.logismos_turbo3_row_bytes(row))
+        kp = torch.randint(0, 256, (seqs * nb, 16, rb), dtype=torch.uint8, device="cuda")
+        vp = torch.randint(0, 256, (seqs * nb, 16, rb), dtype=torch.uint8, device="cuda")
+        kp[..., 0::14] = 0; kp[..., 1::14] = 0x3c; vp[..., 0::14] = 0; vp[..., 1::14] = 0x3c   # fp16 norm 1.0 in every block header
+    else:
+        kp = torch.randn((seqs * nb, 16, row), device="cuda").to(torch.bfloat16)
+        vp = torch.randn((seqs * nb, 16, row), device="cuda").to(torch.bfloat16)
+    q = torch.randn((T, n_heads * d), device="cuda").to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, chunk, dtype=torch.int32, device="cuda")
+    kv = torch.full((seqs,), kv_len, dtype=torch.int32, device="cuda")
+    out = torch.empty((T, n_heads * d), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(int(lib.logismos_paged_prefix_attention_scratch_bytes(seqs * kv_len, seqs, n_kv, d)), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lib.logismos_launch_paged_prefix_attention_turbo3_bf16 if turbo3 else lib.logismos_launch_paged_prefix_attention_tc_bf16
+
+    def run(i):
+        ops.check(fn(q.data_ptr(), q.shape[1], cu.data_ptr(), kv.data_ptr(), kp.data_ptr(), vp.data_ptr(), tables.data_ptr(), nb, seqs * nb,
+                     out.data_ptr(), scratch.data_ptr(), T, seqs * kv_len, seqs, chunk, kv_len, n_heads, n_kv, d, status.data_ptr(),
+                     torch.cuda.current_stream().cuda_stream), "paged_prefix_attention")
+    t = timeit(run, iters)
+    fl = 4.0 * n_heads * d * seqs * (chunk * prefix + chunk * (chunk + 1) / 2.0)
+    return {"kernel": "paged_prefix_attention" + ("_turbo3" if turbo3 else ""), "seqs": seqs, "chunk": chunk, "prefix": prefix, "us": t * 1e6,
+            "TFLOPs": fl / t / 1e12, "gathered_bytes": 2 * seqs * kv_len * row * 2, "device_status": int(status.item())}
+
+
+def bench_sampling(rows, vocab, iters):
+    """The device sampling chain over fp32 logits [rows, vocab]: time per launch of each processor and of the sampler."""
+    from logismos_b200 import sampling as S
+    base = torch.randn((rows, vocab), device="cuda") * 3.0
+    work = base.clone()
+    uni = torch.rand((rows,), device="cuda")
+    tok = torch.empty((rows,), dtype=torch.int32, device="cuda")
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    out = {"kernel": "sampling", "rows": rows, "vocab": vocab, "logit_bytes": rows * vocab * 4}
+
+    def timed(name, fn):
+        def run(i):
+            work.copy_(base)
+            fn()
+        def ref(i):
+            work.copy_(base)
+        out["us_" + name] = (timeit(run, iters) - timeit(ref, iters)) * 1e6
+    timed("temperature", lambda: ops.check(lib.logismos_launch_temperature_f32(work.data_ptr(), rows, vocab, 0.8, st()), "temperature"))
+    timed("top_k_50", lambda: ops.check(lib.logismos_launch_top_k_f32(work.data_ptr(), rows, vocab, 50, st()), "top_k"))
+    timed("top_p_0.95", lambda: ops.check(lib.logismos_launch_top_p_f32(work.data_ptr(), rows, vocab, 0.95, st()), "top_p"))
+    timed("min_p_0.05", lambda: ops.check(lib.logismos_launch_min_p_f32(work.data_ptr(), rows, vocab, 0.05, st()), "min_p"))
+    timed("multinomial", lambda: ops.check(lib.logismos_launch_multinomial_f32(work.data_ptr(), rows, vocab, uni.data_ptr(), tok.data_ptr(), st()), "multinomial"))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="bench_kernels.py")
-    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "gdn", "paged", "attn", "sweep"])
+    ap.add_argument("what", choices=["gemv", "gemm", "qlinear", "qdense", "gdn", "paged", "attn", "prefix", "sampling", "sweep"])
     ap.add_argument("--m", type=int, default=2176)
     ap.add_argument("--n", type=int, default=151936)
     ap.add_argument("--k", type=int, default=1536)
@@ -208,6 +270,8 @@ def main(argv=None):
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--chunk", type=int, default=0, help="paged: tokens per chunk; 0 = the library's choice for the contexts")
     ap.add_argument("--head-dim", type=int, default=128, help="paged: 128 or 256")
+    ap.add_argument("--prefix", type=int, default=2048, help="prefix: cached tokens in front of every chunk of --len tokens")
+    ap.add_argument("--turbo3", action="store_true", help="prefix: TurboQuant 3-bit pool rows")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-graph", action="store_true", help="time back-to-back launches from Python instead of a CUDA graph")
     a = ap.parse_args(argv)
@@ -226,6 +290,10 @@ def main(argv=None):
         print(json.dumps(bench_paged(a.seqs, a.min_ctx, a.max_ctx, a.chunk, a.iters, d=a.head_dim)))
     elif a.what == "attn":
         print(json.dumps(bench_attn(a.seqs, a.len, a.iters)))
+    elif a.what == "prefix":
+        print(json.dumps(bench_prefix(a.seqs, a.len, a.prefix, a.iters, turbo3=a.turbo3)))
+    elif a.what == "sampling":
+        print(json.dumps(bench_sampling(a.seqs, a.n, a.iters)))
     else:
         pk = peaks()
         for (n, k) in [(1536, 1536), (8960, 1536), (1536, 8960), (151936, 1536)]:

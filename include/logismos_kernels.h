@@ -222,11 +222,13 @@ uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes_u8, const void* sca
                                            const void* x_bf16, void* y_f32, int32_t batch, int32_t n,
                                            int32_t k, void* stream);
 
-/* The same product, y bf16 [batch, n], with the kernel chosen by batch: up to 16 rows the streaming
- * GEMV; from 17 to 64 rows (k % 256 == 0, n % 4 == 0) the fused-dequant tensor-core linear below,
- * accumulating in workspace_f32 [batch, n] (16-byte aligned, ALL ZERO on entry, left all zero on
- * return) and rounded once to bf16. workspace_f32 == NULL keeps the GEMV at every batch. status_i32
- * as for logismos_launch_qlinear_int4_g32_acc_f32. Two launches above 16 rows. */
+/* The same product, y bf16 [batch, n], with the kernel chosen by shape and batch
+ * (logismos_skinny_int4_route: 0 = the streaming GEMV, 1 = the fused-dequant tensor-core linear below,
+ * taken above 16 rows, for k >= 3 n, and from 8 rows up to n = 16384; needs k % 256 == 0, n % 4 == 0).
+ * Route 1 accumulates in workspace_f32 [batch, n] (16-byte aligned, ALL ZERO on entry, left all zero
+ * on return) and rounds once to bf16: two launches. workspace_f32 == NULL keeps the GEMV at every
+ * batch. status_i32 as for logismos_launch_qlinear_int4_g32_acc_f32. */
+int32_t logismos_skinny_int4_route(int32_t batch, int32_t n, int32_t k);
 uint32_t logismos_launch_skinny_int4_g32_bf16(const void* codes_u8, const void* scales_f16,
                                               const void* x_bf16, void* y_bf16, int32_t batch, int32_t n,
                                               int32_t k, void* workspace_f32, void* status_i32, void* stream);

@@ -79,6 +79,7 @@ def _declare(l):
         "logismos_launch_gemv_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp],
         "logismos_launch_gemv_int4_g32_f32": [vp, vp, vp, vp, i32, i32, i32, vp],
         "logismos_launch_skinny_int4_g32_bf16": [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp],
+        "logismos_skinny_int4_route": [i32, i32, i32],
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_qlinear_int4_g32_acc_f32": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_qlinear_finish_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
@@ -163,6 +164,7 @@ def _declare(l):
     l.logismos_set_deterministic.restype = None
     l.logismos_get_deterministic.argtypes = []
     l.logismos_get_deterministic.restype = i32
+    l.logismos_skinny_int4_route.restype = i32
     l.lg_safetensors_close.argtypes = [vp]
     l.lg_safetensors_close.restype = None
     l.lg_safetensors_len.argtypes = [vp]

@@ -824,18 +824,30 @@ extern "C" uint32_t logismos_launch_gemv_int4_g32_f32(const void* codes, const v
   return launch_gemv(codes, scales_f16, x_bf16, y_f32, 1, batch, n, k, stream);
 }
 
-// The same product for any batch up to 64 with the route chosen by row count: up to 16 rows the
-// streaming GEMV above; from 17 rows the fused-dequant tensor-core kernel (qgemm_tcgen05.cu), whose
-// fp32 sums go through `workspace` and are rounded to bf16 by its finishing kernel. The mma.sync GEMV
-// re-reads the activation fragments from shared memory for every 16 weight rows, which at 64 batch
-// rows costs several times the weight stream; the tensor-core kernel keeps them in one operand tile.
+// The same product for any batch up to 64 with the route chosen by shape and row count: the streaming
+// GEMV above, or the fused-dequant tensor-core kernel (qgemm_tcgen05.cu), whose fp32 sums go through
+// `workspace` and are rounded to bf16 by its finishing kernel. The mma.sync GEMV re-reads the activation
+// fragments from shared memory for every 16 weight rows (at 64 batch rows that costs several times the
+// weight stream) and walks k serially per row tile, so few long rows leave most SMs idle; the
+// tensor-core kernel keeps the activations in one operand tile and splits k over the CTAs. Measured
+// crossovers (time per launch, weights from HBM): above 16 rows always; k >= 3 n at every batch
+// (1536 x 8960: 10.9 against 19.9 us at one row, 58 us at 16); 8 to 16 rows up to n = 16384 (7.8 against
+// 9.1 / 18.6 us for 1536 x 1536). The vocabulary-sized matrices stay on the GEMV up to 16 rows (55
+// against 67 us).
+extern "C" int32_t logismos_skinny_int4_route(int32_t batch, int32_t n, int32_t k) {
+  if ((k % 256) != 0 || (n % 4) != 0 || batch < 1 || batch > 64) return 0;
+  if (batch > 16) return 1;
+  if ((int64_t)k >= 3 * (int64_t)n) return 1;
+  return batch >= 8 && n <= 16384 ? 1 : 0;
+}
+
 extern "C" uint32_t logismos_launch_skinny_int4_g32_bf16(const void* codes, const void* scales_f16, const void* x_bf16, void* y_bf16,
                                                          int32_t batch, int32_t n, int32_t k, void* workspace_f32, void* status_i32,
                                                          void* stream) {
   lg::LaunchScope launch_scope_;
-  if (batch <= 16 || (k % 256) != 0 || (n % 4) != 0 || workspace_f32 == nullptr)
+  if (workspace_f32 == nullptr || !logismos_skinny_int4_route(batch, n, k))
     return launch_gemv(codes, scales_f16, x_bf16, y_bf16, 0, batch, n, k, stream);
-  if (batch > 64 || ((uintptr_t)workspace_f32 & 15)) return lg::kInvalidValue;
+  if ((uintptr_t)workspace_f32 & 15) return lg::kInvalidValue;
   const uint32_t rc = logismos_launch_qlinear_int4_g32_acc_f32(x_bf16, codes, scales_f16, workspace_f32, batch, n, k, k, n, status_i32, stream);
   if (rc) return rc;
   return logismos_launch_qlinear_finish_bf16(workspace_f32, nullptr, y_bf16, batch, n, n, n, 0, stream);

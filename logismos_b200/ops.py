@@ -298,8 +298,9 @@ def gemv_int4(codes, scales, x, out=None, sync=True, out_f32=False):
 
 
 def skinny_int4(codes, scales, x, workspace, out=None, status=None, sync=True):
-    """y = x @ dequant(codes, scales)^T for 1..64 rows with the kernel chosen by row count (GEMV up to 16
-    rows, fused-dequant tensor-core linear above). ``workspace``: fp32 CUDA tensor of at least
+    """y = x @ dequant(codes, scales)^T for 1..64 rows with the kernel chosen by shape and row count
+    (``lib.logismos_skinny_int4_route``: streaming GEMV, or the fused-dequant tensor-core linear above 16
+    rows, for k >= 3 n, and from 8 rows up to n = 16384). ``workspace``: fp32 CUDA tensor of at least
     batch * n elements, all zero on entry; it is left all zero."""
     _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2); _req(x, "x", torch.bfloat16, 2)
     _req(workspace, "workspace", torch.float32, None)

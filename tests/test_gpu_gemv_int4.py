@@ -129,11 +129,15 @@ def test_tall_ragged_matrix_every_row(n, k, b):
     assert max_rel(y, ref) <= TOL
 
 
-@pytest.mark.parametrize("n,k,b", [(1536, 1536, 64), (8960, 1536, 17), (1536, 8960, 33), (151936, 1536, 64), (1000, 1536, 40), (256, 640, 64)])
-def test_skinny_route_above_16_rows(n, k, b):
-    """The entry point that picks the kernel by row count: from 17 rows (k a multiple of 256) the
-    fused-dequant tensor-core linear through a zeroed fp32 workspace, which it must leave zeroed; other
-    shapes stay on the GEMV. Same oracle, same bar."""
+@pytest.mark.parametrize("n,k,b", [(1536, 1536, 64), (8960, 1536, 17), (1536, 8960, 33), (151936, 1536, 64), (1000, 1536, 40), (256, 640, 64),
+                                   (1536, 8960, 1), (1536, 8960, 4), (2048, 6144, 16), (1536, 1536, 8), (8960, 1536, 12), (17920, 1536, 16)])
+def test_skinny_route_by_shape_and_rows(n, k, b):
+    """The entry point that picks the kernel by shape and row count (k a multiple of 256): above 16 rows,
+    for k >= 3 n at any batch and from 8 rows up to n = 16384 the fused-dequant tensor-core linear through
+    a zeroed fp32 workspace, which it must leave zeroed; other shapes stay on the GEMV. Same oracle,
+    same bar."""
+    expect = int(k % 256 == 0 and n % 4 == 0 and (b > 16 or k >= 3 * n or (b >= 8 and n <= 16384)))
+    assert ops.lib.logismos_skinny_int4_route(b, n, k) == expect
     codes, packed, scales, x_t, x = make_case(n, k, b, n + 3 * b)
     ws = torch.zeros(b * n, dtype=torch.float32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
