@@ -35,6 +35,14 @@ extern "C" {
 void logismos_set_deterministic(int32_t on);
 int32_t logismos_get_deterministic(void);
 
+/* Process-wide switch, on by default (LOGISMOS_DEPENDENT_LAUNCH=0 sets the initial value to off): the
+ * kernels of the model steps are launched with programmatic stream serialisation, i.e. the next kernel
+ * of the same stream is scheduled while the current one drains and waits on the device for its
+ * completion before touching memory. Results do not change; the gaps between dependent launches
+ * shrink. Off, every launch is an ordinary stream-ordered launch. No reference counterpart. */
+void logismos_set_dependent_launch(int32_t on);
+int32_t logismos_get_dependent_launch(void);
+
 /* ====================================================================================
  * The reference's four fp16 launchers, same symbols and argument lists.
  * ==================================================================================== */

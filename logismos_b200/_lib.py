@@ -165,6 +165,10 @@ def _declare(l):
     l.logismos_get_deterministic.argtypes = []
     l.logismos_get_deterministic.restype = i32
     l.logismos_skinny_int4_route.restype = i32
+    l.logismos_set_dependent_launch.argtypes = [i32]
+    l.logismos_set_dependent_launch.restype = None
+    l.logismos_get_dependent_launch.argtypes = []
+    l.logismos_get_dependent_launch.restype = i32
     l.lg_safetensors_close.argtypes = [vp]
     l.lg_safetensors_close.restype = None
     l.lg_safetensors_len.argtypes = [vp]

@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(kVarlenThreads, HD == 128 ? 3 : 1)
 varlen_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu,
                         __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int row_stride,
                         int k_off, int v_off, float sl2) {
+  lg::pdl_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int seq = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
   const int s0 = cu[seq], len = cu[seq + 1] - s0;
@@ -291,6 +292,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
                     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                     int* __restrict__ status, int n_seqs, int chunk_tokens, int max_blocks, int n_pool_blocks,
                     int n_heads, int n_kv, float sl2) {
+  lg::pdl_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int chunk_id = blockIdx.x, kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -470,6 +472,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
 __global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           const int* __restrict__ chunk_offsets, __nv_bfloat16* __restrict__ out,
                                           int n_heads, int D, float sl2) {
+  lg::pdl_prologue();
   const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int c0 = chunk_offsets[seq], c1 = chunk_offsets[seq + 1];
   if (c1 - c0 <= 1) return;  // single-chunk sequences were finished by the main kernel
@@ -491,6 +494,7 @@ __global__ void paged_kv_store_kernel(const __nv_bfloat16* __restrict__ k, const
                                       int src_stride, __nv_bfloat16* __restrict__ kpool,
                                       __nv_bfloat16* __restrict__ vpool, const int64_t* __restrict__ slots,
                                       int n_tokens, int row_elems, int64_t n_slots, int* __restrict__ status) {
+  lg::pdl_prologue();
   const int chunks = row_elems >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n_tokens * chunks) return;
@@ -508,6 +512,7 @@ __global__ void paged_kv_gather_kernel(const __nv_bfloat16* __restrict__ kpool, 
                                        const int* __restrict__ table, int table_len, int len, int row_elems,
                                        int n_pool_blocks, __nv_bfloat16* __restrict__ kout,
                                        __nv_bfloat16* __restrict__ vout, int* __restrict__ status) {
+  lg::pdl_prologue();
   const int chunks = row_elems >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)len * chunks) return;
@@ -542,7 +547,7 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv, const void* cu_s
   auto launch = [&](auto kern) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, kVarlenThreads, smem, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, (__nv_bfloat16*)out,
+    lg::launch(kern, grid, dim3(kVarlenThreads), smem, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, (__nv_bfloat16*)out,
                                                              n_heads, n_kv_heads, row_stride, k_off, v_off, sl2);
     return lg::launch_status();
   };
@@ -574,7 +579,7 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
   auto launch = [&](auto kern, int warps, int smem) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, warps * 32, smem, (cudaStream_t)stream>>>(
+    lg::launch(kern, grid, dim3(warps * 32), smem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)q, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)new_k,
         (const __nv_bfloat16*)new_v, (const int*)block_tables, (const int*)context_lens, (const int*)chunk_offsets,
         (__nv_bfloat16*)out, part_o, part_ml, (int*)status, n_seqs, chunk_tokens, max_blocks, n_pool_blocks, n_heads,
@@ -595,7 +600,7 @@ uint32_t logismos_launch_paged_attention_decode_bf16(
   if (rc) return rc;
   if (total_chunks > n_seqs) {  // at least one sequence spans several chunks
     dim3 mgrid(n_seqs, n_heads);
-    paged_decode_merge_kernel<<<mgrid, head_dim, 0, (cudaStream_t)stream>>>(part_o, part_ml, (const int*)chunk_offsets,
+    lg::launch(paged_decode_merge_kernel, mgrid, dim3(head_dim), 0, (cudaStream_t)stream, part_o, part_ml, (const int*)chunk_offsets,
                                                                            (__nv_bfloat16*)out, n_heads, head_dim, sl2);
     rc = lg::launch_status();
   }
@@ -610,7 +615,7 @@ uint32_t logismos_launch_paged_kv_store_bf16(const void* k, const void* v, int32
     return lg::kInvalidValue;
   if (n_tokens == 0) return 0;
   const int64_t total = (int64_t)n_tokens * (row_elems / 8);
-  paged_kv_store_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(paged_kv_store_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, src_row_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
       (const int64_t*)slot_mapping, n_tokens, row_elems, n_pool_slots, (int*)status);
   return lg::launch_status();
@@ -624,7 +629,7 @@ uint32_t logismos_launch_paged_kv_gather_bf16(const void* k_pool, const void* v_
   if (table_len < 0 || len < 0 || row_elems <= 0 || (row_elems % 8)) return lg::kInvalidValue;
   if (len == 0) return 0;
   const int64_t total = (int64_t)len * (row_elems / 8);
-  paged_kv_gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(paged_kv_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const int*)block_table, table_len, len, row_elems,
       n_pool_blocks, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (int*)status);
   return lg::launch_status();

@@ -129,6 +129,7 @@ template <int HD>
 __global__ void __launch_bounds__(256)
 transpose_v_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ cu, __nv_bfloat16* __restrict__ vt,
                    int* __restrict__ pstart, int n_seqs, int row_stride, int v_off, int tp, int tx, int n_kv, RopeArgs rope) {
+  lg::pdl_prologue();
   __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
   constexpr int kParts = 256 / HD, kChunks = HD / 8;  // threads per d row; 16-byte chunks per token row
   __shared__ int p0_s;
@@ -196,6 +197,7 @@ gather_paged_kv_kernel(const __nv_bfloat16* __restrict__ kpool, const __nv_bfloa
                        const int* __restrict__ tables, int max_blocks, int n_pool_blocks, const int* __restrict__ kv_lens,
                        __nv_bfloat16* __restrict__ kbuf, __nv_bfloat16* __restrict__ vt, int* __restrict__ pstart, int n_seqs,
                        int tp, int tx, int n_kv, int* __restrict__ status) {
+  lg::pdl_prologue();
   __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
   constexpr int kParts = 256 / HD, kChunks = HD / 8;
   __shared__ int p0_s;
@@ -273,6 +275,7 @@ gather_paged_kv_turbo3_kernel(const uint8_t* __restrict__ kpool, const uint8_t* 
                               int max_blocks, int n_pool_blocks, const int* __restrict__ kv_lens, __nv_bfloat16* __restrict__ kbuf,
                               __nv_bfloat16* __restrict__ vt, int* __restrict__ pstart, int n_seqs, int tp, int tx, int n_kv,
                               int* __restrict__ status) {
+  lg::pdl_prologue();
   __shared__ __align__(16) __nv_bfloat16 tile[64][HD + 8];
   __shared__ uint32_t words[8][16];
   constexpr int kParts = 256 / HD, kCh = HD / 128;  // threads per d row; head chunks per key
@@ -351,6 +354,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ cu, const int* __restrict__ pstart,
                     const int* __restrict__ kv_lens, __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int k_off,
                     float sl2, int* __restrict__ status) {
+  lg::pdl_prologue();
   using C = Attn<HD>;
   constexpr int kQBytes = C::kQBytes, kKBytes = C::kKBytes, kVBytes = C::kVBytes, kVTile = C::kVTile;
   constexpr uint32_t kTmemCols = C::kTmemCols;
@@ -622,10 +626,10 @@ static uint32_t launch_attn_tc(const void* qkv, const void* cu_seqlens, void* ou
   const int64_t blocks = (int64_t)tx * n_kv_heads * n_seqs + (rope_threads + 255) / 256;
   if (blocks > 0x7fffffff) return lg::kInvalidValue;
   if (D == 128)
-    transpose_v_kernel<128><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
+    lg::launch(transpose_v_kernel<128>, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
                                                              row_stride, v_off, tp, tx, n_kv_heads, rope);
   else
-    transpose_v_kernel<256><<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
+    lg::launch(transpose_v_kernel<256>, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)qkv, (const int*)cu_seqlens, vt, pstart, n_seqs,
                                                              row_stride, v_off, tp, tx, n_kv_heads, rope);
   uint32_t rc = lg::launch_status();
   if (rc) return rc;
@@ -634,7 +638,7 @@ static uint32_t launch_attn_tc(const void* qkv, const void* cu_seqlens, void* ou
   auto launch = [&](auto kern, size_t smem) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, 192, smem, s>>>(map_qk, map_qk, map_vt, (const int*)cu_seqlens, pstart, (const int*)nullptr, (__nv_bfloat16*)out,
+    lg::launch(kern, grid, dim3(192), smem, s, map_qk, map_qk, map_vt, (const int*)cu_seqlens, pstart, (const int*)nullptr, (__nv_bfloat16*)out,
                                  n_heads, n_kv_heads, k_off, sl2, (int*)status);
     return lg::launch_status();
   };
@@ -699,7 +703,7 @@ static uint32_t launch_prefix_attn(const void* q, int32_t q_row_stride, const vo
   if (blocks > 0x7fffffff) return lg::kInvalidValue;
   if (blocks > 0) {
     auto go = [&](auto kern, auto* kp, auto* vp) {
-      kern<<<(unsigned)blocks, 256, 0, s>>>(kp, vp, (const int*)block_tables, max_blocks, n_pool_blocks, (const int*)kv_lens, kbuf, vt, pstart,
+      lg::launch(kern, dim3((unsigned)blocks), dim3(256), 0, s, kp, vp, (const int*)block_tables, max_blocks, n_pool_blocks, (const int*)kv_lens, kbuf, vt, pstart,
                                             n_seqs, tp, tx, n_kv_heads, (int*)status);
     };
     if (turbo3) {
@@ -717,7 +721,7 @@ static uint32_t launch_prefix_attn(const void* q, int32_t q_row_stride, const vo
   auto launch = [&](auto kern, size_t smem) -> uint32_t {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (uint32_t)e;
-    kern<<<grid, 192, smem, s>>>(map_q, map_k, map_vt, (const int*)cu_seqlens_q, pstart, (const int*)kv_lens, (__nv_bfloat16*)out,
+    lg::launch(kern, grid, dim3(192), smem, s, map_q, map_k, map_vt, (const int*)cu_seqlens_q, pstart, (const int*)kv_lens, (__nv_bfloat16*)out,
                                  n_heads, n_kv_heads, 0, sl2, (int*)status);
     return lg::launch_status();
   };

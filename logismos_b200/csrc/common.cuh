@@ -25,6 +25,42 @@ struct LaunchScope {
 // not depend on how many rows share a launch.
 bool deterministic();
 
+// Process-wide switch (logismos_set_dependent_launch, default on): kernels of the model steps are
+// launched with programmatic stream serialisation, so that the next kernel of the stream is scheduled
+// while the current one drains. The contract every kernel launched through lg::launch keeps:
+// pdl_prologue() is the first statement of the kernel, before any access to global memory and before
+// any tensor-memory allocation. It first lets the dependent grid be scheduled (its blocks then wait at
+// their own prologue) and then blocks until every grid this one depends on has completed and its
+// writes are visible. Because each kernel of a chain passes that wait before it can complete,
+// completion of the direct predecessor implies completion of everything before it. Allocating tensor
+// memory only after the wait matters: a dependent block that took tensor memory before a block of the
+// running grid on the same SM had allocated its own would wait for a grid that waits for it.
+bool dependent_launch();
+
+LG_DEVINL void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+LG_DEVINL void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+LG_DEVINL void pdl_prologue() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+// kern<<<grid, block, smem, stream>>>(args...) with the programmatic-serialisation attribute when the
+// switch is on. The launch status is read by the caller with launch_status(), as after <<<>>>.
+template <typename... P, typename... A>
+inline void launch(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = dependent_launch() ? 1u : 0u;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 // Shape-guard failures are reported as cudaErrorInvalidValue (1) without launching.
 constexpr uint32_t kInvalidValue = 1u;
 

@@ -188,10 +188,22 @@ bool deterministic() {
   }
   return v != 0;
 }
+static std::atomic<int> g_dependent_launch{-1};
+bool dependent_launch() {
+  int v = g_dependent_launch.load(std::memory_order_relaxed);
+  if (v < 0) {  // first use: on unless the environment says 0
+    const char* e = std::getenv("LOGISMOS_DEPENDENT_LAUNCH");
+    v = (e && e[0] == '0') ? 0 : 1;
+    g_dependent_launch.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
 }  // namespace lg
 
 extern "C" {
 
+void logismos_set_dependent_launch(int32_t on) { lg::g_dependent_launch.store(on ? 1 : 0, std::memory_order_relaxed); }
+int32_t logismos_get_dependent_launch(void) { return lg::dependent_launch() ? 1 : 0; }
 void logismos_set_deterministic(int32_t on) { lg::g_deterministic.store(on ? 1 : 0, std::memory_order_relaxed); }
 int32_t logismos_get_deterministic(void) { return lg::deterministic() ? 1 : 0; }
 

@@ -14,6 +14,7 @@ using namespace lg;
 
 __global__ void dequant_int4_g32_kernel(const uint32_t* __restrict__ codes, const __half* __restrict__ scales,
                                         __nv_bfloat16* __restrict__ out, int64_t n_words, int words_per_row) {
+  lg::pdl_prologue();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 32-bit word = 8 weights
   if (idx >= n_words) return;
   const int64_t row = idx / words_per_row;
@@ -34,6 +35,7 @@ __global__ void dequant_int4_g32_kernel(const uint32_t* __restrict__ codes, cons
 // two per byte, even k in the low nibble. Integer output: bit-exact against the CPU definition.
 __global__ void quantize_int4_g32_kernel(const float* __restrict__ w, uint32_t* __restrict__ codes, __half* __restrict__ scales,
                                          int64_t n_groups) {
+  lg::pdl_prologue();
   const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= n_groups) return;
   const float4* src = reinterpret_cast<const float4*>(w + g * 32);
@@ -74,7 +76,7 @@ extern "C" uint32_t logismos_launch_quantize_int4_g32(const void* w_f32, void* c
   const int64_t groups = (int64_t)n * (k / 32);
   const int64_t blocks = (groups + 127) / 128;
   if (blocks > 2147483647ll) return lg::kInvalidValue;
-  quantize_int4_g32_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>((const float*)w_f32, (uint32_t*)codes_u8, (__half*)scales_f16, groups);
+  lg::launch(quantize_int4_g32_kernel, dim3((unsigned)blocks), dim3(128), 0, (cudaStream_t)stream, (const float*)w_f32, (uint32_t*)codes_u8, (__half*)scales_f16, groups);
   return lg::launch_status();
 }
 
@@ -86,7 +88,7 @@ extern "C" uint32_t logismos_launch_dequant_int4_g32_bf16(const void* codes, con
   const int bs = 256;
   const int64_t blocks = (n_words + bs - 1) / bs;
   if (blocks > 2147483647ll) return lg::kInvalidValue;
-  dequant_int4_g32_kernel<<<(unsigned)blocks, bs, 0, (cudaStream_t)stream>>>(
+  lg::launch(dequant_int4_g32_kernel, dim3((unsigned)blocks), dim3(bs), 0, (cudaStream_t)stream, 
       (const uint32_t*)codes, (const __half*)scales, (__nv_bfloat16*)out_bf16, n_words, k / 8);
   return lg::launch_status();
 }

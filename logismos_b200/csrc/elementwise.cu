@@ -13,6 +13,7 @@ using namespace lg;
 __global__ void embed_lookup_kernel(const __nv_bfloat16* __restrict__ table,
                                     const uint32_t* __restrict__ ids, float* __restrict__ out,
                                     int n_ids, int hidden, int vocab) {
+  lg::pdl_prologue();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_ids) return;
   const int lane = threadIdx.x & 31;
@@ -36,6 +37,7 @@ __global__ void embed_lookup_kernel(const __nv_bfloat16* __restrict__ table,
 template <bool OUT_F32>
 __global__ void rms_norm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                     void* __restrict__ y, int n, float eps) {
+  lg::pdl_prologue();
   __shared__ float red[32];
   const float* row = x + (size_t)blockIdx.x * n;
   float4 v[8];
@@ -69,6 +71,7 @@ template <bool OUT_F32, int NV>
 __global__ void __launch_bounds__(256)
 rms_norm_f32_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, void* __restrict__ y,
                          int rows, int n, float eps) {
+  lg::pdl_prologue();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -104,7 +107,7 @@ rms_norm_f32_warp_kernel(const float* __restrict__ x, const float* __restrict__ 
 
 template <bool OUT_F32, int NV>
 void launch_rms_warp(const void* x, const void* w, void* y, int rows, int n, float eps, cudaStream_t s) {
-  rms_norm_f32_warp_kernel<OUT_F32, NV><<<(rows + 7) / 8, 256, 0, s>>>((const float*)x, (const float*)w, y, rows, n, eps);
+  lg::launch(rms_norm_f32_warp_kernel<OUT_F32, NV>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)x, (const float*)w, y, rows, n, eps);
 }
 
 template <bool OUT_F32>
@@ -122,6 +125,7 @@ __global__ void rope_halves_kernel(__nv_bfloat16* __restrict__ qk, const float* 
                                    const float* __restrict__ sinT, const int* __restrict__ positions,
                                    int n_tokens, int n_heads, int head_dim, int row_stride,
                                    int max_pos, int* __restrict__ status) {
+  lg::pdl_prologue();
   const int half = head_dim >> 1, pairs = half >> 1;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)n_tokens * n_heads * pairs;
@@ -149,6 +153,7 @@ __global__ void rope_halves_vec8_kernel(__nv_bfloat16* __restrict__ qk, const fl
                                         const float* __restrict__ sinT, const int* __restrict__ positions,
                                         int n_tokens, int n_heads, int head_dim, int row_stride,
                                         int max_pos, int* __restrict__ status) {
+  lg::pdl_prologue();
   const int half = head_dim >> 1, octs = half >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t total = (int64_t)n_tokens * n_heads * octs;
@@ -185,6 +190,7 @@ __global__ void rope_halves_vec8_kernel(__nv_bfloat16* __restrict__ qk, const fl
 // cpu_f32::silu (x / (1 + e^-x), mod.rs:349-351) times up (hadamard, :365-374).
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                               int rows, int inter) {
+  lg::pdl_prologue();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // 8 outputs per thread
   const int per_row = inter >> 3;
   if (idx >= (int64_t)rows * per_row) return;
@@ -209,6 +215,7 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
 //   l2_rows:   CTA = sequence
 __global__ void pool_mean_kernel(const float* __restrict__ hs, const int* __restrict__ cu,
                                  float* __restrict__ pooled, int hidden) {
+  lg::pdl_prologue();
   const int s0 = cu[blockIdx.x], s1 = cu[blockIdx.x + 1];
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   if (j >= hidden) return;
@@ -230,6 +237,7 @@ __global__ void pool_mean_kernel(const float* __restrict__ hs, const int* __rest
 
 __global__ void head_rows_kernel(const float* __restrict__ pooled, const __nv_bfloat16* __restrict__ hw,
                                  const float* __restrict__ hb, float* __restrict__ out, int hidden, int dim) {
+  lg::pdl_prologue();
   extern __shared__ float pn[];  // normalised pooled vector
   __shared__ float red[32];
   const float* pv = pooled + (size_t)blockIdx.x * hidden;
@@ -256,6 +264,7 @@ __global__ void head_rows_kernel(const float* __restrict__ pooled, const __nv_bf
 }
 
 __global__ void l2_rows_kernel(float* __restrict__ y, int dim) {
+  lg::pdl_prologue();
   __shared__ float red[32];
   float* row = y + (size_t)blockIdx.x * dim;
   float sq = 0.0f;
@@ -269,6 +278,7 @@ __global__ void l2_rows_kernel(float* __restrict__ y, int dim) {
 // and NaN is never selected. One CTA per row; ties across threads resolve to the lowest index.
 template <typename T>
 __global__ void greedy_argmax_kernel(const T* __restrict__ logits, uint32_t* __restrict__ out, int n) {
+  lg::pdl_prologue();
   __shared__ float bv[32];
   __shared__ int bi[32];
   const T* row = logits + (size_t)blockIdx.x * n;
@@ -327,7 +337,7 @@ uint32_t logismos_launch_embed_lookup_bf16(const void* table, const void* ids, v
   if (n_ids < 0 || hidden <= 0 || vocab <= 0 || (hidden % 8)) return lg::kInvalidValue;
   if (n_ids == 0) return 0;
   const int wpb = 8;
-  embed_lookup_kernel<<<(n_ids + wpb - 1) / wpb, wpb * 32, 0, (cudaStream_t)stream>>>(
+  lg::launch(embed_lookup_kernel, dim3((n_ids + wpb - 1) / wpb), dim3(wpb * 32), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)table, (const uint32_t*)ids, (float*)out, n_ids, hidden, vocab);
   return lg::launch_status();
 }
@@ -345,9 +355,9 @@ uint32_t logismos_launch_rms_norm_f32(const void* x, const void* w, void* y, int
   int bs = 32;
   while (bs * 4 * 2 < n && bs < 256) bs <<= 1;  // aim for ~2 float4 per thread
   if (out_f32)
-    rms_norm_f32_kernel<true><<<rows, bs, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)w, y, n, eps);
+    lg::launch(rms_norm_f32_kernel<true>, dim3(rows), dim3(bs), 0, (cudaStream_t)stream, (const float*)x, (const float*)w, y, n, eps);
   else
-    rms_norm_f32_kernel<false><<<rows, bs, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)w, y, n, eps);
+    lg::launch(rms_norm_f32_kernel<false>, dim3(rows), dim3(bs), 0, (cudaStream_t)stream, (const float*)x, (const float*)w, y, n, eps);
   return lg::launch_status();
 }
 
@@ -364,13 +374,13 @@ uint32_t logismos_launch_rope_halves_bf16(void* qk, const void* cos_f32, const v
   const int bs = 256;
   if (head_dim % 16 == 0 && row_stride % 8 == 0 && (((uintptr_t)qk | (uintptr_t)cos_f32 | (uintptr_t)sin_f32) % 16) == 0) {
     const int64_t total8 = (int64_t)n_tokens * n_rot_heads * (head_dim / 16);
-    rope_halves_vec8_kernel<<<(unsigned)((total8 + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+    lg::launch(rope_halves_vec8_kernel, dim3((unsigned)((total8 + bs - 1) / bs)), dim3(bs), 0, (cudaStream_t)stream, 
         (__nv_bfloat16*)qk, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions,
         n_tokens, n_rot_heads, head_dim, row_stride, max_pos, (int*)status);
     return lg::launch_status();
   }
   const int64_t total = (int64_t)n_tokens * n_rot_heads * (head_dim / 4);
-  rope_halves_kernel<<<(unsigned)((total + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+  lg::launch(rope_halves_kernel, dim3((unsigned)((total + bs - 1) / bs)), dim3(bs), 0, (cudaStream_t)stream, 
       (__nv_bfloat16*)qk, (const float*)cos_f32, (const float*)sin_f32, (const int*)positions,
       n_tokens, n_rot_heads, head_dim, row_stride, max_pos, (int*)status);
   return lg::launch_status();
@@ -383,7 +393,7 @@ uint32_t logismos_launch_swiglu_bf16(const void* gu, void* out, int32_t rows, in
   if (rows == 0) return 0;
   const int64_t total = (int64_t)rows * (inter / 8);
   const int bs = 256;
-  swiglu_kernel<<<(unsigned)((total + bs - 1) / bs), bs, 0, (cudaStream_t)stream>>>(
+  lg::launch(swiglu_kernel, dim3((unsigned)((total + bs - 1) / bs)), dim3(bs), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, inter);
   return lg::launch_status();
 }
@@ -396,15 +406,15 @@ uint32_t logismos_launch_pool_head_f32(const void* hidden_f32, const void* cu, c
     return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  pool_mean_kernel<<<dim3(n_seqs, (hidden + 127) / 128), 128, 0, s>>>((const float*)hidden_f32, (const int*)cu,
+  lg::launch(pool_mean_kernel, dim3(n_seqs, (hidden + 127) / 128), dim3(128), 0, s, (const float*)hidden_f32, (const int*)cu,
                                                                       (float*)scratch_f32, hidden);
   uint32_t rc = lg::launch_status();
   if (rc) return rc;
-  head_rows_kernel<<<dim3(n_seqs, (dim + 63) / 64), 256, (size_t)hidden * 4, s>>>(
+  lg::launch(head_rows_kernel, dim3(n_seqs, (dim + 63) / 64), dim3(256), (size_t)hidden * 4, s, 
       (const float*)scratch_f32, (const __nv_bfloat16*)head_w, (const float*)head_b, (float*)out, hidden, dim);
   rc = lg::launch_status();
   if (rc) return rc;
-  l2_rows_kernel<<<n_seqs, 256, 0, s>>>((float*)out, dim);
+  lg::launch(l2_rows_kernel, dim3(n_seqs), dim3(256), 0, s, (float*)out, dim);
   return lg::launch_status();
 }
 
@@ -414,9 +424,9 @@ uint32_t logismos_launch_greedy_argmax(const void* logits, int32_t logits_f32, v
   if (rows < 0 || n <= 0) return lg::kInvalidValue;
   if (rows == 0) return 0;
   if (logits_f32)
-    greedy_argmax_kernel<float><<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, (uint32_t*)out, n);
+    lg::launch(greedy_argmax_kernel<float>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const float*)logits, (uint32_t*)out, n);
   else
-    greedy_argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, (uint32_t*)out, n);
+    lg::launch(greedy_argmax_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, (const __nv_bfloat16*)logits, (uint32_t*)out, n);
   return lg::launch_status();
 }
 
@@ -427,6 +437,7 @@ namespace {
 __global__ void gather_rows_f32_kernel(const float* __restrict__ src, const int* __restrict__ idx,
                                        float* __restrict__ dst, int n_rows, int width, int n_src_rows,
                                        int* __restrict__ status) {
+  lg::pdl_prologue();
   const int r = blockIdx.x;
   const int s = idx[r];
   if (s < 0 || s >= n_src_rows) {
@@ -446,7 +457,7 @@ extern "C" uint32_t logismos_launch_gather_rows_f32(const void* src_f32, const v
   lg::LaunchScope launch_scope_;
   if (n_rows < 0 || width <= 0 || (width % 4) || n_src_rows < 0) return lg::kInvalidValue;
   if (n_rows == 0) return 0;
-  gather_rows_f32_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const float*)src_f32, (const int*)idx_i32,
+  lg::launch(gather_rows_f32_kernel, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream, (const float*)src_f32, (const int*)idx_i32,
                                                                   (float*)dst_f32, n_rows, width, n_src_rows,
                                                                   (int*)status_i32);
   return lg::launch_status();
@@ -456,6 +467,7 @@ extern "C" uint32_t logismos_launch_gather_rows_f32(const void* src_f32, const v
 namespace {
 __global__ void gated_mul_kernel(__nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ gate,
                                  int gate_stride, int rows, int n, int mode) {
+  lg::pdl_prologue();
   const int per_row = n >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)rows * per_row) return;
@@ -481,7 +493,7 @@ extern "C" uint32_t logismos_launch_gated_mul_bf16(void* x, int32_t x_stride, co
   if (rows < 0 || n <= 0 || (n % 8) || (x_stride % 8) || (gate_stride % 8) || x_stride < n || gate_stride < n) return lg::kInvalidValue;
   if (rows == 0) return 0;
   const int64_t total = (int64_t)rows * (n / 8);
-  gated_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(gated_mul_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
       (__nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate, gate_stride, rows, n, mode);
   return lg::launch_status();
 }
@@ -489,6 +501,7 @@ extern "C" uint32_t logismos_launch_gated_mul_bf16(void* x, int32_t x_stride, co
 // ---- x += d (fp32): joins an all-reduced partial sum into the residual stream ------------------
 namespace {
 __global__ void add_f32_kernel(float* __restrict__ x, const float* __restrict__ d, int64_t n4) {
+  lg::pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
   float4 a = reinterpret_cast<float4*>(x)[i];
@@ -502,6 +515,6 @@ extern "C" uint32_t logismos_launch_add_f32(void* x, const void* d, int64_t n, v
   lg::LaunchScope launch_scope_;
   if (n < 0 || (n % 4) || ((uintptr_t)x & 15) || ((uintptr_t)d & 15)) return lg::kInvalidValue;
   if (n == 0) return 0;
-  add_f32_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)x, (const float*)d, n / 4);
+  lg::launch(add_f32_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, (float*)x, (const float*)d, n / 4);
   return lg::launch_status();
 }

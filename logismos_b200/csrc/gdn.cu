@@ -22,6 +22,7 @@ gdn_decode_step_kernel(float* __restrict__ state, const __nv_bfloat16* __restric
                        const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                        const float* __restrict__ g, const float* __restrict__ beta,
                        __nv_bfloat16* __restrict__ o, float scale) {
+  lg::pdl_prologue();
   __shared__ float ks[KD], qs[KD];
   __shared__ float4 red[4][32];
   const int64_t sh = blockIdx.x;  // seq * heads + head
@@ -116,6 +117,7 @@ gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ 
                    const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                    __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
                    const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
+  lg::pdl_prologue();
   using C = PfCfg<CPT, KS>;
   constexpr int R = C::kRows, R4 = R / 4;
   __shared__ __align__(16) PfRaw<C::kCols> raw[2];
@@ -271,6 +273,7 @@ __global__ void gdn_prepare_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16*
                                    const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                    float* __restrict__ g, float* __restrict__ beta, int64_t rows, int heads,
                                    int64_t qk_stride, int ab_stride) {
+  lg::pdl_prologue();
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -303,6 +306,7 @@ __global__ void gdn_prepare_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16*
 __global__ void gdn_finish_kernel(float* __restrict__ acc, int64_t ld_acc, const float* __restrict__ A_log,
                                   const float* __restrict__ dt_bias, __nv_bfloat16* __restrict__ proj, int64_t ld_proj,
                                   float* __restrict__ g, float* __restrict__ beta, int64_t rows, int heads) {
+  lg::pdl_prologue();
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -350,7 +354,7 @@ extern "C" uint32_t logismos_launch_gdn_finish(void* acc, int32_t ld_acc, const 
   if (((uintptr_t)acc & 15) || ((uintptr_t)proj & 7)) return lg::kInvalidValue;
   const int64_t rows = (int64_t)n_tokens * heads;
   const int wpb = 8;
-  gdn_finish_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+  lg::launch(gdn_finish_kernel, dim3((unsigned)((rows + wpb - 1) / wpb)), dim3(wpb * 32), 0, (cudaStream_t)stream, 
       (float*)acc, (int64_t)ld_acc, (const float*)A_log, (const float*)dt_bias, (__nv_bfloat16*)proj, (int64_t)ld_proj, (float*)g,
       (float*)beta, rows, heads);
   return lg::launch_status();
@@ -365,7 +369,7 @@ extern "C" uint32_t logismos_launch_gdn_decode_step(void* state, const void* q, 
   if (((uintptr_t)state & 15) || ((uintptr_t)v & 7) || ((uintptr_t)o & 7)) return lg::kInvalidValue;
   const int64_t ctas = (int64_t)n_seqs * heads;
   if (ctas > 2147483647ll) return lg::kInvalidValue;
-  gdn_decode_step_kernel<<<(unsigned)ctas, 128, 0, (cudaStream_t)stream>>>(
+  lg::launch(gdn_decode_step_kernel, dim3((unsigned)ctas), dim3(128), 0, (cudaStream_t)stream, 
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g,
       (const float*)beta, (__nv_bfloat16*)o, scale);
   return lg::launch_status();
@@ -390,7 +394,7 @@ extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, cons
   const int64_t ctas = (int64_t)n_seqs * heads * (latency ? PfCfg<1, 4>::kParts : PfCfg<2, 4>::kParts);
   if (ctas > 2147483647ll) return lg::kInvalidValue;
   auto kern = latency ? gdn_prefill_kernel<1, 4> : gdn_prefill_kernel<2, 4>;
-  kern<<<(unsigned)ctas, 128, 0, (cudaStream_t)stream>>>(
+  lg::launch(kern, dim3((unsigned)ctas), dim3(128), 0, (cudaStream_t)stream, 
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g,
       (const float*)beta, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate_z, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
       (int64_t)qkv_stride, scale);
@@ -406,7 +410,7 @@ extern "C" uint32_t logismos_launch_gdn_prepare(void* q, void* k, const void* a,
   if (((uintptr_t)q & 7) || ((uintptr_t)k & 7)) return lg::kInvalidValue;
   const int64_t rows = (int64_t)n_tokens * heads;
   const int wpb = 8;
-  gdn_prepare_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+  lg::launch(gdn_prepare_kernel, dim3((unsigned)((rows + wpb - 1) / wpb)), dim3(wpb * 32), 0, (cudaStream_t)stream, 
       (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const float*)a, (const float*)b, (const float*)A_log, (const float*)dt_bias,
       (float*)g, (float*)beta, rows, heads, (int64_t)qk_stride, ab_stride);
   return lg::launch_status();

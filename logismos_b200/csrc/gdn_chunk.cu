@@ -115,6 +115,7 @@ gdn_chunk_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q,
                  const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                  __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
                  const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
+  lg::pdl_prologue();
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u));
   const int part = blockIdx.x & 1, sh = blockIdx.x >> 1;
@@ -411,7 +412,7 @@ extern "C" uint32_t logismos_launch_gdn_chunked(void* state, const void* q, cons
   const int smem = (int)sizeof(Smem) + 128;
   cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (uint32_t)e;
-  gdn_chunk_kernel<<<(unsigned)ctas, kThreads, smem, (cudaStream_t)stream>>>(
+  lg::launch(gdn_chunk_kernel, dim3((unsigned)ctas), dim3(kThreads), smem, (cudaStream_t)stream, 
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g, (const float*)beta,
       (__nv_bfloat16*)o, (const __nv_bfloat16*)gate_z, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
       (int64_t)qkv_stride, scale);

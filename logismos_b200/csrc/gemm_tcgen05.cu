@@ -51,6 +51,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
                         void* __restrict__ out, int M, int N, int K, int ldc, int splits, int* __restrict__ status) {
   using C = Cfg<BN>;
+  lg::pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -81,6 +82,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
+  lg::pdl_wait();  // everything before this touched shared memory only
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -318,7 +320,7 @@ uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, 
   }
   const int items = tiles * splits;
   const int grid = items < sm_count() ? items : sm_count();
-  kern<<<grid, kThreads, Cfg<BN>::kSmem, stream>>>(ma, mw, mo, bias, out, m, n, k, ldc, splits, status);
+  lg::launch(kern, dim3(grid), dim3(kThreads), Cfg<BN>::kSmem, stream, ma, mw, mo, bias, out, m, n, k, ldc, splits, status);
   return lg::launch_status();
 }
 

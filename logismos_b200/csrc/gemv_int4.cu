@@ -140,6 +140,7 @@ __global__ void __launch_bounds__(256)
 gemv_int4_g32_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
                      const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                      int N, int K, int kc, int rt, int ks) {
+  lg::pdl_prologue();
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -290,6 +291,7 @@ __global__ void __launch_bounds__(STAGES == 8 ? 256 : (RT == 2 ? 384 : (NT <= 2 
 gemv_int4_g32_stream_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
                             const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                             int N, int K) {
+  lg::pdl_prologue();
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int kSlot = slot_bytes(RT);
   constexpr int kRows = 16 * RT;
@@ -486,6 +488,7 @@ __global__ void __launch_bounds__(384)
 gemv_int4_g32_wide_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
                           const __nv_bfloat16* __restrict__ x, void* __restrict__ y, int out_f32, int batch,
                           int N, int K) {
+  lg::pdl_prologue();
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int kWidePitch = Wide<KS>::kPitch, kSPitch = Wide<KS>::kSPitch, kWideSlot = Wide<KS>::kSlot;
   constexpr uint32_t kScaleOff = 32 * kWidePitch;
@@ -689,7 +692,7 @@ uint32_t launch_stream(const void* codes, const void* scales, const void* x, voi
   cudaError_t e = cudaFuncSetAttribute(gemv_int4_g32_stream_kernel<NT, STAGES, RT>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (uint32_t)e;
-  gemv_int4_g32_stream_kernel<NT, STAGES, RT><<<grid, warps * 32, smem, stream>>>(
+  lg::launch(gemv_int4_g32_stream_kernel<NT, STAGES, RT>, grid, dim3(warps * 32), smem, stream, 
       (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, y, out_f32, batch, N, K);
   return lg::launch_status();
 }
@@ -745,7 +748,7 @@ bool try_launch_stream(const void* codes, const void* scales, const void* x, voi
       auto kern = gemv_int4_g32_wide_kernel<NT, 2, 2>;
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
       if (e != cudaSuccess) { *rc = (uint32_t)e; return true; }
-      kern<<<sms, warps * 32, wsmem, stream>>>((const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x,
+      lg::launch(kern, dim3(sms), dim3(warps * 32), wsmem, stream, (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x,
                                                y, out_f32, batch, N, K);
       *rc = lg::launch_status();
       return true;
@@ -788,7 +791,7 @@ uint32_t launch_nt(const void* codes, const void* scales, const void* x, void* y
     if (e != cudaSuccess) return (uint32_t)e;
   }
   const int grid = (row_tiles + rt - 1) / rt;
-  gemv_int4_g32_kernel<NT><<<grid, threads, smem, stream>>>(
+  lg::launch(gemv_int4_g32_kernel<NT>, grid, dim3(threads), smem, stream, 
       (const uint8_t*)codes, (const __half*)scales, (const __nv_bfloat16*)x, y, out_f32,
       batch, N, K, kc, rt, ks);
   return lg::launch_status();

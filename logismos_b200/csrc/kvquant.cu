@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(256)
 turbo3_store_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, int src_stride, uint8_t* __restrict__ kpool,
                     uint8_t* __restrict__ vpool, const int64_t* __restrict__ slots, int n_tokens, int chunks, int64_t n_slots,
                     int* __restrict__ status) {
+  lg::pdl_prologue();
   __shared__ float sq[8][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t task = (int64_t)blockIdx.x * 8 + warp;  // (token, chunk, k-or-v)
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(256)
 turbo3_gather_kernel(const uint8_t* __restrict__ kpool, const uint8_t* __restrict__ vpool, const int* __restrict__ table, int table_len,
                      int len, int chunks, int n_pool_blocks, __nv_bfloat16* __restrict__ kout, __nv_bfloat16* __restrict__ vout,
                      int* __restrict__ status) {
+  lg::pdl_prologue();
   __shared__ uint32_t words[8][16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t task = (int64_t)blockIdx.x * 8 + warp;
@@ -80,7 +82,7 @@ uint32_t logismos_launch_paged_kv_store_turbo3(const void* k_bf16, const void* v
   if (n_tokens == 0) return 0;
   const int chunks = row_elems / 128;
   const int64_t tasks = (int64_t)n_tokens * chunks * 2;
-  turbo3_store_kernel<<<(unsigned)((tasks + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(turbo3_store_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)k_bf16, (const __nv_bfloat16*)v_bf16, src_row_stride, (uint8_t*)k_pool_t3, (uint8_t*)v_pool_t3,
       (const int64_t*)slot_mapping_i64, n_tokens, chunks, n_pool_slots, (int*)status_i32);
   return lg::launch_status();
@@ -96,7 +98,7 @@ uint32_t logismos_launch_paged_kv_gather_turbo3(const void* k_pool_t3, const voi
   if (len == 0) return 0;
   const int chunks = row_elems / 128;
   const int64_t tasks = (int64_t)len * chunks * 2;
-  turbo3_gather_kernel<<<(unsigned)((tasks + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(turbo3_gather_kernel, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (const uint8_t*)k_pool_t3, (const uint8_t*)v_pool_t3, (const int*)block_table_i32, table_len, len, chunks, n_pool_blocks,
       (__nv_bfloat16*)k_out_bf16, (__nv_bfloat16*)v_out_bf16, (int*)status_i32);
   return lg::launch_status();

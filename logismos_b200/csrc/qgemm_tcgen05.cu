@@ -131,6 +131,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                             const __grid_constant__ CUtensorMap map_scales, float* __restrict__ acc, int M, int N, int ldc,
                             int n_raw, int total_units, int whole_tiles, int* __restrict__ status) {
   using C = QCfg<NT>;
+  lg::pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -180,6 +181,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
+  lg::pdl_wait();  // everything before this touched shared memory only
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -384,6 +386,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 // then the 32 matching up columns); acc is left zeroed for the next accumulation.
 __global__ void qlinear_finish_kernel(float* __restrict__ acc, const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
                                       int m, int n, int ld_acc, int ldc, int swiglu) {
+  lg::pdl_prologue();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   if (!swiglu) {
@@ -454,7 +457,7 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
   const int whole = lg::deterministic() ? 1 : 0;
   const long work = whole ? (long)n_tiles : total;
   const int grid = work < slots ? (int)work : slots;
-  kern<<<grid, kQThreads, QCfg<NT>::kSmem, stream>>>(ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, status);
+  lg::launch(kern, grid, dim3(kQThreads), QCfg<NT>::kSmem, stream, ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, status);
   return lg::launch_status();
 }
 
@@ -493,7 +496,7 @@ uint32_t logismos_launch_qlinear_finish_bf16(void* acc, const void* bias, void* 
   if (((uintptr_t)acc & 15) || ((uintptr_t)out & 7)) return lg::kInvalidValue;
   if (m == 0) return 0;
   const int64_t total = (int64_t)m * ((swiglu ? n / 2 : n) / 4);
-  qlinear_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+  lg::launch(qlinear_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
       (float*)acc, (const float*)bias, (__nv_bfloat16*)out, m, n, ld_acc, ldc, swiglu);
   return lg::launch_status();
 }

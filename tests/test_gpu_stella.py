@@ -48,6 +48,32 @@ def test_golden_fixture_and_oracle_parity(tiny, fuse):
     m.close()
 
 
+def test_dependent_launch_switch_does_not_change_results(tiny):
+    """Programmatic dependent launch only moves the scheduling of a kernel ahead of its predecessor's
+    end; every kernel waits on the device before it touches memory. With the summation order fixed, the
+    embeddings and hidden states with the switch on and off are bit-identical, forward after forward."""
+    from logismos_b200._lib import lib
+    g, w, _ = tiny
+    ids, cu = g["ids"], g["cu_seqlens"]
+    m = StellaModel(TINY, w, max_batch_tokens=512, max_batch_seqs=16)
+    lib.logismos_set_deterministic(1)
+    try:
+        assert lib.logismos_get_dependent_launch() == 1   # the default
+        on = [m.encode_ids_batch(ids, cu).copy() for _ in range(5)]
+        hs_on = m.last_hidden(int(cu[-1])).copy()
+        lib.logismos_set_dependent_launch(0)
+        assert lib.logismos_get_dependent_launch() == 0
+        off = m.encode_ids_batch(ids, cu)
+        hs_off = m.last_hidden(int(cu[-1]))
+        for e in on:
+            assert np.array_equal(e, off)
+        assert np.array_equal(hs_on, hs_off) and m.device_status() == 0
+    finally:
+        lib.logismos_set_dependent_launch(1)
+        lib.logismos_set_deterministic(0)
+        m.close()
+
+
 def test_embedding_model_contract(tiny):  # crates/core/src/lib.rs:139-163, crates/embed/src/stella.rs:296-378
     g, w, _ = tiny
     rng = np.random.default_rng(0)
