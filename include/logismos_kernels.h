@@ -94,8 +94,13 @@ uint32_t logismos_launch_rms_norm_f32(const void* x_f32, const void* w_f32, void
  * bias_f32 may be NULL. ldc is the row stride of out in elements. status_i32 (may be NULL)
  * receives 2 if a bounded wait inside the kernel expired (the output is then invalid).
  * With few output tiles and a long reduction the accumulating epilogue splits k over CTAs; the
- * slices meet in the fp32 reduce-add, so the last bits of the sum can differ between runs. */
-enum { LG_EPI_BF16 = 0, LG_EPI_RESID_F32 = 1, LG_EPI_SWIGLU = 2 };
+ * slices meet in the fp32 reduce-add, so the last bits of the sum can differ between runs.
+ *
+ * LG_EPI_STATIC_W, or-ed into `epilogue`, is the caller's promise that no work still in flight on the
+ * stream writes `w_bf16` (model weights uploaded once). With dependent launch on, the kernel then
+ * requests its first weight stages before the preceding kernel has finished. Without the flag the
+ * weights are read only after everything before the launch has completed. */
+enum { LG_EPI_BF16 = 0, LG_EPI_RESID_F32 = 1, LG_EPI_SWIGLU = 2, LG_EPI_STATIC_W = 0x100 };
 uint32_t logismos_launch_linear_t_bf16(const void* a_bf16, const void* w_bf16,
                                        const void* bias_f32, void* out, int32_t m, int32_t n,
                                        int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
@@ -266,6 +271,13 @@ uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a_bf16, const void
                                                   const void* scales_f16, void* acc_f32, int32_t m,
                                                   int32_t n, int32_t k, int32_t lda, int32_t ldc,
                                                   void* status_i32, void* stream);
+/* The same launch with the caller's promise that no work still in flight on the stream writes the
+ * codes or scales (model weights uploaded once): with dependent launch on, the kernel fills its weight
+ * ring before the preceding kernel has finished. */
+uint32_t logismos_launch_qlinear_int4_g32_acc_f32_static(const void* a_bf16, const void* codes_u8,
+                                                         const void* scales_f16, void* acc_f32,
+                                                         int32_t m, int32_t n, int32_t k, int32_t lda,
+                                                         int32_t ldc, void* status_i32, void* stream);
 /* Finishes an accumulation workspace: out bf16 [m, n] = acc (+ bias), or with swiglu != 0,
  * out bf16 [m, n/2] = silu(gate) * up over columns interleaved in blocks of 32 (the LG_EPI_SWIGLU
  * row order); acc is left zeroed for the next accumulation. n % 4 == 0 (n % 64 == 0 for swiglu). */
@@ -385,7 +397,12 @@ uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, co
  * NULL), addressed like q, k, v, applies the layer's output gate in the same pass:
  * o *= silu(z) in fp32 before the bf16 rounding. mode selects the kernel shape: 1 = throughput (64
  * value columns per CTA; decode and many sequences), 2 = latency (32 columns per CTA: more
- * CTAs per head for a few long sequences), 0 = by the number of (sequence, head) pairs. */
+ * CTAs per head for a few long sequences), 0 = by the number of (sequence, head) pairs.
+ * LG_GDN_STATIC_STATE, or-ed into mode, is the caller's promise that no work still in flight on the
+ * stream writes the state pool, cu_seqlens, state_slots or fresh (they were left by an earlier model
+ * step that has completed): with dependent launch on, the kernel then reads its states while the
+ * kernels that produce q, k, v and the gates are still running. */
+enum { LG_GDN_STATIC_STATE = 0x100 };
 uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const void* k_bf16,
                                      const void* v_bf16, const void* g_f32, const void* beta_f32,
                                      void* o_bf16, const void* gate_z_bf16, const void* cu_seqlens_i32,

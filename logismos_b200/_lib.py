@@ -82,6 +82,7 @@ def _declare(l):
         "logismos_skinny_int4_route": [i32, i32, i32],
         "logismos_launch_dequant_int4_g32_bf16": [vp, vp, vp, i32, i32, vp],
         "logismos_launch_qlinear_int4_g32_acc_f32": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
+        "logismos_launch_qlinear_int4_g32_acc_f32_static": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
         "logismos_launch_qlinear_finish_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "logismos_launch_paged_attention_decode_bf16": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32,
                                                         i32, i32, i32, i32, i32, vp],

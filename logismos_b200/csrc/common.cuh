@@ -61,6 +61,20 @@ inline void launch(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaS
   (void)cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
 }
 
+// The same launch without the attribute: an ordinary stream-ordered launch, which starts only after
+// everything before it on the stream has completed. The model steps begin with one (the embedding
+// lookup), so a kernel of a step may read, ahead of its own dependency wait, anything that earlier
+// steps wrote (recurrent states, cached keys and values) besides the static weights.
+template <typename... P, typename... A>
+inline void launch_ordered(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 // Shape-guard failures are reported as cudaErrorInvalidValue (1) without launching.
 constexpr uint32_t kInvalidValue = 1u;
 

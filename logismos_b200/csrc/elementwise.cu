@@ -337,7 +337,8 @@ uint32_t logismos_launch_embed_lookup_bf16(const void* table, const void* ids, v
   if (n_ids < 0 || hidden <= 0 || vocab <= 0 || (hidden % 8)) return lg::kInvalidValue;
   if (n_ids == 0) return 0;
   const int wpb = 8;
-  lg::launch(embed_lookup_kernel, dim3((n_ids + wpb - 1) / wpb), dim3(wpb * 32), 0, (cudaStream_t)stream, 
+  // an ordered launch: the first kernel of every model step is the barrier between steps
+  lg::launch_ordered(embed_lookup_kernel, dim3((n_ids + wpb - 1) / wpb), dim3(wpb * 32), 0, (cudaStream_t)stream,
       (const __nv_bfloat16*)table, (const uint32_t*)ids, (float*)out, n_ids, hidden, vocab);
   return lg::launch_status();
 }

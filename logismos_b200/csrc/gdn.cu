@@ -116,8 +116,13 @@ __global__ void __launch_bounds__(128)
 gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                    __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
-                   const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale) {
-  lg::pdl_prologue();
+                   const int* __restrict__ slots, const uint8_t* __restrict__ fresh, int heads, int64_t qkv_stride, float scale,
+                   int state_static) {
+  // state_static: no kernel still in flight writes the states or the index arrays (they were left by an
+  // earlier model step), so the 64 KB of state are read ahead of the dependency wait, while the
+  // kernels that produce this step's q, k, v and gates are still running
+  lg::pdl_trigger();
+  if (!state_static) lg::pdl_wait();
   using C = PfCfg<CPT, KS>;
   constexpr int R = C::kRows, R4 = R / 4;
   __shared__ __align__(16) PfRaw<C::kCols> raw[2];
@@ -129,7 +134,10 @@ gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ 
   const int lcol = CPT * (warp * (32 / KS) + lane / KS);           // first of this thread's columns inside the CTA's block
   const int col = part * C::kCols + lcol;
   const int t0 = cu[seq], t1 = cu[seq + 1];
-  if (t1 <= t0) return;
+  if (t1 <= t0) {
+    if (state_static) lg::pdl_wait();  // every block passes the wait before it retires
+    return;
+  }
   const int64_t slot = slots ? slots[seq] : seq;
   float* hp = state + (slot * heads + head) * (int64_t)(KD * VD) + (int64_t)(kq * R) * VD + col;
   const bool zero_start = fresh && fresh[seq];  // a sequence that starts here begins from the zero state
@@ -145,6 +153,7 @@ gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ 
       for (int c = 0; c < CPT; ++c) h[i][c] = zero_start ? 0.f : hp[i * VD + c];
     }
   }
+  if (state_static) lg::pdl_wait();
 
   // thread tid fetches 16-byte piece (tid % 16) of token (tid / 16) of k and of q; the first threads the
   // 16-byte pieces of the v (and z) slices; threads 0..7 the two gates of token tid
@@ -380,6 +389,8 @@ extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, cons
                                                 const void* state_slots, const void* fresh, int32_t n_seqs,
                                                 int32_t heads, int32_t qkv_stride, float scale, int32_t mode, void* stream) {
   lg::LaunchScope launch_scope_;
+  const int state_static = (mode & LG_GDN_STATIC_STATE) ? 1 : 0;
+  mode &= ~LG_GDN_STATIC_STATE;
   if (n_seqs < 0 || heads <= 0 || qkv_stride < heads * KD || (qkv_stride % 8) || mode < 0 || mode > 2) return lg::kInvalidValue;
   if (n_seqs == 0) return 0;
   // rows are fetched in 16-byte pieces
@@ -397,7 +408,7 @@ extern "C" uint32_t logismos_launch_gdn_prefill(void* state, const void* q, cons
   lg::launch(kern, dim3((unsigned)ctas), dim3(128), 0, (cudaStream_t)stream, 
       (float*)state, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const float*)g,
       (const float*)beta, (__nv_bfloat16*)o, (const __nv_bfloat16*)gate_z, (const int*)cu_seqlens, (const int*)state_slots, (const uint8_t*)fresh, heads,
-      (int64_t)qkv_stride, scale);
+      (int64_t)qkv_stride, scale, state_static);
   return lg::launch_status();
 }
 

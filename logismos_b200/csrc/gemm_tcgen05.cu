@@ -49,7 +49,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
-                        void* __restrict__ out, int M, int N, int K, int ldc, int splits, int* __restrict__ status) {
+                        void* __restrict__ out, int M, int N, int K, int ldc, int splits, int w_static,
+                        int* __restrict__ status) {
   using C = Cfg<BN>;
   lg::pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
@@ -82,7 +83,20 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  lg::pdl_wait();  // everything before this touched shared memory only
+  // w_static: nothing still in flight writes the weights, so the weight halves of the first stages of
+  // this CTA's first tile are requested before the dependency wait (they land while the preceding
+  // kernel drains); each stage's barrier already expects the bytes of both halves
+  int pre_w = 0;
+  if (w_static && threadIdx.x == 0 && (int)blockIdx.x < total_tiles) {
+    const int ot = (int)blockIdx.x % out_tiles, sp = (int)blockIdx.x / out_tiles;
+    const int n_blk = ot / m_tiles;
+    const int kb0 = sp * kb_per, kb1 = min(all_kb, kb0 + kb_per);
+    for (int kb = kb0; kb < kb1 && pre_w < C::kStages; ++kb, ++pre_w) {
+      mbar_expect_tx(full_bar(pre_w), (uint32_t)C::kStage);
+      tma_load_2d(smem_base + pre_w * C::kStage + C::kStageA, &map_w, full_bar(pre_w), kb * BK, n_blk * BN);
+    }
+  }
+  lg::pdl_wait();  // everything before this touched shared memory or read the static weights only
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -104,10 +118,12 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int kb0 = sp * kb_per, kb1 = min(all_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), (uint32_t)C::kStage);
+          const bool have_w = pre_w > 0;  // requested before the dependency wait (first stages of the first tile)
+          if (!have_w) mbar_expect_tx(full_bar(stage), (uint32_t)C::kStage);
           const uint32_t sa = smem_base + stage * C::kStage;
           tma_load_2d(sa, &map_a, full_bar(stage), kb * BK, m_blk * BM);
-          tma_load_2d(sa + C::kStageA, &map_w, full_bar(stage), kb * BK, n_blk * BN);
+          if (!have_w) tma_load_2d(sa + C::kStageA, &map_w, full_bar(stage), kb * BK, n_blk * BN);
+          else --pre_w;
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -293,7 +309,7 @@ __global__ void linear_t_naive_kernel(const __nv_bfloat16* __restrict__ a, const
 
 template <int BN, int EPI>
 uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, int m, int n, int k, int lda,
-                    int ldc, int* status, cudaStream_t stream) {
+                    int ldc, int w_static, int* status, cudaStream_t stream) {
   CUtensorMap ma, mw, mo;
   if (!make_map(&ma, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM)) return lg::kInvalidValue;
   if (!make_map(&mw, w, (uint64_t)n, (uint64_t)k, (uint64_t)k, BN)) return lg::kInvalidValue;
@@ -320,13 +336,13 @@ uint32_t launch_cfg(const void* a, const void* w, const float* bias, void* out, 
   }
   const int items = tiles * splits;
   const int grid = items < sm_count() ? items : sm_count();
-  lg::launch(kern, dim3(grid), dim3(kThreads), Cfg<BN>::kSmem, stream, ma, mw, mo, bias, out, m, n, k, ldc, splits, status);
+  lg::launch(kern, dim3(grid), dim3(kThreads), Cfg<BN>::kSmem, stream, ma, mw, mo, bias, out, m, n, k, ldc, splits, w_static, status);
   return lg::launch_status();
 }
 
 template <int EPI>
 uint32_t launch_epi(const void* a, const void* w, const float* bias, void* out, int m, int n, int k, int lda,
-                    int ldc, int* status, cudaStream_t stream) {
+                    int ldc, int w_static, int* status, cudaStream_t stream) {
   // tile width by wave quantisation: time ~ waves(BN) * BN; ties go to the wider tile
   const int sms = sm_count();
   const int mt = (m + BM - 1) / BM;
@@ -340,9 +356,9 @@ uint32_t launch_epi(const void* a, const void* w, const float* bias, void* out, 
     const long cost = waves * bn;
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
   }
-  if (best_bn == 256) return launch_cfg<256, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
-  if (best_bn == 192) return launch_cfg<192, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
-  return launch_cfg<128, EPI>(a, w, bias, out, m, n, k, lda, ldc, status, stream);
+  if (best_bn == 256) return launch_cfg<256, EPI>(a, w, bias, out, m, n, k, lda, ldc, w_static, status, stream);
+  if (best_bn == 192) return launch_cfg<192, EPI>(a, w, bias, out, m, n, k, lda, ldc, w_static, status, stream);
+  return launch_cfg<128, EPI>(a, w, bias, out, m, n, k, lda, ldc, w_static, status, stream);
 }
 
 }  // namespace
@@ -353,6 +369,8 @@ uint32_t logismos_launch_linear_t_bf16(const void* a, const void* w, const void*
                                        int32_t n, int32_t k, int32_t lda, int32_t ldc, int32_t epilogue,
                                        void* status_i32, void* stream) {
   lg::LaunchScope launch_scope_;
+  const int w_static = (epilogue & LG_EPI_STATIC_W) ? 1 : 0;
+  epilogue &= ~LG_EPI_STATIC_W;
   if (m <= 0 || n <= 0 || k <= 0 || (k % BK) || (n % 16) || (lda % 8) || lda < k) return lg::kInvalidValue;
   if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return lg::kInvalidValue;
   if (epilogue == LG_EPI_SWIGLU && (n % 64)) return lg::kInvalidValue;
@@ -362,9 +380,9 @@ uint32_t logismos_launch_linear_t_bf16(const void* a, const void* w, const void*
   const float* b = (const float*)bias;
   int* st = (int*)status_i32;
   switch (epilogue) {
-    case LG_EPI_BF16: return launch_epi<LG_EPI_BF16>(a, w, b, out, m, n, k, lda, ldc, st, s);
-    case LG_EPI_RESID_F32: return launch_epi<LG_EPI_RESID_F32>(a, w, b, out, m, n, k, lda, ldc, st, s);
-    case LG_EPI_SWIGLU: return launch_epi<LG_EPI_SWIGLU>(a, w, b, out, m, n, k, lda, ldc, st, s);
+    case LG_EPI_BF16: return launch_epi<LG_EPI_BF16>(a, w, b, out, m, n, k, lda, ldc, w_static, st, s);
+    case LG_EPI_RESID_F32: return launch_epi<LG_EPI_RESID_F32>(a, w, b, out, m, n, k, lda, ldc, w_static, st, s);
+    case LG_EPI_SWIGLU: return launch_epi<LG_EPI_SWIGLU>(a, w, b, out, m, n, k, lda, ldc, w_static, st, s);
     default: return lg::kInvalidValue;
   }
 }

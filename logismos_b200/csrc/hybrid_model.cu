@@ -176,7 +176,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
         // one fused-dequant accumulation of all six blocks, finished by the kernel that also normalises
         // q, k and computes the gates from the fp32 sums
         const int ld = GN + 2 * GH;
-        LG_TRY(logismos_launch_qlinear_int4_g32_acc_f32(m->h.p, L.w_in.codes.p, L.w_in.scales.p, m->accws.p, T, ld, H, H, ld, st, s),
+        LG_TRY(logismos_launch_qlinear_int4_g32_acc_f32_static(m->h.p, L.w_in.codes.p, L.w_in.scales.p, m->accws.p, T, ld, H, H, ld, st, s),
                "int4 linear");
         LG_TRY(logismos_launch_gdn_finish(m->accws.p, ld, L.A_log.p, L.dt_bias.p, m->proj.p, GN, m->g.p, m->beta.p, T, GH, s), "gdn_finish");
         m->launches += 2;
@@ -200,7 +200,8 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       const float gscale = 1.0f / std::sqrt((float)kGdnDim);
       if (m->n_dec > 0) {
         LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
-                                           m->cu_all.p, m->state_slots.p, m->fresh.p, m->n_dec, GH, GN, gscale, 1, s),
+                                           m->cu_all.p, m->state_slots.p, m->fresh.p, m->n_dec, GH, GN, gscale,
+                                           1 | LG_GDN_STATIC_STATE /* states and index arrays date from before this step's first kernel */, s),
                "gdn recurrence (decode rows)");
         m->launches += 1;
       }

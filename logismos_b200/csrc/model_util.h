@@ -94,10 +94,10 @@ inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void
   if (fused_ok) {
     if (epi == LG_EPI_RESID_F32 && !bias) {
       *launches += 1;
-      return logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);
+      return logismos_launch_qlinear_int4_g32_acc_f32_static(a, w.codes.p, w.scales.p, out, T, w.n, w.k, lda, ldc, status, s);
     }
     if (epi != LG_EPI_RESID_F32) {
-      rc = logismos_launch_qlinear_int4_g32_acc_f32(a, w.codes.p, w.scales.p, accws, T, w.n, w.k, lda, w.n, status, s);
+      rc = logismos_launch_qlinear_int4_g32_acc_f32_static(a, w.codes.p, w.scales.p, accws, T, w.n, w.k, lda, w.n, status, s);
       if (rc) return rc;
       *launches += 2;
       return logismos_launch_qlinear_finish_bf16(accws, bias, out, T, w.n, w.n, ldc, epi == LG_EPI_SWIGLU ? 1 : 0, s);
@@ -105,7 +105,7 @@ inline uint32_t qlinear_any(const void* a, const QMat& w, const void* bias, void
   }
   if (w.dense.p) {
     *launches += 1;
-    return logismos_launch_linear_t_bf16(a, w.dense.p, bias, out, T, w.n, w.k, lda, ldc, epi, status, s);
+    return logismos_launch_linear_t_bf16(a, w.dense.p, bias, out, T, w.n, w.k, lda, ldc, epi | LG_EPI_STATIC_W, status, s);  // the copy is made once at load
   }
   rc = logismos_launch_dequant_int4_g32_bf16(w.codes.p, w.scales.p, wscratch, w.n, w.k, s);
   if (rc) return rc;
@@ -129,7 +129,7 @@ inline uint32_t lm_head_and_greedy(const QMat& lm_head, const void* hidden_bf16,
       const int nb = rows - b0 < kFusedDequantMaxRows ? rows - b0 : kFusedDequantMaxRows;
       float* dst = (float*)logits + (size_t)b0 * vocab;
       if (cudaMemsetAsync(dst, 0, (size_t)nb * vocab * 4, s) != cudaSuccess) return (uint32_t)cudaGetLastError();
-      rc = logismos_launch_qlinear_int4_g32_acc_f32((const uint16_t*)hidden_bf16 + (size_t)b0 * hidden, lm_head.codes.p,
+      rc = logismos_launch_qlinear_int4_g32_acc_f32_static((const uint16_t*)hidden_bf16 + (size_t)b0 * hidden, lm_head.codes.p,
                                                     lm_head.scales.p, dst, nb, vocab, hidden, hidden, vocab, status, s);
       if (rc) return rc;
       *launches += 1;

@@ -32,6 +32,7 @@
 // flight land, frees its TMEM and returns. No cluster launch and no multicast.
 #include <cuda.h>
 
+#include <cstdlib>
 #include "common.cuh"
 #include "logismos_kernels.h"
 #include "tcgen05.cuh"
@@ -129,7 +130,7 @@ template <int NT>
 __global__ void __launch_bounds__(kQThreads, 1)
 qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_codes,
                             const __grid_constant__ CUtensorMap map_scales, float* __restrict__ acc, int M, int N, int ldc,
-                            int n_raw, int total_units, int whole_tiles, int* __restrict__ status) {
+                            int n_raw, int total_units, int whole_tiles, int w_static, int* __restrict__ status) {
   using C = QCfg<NT>;
   lg::pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
@@ -181,7 +182,24 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  lg::pdl_wait();  // everything before this touched shared memory only
+  // the raw-weight producer's position in its span; thread 0 carries it across the dependency wait
+  int p_rs = 0, p_u = u0, p_tile = u0 / n_raw, p_rb = u0 % n_raw;
+  uint32_t p_phase = 0;
+  auto issue_raw = [&]() {  // requests unit p_u's codes and scales into ring slot p_rs and advances
+    mbar_expect_tx(raw_full(p_rs), (uint32_t)kRawStage);
+    const uint32_t dst = raw_base + p_rs * kRawStage;
+    const int kk = p_rb * kRawK;
+    tma_load_2d(dst, &map_codes, raw_full(p_rs), kk / 2, p_tile * kWRows);
+    tma_load_2d(dst + kRawCodes, &map_scales, raw_full(p_rs), kk / 32, p_tile * kWRows);
+    if (++p_rs == kRawStages) { p_rs = 0; p_phase ^= 1u; }
+    if (++p_rb == n_raw) { p_rb = 0; ++p_tile; }
+    ++p_u;
+  };
+  // w_static: nothing still in flight writes the weights, so the ring is filled before the dependency
+  // wait (the first slots are free by construction) and lands while the preceding kernel drains
+  if (w_static && threadIdx.x == 0)
+    while (p_u < u1 && p_u - u0 < kRawStages) issue_raw();
+  lg::pdl_wait();  // everything before this touched shared memory or read the static weights only
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)C::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -194,19 +212,10 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   if (warp == 0) {
     // ---------------- raw int4 producer ----------------
     if (lane == 0) {
-      int rs = 0;
-      uint32_t rphase = 0;
-      int tile = u0 / n_raw, rb = u0 % n_raw;  // carried along: no division in the loop
-      for (int u = u0; u < u1; ++u) {
-        const int kk = rb * kRawK;
-        if (!mbar_wait_sleep(raw_empty(rs), rphase ^ 1u, abort_flag, 100)) break;
-        mbar_expect_tx(raw_full(rs), (uint32_t)kRawStage);
-        const uint32_t dst = raw_base + rs * kRawStage;
-        tma_load_2d(dst, &map_codes, raw_full(rs), kk / 2, tile * kWRows);
-        tma_load_2d(dst + kRawCodes, &map_scales, raw_full(rs), kk / 32, tile * kWRows);
-        QTRACE(u - u0, 0);
-        if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
-        if (++rb == n_raw) { rb = 0; ++tile; }
+      while (p_u < u1) {
+        if (!mbar_wait_sleep(raw_empty(p_rs), p_phase ^ 1u, abort_flag, 100)) break;
+        QTRACE(p_u - u0, 0);
+        issue_raw();
       }
     }
   } else if (warp == 1) {
@@ -437,7 +446,7 @@ bool make_map_generic(CUtensorMap* map, CUtensorMapDataType dt, uint64_t esz, co
 
 template <int NT>
 uint32_t launch_q(const void* a, const void* codes, const void* scales, float* acc, int m, int n, int k, int lda, int ldc,
-                  int* status, cudaStream_t stream) {
+                  int w_static, int* status, cudaStream_t stream) {
   CUtensorMap ma, mc, ms;
   if (!make_map(&ma, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, NT)) return lg::kInvalidValue;
   if (!make_map_generic(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2, 128, kWRows,
@@ -454,10 +463,11 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
   const long total = (long)n_tiles * n_raw;
   if (total > 2147483647l) return lg::kInvalidValue;
   const int slots = sm_count();
-  const int whole = lg::deterministic() ? 1 : 0;
+  static const int dev_whole_min = [] { const char* e = std::getenv("LOGISMOS_QWHOLE_MIN_TILES"); return e ? atoi(e) : 0; }();
+  const int whole = (lg::deterministic() || (dev_whole_min > 0 && n_tiles >= dev_whole_min && n_tiles <= 4 * slots)) ? 1 : 0;
   const long work = whole ? (long)n_tiles : total;
   const int grid = work < slots ? (int)work : slots;
-  lg::launch(kern, grid, dim3(kQThreads), QCfg<NT>::kSmem, stream, ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, status);
+  lg::launch(kern, grid, dim3(kQThreads), QCfg<NT>::kSmem, stream, ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, w_static, status);
   return lg::launch_status();
 }
 
@@ -465,9 +475,8 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
 
 extern "C" {
 
-uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a, const void* codes, const void* scales, void* acc, int32_t m,
-                                                  int32_t n, int32_t k, int32_t lda, int32_t ldc, void* status_i32,
-                                                  void* stream) {
+static uint32_t qlinear_acc(const void* a, const void* codes, const void* scales, void* acc, int32_t m, int32_t n, int32_t k,
+                            int32_t lda, int32_t ldc, int w_static, void* status_i32, void* stream) {
   lg::LaunchScope launch_scope_;
   if (m <= 0 || m > 256 || n <= 0 || k <= 0 || (k % kRawK) || (lda % 8) || lda < k || ldc < n) return lg::kInvalidValue;
   if (((uintptr_t)a & 15) || ((uintptr_t)codes & 15) || ((uintptr_t)scales & 15) || ((uintptr_t)acc & 3)) return lg::kInvalidValue;
@@ -480,12 +489,24 @@ uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a, const void* cod
     const int mt = m - t0 < 128 ? m - t0 : 128;
     const void* at = (const uint16_t*)a + (size_t)t0 * lda;
     float* o = (float*)acc + (size_t)t0 * ldc;
-    const uint32_t rc = mt <= 32   ? launch_q<32>(at, codes, scales, o, mt, n, k, lda, ldc, st, s)
-                        : mt <= 64 ? launch_q<64>(at, codes, scales, o, mt, n, k, lda, ldc, st, s)
-                                   : launch_q<128>(at, codes, scales, o, mt, n, k, lda, ldc, st, s);
+    const uint32_t rc = mt <= 32   ? launch_q<32>(at, codes, scales, o, mt, n, k, lda, ldc, w_static, st, s)
+                        : mt <= 64 ? launch_q<64>(at, codes, scales, o, mt, n, k, lda, ldc, w_static, st, s)
+                                   : launch_q<128>(at, codes, scales, o, mt, n, k, lda, ldc, w_static, st, s);
     if (rc) return rc;
   }
   return 0;
+}
+
+uint32_t logismos_launch_qlinear_int4_g32_acc_f32(const void* a, const void* codes, const void* scales, void* acc, int32_t m,
+                                                  int32_t n, int32_t k, int32_t lda, int32_t ldc, void* status_i32,
+                                                  void* stream) {
+  return qlinear_acc(a, codes, scales, acc, m, n, k, lda, ldc, 0, status_i32, stream);
+}
+
+uint32_t logismos_launch_qlinear_int4_g32_acc_f32_static(const void* a, const void* codes, const void* scales, void* acc,
+                                                         int32_t m, int32_t n, int32_t k, int32_t lda, int32_t ldc,
+                                                         void* status_i32, void* stream) {
+  return qlinear_acc(a, codes, scales, acc, m, n, k, lda, ldc, 1, status_i32, stream);
 }
 
 uint32_t logismos_launch_qlinear_finish_bf16(void* acc, const void* bias, void* out, int32_t m, int32_t n, int32_t ld_acc,

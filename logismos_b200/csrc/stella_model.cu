@@ -115,7 +115,7 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = m->layers[l];
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm1.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
-    LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wqkv.p, L.bqkv.p, m->qkv.p, T, QKV, H, H, QKV, LG_EPI_BF16, st, s), "qkv_proj");
+    LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wqkv.p, L.bqkv.p, m->qkv.p, T, QKV, H, H, QKV, LG_EPI_BF16 | LG_EPI_STATIC_W, st, s), "qkv_proj");
     if (D == 128) {  // tcgen05 kernel; its first launch rotates q and k and transposes V into attn_ws
       LG_TRY(logismos_launch_rope_varlen_attention_tc_bf16(m->qkv.p, m->cos.p, m->sin.p, pos, c.n_heads + c.n_kv_heads, c.max_pos, cu,
                                                            m->attn.p, m->attn_ws.p, T, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads, D,
@@ -126,15 +126,15 @@ uint32_t forward_device(Stella* m, const void* ids, const void* cu, const void* 
       LG_TRY(logismos_launch_varlen_attention_bf16(m->qkv.p, cu, m->attn.p, n_seqs, max_seqlen, c.n_heads, c.n_kv_heads,
                                                    D, QKV, H, H + c.n_kv_heads * D, causal, s), "attention");
     }
-    LG_TRY(logismos_launch_linear_t_bf16(m->attn.p, L.wo.p, nullptr, m->x.p, T, H, H, H, H, LG_EPI_RESID_F32, st, s), "o_proj");
+    LG_TRY(logismos_launch_linear_t_bf16(m->attn.p, L.wo.p, nullptr, m->x.p, T, H, H, H, H, LG_EPI_RESID_F32 | LG_EPI_STATIC_W, st, s), "o_proj");
     LG_TRY(logismos_launch_rms_norm_f32(m->x.p, L.norm2.p, m->h.p, T, H, c.rms_eps, 0, s), "rms_norm");
     if (c.fuse_swiglu) {
-      LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wgu.p, nullptr, m->act.p, T, 2 * I, H, H, I, LG_EPI_SWIGLU, st, s), "gate_up_swiglu");
+      LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wgu.p, nullptr, m->act.p, T, 2 * I, H, H, I, LG_EPI_SWIGLU | LG_EPI_STATIC_W, st, s), "gate_up_swiglu");
     } else {
-      LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wgu.p, nullptr, m->gu.p, T, 2 * I, H, H, 2 * I, LG_EPI_BF16, st, s), "gate_up");
+      LG_TRY(logismos_launch_linear_t_bf16(m->h.p, L.wgu.p, nullptr, m->gu.p, T, 2 * I, H, H, 2 * I, LG_EPI_BF16 | LG_EPI_STATIC_W, st, s), "gate_up");
       LG_TRY(logismos_launch_swiglu_bf16(m->gu.p, m->act.p, T, I, s), "swiglu");
     }
-    LG_TRY(logismos_launch_linear_t_bf16(m->act.p, L.wdown.p, nullptr, m->x.p, T, H, I, I, H, LG_EPI_RESID_F32, st, s), "down_proj");
+    LG_TRY(logismos_launch_linear_t_bf16(m->act.p, L.wdown.p, nullptr, m->x.p, T, H, I, I, H, LG_EPI_RESID_F32 | LG_EPI_STATIC_W, st, s), "down_proj");
   }
   LG_TRY(logismos_launch_rms_norm_f32(m->x.p, m->final_norm.p, m->hidden_out.p, T, H, c.rms_eps, 1, s), "final_norm");
   LG_TRY(logismos_launch_pool_head_f32(m->hidden_out.p, cu, m->head_w[dim_idx].p, m->head_b[dim_idx].p, out, m->pooled.p,
