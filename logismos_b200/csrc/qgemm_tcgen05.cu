@@ -32,7 +32,6 @@
 // flight land, frees its TMEM and returns. No cluster launch and no multicast.
 #include <cuda.h>
 
-#include <cstdlib>
 #include "common.cuh"
 #include "logismos_kernels.h"
 #include "tcgen05.cuh"
@@ -463,8 +462,11 @@ uint32_t launch_q(const void* a, const void* codes, const void* scales, float* a
   const long total = (long)n_tiles * n_raw;
   if (total > 2147483647l) return lg::kInvalidValue;
   const int slots = sm_count();
-  static const int dev_whole_min = [] { const char* e = std::getenv("LOGISMOS_QWHOLE_MIN_TILES"); return e ? atoi(e) : 0; }();
-  const int whole = (lg::deterministic() || (dev_whole_min > 0 && n_tiles >= dev_whole_min && n_tiles <= 4 * slots)) ? 1 : 0;
+  // spans that end at tile boundaries leave no fp32 reductions in flight for the next kernel to wait on.
+  // Above 32 rows that is worth more than the even split when the tiles still spread over the SMs
+  // (a 64-row decode step of the hybrid model: 4.77 against 4.89 ms); at up to 32 rows and for matrices
+  // of a few tiles or of many waves the even split wins
+  const int whole = (lg::deterministic() || (m > 32 && n_tiles >= 32 && n_tiles <= 4 * slots)) ? 1 : 0;
   const long work = whole ? (long)n_tiles : total;
   const int grid = work < slots ? (int)work : slots;
   lg::launch(kern, grid, dim3(kQThreads), QCfg<NT>::kSmem, stream, ma, mc, ms, acc, m, n, ldc, n_raw, (int)total, whole, w_static, status);

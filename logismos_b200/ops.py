@@ -112,6 +112,8 @@ def rope_apply(x, cos_sin, sync=True):
 # ---- encoder path ----------------------------------------------------------------------------
 
 EPI_BF16, EPI_RESID_F32, EPI_SWIGLU = 0, 1, 2
+EPI_STATIC_W = 0x100       # or-ed into the epilogue: nothing in flight writes the weights
+GDN_STATIC_STATE = 0x100   # or-ed into the gdn_prefill mode: nothing in flight writes the states
 
 
 def embed_lookup(table, ids, sync=True):
@@ -132,9 +134,10 @@ def rms_norm_f32(x, w, eps, out_f32=False, sync=True):
     return y
 
 
-def linear_t(a, w, bias=None, residual=None, swiglu=False, naive=False, sync=True):
+def linear_t(a, w, bias=None, residual=None, swiglu=False, naive=False, sync=True, static_w=False):
     """C = A W^T (+bias). residual: fp32 tensor updated in place (returns it). swiglu: W holds gate/up
-    rows interleaved in blocks of 32; returns silu(gate)*up."""
+    rows interleaved in blocks of 32; returns silu(gate)*up. static_w: the caller's promise that nothing
+    still in flight writes w (the kernel may then fetch weights before the preceding kernel has finished)."""
     _req(a, "a", torch.bfloat16, 2); _req(w, "w", torch.bfloat16, 2)
     if bias is not None:
         _req(bias, "bias", torch.float32, 1)
@@ -154,7 +157,8 @@ def linear_t(a, w, bias=None, residual=None, swiglu=False, naive=False, sync=Tru
         if naive:
             check(lib.logismos_launch_linear_t_naive_bf16(_p(a), _p(w), _p(bias), _p(out), m, n, k, k, ldc, epi, _stream()), "linear_t_naive")
         else:
-            check(lib.logismos_launch_linear_t_bf16(_p(a), _p(w), _p(bias), _p(out), m, n, k, k, ldc, epi, _p(status), _stream()), "linear_t")
+            check(lib.logismos_launch_linear_t_bf16(_p(a), _p(w), _p(bias), _p(out), m, n, k, k, ldc, epi | (EPI_STATIC_W if static_w else 0),
+                                                    _p(status), _stream()), "linear_t")
         _done(sync)
         if sync and not naive and int(status.item()) != 0:
             raise InvalidOp(f"linear_t: device status {int(status.item())} (a bounded wait expired)")
@@ -327,9 +331,10 @@ def dequant_int4(codes, scales, sync=True):
     return out
 
 
-def qlinear_int4_acc_(acc, a, codes, scales, sync=True):
+def qlinear_int4_acc_(acc, a, codes, scales, sync=True, static_w=False):
     """acc f32 [m, n] += a bf16 [m, k] @ dequant(codes, scales)[n, k]^T for m <= 256 (fused dequant on
-    the tensor cores). Rows of a and acc may be strided. Returns the device status word's tensor."""
+    the tensor cores). Rows of a and acc may be strided. Returns the device status word's tensor.
+    static_w: the caller's promise that nothing still in flight writes codes or scales."""
     _req(a, "a", torch.bfloat16, 2, contiguous=False); _req(acc, "acc", torch.float32, 2, contiguous=False)
     _req(codes, "codes", torch.uint8, 2); _req(scales, "scales", torch.float16, 2)
     m, k = a.shape
@@ -340,8 +345,8 @@ def qlinear_int4_acc_(acc, a, codes, scales, sync=True):
         raise InvalidOp("qlinear_int4_acc_: needs 1 <= m <= 256 and k % 256 == 0")
     status = torch.zeros(1, dtype=torch.int32, device=a.device)
     with torch.cuda.device(a.device):
-        check(lib.logismos_launch_qlinear_int4_g32_acc_f32(_p(a), _p(codes), _p(scales), _p(acc), m, n, k, a.stride(0), acc.stride(0),
-                                                           _p(status), _stream()), "qlinear_int4_g32")
+        fn = lib.logismos_launch_qlinear_int4_g32_acc_f32_static if static_w else lib.logismos_launch_qlinear_int4_g32_acc_f32
+        check(fn(_p(a), _p(codes), _p(scales), _p(acc), m, n, k, a.stride(0), acc.stride(0), _p(status), _stream()), "qlinear_int4_g32")
         _done(sync)
     return status
 
@@ -470,9 +475,10 @@ def gdn_decode_step_(state, q, k, v, g, beta, scale, sync=True):
     return o
 
 
-def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, mode=0, sync=True):
+def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, mode=0, sync=True, static_state=False):
     """Gated delta rule over a ragged batch; q, k, v bf16 [T, heads, 128]; state updated in place.
-    gate_z bf16 [T, heads, 128] (optional) multiplies the output by silu(z) in the same pass."""
+    gate_z bf16 [T, heads, 128] (optional) multiplies the output by silu(z) in the same pass.
+    static_state: the caller's promise that nothing still in flight writes state or cu_seqlens."""
     _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
     _req(v, "v", torch.bfloat16, 3); _req(g, "g", torch.float32, 2); _req(beta, "beta", torch.float32, 2)
     _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
@@ -481,7 +487,8 @@ def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, mode=0
     o = torch.empty_like(v)
     with torch.cuda.device(state.device):
         check(lib.logismos_launch_gdn_prefill(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(gate_z) if gate_z is not None else None, _p(cu_seqlens), _p(None), _p(None),
-                                              state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale), int(mode), _stream()), "gdn_prefill")
+                                              state.shape[0], state.shape[1], q.shape[1] * q.shape[2], float(scale),
+                                              int(mode) | (GDN_STATIC_STATE if static_state else 0), _stream()), "gdn_prefill")
         _done(sync)
     return o
 

@@ -146,6 +146,32 @@ def test_both_kernel_shapes_agree_with_the_reference():
     assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-5 * np.abs(outs[0][1]).max()
 
 
+def test_static_state_promise_changes_nothing_but_the_fetch_order():
+    """With the static-state flag the recurrence reads its states ahead of the dependency wait. After a
+    synchronisation (nothing in flight writes them) and right behind the kernel that prepares q, k and
+    the gates, outputs and final states equal those without the flag bit for bit."""
+    rng = np.random.default_rng(23)
+    heads, D, n = 4, 128, 24
+    nrm = lambda x: x / np.linalg.norm(x, axis=-1, keepdims=True)
+    q_t, _ = bf16_cuda(rng.standard_normal((n, heads, D))); k_t, _ = bf16_cuda(rng.standard_normal((n, heads, D)))
+    v_t, _ = bf16_cuda(rng.standard_normal((n, heads, D)))
+    a = torch.from_numpy(rng.standard_normal((n, heads)).astype(np.float32)).to(DEV)
+    b = torch.from_numpy(rng.standard_normal((n, heads)).astype(np.float32)).to(DEV)
+    A_log = torch.from_numpy(rng.uniform(-1, 1, heads).astype(np.float32)).to(DEV)
+    dt_bias = torch.from_numpy(rng.uniform(-1, 1, heads).astype(np.float32)).to(DEV)
+    cu = torch.arange(0, n + 1, dtype=torch.int32, device=DEV)
+    state0 = torch.from_numpy((rng.standard_normal((n, heads, D, D)) * 0.05).astype(np.float32)).to(DEV)
+    outs = []
+    for static in (False, True):
+        st, qq, kk = state0.clone(), q_t.clone(), k_t.clone()
+        torch.cuda.synchronize()
+        g, beta = ops.gdn_prepare_(qq, kk, a, b, A_log, dt_bias, sync=False)          # normalises q, k in place; the producer
+        o = ops.gdn_prefill_(st, qq, kk, v_t, g, beta, cu, D ** -0.5, mode=1, static_state=static)
+        outs.append((to_np(o), to_np(st)))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert np.isfinite(outs[0][0]).all()
+
+
 def test_chunk_parallel_form_matches_the_recurrence():
     """The chunk-parallel kernel (triangular solve + tensor-core products per 64 tokens) against the
     oracle's recurrence: lengths below, at and across chunk boundaries, a non-zero incoming state,

@@ -30,6 +30,32 @@ def test_bf16_epilogue_matches_oracle_linear_t(m, n, k):
     assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-5  # only the bf16 store rounds
 
 
+@pytest.mark.parametrize("m,n,k,kind", [(64, 2048, 2048, "bf16"), (300, 1536, 1536, "resid"), (64, 12288, 2048, "swiglu"), (2, 256, 64, "bf16")])
+def test_static_weight_promise_changes_nothing_but_the_fetch_order(m, n, k, kind):
+    """With the static-weights flag the kernel requests its first weight stages ahead of the dependency
+    wait; launched behind a kernel of this library that rewrites the ACTIVATIONS (so the early start
+    really overlaps a producer), the result equals the one without the flag bit for bit."""
+    from logismos_b200._lib import lib
+    a_t, a, w_t, w, b = case(m, n, k, 5 * m + n + k, bias=False)
+    lib.logismos_set_deterministic(1)   # no split over k: a fixed summation order
+    try:
+        outs = []
+        for static in (False, True):
+            res = torch.zeros((m, n), dtype=torch.float32, device=DEV) if kind == "resid" else None
+            x = torch.zeros((m, k), dtype=torch.float32, device=DEV)
+            src = a_t.float().contiguous()
+            # the producer ahead of the GEMM: this library's rms_norm (unit gains) of rows pre-scaled to unit RMS
+            rms = src.pow(2).mean(dim=1, keepdim=True).sqrt()
+            x.copy_(src / rms)
+            ones = torch.ones(k, dtype=torch.float32, device=DEV)
+            torch.cuda.synchronize()
+            h = ops.rms_norm_f32(x, ones, 0.0, sync=False)
+            outs.append(to_np(ops.linear_t(h, w_t, residual=res, swiglu=(kind == "swiglu"), static_w=static)))
+        assert np.array_equal(outs[0], outs[1])
+    finally:
+        lib.logismos_set_deterministic(0)
+
+
 def test_matches_the_naive_anchor_on_device():
     a_t, a, w_t, w, b = case(300, 768, 1024, 5)
     bt = torch.from_numpy(b).to(DEV)

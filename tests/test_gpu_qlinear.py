@@ -38,6 +38,28 @@ def test_accumulates_linear_on_dequantised_weights(m, n, k):
     assert np.abs(to_np(acc) - 2 * ref).max() <= 2 ** -6 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 8224, 2048), (64, 8224, 2048), (3, 256, 256)])
+def test_static_weight_promise_changes_nothing_but_the_fetch_order(m, n, k):
+    """The entry point that fills its weight ring ahead of the dependency wait, launched right behind
+    another kernel of this library, gives the same sums as the plain entry point (whole-tile spans, so
+    the summation order is fixed)."""
+    from logismos_b200._lib import lib
+    codes, scales, a_t, ref = make_case(m, n, k, 3 * m + n + k)
+    lib.logismos_set_deterministic(1)
+    try:
+        outs = []
+        for static in (False, True):
+            acc = torch.zeros((m, n), dtype=torch.float32, device=DEV)
+            warm = torch.zeros((m, n), dtype=torch.float32, device=DEV)
+            ops.qlinear_int4_acc_(warm, a_t, codes, scales, sync=False)            # the kernel ahead of it
+            status = ops.qlinear_int4_acc_(acc, a_t, codes, scales, static_w=static)
+            assert int(status.item()) == 0
+            outs.append(to_np(acc))
+        assert np.array_equal(outs[0], outs[1]) and max_rel(outs[0], ref) <= TOL
+    finally:
+        lib.logismos_set_deterministic(0)
+
+
 def test_exact_for_exactly_representable_inputs():
     """Power-of-two scales and small integer activations: every product and partial sum is exact in
     bf16 / fp32, so the result must equal the integer dot product bit for bit (nibble order, sign
