@@ -121,8 +121,10 @@ def bench_gdn(n_seq, length, iters, heads=16, pk=None):
     out = {"kernel": "gated_delta_rule", "seqs": n_seq, "len": length, "heads": heads, "us_token_serial": t_serial * 1e6,
            "state_GBps_token_serial": 2.0 * n_seq * heads * D * D * 4 / t_serial / 1e9, "peak": pk["hbm"], "peak_src": pk["src"]}
     if length > 1:
-        t_chunk = timeit(lambda i: ops.gdn_chunked_(st, q, k, v, g, beta, cu, D ** -0.5, gate_z=z, sync=False), iters)
-        out.update({"us_chunk_parallel": t_chunk * 1e6, "us_per_token_chunk_parallel": t_chunk * 1e6 / length,
+        scratch = torch.empty(int(lib.logismos_gdn_chunked_scratch_bytes(T, n_seq, heads)), dtype=torch.uint8, device="cuda")
+        t_chunk = timeit(lambda i: ops.gdn_chunked_(st, q, k, v, g, beta, cu, D ** -0.5, gate_z=z, sync=False, scratch=scratch), iters)
+        t_one = timeit(lambda i: ops.gdn_chunked_(st, q, k, v, g, beta, cu, D ** -0.5, gate_z=z, sync=False, split=False), iters)
+        out.update({"us_chunk_parallel": t_chunk * 1e6, "us_chunk_parallel_one_launch": t_one * 1e6, "us_per_token_chunk_parallel": t_chunk * 1e6 / length,
                     "us_per_token_serial": t_serial * 1e6 / length, "speedup": t_serial / t_chunk})
     else:
         out["frac_hbm_token_serial"] = out["state_GBps_token_serial"] / pk["hbm"]

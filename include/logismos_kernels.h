@@ -413,12 +413,20 @@ uint32_t logismos_launch_gdn_prefill(void* state_f32, const void* q_bf16, const 
  * of a chunk are resolved together by matrix products (a triangular solve for the in-chunk
  * dependencies, tensor-core products against the carried state), so a long prompt is not bound by a
  * token-serial chain. Arguments as logismos_launch_gdn_prefill. The state stays fp32 and enters the
- * products rounded to bf16: outputs within 2e-2 of the recurrence, final state within 1e-2. */
+ * products rounded to bf16: outputs within 2e-2 of the recurrence, final state within 1e-2.
+ * scratch (128-byte aligned, logismos_gdn_chunked_scratch_bytes(n_tokens, n_seqs, heads) bytes, n_tokens
+ * = cu_seqlens[n_seqs] - cu_seqlens[0] or more) selects the two-launch form: everything of a chunk that
+ * does not involve the carried state is computed for all chunks of the batch at once (a CTA per chunk
+ * and head) and parked in scratch, then each sequence's chunks are chained with the three products that
+ * touch the state. scratch == NULL keeps the one-launch form (a CTA per sequence, head and value-column
+ * half does all of it chunk after chunk). Same results within the stated tolerance. */
+size_t logismos_gdn_chunked_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t heads);
 uint32_t logismos_launch_gdn_chunked(void* state_f32, const void* q_bf16, const void* k_bf16,
                                      const void* v_bf16, const void* g_f32, const void* beta_f32,
                                      void* o_bf16, const void* gate_z_bf16, const void* cu_seqlens_i32,
                                      const void* state_slots_i32, const void* fresh_u8, int32_t n_seqs,
-                                     int32_t heads, int32_t qkv_stride, float scale, void* stream);
+                                     int32_t heads, int32_t qkv_stride, float scale, void* scratch,
+                                     int32_t n_tokens, void* stream);
 /* Inputs of the recurrence from the layer's projections (no reference code; the formulas are
  * those of research/14-gdn-aiter-preflight.md:190-198, :209-219): q, k bf16 [n_tokens, heads, 128]
  * are L2-normalised per head row in place (l2_norm_in_place, cpu.rs:19-34);

@@ -95,7 +95,7 @@ def _declare(l):
         "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],
         "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
         "logismos_launch_gdn_prefill": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
-        "logismos_launch_gdn_chunked": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp],
+        "logismos_launch_gdn_chunked": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp, i32, vp],
         "logismos_launch_gdn_prepare": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
         "logismos_launch_gated_mul_bf16": [vp, i32, vp, i32, i32, i32, i32, vp],
         "logismos_launch_greedy_argmax": [vp, i32, vp, i32, i32, vp],
@@ -166,6 +166,8 @@ def _declare(l):
     l.logismos_get_deterministic.argtypes = []
     l.logismos_get_deterministic.restype = i32
     l.logismos_skinny_int4_route.restype = i32
+    l.logismos_gdn_chunked_scratch_bytes.argtypes = [i32, i32, i32]
+    l.logismos_gdn_chunked_scratch_bytes.restype = sz
     l.logismos_set_dependent_launch.argtypes = [i32]
     l.logismos_set_dependent_launch.restype = None
     l.logismos_get_dependent_launch.argtypes = []

@@ -59,6 +59,7 @@ struct Hybrid {
   lg_reduce_add_f32_fn reduce_add = nullptr;  // reduction fused with the residual add (takes precedence)
   void* reduce_add_user = nullptr;
   Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
+  Buf gdn_scratch;  // per (chunk, head) intermediates of the chunk-parallel recurrence (two-launch form)
   Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh, pre_kv;
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
@@ -208,9 +209,9 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       if (m->n_pre > 0) {
         LG_TRY(logismos_launch_gdn_chunked(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
                                            (const int32_t*)m->cu_all.p + m->n_dec, (const int32_t*)m->state_slots.p + m->n_dec,
-                                           (const uint8_t*)m->fresh.p + m->n_dec, m->n_pre, GH, GN, gscale, s),
+                                           (const uint8_t*)m->fresh.p + m->n_dec, m->n_pre, GH, GN, gscale, m->gdn_scratch.p, T, s),
                "gdn chunk-parallel (prefill rows)");
-        m->launches += 1;
+        m->launches += 2;
       }
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, GW, s)) return rc;
     }
@@ -330,6 +331,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
        m->pos.alloc(T * 4) && m->slots.alloc(T * 8) && m->cu_all.alloc((S + 1) * 4) && m->cu_prefill.alloc((S + 1) * 4) &&
        m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) && m->dec_chunks.alloc((S + 1) * 4) &&
        m->state_slots.alloc(S * 4) && m->fresh.alloc(S) && m->pre_kv.alloc(S * 4) &&
+       m->gdn_scratch.alloc(logismos_gdn_chunked_scratch_bytes((int32_t)T, (int32_t)S, GH)) &&
        m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim));
   {
     // the attention workspace serves both prefill routes; the gather route holds one run of sequences at
@@ -362,7 +364,7 @@ void lg_hybrid_destroy(void* model) {
   Buf* bufs[] = {&m->delta, &m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
                  &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens,
                  &m->status, &m->ids, &m->pos, &m->slots, &m->cu_all, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables,
-                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh, &m->pre_kv};
+                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh, &m->pre_kv, &m->gdn_scratch};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.kpool, &L.vpool, &L.state, &L.A_log, &L.dt_bias, &L.w_in.codes, &L.w_in.scales,

@@ -493,19 +493,25 @@ def gdn_prefill_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, mode=0
     return o
 
 
-def gdn_chunked_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, sync=True):
+def gdn_chunked_(state, q, k, v, g, beta, cu_seqlens, scale, gate_z=None, sync=True, scratch=None, split=True):
     """Chunk-parallel gated delta rule over a ragged batch (same arguments and results as gdn_prefill_,
-    to tensor-core precision); state updated in place."""
+    to tensor-core precision); state updated in place. split: the two-launch form (state-independent part
+    of all chunks at once, then the chains) through ``scratch`` (uint8 CUDA tensor, allocated here when
+    None); split=False: the one-launch form."""
     _req(state, "state", torch.float32, 4); _req(q, "q", torch.bfloat16, 3); _req(k, "k", torch.bfloat16, 3)
     _req(v, "v", torch.bfloat16, 3); _req(g, "g", torch.float32, 2); _req(beta, "beta", torch.float32, 2)
     _req(cu_seqlens, "cu_seqlens", torch.int32, 1)
     if tuple(state.shape[2:]) != (128, 128) or state.shape[0] != cu_seqlens.shape[0] - 1:
         raise InvalidOp("gdn_chunked: state must be [n_seqs, heads, 128, 128]")
     o = torch.empty_like(v)
+    n_tokens = q.shape[0]
+    if split and scratch is None:
+        scratch = torch.empty(max(128, int(lib.logismos_gdn_chunked_scratch_bytes(n_tokens, state.shape[0], state.shape[1]))),
+                              dtype=torch.uint8, device=state.device)
     with torch.cuda.device(state.device):
         check(lib.logismos_launch_gdn_chunked(_p(state), _p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(gate_z) if gate_z is not None else None,
                                               _p(cu_seqlens), _p(None), _p(None), state.shape[0], state.shape[1], q.shape[1] * q.shape[2],
-                                              float(scale), _stream()), "gdn_chunked")
+                                              float(scale), _p(scratch) if split else None, n_tokens, _stream()), "gdn_chunked")
         _done(sync)
     return o
 

@@ -172,13 +172,15 @@ def test_static_state_promise_changes_nothing_but_the_fetch_order():
     assert np.isfinite(outs[0][0]).all()
 
 
-def test_chunk_parallel_form_matches_the_recurrence():
-    """The chunk-parallel kernel (triangular solve + tensor-core products per 64 tokens) against the
-    oracle's recurrence: lengths below, at and across chunk boundaries, a non-zero incoming state,
-    strong and weak decays, the fused output gate; and against the token-serial kernel."""
+@pytest.mark.parametrize("split", [True, False])
+def test_chunk_parallel_form_matches_the_recurrence(split):
+    """The chunk-parallel kernels (triangular solve + tensor-core products per 64 tokens; as two launches
+    through a scratch buffer, and as one launch) against the oracle's recurrence: lengths below, at and
+    across chunk boundaries, an empty sequence, a non-zero incoming state, strong and weak decays, the
+    fused output gate; and against the token-serial kernel."""
     rng = np.random.default_rng(23)
     heads, D = 2, 128
-    lens = [64, 5, 150, 1, 200]
+    lens = [64, 5, 150, 0, 1, 200]
     T = sum(lens)
     cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
     nrm = lambda x: x / np.linalg.norm(x, axis=-1, keepdims=True)
@@ -190,17 +192,44 @@ def test_chunk_parallel_form_matches_the_recurrence():
     state0 = (rng.standard_normal((len(lens), heads, D, D)) * 0.05).astype(np.float32)
     g_t, beta_t, cu_t = torch.from_numpy(g).to(DEV), torch.from_numpy(beta).to(DEV), torch.from_numpy(cu).to(DEV)
     st = torch.from_numpy(state0.copy()).to(DEV)
-    o = to_np(ops.gdn_chunked_(st, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5))
+    o = to_np(ops.gdn_chunked_(st, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5, split=split))
     final = to_np(st)
     for s in range(len(lens)):
         sl = slice(cu[s], cu[s + 1])
+        if lens[s] == 0:
+            assert np.array_equal(final[s], state0[s])   # an empty sequence leaves its state alone
+            continue
         for h in range(heads):
             o_ref, states = O.gdn_chunk_fwd(q[sl, h], k[sl, h], v[sl, h], beta[sl, h], g[sl, h], D ** -0.5, state0[s, h], D, D, 64)
             assert max_rel(o[sl, h], o_ref.reshape(-1, D)) <= 2e-2, (s, h)
             assert max_rel(final[s, h], states[-1].reshape(D, D)) <= 1e-2, (s, h)
     # the gate, and agreement with the token-serial kernel on the same inputs
     st_a = torch.from_numpy(state0.copy()).to(DEV); st_b = st_a.clone()
-    o_chunk = to_np(ops.gdn_chunked_(st_a, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5, gate_z=z_t))
+    o_chunk = to_np(ops.gdn_chunked_(st_a, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5, gate_z=z_t, split=split))
     o_serial = to_np(ops.gdn_prefill_(st_b, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5, gate_z=z_t))
     assert max_rel(o_chunk, o_serial) <= 2e-2
     assert max_rel(to_np(st_a), to_np(st_b)) <= 1e-2
+
+
+def test_two_launch_chunk_form_equals_the_one_launch_form_on_many_chunks():
+    """Both forms do the same arithmetic in the same order per chunk, so on a batch with many chunks per
+    sequence (the scratch slots of several sequences interleaved in batch order) outputs and final states
+    agree to rounding of the intermediates they both round (bf16 W, P; fp32 U)."""
+    rng = np.random.default_rng(29)
+    heads, D = 4, 128
+    lens = [700, 64, 129, 1000, 63]
+    T = sum(lens)
+    cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
+    nrm = lambda x: x / np.linalg.norm(x, axis=-1, keepdims=True)
+    q_t, _ = bf16_cuda(nrm(rng.standard_normal((T, heads, D)))); k_t, _ = bf16_cuda(nrm(rng.standard_normal((T, heads, D))))
+    v_t, _ = bf16_cuda(rng.standard_normal((T, heads, D))); z_t, _ = bf16_cuda(rng.standard_normal((T, heads, D)))
+    g_t = torch.from_numpy((-np.abs(rng.standard_normal((T, heads))) * 0.1).astype(np.float32)).to(DEV)
+    beta_t = torch.from_numpy(rng.uniform(0, 1, (T, heads)).astype(np.float32)).to(DEV)
+    cu_t = torch.from_numpy(cu).to(DEV)
+    state0 = torch.from_numpy((rng.standard_normal((len(lens), heads, D, D)) * 0.05).astype(np.float32)).to(DEV)
+    res = []
+    for split in (True, False):
+        st = state0.clone()
+        o = ops.gdn_chunked_(st, q_t, k_t, v_t, g_t, beta_t, cu_t, D ** -0.5, gate_z=z_t, split=split)
+        res.append((to_np(o), to_np(st)))
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
