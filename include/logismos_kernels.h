@@ -386,6 +386,19 @@ uint32_t logismos_launch_gdn_decode_step(void* state_f32, const void* q_bf16, co
                                          const void* beta_f32, void* o_bf16, int32_t n_seqs,
                                          int32_t heads, float scale, void* stream);
 
+/* One decode token per sequence straight from the fp32 accumulation workspace of the fused input
+ * projection (logismos_launch_qlinear_int4_g32_acc_f32 over the row blocks q | k | v | z | a | b):
+ * logismos_launch_gdn_finish and the one-token case of logismos_launch_gdn_prefill (with the output gate)
+ * in a single launch, same arithmetic in the same order. acc f32 [n_seqs, ld_acc] is left zeroed. Row i
+ * is sequence i; o bf16 [n_seqs, heads, 128]; state pool, state_slots and fresh as below. pair_count i32
+ * [n_seqs * heads], all zero on entry and on return. The states, state_slots and fresh must not be
+ * written by work still in flight on the stream (they are read ahead of the dependency wait). */
+uint32_t logismos_launch_gdn_decode_from_acc(void* state_f32, void* acc_f32, int32_t ld_acc,
+                                             const void* A_log_f32, const void* dt_bias_f32, void* o_bf16,
+                                             const void* state_slots_i32, const void* fresh_u8,
+                                             void* pair_count_i32, int32_t n_seqs, int32_t heads,
+                                             float scale, void* stream);
+
 /* gated_delta_rule_chunk_fwd / recurrent_fwd over a ragged batch (cpu.rs:92-249): sequence i owns
  * token rows cu_seqlens[i] .. cu_seqlens[i+1] of q, k, v bf16 [n_tokens, heads, 128], g, beta f32
  * [n_tokens, heads]; state f32 [n_seqs, heads, 128, 128] is the initial state on entry and the

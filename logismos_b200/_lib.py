@@ -95,6 +95,7 @@ def _declare(l):
         "logismos_launch_gather_rows_f32": [vp, vp, vp, i32, i32, i32, vp, vp],
         "logismos_launch_gdn_decode_step": [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
         "logismos_launch_gdn_prefill": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
+        "logismos_launch_gdn_decode_from_acc": [vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp],
         "logismos_launch_gdn_chunked": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp, i32, vp],
         "logismos_launch_gdn_prepare": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
         "logismos_launch_gated_mul_bf16": [vp, i32, vp, i32, i32, i32, i32, vp],

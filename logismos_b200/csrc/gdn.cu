@@ -351,6 +351,152 @@ __global__ void gdn_finish_kernel(float* __restrict__ acc, int64_t ld_acc, const
   }
 }
 
+
+// One decode token per sequence straight from the fp32 accumulation workspace of the input projection:
+// gdn_finish_kernel and the <2, 4> shape of gdn_prefill_kernel in one launch, with the same arithmetic
+// in the same order (fp32 L2 norms over float4 pieces and a warp butterfly, one bf16 rounding of q, k,
+// v, z, the gates, then the recurrence), so a pure decode step gives the bits of the two-launch route.
+// CTA = (sequence, head, half of the value columns), 128 threads. The 64 KB of state are read ahead of
+// the dependency wait (they date from an earlier step). The two CTAs of a (sequence, head) both read
+// its q, k, a, b; each zeroes its own v and z columns, and the one that arrives second at the pair's
+// counter zeroes the shared columns and resets the counter.
+__global__ void __launch_bounds__(128)
+gdn_decode_fused_kernel(float* __restrict__ state, float* __restrict__ acc, int64_t ld_acc, const float* __restrict__ A_log,
+                        const float* __restrict__ dt_bias, __nv_bfloat16* __restrict__ o, const int* __restrict__ slots,
+                        const uint8_t* __restrict__ fresh, int* __restrict__ pair_count, int heads, float scale) {
+  lg::pdl_trigger();
+  using C = PfCfg<2, 4>;
+  constexpr int R = C::kRows, R4 = R / 4, KS = 4, CPT = 2;
+  __shared__ __align__(16) float kf[KS * C::kPitch], qf[KS * C::kPitch];
+  __shared__ float vs[C::kCols], zs[C::kCols];
+  __shared__ float gate_s[2];
+  __shared__ int last_s;
+  const int part = blockIdx.x % C::kParts, sh = blockIdx.x / C::kParts;
+  const int seq = sh / heads, head = sh % heads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kq = lane % KS;
+  const int lcol = CPT * (warp * (32 / KS) + lane / KS);
+  const int col = part * C::kCols + lcol;
+  const int64_t slot = slots ? slots[seq] : seq;
+  float* hp = state + (slot * heads + head) * (int64_t)(KD * VD) + (int64_t)(kq * R) * VD + col;
+  const bool zero_start = fresh && fresh[seq];
+  float h[R][CPT];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const float2 x = zero_start ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(hp + i * VD);
+    h[i][0] = x.x;
+    h[i][1] = x.y;
+  }
+  lg::pdl_wait();
+  const int w = heads * KD;
+  float* arow = acc + (int64_t)seq * ld_acc;
+  if (warp < 2) {  // q (warp 0) and k (warp 1): unit L2 norm in fp32, one bf16 rounding, into the pitched layout
+    const float4 x0 = *reinterpret_cast<const float4*>(arow + warp * w + head * KD + lane * 4);
+    float4 x = x0;
+    const float sq = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+    const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-12f);
+    x.x *= inv; x.y *= inv; x.z *= inv; x.w *= inv;
+    const float2 lo = unpack_bf16x2(pack_bf16x2(x.x, x.y)), hi = unpack_bf16x2(pack_bf16x2(x.z, x.w));
+    float* dst = (warp == 0 ? qf : kf) + ((lane * 4) / R) * C::kPitch + (lane * 4) % R;
+    *reinterpret_cast<float4*>(dst) = make_float4(lo.x, lo.y, hi.x, hi.y);
+  } else {  // v (warp 2) and z (warp 3): this CTA's 64 columns, rounded once; the workspace columns are this CTA's to clear
+    float* src = arow + (warp == 2 ? 2 : 3) * w + head * KD + part * C::kCols + lane * 2;
+    const float2 x = *reinterpret_cast<const float2*>(src);
+    *reinterpret_cast<float2*>(src) = make_float2(0.f, 0.f);
+    const float2 r = unpack_bf16x2(pack_bf16x2(x.x, x.y));
+    float* dst = (warp == 2 ? vs : zs) + lane * 2;
+    dst[0] = r.x;
+    dst[1] = r.y;
+    if (warp == 2 && lane == 0) {
+      const float* ab = arow + 4 * w;
+      const float x = ab[head] + dt_bias[head];
+      const float sp = x > 20.0f ? x : log1pf(expf(x));
+      gate_s[0] = -expf(A_log[head]) * sp;
+      gate_s[1] = 1.0f / (1.0f + expf(-ab[heads + head]));
+    }
+  }
+  __syncthreads();  // every read of the shared workspace columns by this CTA is done
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(pair_count + (int64_t)seq * heads + head, 1);
+    last_s = old == C::kParts - 1;
+    if (old == C::kParts - 1) pair_count[(int64_t)seq * heads + head] = 0;
+  }
+  __syncthreads();
+  if (last_s) {  // the other CTA of the pair has read q, k, a, b: clear them for the next accumulation
+    arow[head * KD + tid] = 0.f;
+    arow[w + head * KD + tid] = 0.f;
+    if (tid == 0) {
+      arow[4 * w + head] = 0.f;
+      arow[4 * w + heads + head] = 0.f;
+    }
+  }
+  // the recurrence for the one token (gdn_prefill_kernel's loop body)
+  const float decay = expf(gate_s[0]);
+  const float b_cur = gate_s[1];
+  float v_cur[CPT];
+#pragma unroll
+  for (int cc = 0; cc < CPT; ++cc) v_cur[cc] = vs[lcol + cc];
+  const float4* k4 = reinterpret_cast<const float4*>(&kf[kq * C::kPitch]);
+  const float4* q4 = reinterpret_cast<const float4*>(&qf[kq * C::kPitch]);
+  float4 kk[R4];
+#pragma unroll
+  for (int j = 0; j < R4; ++j) kk[j] = k4[j];
+  float a4[4][CPT];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) a4[a][cc] = 0.f;
+#pragma unroll
+  for (int j = 0; j < R4; ++j)
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) {
+      a4[0][cc] += h[4 * j][cc] * kk[j].x;
+      a4[1][cc] += h[4 * j + 1][cc] * kk[j].y;
+      a4[2][cc] += h[4 * j + 2][cc] * kk[j].z;
+      a4[3][cc] += h[4 * j + 3][cc] * kk[j].w;
+    }
+  float vd[CPT];
+#pragma unroll
+  for (int cc = 0; cc < CPT; ++cc) {
+    float hk = (a4[0][cc] + a4[1][cc]) + (a4[2][cc] + a4[3][cc]);
+#pragma unroll
+    for (int m = 1; m < KS; m <<= 1) hk += __shfl_xor_sync(0xffffffffu, hk, m);
+    vd[cc] = b_cur * (v_cur[cc] - decay * hk);
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) a4[a][cc] = 0.f;
+#pragma unroll
+  for (int j = 0; j < R4; ++j) {
+    const float4 qq = q4[j];
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) {
+      h[4 * j][cc] = fmaf(h[4 * j][cc], decay, kk[j].x * vd[cc]);
+      h[4 * j + 1][cc] = fmaf(h[4 * j + 1][cc], decay, kk[j].y * vd[cc]);
+      h[4 * j + 2][cc] = fmaf(h[4 * j + 2][cc], decay, kk[j].z * vd[cc]);
+      h[4 * j + 3][cc] = fmaf(h[4 * j + 3][cc], decay, kk[j].w * vd[cc]);
+      a4[0][cc] += h[4 * j][cc] * qq.x;
+      a4[1][cc] += h[4 * j + 1][cc] * qq.y;
+      a4[2][cc] += h[4 * j + 2][cc] * qq.z;
+      a4[3][cc] += h[4 * j + 3][cc] * qq.w;
+    }
+  }
+#pragma unroll
+  for (int cc = 0; cc < CPT; ++cc) {
+    float ov = (a4[0][cc] + a4[1][cc]) + (a4[2][cc] + a4[3][cc]);
+#pragma unroll
+    for (int m = 1; m < KS; m <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, m);
+    ov *= scale;
+    const float zc = zs[lcol + cc];
+    ov *= zc / (1.0f + __expf(-zc));
+    if (kq == 0) o[((int64_t)seq * heads + head) * VD + col + cc] = __float2bfloat16(ov);
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i) *reinterpret_cast<float2*>(hp + i * VD) = make_float2(h[i][0], h[i][1]);
+}
+
 }  // namespace
 
 extern "C" uint32_t logismos_launch_gdn_finish(void* acc, int32_t ld_acc, const void* A_log, const void* dt_bias, void* proj,
@@ -366,6 +512,22 @@ extern "C" uint32_t logismos_launch_gdn_finish(void* acc, int32_t ld_acc, const 
   lg::launch(gdn_finish_kernel, dim3((unsigned)((rows + wpb - 1) / wpb)), dim3(wpb * 32), 0, (cudaStream_t)stream, 
       (float*)acc, (int64_t)ld_acc, (const float*)A_log, (const float*)dt_bias, (__nv_bfloat16*)proj, (int64_t)ld_proj, (float*)g,
       (float*)beta, rows, heads);
+  return lg::launch_status();
+}
+
+extern "C" uint32_t logismos_launch_gdn_decode_from_acc(void* state, void* acc, int32_t ld_acc, const void* A_log, const void* dt_bias,
+                                                        void* o, const void* state_slots, const void* fresh, void* pair_count,
+                                                        int32_t n_seqs, int32_t heads, float scale, void* stream) {
+  lg::LaunchScope launch_scope_;
+  const int w = heads * KD;
+  if (n_seqs < 0 || heads <= 0 || ld_acc < 4 * w + 2 * heads || (ld_acc % 4) || !pair_count) return lg::kInvalidValue;
+  if (n_seqs == 0) return 0;
+  if (((uintptr_t)state & 15) || ((uintptr_t)acc & 15) || ((uintptr_t)o & 1) || ((uintptr_t)pair_count & 3)) return lg::kInvalidValue;
+  const int64_t ctas = (int64_t)n_seqs * heads * PfCfg<2, 4>::kParts;
+  if (ctas > 2147483647ll) return lg::kInvalidValue;
+  lg::launch(gdn_decode_fused_kernel, dim3((unsigned)ctas), dim3(128), 0, (cudaStream_t)stream, (float*)state, (float*)acc,
+             (int64_t)ld_acc, (const float*)A_log, (const float*)dt_bias, (__nv_bfloat16*)o, (const int*)state_slots,
+             (const uint8_t*)fresh, (int*)pair_count, heads, scale);
   return lg::launch_status();
 }
 

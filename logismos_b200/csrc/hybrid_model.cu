@@ -60,6 +60,7 @@ struct Hybrid {
   void* reduce_add_user = nullptr;
   Buf x, h, proj, mix, qdec, ab, g, beta, act, wscratch, accws, last, last_bf16, logits, tokens, status;
   Buf gdn_scratch;  // per (chunk, head) intermediates of the chunk-parallel recurrence (two-launch form)
+  Buf gdn_pairs;    // arrival counters of the fused decode kernel's CTA pairs, all zero between launches
   Buf ids, pos, slots, cu_all, cu_prefill, last_idx, dec_ctx, dec_tables, dec_chunks, dec_scratch, attn_ws, state_slots, fresh, pre_kv;
   uint8_t* pinned = nullptr;
   size_t pinned_bytes = 0;
@@ -117,6 +118,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
   m->launches = 0;
   if (m->acc_dirty) {
     LG_TRY(cudaMemsetAsync(m->accws.p, 0, m->accws_bytes, s), "clear accumulation workspace");
+    LG_TRY(cudaMemsetAsync(m->gdn_pairs.p, 0, (size_t)m->cfg.max_step_seqs * m->cfg.gdn_heads * 4, s), "clear pair counters");
     m->acc_dirty = false;
   }
   LG_TRY(logismos_launch_embed_lookup_bf16(m->tok_embed.p, m->ids.p, m->x.p, T, H, c.vocab, s), "embed_lookup");
@@ -173,14 +175,24 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       // the one accumulation + finishing kernel (16 + 18 us at 64 rows, the finishing kernel waiting for
       // the fp32 reductions to drain) still beats GEMM + memset + a|b GEMM + prepare (5.72 against 5.97 ms
       // per 64-sequence step); at 128 rows the two routes are level
+      bool recurrence_done = false;
       if (T <= (L.w_in.dense.p ? 96 : kFusedDequantMaxRows)) {
         // one fused-dequant accumulation of all six blocks, finished by the kernel that also normalises
         // q, k and computes the gates from the fp32 sums
         const int ld = GN + 2 * GH;
         LG_TRY(logismos_launch_qlinear_int4_g32_acc_f32_static(m->h.p, L.w_in.codes.p, L.w_in.scales.p, m->accws.p, T, ld, H, H, ld, st, s),
                "int4 linear");
-        LG_TRY(logismos_launch_gdn_finish(m->accws.p, ld, L.A_log.p, L.dt_bias.p, m->proj.p, GN, m->g.p, m->beta.p, T, GH, s), "gdn_finish");
-        m->launches += 2;
+        if (m->n_pre == 0) {
+          // a pure decode step: normalisation, gates and the recurrence in one launch from the fp32 sums
+          LG_TRY(logismos_launch_gdn_decode_from_acc(L.state.p, m->accws.p, ld, L.A_log.p, L.dt_bias.p, m->mix.p, m->state_slots.p,
+                                                     m->fresh.p, m->gdn_pairs.p, m->n_dec, GH, 1.0f / std::sqrt((float)kGdnDim), s),
+                 "gdn decode from the accumulation workspace");
+          m->launches += 2;
+          recurrence_done = true;
+        } else {
+          LG_TRY(logismos_launch_gdn_finish(m->accws.p, ld, L.A_log.p, L.dt_bias.p, m->proj.p, GN, m->g.p, m->beta.p, T, GH, s), "gdn_finish");
+          m->launches += 2;
+        }
       } else {
         // dense path: q | k | v | z to bf16, a | b as fp32 through the accumulate epilogue
         QMat main_rows = L.w_in, ab_rows = L.w_in;  // views of the row blocks (no ownership)
@@ -199,7 +211,7 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       // decode sequences (one token each, bound by the state traffic) run the token-serial kernel,
       // prefill sequences the chunk-parallel one; they are disjoint runs of the packed batch
       const float gscale = 1.0f / std::sqrt((float)kGdnDim);
-      if (m->n_dec > 0) {
+      if (m->n_dec > 0 && !recurrence_done) {
         LG_TRY(logismos_launch_gdn_prefill(L.state.p, p16, p16 + GW, p16 + 2 * GW, m->g.p, m->beta.p, m->mix.p, p16 + 3 * GW,
                                            m->cu_all.p, m->state_slots.p, m->fresh.p, m->n_dec, GH, GN, gscale,
                                            1 | LG_GDN_STATIC_STATE /* states and index arrays date from before this step's first kernel */, s),
@@ -331,7 +343,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
        m->pos.alloc(T * 4) && m->slots.alloc(T * 8) && m->cu_all.alloc((S + 1) * 4) && m->cu_prefill.alloc((S + 1) * 4) &&
        m->last_idx.alloc(S * 4) && m->dec_ctx.alloc(S * 4) && m->dec_tables.alloc(S * MB * 4) && m->dec_chunks.alloc((S + 1) * 4) &&
        m->state_slots.alloc(S * 4) && m->fresh.alloc(S) && m->pre_kv.alloc(S * 4) &&
-       m->gdn_scratch.alloc(logismos_gdn_chunked_scratch_bytes((int32_t)T, (int32_t)S, GH)) &&
+       m->gdn_scratch.alloc(logismos_gdn_chunked_scratch_bytes((int32_t)T, (int32_t)S, GH)) && m->gdn_pairs.alloc(S * GH * 4) &&
        m->dec_scratch.alloc(logismos_paged_decode_scratch_bytes((int32_t)m->max_chunks, c.n_heads, c.attn_head_dim));
   {
     // the attention workspace serves both prefill routes; the gather route holds one run of sequences at
@@ -345,6 +357,7 @@ uint32_t lg_hybrid_create(int32_t device, const lg_hybrid_config_t* cfg, const l
   ok = ok && cudaMemset(m->status.p, 0, 4) == cudaSuccess;
   m->accws_bytes = (size_t)kFusedDequantMaxRows * acc_n * 4;
   ok = ok && cudaMemset(m->accws.p, 0, m->accws_bytes) == cudaSuccess;
+  ok = ok && cudaMemset(m->gdn_pairs.p, 0, S * GH * 4) == cudaSuccess;
   m->pinned_bytes = T * 16 + (S + 1) * 4 * 4 + S * MB * 4 + S * 4 + S * 4 + S * 4 + S + 64;
   ok = ok && cudaMallocHost((void**)&m->pinned, m->pinned_bytes) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -364,7 +377,7 @@ void lg_hybrid_destroy(void* model) {
   Buf* bufs[] = {&m->delta, &m->tok_embed, &m->final_norm, &m->cos, &m->sin, &m->lm_head.codes, &m->lm_head.scales, &m->x, &m->h, &m->proj,
                  &m->mix, &m->qdec, &m->ab, &m->g, &m->beta, &m->act, &m->wscratch, &m->accws, &m->last, &m->last_bf16, &m->logits, &m->tokens,
                  &m->status, &m->ids, &m->pos, &m->slots, &m->cu_all, &m->cu_prefill, &m->last_idx, &m->dec_ctx, &m->dec_tables,
-                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh, &m->pre_kv, &m->gdn_scratch};
+                 &m->dec_chunks, &m->dec_scratch, &m->attn_ws, &m->state_slots, &m->fresh, &m->pre_kv, &m->gdn_scratch, &m->gdn_pairs};
   for (Buf* b : bufs) b->release();
   for (auto& L : m->layers) {
     Buf* lb[] = {&L.norm1, &L.norm2, &L.kpool, &L.vpool, &L.state, &L.A_log, &L.dt_bias, &L.w_in.codes, &L.w_in.scales,

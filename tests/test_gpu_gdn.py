@@ -118,6 +118,48 @@ def test_finish_of_the_input_projection_workspace():
     assert np.abs(to_np(g) - g_ref).max() <= 1e-5 * max(1, np.abs(g_ref).max()) and np.abs(to_np(beta) - beta_ref).max() <= 1e-6
 
 
+def test_decode_from_the_workspace_equals_finish_then_recurrence():
+    """The one-launch decode path (normalisation, gates and the one-token recurrence straight from the fp32
+    workspace) against the two-launch route on the same workspace: same outputs and states bit for bit,
+    workspace and pair counters handed back zeroed; state slots permuted, one sequence fresh."""
+    from logismos_b200._lib import check, lib
+    rng = np.random.default_rng(31)
+    T, heads, D = 37, 8, 128
+    W = heads * D
+    ld = 4 * W + 2 * heads
+    acc_np = rng.standard_normal((T, ld)).astype(np.float32)
+    A_t = torch.from_numpy(rng.uniform(-1, 0.5, heads).astype(np.float32)).to(DEV)
+    dt_t = torch.from_numpy(rng.standard_normal(heads).astype(np.float32)).to(DEV)
+    state0 = torch.from_numpy((rng.standard_normal((T + 3, heads, D, D)) * 0.05).astype(np.float32)).to(DEV)
+    slots = torch.from_numpy(rng.permutation(T + 3)[:T].astype(np.int32)).to(DEV)
+    fresh_np = np.zeros(T, np.uint8); fresh_np[5] = 1
+    fresh = torch.from_numpy(fresh_np).to(DEV)
+    cu = torch.arange(0, T + 1, dtype=torch.int32, device=DEV)
+    s = lambda: torch.cuda.current_stream().cuda_stream
+    # route A: finish, then the token-serial kernel (throughput shape) with the fused output gate
+    acc = torch.from_numpy(acc_np.copy()).to(DEV)
+    proj = torch.empty((T, 4 * W), dtype=torch.bfloat16, device=DEV)
+    g = torch.empty((T, heads), dtype=torch.float32, device=DEV); beta = torch.empty_like(g)
+    st_a = state0.clone(); o_a = torch.empty((T, W), dtype=torch.bfloat16, device=DEV)
+    check(lib.logismos_launch_gdn_finish(acc.data_ptr(), ld, A_t.data_ptr(), dt_t.data_ptr(), proj.data_ptr(), 4 * W, g.data_ptr(),
+                                         beta.data_ptr(), T, heads, s()), "gdn_finish")
+    p = proj.data_ptr()
+    check(lib.logismos_launch_gdn_prefill(st_a.data_ptr(), p, p + 2 * W, p + 4 * W, g.data_ptr(), beta.data_ptr(), o_a.data_ptr(), p + 6 * W,
+                                          cu.data_ptr(), slots.data_ptr(), fresh.data_ptr(), T, heads, 4 * W, D ** -0.5, 1, s()), "gdn_prefill")
+    # route B: one launch
+    acc_b = torch.from_numpy(acc_np.copy()).to(DEV)
+    pairs = torch.zeros(T * heads, dtype=torch.int32, device=DEV)
+    st_b = state0.clone(); o_b = torch.empty((T, W), dtype=torch.bfloat16, device=DEV)
+    torch.cuda.synchronize()
+    check(lib.logismos_launch_gdn_decode_from_acc(st_b.data_ptr(), acc_b.data_ptr(), ld, A_t.data_ptr(), dt_t.data_ptr(), o_b.data_ptr(),
+                                                  slots.data_ptr(), fresh.data_ptr(), pairs.data_ptr(), T, heads, D ** -0.5, s()), "gdn_decode_from_acc")
+    torch.cuda.synchronize()
+    assert float(acc_b.abs().max()) == 0.0 and int(pairs.abs().max()) == 0
+    assert np.array_equal(to_np(o_a), to_np(o_b))
+    assert np.array_equal(to_np(st_a), to_np(st_b))
+    assert np.isfinite(to_np(o_b)).all()
+
+
 def test_both_kernel_shapes_agree_with_the_reference():
     """The throughput shape (64 columns per CTA, key rows in quarters) and the latency shape (32 columns, one per thread) against the oracle's recurrence, from a non-zero state, ragged lengths that
     end inside and on the eight-token staging chunks."""
