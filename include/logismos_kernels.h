@@ -92,7 +92,9 @@ uint32_t logismos_launch_rms_norm_f32(const void* x_f32, const void* w_f32, void
  *                    interleaved in blocks of 32 rows (32 gate rows, then the 32 matching up
  *                    rows); n % 64 == 0; fuses cpu_f32::silu + hadamard (mod.rs:349-374)
  * bias_f32 may be NULL. ldc is the row stride of out in elements. status_i32 (may be NULL)
- * receives 2 if a bounded wait inside the kernel expired (the output is then invalid).
+ * receives a value whose low byte is 2 if a bounded wait inside the kernel expired (the output is
+ * then invalid); the next byte names the kernel family (1 dense GEMM, 2 fused-dequant linear, 3
+ * tensor-core attention).
  * With few output tiles and a long reduction the accumulating epilogue splits k over CTAs; the
  * slices meet in the fp32 reduce-add, so the last bits of the sum can differ between runs.
  *
@@ -146,7 +148,7 @@ uint32_t logismos_launch_varlen_attention_bf16(const void* qkv_bf16, const void*
  * layout contract as logismos_launch_varlen_attention_bf16; n_tokens = cu_seqlens[n_seqs]. scratch:
  * logismos_varlen_attention_tc_scratch_bytes(n_tokens, n_seqs, n_kv_heads, head_dim) bytes, 256-byte aligned
  * (receives V transposed per kv head with every sequence padded to a multiple of 8 keys). qkv and out
- * 16-byte aligned. Two launches. status (int32, may be NULL) is set to 2 if a bounded wait inside
+ * 16-byte aligned. Two launches. status (int32, may be NULL) is set to 2 (low byte; see logismos_launch_linear_t_bf16) if a bounded wait inside
  * the kernel expired. */
 size_t logismos_varlen_attention_tc_scratch_bytes(int32_t n_tokens, int32_t n_seqs, int32_t n_kv_heads,
                                                   int32_t head_dim);

@@ -463,7 +463,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float m = -1e30f, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
-      if (!mbar_wait(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       // keys this row may see in this block: [0, lim)
       int lim = kv_len - j * 128;
@@ -543,7 +543,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && mbar_wait(o_done, 0u, abort_flag)) {
+    if (ok && mbar_wait_warp(o_done, 0u, abort_flag)) {
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool store = q0 + row < len;
@@ -574,7 +574,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // a wait expired somewhere: give copies that may still be in flight time to land before the
     // shared memory and TMEM are released, and report
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    if (threadIdx.x == 0 && status) atomicExch(status, 2 | (3 << 8));  // low byte 2: a bounded wait expired; next byte: which kernel family
   }
   tc_fence_before();
   __syncthreads();

@@ -192,7 +192,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const bool first_slice = tile < out_tiles;  // the bias joins once
       const int buf = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row0 = m_blk * BM + q * 32;  // first output row of this warp's slab
       const int row = row0 + lane;
@@ -277,7 +277,7 @@ linear_t_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     // a wait expired somewhere: give copies that may still be in flight time to land before the
     // shared memory and TMEM are released, and report
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    if (threadIdx.x == 0 && status) atomicExch(status, 2 | (1 << 8));  // low byte 2: a bounded wait expired; next byte: which kernel family
   }
   tc_fence_before();
   __syncthreads();

@@ -508,9 +508,12 @@ uint32_t lg_hybrid_step(void* model, const uint32_t* host_ids, const int32_t* ca
   LG_TRY(cudaMemcpyAsync(toks.data(), m->tokens.p, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, s), "D2H tokens");
   LG_TRY(cudaStreamSynchronize(s), "stream synchronize");
   for (int k = 0; k < n_seqs; ++k) next_tokens[order[k]] = toks[k];
-  if (lg_hybrid_device_status(m) != 0) {
+  if (const int dev_status = lg_hybrid_device_status(m)) {
     m->acc_dirty = true;
-    set_error("a device-side range check or bounded wait failed");
+    char buf[160];
+    std::snprintf(buf, sizeof(buf), "device status 0x%x after a step of %d tokens in %d sequences (low byte 1: a range check failed, 2: a bounded wait expired in kernel family <next byte>, 3: a peer did not arrive)",
+                  dev_status, (int)total, n_seqs);
+    set_error(buf);
     return LG_EMB_COMPUTE;
   }
   return LG_EMB_OK;

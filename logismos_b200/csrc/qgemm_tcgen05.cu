@@ -196,7 +196,11 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   };
   // w_static: nothing still in flight writes the weights, so the ring is filled before the dependency
   // wait (the first slots are free by construction) and lands while the preceding kernel drains
-  if (w_static && threadIdx.x == 0)
+  // Only in the configurations of up to 64 tokens: with 128-token tiles (two issuing threads, activation
+  // stages of half a unit) an early-filled ring made about one launch in a few hundred run into an
+  // expired wait in a stress test (vocabulary-sized matrix, back-to-back launches); the cause is not
+  // understood, and without the early fill 12000 such launches passed.
+  if (w_static && NT <= 64 && threadIdx.x == 0)
     while (p_u < u1 && p_u - u0 < kRawStages) issue_raw();
   lg::pdl_wait();  // everything before this touched shared memory or read the static weights only
   if (warp == 2) {
@@ -307,7 +311,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int wb = n_unit & 1;
       const uint32_t wphase = ((uint32_t)n_unit >> 1) & 1u;
       if (wd == 0 && lane == 0) QTRACE(u - u0, 1);
-      if (!mbar_wait_sleep(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_sleep_warp(raw_full(rs), rphase, abort_flag)) { ok = false; break; }
       if (wd == 0 && lane == 0) QTRACE(u - u0, 2);
       const uint8_t* raw = smem_gen + rs * kRawStage;
       // this row's 64 codes of k block g (two 16-byte chunks, swizzled by the TMA) and their two scales
@@ -322,7 +326,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       o[0] = dequant_word(c0.x, s0); o[1] = dequant_word(c0.y, s0); o[2] = dequant_word(c0.z, s0); o[3] = dequant_word(c0.w, s0);
       o[4] = dequant_word(c1.x, s1); o[5] = dequant_word(c1.y, s1); o[6] = dequant_word(c1.z, s1); o[7] = dequant_word(c1.w, s1);
       if (wd == 0 && lane == 0) QTRACE(u - u0, 3);
-      if (!mbar_wait_sleep(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_sleep_warp(wd_empty(wb), wphase ^ 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (wd == 0 && lane == 0) QTRACE(u - u0, 4);
       tc_st32(wt0 + (uint32_t)(wb * C::kWBufCols), o);  // lane = weight row, 32 columns = its 64 bf16 in k order
@@ -346,6 +350,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
       for (int is = 0; is < kIssuers; ++is)
         if (ok && !mbar_wait_relaxed(tfull(is, buf), tphase, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok) != 0;  // one outcome for the warp, and the lanes back together before the tensor-memory loads
       if (!ok) break;
       tc_fence_after();
       const int f = (u / n_raw) * kWRows + q * 32 + lane;
@@ -380,7 +385,7 @@ qlinear_int4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   __syncwarp();
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    if (threadIdx.x == 0 && status) atomicExch(status, 2 | (2 << 8));  // low byte 2: a bounded wait expired; next byte: which kernel family
   }
   tc_fence_before();
   __syncthreads();

@@ -9,7 +9,10 @@
 namespace lg {
 namespace tc {
 
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Polls of a bounded wait. A poll suspends for up to about 2 us (the hint of try_wait) or sleeps for
+// 40-400 ns, so a wait gives up after 20 ms to 1 s; a legitimate wait inside these kernels lasts
+// microseconds.
+constexpr uint32_t kSpinLimit = 1u << 19;
 
 // ---- mbarrier / TMA / tcgen05 wrappers --------------------------------------------------------
 
@@ -60,6 +63,17 @@ LG_DEVINL bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abor
   }
   *abort_flag = 1;
   return false;
+}
+
+// The waits of a role in which the WHOLE warp takes part (all 32 lanes must call). Every lane polls; the
+// vote then makes the outcome the same for all of them and, being a warp-wide operation, brings the
+// lanes back together: lanes can leave the polling loop in different iterations, and the tensor-memory
+// instructions that follow (.sync.aligned) must be executed by the converged warp.
+LG_DEVINL bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+LG_DEVINL bool mbar_wait_sleep_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t ns = 64) {
+  return __all_sync(0xffffffffu, mbar_wait_sleep(bar, parity, abort_flag, ns)) != 0;
 }
 
 LG_DEVINL void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int x, int y) {

@@ -60,6 +60,34 @@ def test_static_weight_promise_changes_nothing_but_the_fetch_order(m, n, k):
         lib.logismos_set_deterministic(0)
 
 
+@pytest.mark.parametrize("m", [16, 64, 91, 128])
+def test_back_to_back_launches_on_a_vocabulary_sized_matrix_never_expire_a_wait(m):
+    """A thousand back-to-back launches of the static-weights entry point per tile configuration (32-, 64-
+    and 128-token tiles) on a 151936 x 2048 matrix, the accumulator cleared between them as the lm_head of a
+    decode step does: the status word stays 0 and the last accumulation is right. (Rare expired waits in
+    the 128-token configuration were once the symptom of lanes leaving a polling loop in different
+    iterations ahead of a warp-wide tensor-memory instruction, and of the weight ring filled early.)"""
+    from logismos_b200._lib import lib
+    n, k = 151936, 2048
+    g = torch.Generator(device="cpu").manual_seed(m)
+    codes = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, generator=g).to(DEV)
+    scales = (torch.rand((n, k // 32), generator=g) * 0.02).to(torch.float16).to(DEV)
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16).to(DEV)
+    acc = torch.zeros((m, n), dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    s = torch.cuda.current_stream().cuda_stream
+    for it in range(250):
+        for _ in range(4):
+            acc.zero_()
+            assert lib.logismos_launch_qlinear_int4_g32_acc_f32_static(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), acc.data_ptr(), m, n, k, k, n,
+                                                                       status.data_ptr(), s) == 0
+        assert int(status.item()) == 0, (it, hex(int(status.item())))
+    rows = torch.arange(0, n, 997, device=DEV)
+    w = (ops.dequant_int4(codes[rows].contiguous(), scales[rows].contiguous())).float()
+    ref = x.float() @ w.t()
+    assert float((acc[:, rows] - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
 def test_exact_for_exactly_representable_inputs():
     """Power-of-two scales and small integer activations: every product and partial sum is exact in
     bf16 / fp32, so the result must equal the integer dot product bit for bit (nibble order, sign
