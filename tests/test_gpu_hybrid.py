@@ -100,6 +100,43 @@ def test_every_linear_route_gives_the_same_model(keep_bf16_copy):
     model.close()
 
 
+def test_the_same_sequence_in_steps_on_both_sides_of_every_routing_threshold():
+    """The executor picks kernels by the number of rows in a step (GEMV lm_head up to 16 rows, fused-dequant
+    linears up to 32, fused input projection and one-launch decode recurrence up to 96, dense GEMMs
+    above). The same prompt and the same decode token, replicated into steps of 1, 16, 17, 33, 97 and 129
+    rows, must give every row the oracle's hidden state and logits, a token that maximises the oracle's
+    logits, and logits that drift across the step sizes by no more than the parity tolerance."""
+    cfg = TINY_HYBRID
+    qw, deq = make_hybrid(cfg, 51)
+    oracle = O.OracleHybrid(cfg, deq)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, cfg["vocab"], 12).astype(np.uint32)
+    h_ref, l_ref = oracle.forward(prompt)
+    t_ref = int(O.greedy(l_ref))
+    h2_ref, l2_ref = oracle.forward(np.concatenate([prompt, [t_ref]]).astype(np.uint32))
+    first = None
+    for n in (1, 16, 17, 33, 97, 129):
+        model = HybridModel(cfg, qw, n_pool_blocks=n + 2, max_blocks_per_seq=2, max_step_tokens=n * len(prompt), max_step_seqs=n, n_state_slots=n)
+        tabs = np.stack([np.array([i, n], np.int32) for i in range(n)])   # one block per sequence (13 tokens), the second entry unused
+        toks = model.step(np.tile(prompt, n), [0] * n, [len(prompt)] * n, tabs, list(range(n)))
+        assert model.device_status() == 0
+        hs, lg = model.last_hidden(), model.last_logits()
+        for r in range(n):
+            assert max_rel(hs[r], h_ref[-1]) <= TOL and max_rel(lg[r], l_ref) <= TOL, (n, r)
+        assert l_ref[toks].min() >= l_ref.max() - TOL * np.abs(l_ref).max(), n
+        toks = model.step([t_ref] * n, [len(prompt)] * n, [1] * n, tabs, list(range(n)))   # the decode step, same token everywhere
+        assert model.device_status() == 0
+        hs, lg = model.last_hidden(), model.last_logits()
+        for r in range(n):
+            assert max_rel(hs[r], h2_ref[-1]) <= TOL and max_rel(lg[r], l2_ref) <= TOL, (n, r)
+        assert l2_ref[toks].min() >= l2_ref.max() - TOL * np.abs(l2_ref).max(), n   # every row decodes a maximum of the oracle's logits
+        if first is None:
+            first = lg[0].copy()
+        else:
+            assert max_rel(lg[0], first) <= TOL, n                            # drift across routes
+        model.close()
+
+
 def test_step_rejects_what_it_cannot_run():
     qw, _ = make_hybrid(TINY_HYBRID_128, 3)
     model = HybridModel(TINY_HYBRID_128, qw, n_pool_blocks=8, max_blocks_per_seq=8, max_step_tokens=64, max_step_seqs=2, n_state_slots=2)
