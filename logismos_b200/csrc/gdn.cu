@@ -417,19 +417,11 @@ gdn_decode_fused_kernel(float* __restrict__ state, float* __restrict__ acc, int6
   }
   __syncthreads();  // every read of the shared workspace columns by this CTA is done
   if (tid == 0) {
+    // the pair's counter: its round trip stays off the critical path (the result is only needed at the end)
     __threadfence();
     const int old = atomicAdd(pair_count + (int64_t)seq * heads + head, 1);
     last_s = old == C::kParts - 1;
     if (old == C::kParts - 1) pair_count[(int64_t)seq * heads + head] = 0;
-  }
-  __syncthreads();
-  if (last_s) {  // the other CTA of the pair has read q, k, a, b: clear them for the next accumulation
-    arow[head * KD + tid] = 0.f;
-    arow[w + head * KD + tid] = 0.f;
-    if (tid == 0) {
-      arow[4 * w + head] = 0.f;
-      arow[4 * w + heads + head] = 0.f;
-    }
   }
   // the recurrence for the one token (gdn_prefill_kernel's loop body)
   const float decay = expf(gate_s[0]);
@@ -495,6 +487,15 @@ gdn_decode_fused_kernel(float* __restrict__ state, float* __restrict__ acc, int6
   }
 #pragma unroll
   for (int i = 0; i < R; ++i) *reinterpret_cast<float2*>(hp + i * VD) = make_float2(h[i][0], h[i][1]);
+  __syncthreads();
+  if (last_s) {  // the other CTA of the pair has read q, k, a, b: clear them for the next accumulation
+    arow[head * KD + tid] = 0.f;
+    arow[w + head * KD + tid] = 0.f;
+    if (tid == 0) {
+      arow[4 * w + head] = 0.f;
+      arow[4 * w + heads + head] = 0.f;
+    }
+  }
 }
 
 }  // namespace
