@@ -171,12 +171,13 @@ uint32_t run_device(Hybrid* m, cudaStream_t s) {
       if (uint32_t rc = out_proj(m, m->mix.p, L.w_out, T, QW, s)) return rc;
     } else {
       // columns: q [GW] | k [GW] | v [GW] | z [GW] | a [GH] | b [GH] of one weight matrix
-      // fused up to 96 rows even when the dense route has a bf16 copy to work on: measured per step,
-      // the one accumulation + finishing kernel (16 + 18 us at 64 rows, the finishing kernel waiting for
-      // the fp32 reductions to drain) still beats GEMM + memset + a|b GEMM + prepare (5.72 against 5.97 ms
-      // per 64-sequence step); at 128 rows the two routes are level
+      // fused up to 64 rows (the 64-token tile of the fused-dequant kernel) even when the dense route has
+      // a bf16 copy to work on. Measured per decode step, fused against dense (GEMM + memset + a|b GEMM +
+      // prepare + recurrence): 56 rows 4.60 against 4.79 ms, 72 rows 4.95 against 4.95, 88 rows 5.61 against
+      // 5.38, 96 rows 5.81 against 5.50, 128 rows 6.44 against 6.10: above 64 rows the fused kernel is on its
+      // 128-token configuration (two issuing threads) and loses
       bool recurrence_done = false;
-      if (T <= (L.w_in.dense.p ? 96 : kFusedDequantMaxRows)) {
+      if (T <= (L.w_in.dense.p ? 64 : kFusedDequantMaxRows)) {
         // one fused-dequant accumulation of all six blocks, finished by the kernel that also normalises
         // q, k and computes the gates from the fp32 sums
         const int ld = GN + 2 * GH;

@@ -102,8 +102,8 @@ def test_every_linear_route_gives_the_same_model(keep_bf16_copy):
 
 def test_the_same_sequence_in_steps_on_both_sides_of_every_routing_threshold():
     """The executor picks kernels by the number of rows in a step (GEMV lm_head up to 16 rows, fused-dequant
-    linears up to 32, fused input projection and one-launch decode recurrence up to 96, dense GEMMs
-    above). The same prompt and the same decode token, replicated into steps of 1, 16, 17, 33, 97 and 129
+    linears up to 32, fused input projection and one-launch decode recurrence up to 64, dense GEMMs
+    above). The same prompt and the same decode token, replicated into steps of 1, 16, 17, 33, 64, 65 and 129
     rows, must give every row the oracle's hidden state and logits, a token that maximises the oracle's
     logits, and logits that drift across the step sizes by no more than the parity tolerance."""
     cfg = TINY_HYBRID
@@ -115,7 +115,7 @@ def test_the_same_sequence_in_steps_on_both_sides_of_every_routing_threshold():
     t_ref = int(O.greedy(l_ref))
     h2_ref, l2_ref = oracle.forward(np.concatenate([prompt, [t_ref]]).astype(np.uint32))
     first = None
-    for n in (1, 16, 17, 33, 97, 129):
+    for n in (1, 16, 17, 33, 64, 65, 129):
         model = HybridModel(cfg, qw, n_pool_blocks=n + 2, max_blocks_per_seq=2, max_step_tokens=n * len(prompt), max_step_seqs=n, n_state_slots=n)
         tabs = np.stack([np.array([i, n], np.int32) for i in range(n)])   # one block per sequence (13 tokens), the second entry unused
         toks = model.step(np.tile(prompt, n), [0] * n, [len(prompt)] * n, tabs, list(range(n)))
