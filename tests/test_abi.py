@@ -115,6 +115,33 @@ def test_build_decode_chunks():
     assert lib.logismos_paged_decode_scratch_bytes(68, 16, 128) == 68 * 16 * 130 * 4
 
 
+def test_skinny_int4_route_table():
+    """The kernel choice of logismos_launch_skinny_int4_g32_bf16 (host arithmetic): the tensor-core route above
+    16 rows, for k >= 3 n at every batch, and from 8 rows up to n = 16384; the GEMV otherwise and whenever
+    the shape rules of the tensor-core kernel do not hold."""
+    want = {(1536, 1536, 1): 0, (1536, 1536, 8): 1, (1536, 1536, 16): 1, (1536, 1536, 64): 1, (8960, 1536, 4): 0, (8960, 1536, 16): 1,
+            (1536, 8960, 1): 1, (1536, 8960, 64): 1, (151936, 1536, 1): 0, (151936, 1536, 16): 0, (151936, 1536, 17): 1,
+            (17920, 1536, 16): 0, (2048, 6144, 2): 1, (256, 640, 64): 0, (1001, 1536, 40): 0, (1536, 1536, 65): 0, (1536, 1536, 0): 0}
+    for (n, k, b), route in want.items():
+        assert lib.logismos_skinny_int4_route(b, n, k) == route, (n, k, b)
+
+
+def test_process_wide_switches_and_scratch_sizes_need_no_device():
+    assert lib.logismos_get_dependent_launch() in (0, 1)
+    before = lib.logismos_get_dependent_launch()
+    lib.logismos_set_dependent_launch(0); assert lib.logismos_get_dependent_launch() == 0
+    lib.logismos_set_dependent_launch(1); assert lib.logismos_get_dependent_launch() == 1
+    lib.logismos_set_dependent_launch(before)
+    det = lib.logismos_get_deterministic()
+    lib.logismos_set_deterministic(1); assert lib.logismos_get_deterministic() == 1
+    lib.logismos_set_deterministic(det)
+    # one slot of 57856 bytes per (64-token chunk, head); every sequence may end in a partial chunk
+    assert lib.logismos_gdn_chunked_scratch_bytes(4096, 4, 16) == (64 + 4) * 16 * 57856
+    assert lib.logismos_gdn_chunked_scratch_bytes(63, 1, 2) == 1 * 2 * 57856
+    assert lib.logismos_gdn_chunked_scratch_bytes(-1, 1, 2) == 0 and lib.logismos_gdn_chunked_scratch_bytes(64, 1, 0) == 0
+    assert lib.logismos_turbo3_row_bytes(256) == 112 and lib.logismos_turbo3_row_bytes(100) == 0
+
+
 def test_python_ops_reject_cpu_operands_without_touching_a_device():  # praxis/src/matmul.rs:154-166
     import torch
     from logismos_b200 import ops
