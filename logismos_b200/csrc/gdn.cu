@@ -112,7 +112,7 @@ struct PfCfg {
 };
 
 template <int CPT, int KS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)  // 128 registers at most: four CTAs per SM (130 registers gave three)
 gdn_prefill_kernel(float* __restrict__ state, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                    __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, const int* __restrict__ cu,
@@ -360,7 +360,7 @@ __global__ void gdn_finish_kernel(float* __restrict__ acc, int64_t ld_acc, const
 // the dependency wait (they date from an earlier step). The two CTAs of a (sequence, head) both read
 // its q, k, a, b; each zeroes its own v and z columns, and the one that arrives second at the pair's
 // counter zeroes the shared columns and resets the counter.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)  // 128 registers at most: four CTAs per SM (130 registers gave three)
 gdn_decode_fused_kernel(float* __restrict__ state, float* __restrict__ acc, int64_t ld_acc, const float* __restrict__ A_log,
                         const float* __restrict__ dt_bias, __nv_bfloat16* __restrict__ o, const int* __restrict__ slots,
                         const uint8_t* __restrict__ fresh, int* __restrict__ pair_count, int heads, float scale) {
