@@ -114,7 +114,6 @@ int orc_attention_forward(const orc_attn_t* a, const float* x, const uint8_t* ma
   const size_t kvw = n_kv * d;
   if (n_kv == 0 || n_h % n_kv != 0 || d * n_h != hidden) return 2;
   if (seq > rope_max_seq) return 1;
-  const size_t groups = n_h / n_kv;
 
   std::vector<float> q(seq * hidden), k(seq * kvw), v(seq * kvw);
   orc_linear_t(x, seq * hidden, a->wq, hidden * hidden, a->bq, hidden, seq, hidden, hidden, q.data());
