@@ -206,7 +206,7 @@ def workload_config(cfg, cu):
 # processed, as the summaries state). bytes per unit: gate/up GEMM at M=2176 (read 61.97 + write 7.44 MB,
 # the bf16 output lands in L2 first); GEMV lm_head (131.30 + 5.89 MB); paged decode 1027 B per context
 # token + 7.09 MB of partials per 328868 tokens.
-NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 4.56e6) / 328868}
+NCU_TRAFFIC = {"gemm_m2176": 69.41e6, "gemm_m2929": 77.52e6, "gemv_lm_head": 135.47e6, "paged_per_context_token": (337.73e6 + 4.56e6) / 328868}
 
 PROFILER_RANGE = False
 
@@ -278,7 +278,9 @@ def micro_rooflines(peaks, T, cfg):
     fl = 2.0 * T * i2 * h
     out["gemm"] = {"kernel": "linear_t_tcgen05 (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": fl / t / 1e12,
                    "peak": peaks["tf_burst"], "unit": "TFLOP/s", "frac": fl / t / 1e12 / peaks["tf_burst"],
-                   "traffic": NCU_TRAFFIC["gemm_m2176"] * T / 2176.0, "traffic_note": "ncu capture at M=2176 scaled by tokens (A and output grow with M; W 55 MB does not, so this over-states slightly above 2176)",
+                   "traffic": NCU_TRAFFIC["gemm_m2929"] if T == 2929 else NCU_TRAFFIC["gemm_m2176"] * T / 2176.0,
+                   "traffic_note": "ncu capture at M=2929 (dram read + write of one launch)" if T == 2929 else
+                                   "ncu capture at M=2176 scaled by tokens (A and output grow with M; W 55 MB does not, so this over-states slightly above 2176)",
                    "flops_per_launch": fl, "us_per_launch": t * 1e6, "peak_source": peaks["src"] + " burst"}
     del ws
     out["gemv_grid"] = gemv_grid(peaks, [("%dx%d" % s, s[0], s[1]) for s in GEMV_SHAPES])
